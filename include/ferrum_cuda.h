@@ -1,0 +1,253 @@
+/*
+ * ferrum_cuda.h - C ABI of libferrum_cuda.so, the sm_100a implementation of ferrum-gpu's
+ * quantised-weight inference hot path (Q8_0 / Q4_0 packed-weight matrix products behind
+ * KV-cached decode and full-sequence scoring, decode attention, and the fused elementwise ops
+ * between them).
+ *
+ * This is what the one `unsafe` Rust crate (`ferrum_cuda`) binds, and what the C++ mirror in
+ * ferrum_cuda.hpp and the Python ctypes harness call. Plain pointers and sizes only.
+ *
+ * Conventions
+ *  - Every call returns an `int` status: FC_OK (0) or a negative FC_ERR_* code. Nothing aborts
+ *    the process. A human-readable message for the last failure on a device is available from
+ *    fc_last_error(); the messages for user errors are the reference's own strings.
+ *  - "host" pointers are ordinary process memory. Entry points whose name ends in `_dev` take
+ *    device pointers (memory on the GPU the handle belongs to) and enqueue on the handle's
+ *    stream without synchronising.
+ *  - Weight matrices are handed over exactly as the reference's host model structs hold them:
+ *    f32, row-major `[in, out]` (ferrum_ref/src/models/llama/mod.rs:L100-L147). A bias or an
+ *    optional tensor that is absent is a NULL pointer.
+ *  - One caller per handle at a time; handles may be used from any thread.
+ */
+#ifndef FERRUM_CUDA_H
+#define FERRUM_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------ */
+enum {
+  FC_OK = 0,
+  FC_ERR_SHAPE = -1,        /* a length does not match its declared shape (ops/mod.rs:L31-L40) */
+  FC_ERR_RANGE = -2,        /* token id >= vocab (ops/mod.rs:L45-L49): an error, never clamped  */
+  FC_ERR_CONTEXT_FULL = -3, /* "context of N tokens is full" (models/llama/mod.rs:L354-L356)   */
+  FC_ERR_OOM = -4,          /* allocation refused, or plan over budget before allocating       */
+  FC_ERR_DEVICE = -5,       /* a CUDA call failed; sticky for the device handle                */
+  FC_ERR_INJECTED = -6,     /* a launch refused by fc_debug_fail_after (test hook)             */
+  FC_ERR_TIMEOUT = -7,      /* a bounded device-side wait ran out                              */
+  FC_ERR_ARG = -8,          /* NULL handle / pointer, bad enum value                           */
+  FC_ERR_UNSUPPORTED = -9   /* shape outside what a kernel was built for                       */
+};
+
+/* Stored precision of a weight matrix. Replaces ferrum_wgpu::ops::quant::QKind
+ * (ferrum_wgpu/src/ops/quant.rs:L27-L44), restricted to the kinds on this path. */
+enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2 };
+
+/* RoPE pairing, ferrum_ref/src/models/llama/ops.rs:L9-L15. */
+enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };
+
+/* Arithmetic of the batched (scoring / forward_all) matrix products.
+ * FC_EXACT_F32: f32 FMA with f32 accumulation, same path as decode (parity <= 1e-5).
+ * FC_TENSOR_BF16: weights dequantised to bf16 in shared memory, tcgen05 MMA with fp32
+ * accumulators in tensor memory (parity <= 2e-2 max-abs per logit, 1e-3 mean NLL). */
+enum { FC_EXACT_F32 = 0, FC_TENSOR_BF16 = 1 };
+
+typedef struct FcDevice FcDevice;
+typedef struct FcQWeight FcQWeight;
+typedef struct FcModel FcModel;
+
+/* ---- device ------------------------------------------------------------------------------ */
+/* Replaces ferrum_wgpu::device::Gpu::open / GpuBackend::open (device/mod.rs:L98-L176,
+ * ferrum_gpu_core/src/engine/gpu.rs:L18-L40). Opens CUDA device `ordinal`, creates the stream
+ * every call on this handle uses. */
+int fc_device_open(int ordinal, FcDevice** out);
+int fc_device_close(FcDevice* dev);
+/* Adapter name as Backend::name() reports it (engine/mod.rs:L259-L270). */
+int fc_device_name(FcDevice* dev, char* buf, size_t buf_len);
+/* Multiprocessor count and total memory, for the pre-flight plan check. */
+int fc_device_props(FcDevice* dev, int* sm_count, uint64_t* total_mem_bytes);
+/* Message of the most recent failing call on this device ("" if none). The pointer stays valid
+ * until the next failing call on the same device. `dev` may be NULL: then it is the message of
+ * the last failure that had no device (fc_device_open itself). */
+const char* fc_last_error(FcDevice* dev);
+/* The CUDA stream (a cudaStream_t) all work of this handle is enqueued on, and a full
+ * synchronise of it. */
+void* fc_device_stream(FcDevice* dev);
+int fc_device_sync(FcDevice* dev);
+/* Kernels launched by this library on this device since it was opened. */
+uint64_t fc_device_launch_count(FcDevice* dev);
+/* Host-side fault injection, replaces Gpu::fail_after / sweep_faults
+ * (ferrum_wgpu/src/device/runtime.rs:L214-L256): after `n_launches` more kernel launches every
+ * further launch is refused with FC_ERR_INJECTED *before it reaches the device*; a negative
+ * value disarms the hook. No GPU fault is ever produced. */
+int fc_debug_fail_after(FcDevice* dev, int64_t n_launches);
+
+/* ---- stand-alone quantised weights and products ------------------------------------------ */
+/* Bytes of a GGUF tensor of `n_elems` elements (ferrum_gguf/src/codec/quant.rs:L17-L46);
+ * 0 when the count does not fill whole 32-element blocks. */
+size_t fc_block_bytes(int kind, size_t n_elems);
+
+/* Quantise an f32 `[k, n]` ([in, out]) host matrix and keep it packed on the device. Replaces
+ * ops::quant::upload_quantised = quantise_matrix + pack + upload
+ * (ferrum_wgpu/src/ops/quant.rs:L238-L288). The encoder runs on the device and produces the
+ * same blocks as ferrum_gguf::quant::encode (codec/quant.rs:L111-L133). `k` must be a multiple
+ * of 32 unless `kind` is FC_F32. */
+int fc_qweight_create(FcDevice* dev, int kind, const float* w_in_out, uint32_t k, uint32_t n,
+                      FcQWeight** out);
+/* Same from GGUF block bytes: `n` rows of `k / 32` blocks of 34 (Q8_0) or 18 (Q4_0) bytes.
+ * Replaces ops::quant::upload_qweight (ops/quant.rs:L266-L277). */
+int fc_qweight_create_from_blocks(FcDevice* dev, int kind, const uint8_t* blocks, size_t n_bytes,
+                                  uint32_t k, uint32_t n, FcQWeight** out);
+int fc_qweight_destroy(FcQWeight* w);
+/* kind / k / n / packed device bytes: QWeight::{kind,k,n,device_bytes} (ops/quant.rs:L158-L183). */
+int fc_qweight_info(const FcQWeight* w, int* kind, uint32_t* k, uint32_t* n, uint64_t* dev_bytes);
+/* The GGUF block bytes the device holds (`n` rows of `k/32` blocks), re-assembled from the
+ * packed planes: the inverse of the upload repack. `out` has fc_block_bytes(kind, k*n) bytes. */
+int fc_qweight_blocks(FcQWeight* w, uint8_t* out, size_t out_bytes);
+/* The f32 values the kernels compute with, `[n, k]` row-major (row = output column), decoded on
+ * the device; bit-identical to ferrum_gguf::quant::decode (codec/quant.rs:L50-L88). Replaces
+ * ops::quant::dequantise_bytes (ops/quant.rs:L254-L264). */
+int fc_dequant(FcQWeight* w, float* out_n_k, size_t out_elems);
+
+/* `y[m, n] = x[m, k] * W` with host buffers (copies inside). Replaces ops::quant::linear_q
+ * (ferrum_wgpu/src/ops/quant.rs:L326-L381). `mode` is FC_EXACT_F32 or FC_TENSOR_BF16. */
+int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mode);
+/* The same on device buffers, enqueued on the device's stream, no synchronisation. */
+int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, int mode);
+
+/* ---- resident models ---------------------------------------------------------------------- */
+/* ferrum_ref::llama::Config + RopeScaling (ferrum_ref/src/models/llama/mod.rs:L24-L52,
+ * ops.rs:L17-L35). */
+typedef struct {
+  uint32_t vocab, ctx, dim, heads, kv_heads, head_dim, layers, hidden, rope_dim;
+  uint32_t rope_type; /* FC_ROPE_NORM | FC_ROPE_NEOX */
+  float rope_base, eps;
+  float rope_linear_factor;  /* 1.0 = none */
+  uint32_t n_freq_factors;   /* 0 or rope_dim / 2 */
+  const float* freq_factors; /* may be NULL when n_freq_factors == 0 */
+  uint32_t tied;             /* head is the transposed embedding */
+} FcLlamaConfig;
+
+/* ferrum_ref::llama::Block (models/llama/mod.rs:L100-L128); biases NULL when absent. */
+typedef struct {
+  const float *attn_norm, *wq, *bq, *wk, *bk, *wv, *bv, *wo, *ffn_norm, *gate, *up, *down;
+} FcLlamaBlock;
+
+/* ferrum_ref::llama::Llama (models/llama/mod.rs:L130-L147). */
+typedef struct {
+  const float* tok;           /* [vocab, dim] */
+  const FcLlamaBlock* blocks; /* cfg.layers of them */
+  const float* out_norm;      /* [dim] */
+  const float* head;          /* [dim, vocab] */
+} FcLlamaWeights;
+
+/* ferrum_ref::gpt2::Config (ferrum_ref/src/models/gpt2/mod.rs:L15-L30). */
+typedef struct {
+  uint32_t vocab, ctx, dim, heads, layers, hidden;
+} FcGpt2Config;
+
+/* ferrum_ref::gpt2::Block (models/gpt2/mod.rs:L62-L96). */
+typedef struct {
+  const float *ln1_g, *ln1_b, *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo, *ln2_g, *ln2_b, *w1, *b1,
+      *w2, *b2;
+} FcGpt2Block;
+
+/* ferrum_ref::gpt2::Gpt2 (models/gpt2/mod.rs:L98-L114). */
+typedef struct {
+  const float* tok; /* [vocab, dim] */
+  const float* pos; /* [ctx, dim] */
+  const FcGpt2Block* blocks;
+  const float *lnf_g, *lnf_b;
+  const float* head; /* [dim, vocab] */
+} FcGpt2Weights;
+
+/* Device bytes a resident model of this shape needs (weights, RoPE tables, KV caches for
+ * `max_streams` streams, decode scratch). Replaces models::llama::plan
+ * (ferrum_wgpu/src/models/llama/mod.rs:L108-L182). 0 for an invalid config. */
+uint64_t fc_llama_plan_bytes(const FcLlamaConfig* cfg, int qkind, uint32_t max_streams);
+uint64_t fc_gpt2_plan_bytes(const FcGpt2Config* cfg, int qkind, uint32_t max_streams);
+
+/* Upload a model: quantise every eligible matrix to `qkind` (FC_F32 keeps f32), build RoPE
+ * tables, zero the KV caches of `max_streams` independent streams. Replaces GpuLlama::new
+ * (ferrum_wgpu/src/models/llama/mod.rs:L219-L314). `budget_bytes` (0 = the device's free
+ * memory) refuses the plan *before* anything is allocated (L241-L243). */
+int fc_llama_create(FcDevice* dev, const FcLlamaConfig* cfg, const FcLlamaWeights* w, int qkind,
+                    uint32_t max_streams, uint64_t budget_bytes, FcModel** out);
+/* Replaces GpuGpt2::new (ferrum_wgpu/src/models/gpt2.rs:L134-L190); `qkind` other than FC_F32
+ * is new: the reference's resident GPT-2 is f32 only. */
+int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* cfg, const FcGpt2Weights* w, int qkind,
+                   uint32_t max_streams, uint64_t budget_bytes, FcModel** out);
+int fc_model_destroy(FcModel* m);
+
+/* GpuLlama::{pos, reset} (models/llama/mod.rs:L331-L340) per stream. reset only rewinds the
+ * position; the cache is overwritten as new tokens arrive. */
+int fc_model_pos(FcModel* m, uint32_t stream_id, uint32_t* pos_out);
+int fc_model_reset(FcModel* m, uint32_t stream_id);
+/* vocab, ctx, max_streams, qkind and packed weight bytes of a resident model. */
+int fc_model_info(FcModel* m, uint32_t* vocab, uint32_t* ctx, uint32_t* max_streams, int* qkind,
+                  uint64_t* weight_bytes);
+
+/* Consume one token at the stream's next position. Replaces GpuLlama::feed / GpuGpt2::feed
+ * (models/llama/mod.rs:L352-L438, models/gpt2.rs:L192-L265). `logits_out` (vocab floats, host)
+ * and `argmax_out` (first maximum, NaN never wins: ferrum_model/src/sampling.rs:L32-L40) may
+ * each be NULL. A failed call leaves the position unchanged. */
+int fc_model_feed(FcModel* m, uint32_t stream_id, int32_t token, float* logits_out,
+                  int32_t* argmax_out);
+/* One decode step for `n` distinct streams at once (new: the reference decodes batch 1 only,
+ * serving/routes.rs:L301-L309). `logits_out` is `[n, vocab]` or NULL, `argmax_out` `[n]` or
+ * NULL. */
+int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* tokens,
+                        float* logits_out, int32_t* argmax_out);
+/* Feed `n` prompt tokens of one stream in one batched pass (new: the reference feeds a prompt
+ * token by token, engine/mod.rs:L226-L229). Equivalent to n calls of fc_model_feed; returns
+ * the last position's logits / argmax when asked. */
+int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, uint32_t n,
+                     float* logits_out, int32_t* argmax_out, int mode);
+/* Stateless full causal forward, every position's logits `[n, vocab]`. Replaces
+ * GpuLlama::forward_all / GpuGpt2::forward_all (models/llama/forward.rs:L13-L17). */
+int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, float* logits_out, int mode);
+/* Score `n_seqs` sequences of `seq_len` ids each: for each i < seq_len-1 the log-probability of
+ * ids[i+1] given ids[..=i] and whether it is the first argmax. Replaces GpuLlama::score
+ * (models/llama/forward.rs:L74-L88) + ops::score (ops/mod.rs:L158-L175), batched over
+ * sequences. `logprob_out` / `greedy_out` are `[n_seqs, seq_len-1]` (nullable);
+ * `nll_sum_out[n_seqs]` is each sequence's -sum of log-probabilities accumulated in f64 in
+ * ascending position (serving/decoder.rs:L69-L83). */
+int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint32_t seq_len, int mode,
+                   float* logprob_out, uint8_t* greedy_out, double* nll_sum_out);
+/* Scoring with the ids already on the device and results left there: the timed kernel-only
+ * region of the benchmark. `ids_dev` is `[n_seqs, seq_len]` int32, `nll_sum_dev[n_seqs]` f64;
+ * `logprob_dev` / `greedy_dev` nullable. Enqueues without synchronising. */
+int fc_model_score_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seqs, uint32_t seq_len,
+                       int mode, float* logprob_dev, uint8_t* greedy_dev, double* nll_sum_dev);
+
+/* ---- vocabulary-split head (multi-GPU scoring) --------------------------------------------
+ * Precedent: Lin::Sharded splits a `[k, n]` weight by output columns, each block quantised and
+ * multiplied on its own (ferrum_wgpu/src/models/llama/lin.rs:L41-L53,L76-L90). Here the blocks
+ * live on different GPUs of one box. Rank r of `n_shards` keeps head rows
+ * [r*ceil(V/n_shards), min(V, (r+1)*ceil(V/n_shards))). */
+/* Restrict the resident model's head to one vocabulary shard (call once, after create). */
+int fc_model_set_head_shard(FcModel* m, uint32_t shard, uint32_t n_shards);
+/* Trunk only: final-norm hidden states of every position, `[n_seqs*seq_len, dim]` bf16 (mode
+ * FC_TENSOR_BF16) or f32 (FC_EXACT_F32), written to `hidden_dev`. */
+int fc_model_trunk_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seqs, uint32_t seq_len,
+                       int mode, void* hidden_dev);
+/* Head over this rank's vocabulary shard for `rows` hidden rows: per row the local maximum, the
+ * local sum of exp(logit - local max), the target's logit if this shard owns the target (else
+ * -inf), and the local first argmax as a global vocabulary index: `partial_dev[rows][4]` f32
+ * (the index is stored as a float-exact integer < 2^24). */
+int fc_model_head_partial_dev(FcModel* m, const void* hidden_dev, const int32_t* targets_dev,
+                              uint32_t rows, int mode, float* partial_dev);
+/* Combine `n_shards` partials (all-gathered into `[n_shards][rows][4]`) into log-probabilities,
+ * greedy flags and per-sequence NLL sums; rows = n_seqs * rows_per_seq. */
+int fc_score_combine_dev(FcDevice* dev, const float* partials_dev, uint32_t n_shards,
+                         const int32_t* targets_dev, uint32_t n_seqs, uint32_t rows_per_seq,
+                         float* logprob_dev, uint8_t* greedy_dev, double* nll_sum_dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FERRUM_CUDA_H */

@@ -1,0 +1,506 @@
+"""Pins the CPU oracle against every known-answer test the reference holds for the hot path.
+
+Each test names the reference test it restates (file:line). CPU only.
+"""
+import math
+
+import numpy as np
+import pytest
+
+from ferrum_gpu_b200._ffi import FC_Q4_0, FC_Q8_0, FC_ROPE_NEOX, FC_ROPE_NORM
+from oracle import oracle as orc
+from tests import helpers
+
+KINDS = [FC_Q8_0, FC_Q4_0]
+
+
+def data(n):
+    """ferrum_gguf/src/codec/quant.rs:L185-L189"""
+    return np.array([np.float32(np.float32(i * 37 % 101) - np.float32(50.0)) / np.float32(13.0)
+                     for i in range(n)], dtype=np.float32)
+
+
+# ---- f16 (ferrum_gguf/src/codec/f16.rs:L59-L95) ---------------------------------------------
+
+def test_f16_known_values():
+    assert orc.f16_to_f32(0x3C00) == 1.0
+    assert orc.f16_to_f32(0xC000) == -2.0
+    assert orc.f16_to_f32(0x0000) == 0.0
+    assert orc.f16_to_f32(0x7BFF) == 65504.0
+    assert orc.f16_to_f32(0x0001) == 2.0 ** -24
+    assert math.isinf(orc.f16_to_f32(0x7C00))
+    assert math.isnan(orc.f16_to_f32(0x7E00))
+    assert orc.f32_to_f16(1.0) == 0x3C00
+    assert orc.f32_to_f16(-2.0) == 0xC000
+    assert orc.f32_to_f16(65504.0) == 0x7BFF
+    assert orc.f32_to_f16(1e9) == 0x7C00
+    assert orc.f32_to_f16(1e-30) == 0
+    assert math.isnan(orc.f16_to_f32(orc.f32_to_f16(float("nan"))))
+
+
+def test_every_half_round_trips_exactly_and_matches_numpy():
+    allh = np.arange(65536, dtype=np.uint16)
+    want = allh.view(np.float16).astype(np.float32)
+    for h in range(65536):
+        x = orc.f16_to_f32(h)
+        if math.isnan(x):
+            assert np.isnan(want[h])
+            continue
+        assert x == want[h]
+        assert orc.f32_to_f16(x) == h, hex(h)
+
+
+def test_f16_rounding_is_to_nearest_even():
+    assert orc.f32_to_f16(1.0 + 2.0 ** -11) == 0x3C00
+    assert orc.f32_to_f16(1.0 + 3.0 * 2.0 ** -11) == 0x3C02
+    assert orc.f32_to_f16(1.0 + 2.0 ** -11 + 2.0 ** -20) == 0x3C01
+    # independent check of RNE against numpy on random floats spanning normal/subnormal halves
+    rng = np.random.default_rng(0)
+    xs = (rng.standard_normal(4000) * 10.0 ** rng.uniform(-9, 5, 4000)).astype(np.float32)
+    for x in xs:
+        assert orc.f32_to_f16(float(x)) == int(np.float32(x).astype(np.float16).view(np.uint16))
+
+
+# ---- block codec (ferrum_gguf/src/codec/quant.rs:L193-L287) ----------------------------------
+
+def test_sizes():
+    assert orc.block_bytes(FC_Q8_0, 64) == 68
+    assert orc.block_bytes(FC_Q4_0, 64) == 36
+    assert orc.block_bytes(FC_Q8_0, 33) == 0
+    assert orc.block_bytes(FC_Q4_0, 31) == 0
+    with pytest.raises(ValueError):
+        orc.encode(FC_Q8_0, np.ones(5, dtype=np.float32))
+
+
+def test_q8_0_error_is_within_half_a_step_of_the_block_scale():
+    d = data(96)
+    back = orc.decode(FC_Q8_0, orc.encode(FC_Q8_0, d), 96)
+    for blk, got in zip(d.reshape(-1, 32), back.reshape(-1, 32)):
+        step = np.abs(blk).max() / 127.0
+        assert np.all(np.abs(blk - got) <= step * 0.51 + 1e-4)
+
+
+def test_q8_0_known_block():
+    blk = np.zeros(32, dtype=np.float32)
+    blk[0], blk[1] = 127.0, -63.5
+    b = orc.encode(FC_Q8_0, blk)
+    assert orc.f16_to_f32(int(b[0]) | int(b[1]) << 8) == 1.0
+    assert np.int8(b[2]) == 127
+    assert b[3:4].view(np.int8)[0] == -64  # -63.5 rounds away from zero
+    assert orc.decode(FC_Q8_0, b, 32)[0] == 127.0
+
+
+def test_q4_0_is_coarse_but_bounded_and_idempotent():
+    d = data(64)
+    once = orc.decode(FC_Q4_0, orc.encode(FC_Q4_0, d), 64)
+    for blk, got in zip(d.reshape(-1, 32), once.reshape(-1, 32)):
+        amax = np.abs(blk).max()
+        assert np.all(np.abs(blk - got) <= amax / 8.0 * 1.01 + 1e-4)
+    twice = orc.decode(FC_Q4_0, orc.encode(FC_Q4_0, once), 64)
+    assert np.array_equal(once, twice)
+
+
+def test_q4_0_nibble_order_is_low_half_first():
+    blk = np.zeros(32, dtype=np.float32)
+    blk[0], blk[16] = -8.0, 7.0
+    back = orc.decode(FC_Q4_0, orc.encode(FC_Q4_0, blk), 32)
+    assert back[0] == -8.0 and back[16] == 7.0 and back[1] == 0.0
+
+
+def test_zero_blocks_and_length_mismatches():
+    z = np.zeros(32, dtype=np.float32)
+    for kind in KINDS:
+        assert np.array_equal(orc.decode(kind, orc.encode(kind, z), 32), z)
+    with pytest.raises(ValueError):
+        orc.decode(FC_Q8_0, np.zeros(7, dtype=np.uint8), 32)
+
+
+def test_q4_0_ties_keep_the_first_largest_magnitude():
+    # +3 before -3: the fold keeps the first, d = 3 / -8 (negative), so +3 -> q = 0
+    blk = np.zeros(32, dtype=np.float32)
+    blk[2], blk[5] = 3.0, -3.0
+    b = orc.encode(FC_Q4_0, blk)
+    d = orc.f16_to_f32(int(b[0]) | int(b[1]) << 8)
+    assert d == np.float32(3.0) / np.float32(-8.0)
+    dec = orc.decode(FC_Q4_0, b, 32)
+    assert dec[2] == 3.0 and dec[5] == np.float32(-3.0 / 8.0 * 7.0)
+
+
+def test_encoders_match_an_independent_numpy_restatement():
+    rng = np.random.default_rng(5)
+    x = np.concatenate([rng.standard_normal(32 * 40).astype(np.float32) * np.float32(0.02),
+                        helpers.nasty(32 * 14)])
+    blocks = x.reshape(-1, 32)
+    # Q8_0
+    amax = np.abs(blocks).max(axis=1)
+    d = (amax / np.float32(127.0)).astype(np.float32)
+    inv = np.where(d != 0, np.float32(1.0) / np.where(d != 0, d, 1), np.float32(0)).astype(np.float32)
+    t = (blocks * inv[:, None]).astype(np.float32)
+    q = np.clip(np.sign(t) * np.floor(np.abs(t) + np.float32(0.5)), -128, 127).astype(np.int8)
+    got = orc.encode(FC_Q8_0, x).reshape(-1, 34)
+    assert np.array_equal(got[:, :2].copy().view(np.uint16)[:, 0], d.astype(np.float16).view(np.uint16))
+    assert np.array_equal(got[:, 2:].view(np.int8), q)
+    # Q4_0
+    idx = np.abs(blocks).argmax(axis=1)  # first maximum
+    mx = blocks[np.arange(len(blocks)), idx]
+    d4 = (mx / np.float32(-8.0)).astype(np.float32)
+    inv4 = np.where(d4 != 0, np.float32(1.0) / np.where(d4 != 0, d4, 1), np.float32(0)).astype(np.float32)
+    t4 = ((blocks * inv4[:, None]).astype(np.float32) + np.float32(8.5)).astype(np.float32)
+    q4 = np.clip(np.trunc(t4), 0, 15).astype(np.uint8)
+    want = q4[:, :16] | (q4[:, 16:] << 4)
+    got4 = orc.encode(FC_Q4_0, x).reshape(-1, 18)
+    assert np.array_equal(got4[:, :2].copy().view(np.uint16)[:, 0], d4.astype(np.float16).view(np.uint16))
+    assert np.array_equal(got4[:, 2:], want)
+
+
+# ---- reference device layout + requantise identity (ferrum_wgpu/src/ops/quant/tests.rs) -------
+
+def test_pack_reorders_blocks_column_major_and_widens_the_scale():
+    """ops/quant/tests.rs:L44-L71"""
+    k, n = 64, 2
+    raw = bytearray()
+    for blk in range(4):
+        h = orc.f32_to_f16(float(blk) + 1.0)
+        raw += bytes([h & 0xFF, h >> 8]) + bytes((i + blk * 40) & 0xFF for i in range(32))
+    w = orc.pack_reference_layout(FC_Q8_0, np.frombuffer(bytes(raw), dtype=np.uint8), k, n)
+    assert w.size == 2 * 2 * 9
+    for b, col, file_blk in [(0, 0, 0), (1, 0, 1), (0, 1, 2), (1, 1, 3)]:
+        rec = w[(b * n + col) * 9:][:9]
+        assert rec[:1].view(np.float32)[0] == float(file_blk) + 1.0
+        first = int.from_bytes(bytes((i + file_blk * 40) & 0xFF for i in range(4)), "little")
+        assert rec[1] == first
+    h = orc.f32_to_f16(0.5)
+    q4 = np.frombuffer(bytes([h & 0xFF, h >> 8]) + bytes(range(16)), dtype=np.uint8)
+    w = orc.pack_reference_layout(FC_Q4_0, q4, 32, 1)
+    assert w.size == 5 and w[:1].view(np.float32)[0] == 0.5
+    assert w[4] == int.from_bytes(bytes([12, 13, 14, 15]), "little")
+
+
+def test_requantising_dequantised_weights_reproduces_the_values():
+    """ops/quant/tests.rs:L89-L104"""
+    for kind in KINDS:
+        for k, n in [(32, 1), (64, 7), (96, 40), (256, 9)]:
+            w = helpers.nasty(k * n)
+            rows = orc.decode(kind, orc.quantise_matrix(kind, w, k, n), k * n)  # [n, k]
+            again = orc.quantise_matrix(kind, orc.transpose(rows, n, k), k, n)
+            assert np.array_equal(orc.decode(kind, again, k * n), rows), (kind, k, n)
+
+
+def test_quantise_refuses_bad_shapes():
+    """ops/quant/tests.rs:L73-L87"""
+    for kind in KINDS:
+        with pytest.raises(ValueError):
+            orc.quantise_matrix(kind, np.zeros(33, dtype=np.float32), 33, 1)
+        with pytest.raises(ValueError):
+            orc.quantise_matrix(kind, np.zeros(63, dtype=np.float32), 32, 2)
+
+
+# ---- matmul (ferrum_ref/src/kernels/matmul.rs:L113-L179) --------------------------------------
+
+def test_matmul_known_values():
+    got = orc.matmul([1, 2, 3, 4, 5, 6], [7, 8, 9, 10, 11, 12], 2, 3, 2)
+    assert got.tolist() == [58.0, 64.0, 139.0, 154.0]
+
+
+def test_matmul_non_square_and_one_row():
+    a, b = orc.rand_vec(7, 1), orc.rand_vec(35, 2)
+    got = orc.matmul(a, b, 1, 7, 5)
+    for j in range(5):
+        want = np.float32(0)
+        for p in range(7):
+            want = np.float32(want + np.float32(a[p] * b[p * 5 + j]))
+        assert got[j] == want  # same order, same roundings
+
+
+def test_matmul_shape_errors_name_the_operand():
+    with pytest.raises(ValueError, match="operand a has 1 elements, shape needs 2"):
+        orc.matmul([1.0], [1.0, 2.0], 2, 1, 1)
+    with pytest.raises(ValueError, match="operand b"):
+        orc.matmul([1.0], [1.0, 2.0], 1, 1, 1)
+
+
+def test_matmul_empty_and_threaded_bit_identical():
+    assert orc.matmul([], [], 2, 0, 2).tolist() == [0.0] * 4
+    m, k, n = 13, 9, 11
+    a, b = orc.rand_vec(m * k, 3), orc.rand_vec(k * n, 4)
+    want = orc.matmul(a, b, m, k, n)
+    for t in [0, 1, 2, 5, 64]:
+        assert np.array_equal(orc.matmul(a, b, m, k, n, threads=t), want)
+
+
+def test_rand_vec_is_deterministic_and_in_range():
+    assert np.array_equal(orc.rand_vec(8, 7), orc.rand_vec(8, 7))
+    assert not np.array_equal(orc.rand_vec(8, 7), orc.rand_vec(8, 8))
+    v = orc.rand_vec(1000, 9)
+    assert np.all((v >= -1.0) & (v < 1.0))
+    # xorshift64 by hand for the first value of seed 7
+    s = 7
+    s ^= (s << 13) & (2 ** 64 - 1)
+    s ^= s >> 7
+    s ^= (s << 17) & (2 ** 64 - 1)
+    assert orc.rand_vec(1, 7)[0] == np.float32(np.float32(s >> 40) / np.float32(1 << 24) * 2 - 1)
+
+
+def test_rng_xorshift64star():
+    """ferrum_ref/src/kernels/rng.rs:L55-L82"""
+    a, b = orc.Rng(7), orc.Rng(7)
+    for _ in range(100):
+        x = a.next_f32()
+        assert x == b.next_f32() and 0.0 <= x < 1.0
+    assert orc.Rng(7).next_u64() != orc.Rng(8).next_u64()
+    assert orc.Rng(0).next_u64() != 0
+    r = orc.Rng(3)
+    seen = [0] * 5
+    for _ in range(2000):
+        seen[r.below(5)] += 1
+    assert all(c > 300 for c in seen)
+    assert orc.Rng(1).below(1) == 0
+    # one step by hand
+    s = 7
+    s ^= s >> 12
+    s ^= (s << 25) & (2 ** 64 - 1)
+    s ^= s >> 27
+    assert orc.Rng(7).next_u64() == (s * 0x2545F4914F6CDD1D) & (2 ** 64 - 1)
+
+
+# ---- nn (ferrum_ref/src/kernels/nn.rs:L147-L243) ----------------------------------------------
+
+def test_gelu_known_values():
+    assert orc.gelu(0.0) == 0.0
+    assert abs(orc.gelu(1.0) - 0.841192) < 1e-5
+    assert abs(orc.gelu(-1.0) + 0.158808) < 1e-5
+    assert orc.gelu(20.0) == 20.0
+
+
+def test_layernorm_normalises_each_row():
+    x = orc.rand_vec(24, 1)
+    y = orc.layernorm(x, np.ones(8), np.zeros(8), 3, 8).reshape(3, 8)
+    for row in y:
+        assert abs(row.mean()) < 1e-5 and abs(row.var() - 1.0) < 1e-3
+    y2 = orc.layernorm(x, np.full(8, 2.0), np.ones(8), 3, 8)
+    assert abs(y2[0] - (2.0 * y[0, 0] + 1.0)) < 1e-5
+
+
+def test_attention_is_causal_and_first_token_returns_v():
+    batch, t, heads, hd = 2, 5, 2, 3
+    n = batch * t * heads * hd
+    q, k, v = orc.rand_vec(n, 1), orc.rand_vec(n, 2), orc.rand_vec(n, 3)
+    out = orc.attention(q, k, v, batch, t, heads, hd)
+    assert abs(out[0] - v[0]) < 1e-6
+    # changing a future key/value must not change earlier rows
+    k2, v2 = k.copy(), v.copy()
+    k2[(t - 1) * heads * hd:t * heads * hd] += 1.0
+    v2[(t - 1) * heads * hd:t * heads * hd] += 1.0
+    out2 = orc.attention(q, k2, v2, batch, t, heads, hd)
+    assert np.array_equal(out[:(t - 1) * heads * hd], out2[:(t - 1) * heads * hd])
+
+
+def test_score_logprob_and_argmax_flag():
+    lp, gr = orc.score([1.0, 3.0, 2.0, 5.0, 5.0, 1.0], [1, 1], 3)
+    assert gr[0] and not gr[1]  # ties resolve to the first maximum
+    row = np.array([1.0, 3.0, 2.0], dtype=np.float64)
+    assert abs(lp[0] - (3.0 - np.log(np.exp(row).sum()))) < 1e-5
+    # cross-entropy of 4 zero logits is ln 4 (nn.rs:L212-L220)
+    lp, _ = orc.score([0.0, 0.0, 0.0, 0.0], [1], 4)
+    assert abs(-lp[0] - math.log(4.0)) < 1e-6
+    # the server's f64 variant counts any tied maximum as greedy (serving/decoder.rs:L80)
+    lp64, gr64 = orc.logprobs_f64([1.0, 3.0, 2.0, 5.0, 5.0, 1.0], [1, 1], 3)
+    assert gr64[0] and gr64[1]
+    assert abs(lp64[0] - (3.0 - np.log(np.exp(row).sum()))) < 1e-9
+
+
+def test_argmax_first_maximum_and_nan_never_wins():
+    """ferrum_model/src/sampling.rs:L32-L40"""
+    assert orc.argmax([1.0, 5.0, 5.0, 2.0]) == 1
+    assert orc.argmax([float("nan"), 1.0, 0.5]) == 1
+    assert orc.argmax([float("nan"), float("nan")]) == 0
+
+
+# ---- Llama ops (ferrum_ref/src/models/llama/ops.rs:L165-L300) ---------------------------------
+
+def test_rmsnorm_matches_the_formula_and_gives_unit_rms():
+    y = orc.rmsnorm([3.0, 4.0], [1.0, 2.0], 1, 2, 0.0)
+    inv = 1.0 / math.sqrt(12.5)
+    assert abs(y[0] - 3.0 * inv) < 1e-6 and abs(y[1] - 8.0 * inv) < 1e-6
+    r = orc.rand_vec(24, 1)
+    y = orc.rmsnorm(r, np.ones(8), 3, 8, 0.0).reshape(3, 8)
+    for row in y:
+        assert abs((row * row).mean() - 1.0) < 1e-4
+
+
+def test_silu_known_values():
+    assert orc.silu(0.0) == 0.0
+    assert abs(orc.silu(1.0) - 0.7310586) < 1e-6
+    assert abs(orc.silu(-20.0)) < 1e-6 and abs(orc.silu(20.0) - 20.0) < 1e-5
+    assert orc.silu(-1e6) == 0.0 and orc.silu(1e6) == 1e6  # saturation stays finite
+
+
+def test_rope_at_position_zero_is_the_identity():
+    c, s = orc.rope_tables(0, 1, 4, 10000.0)
+    assert c.tolist() == [1.0, 1.0] and s.tolist() == [0.0, 0.0]
+    x = orc.rand_vec(8, 2)
+    assert np.array_equal(orc.apply_rope(x, 1, 2, 4, 4, c, s, FC_ROPE_NORM), x)
+
+
+def test_rope_preserves_pair_norms_and_the_two_pairings_differ():
+    x0 = orc.rand_vec(8, 3)
+    c, s = orc.rope_tables(5, 1, 8, 10000.0)
+    n = orc.apply_rope(x0, 1, 1, 8, 8, c, s, FC_ROPE_NORM)
+    e = orc.apply_rope(x0, 1, 1, 8, 8, c, s, FC_ROPE_NEOX)
+    for i in range(4):
+        assert abs((x0[2 * i] ** 2 + x0[2 * i + 1] ** 2) - (n[2 * i] ** 2 + n[2 * i + 1] ** 2)) < 1e-5
+        assert abs((x0[i] ** 2 + x0[i + 4] ** 2) - (e[i] ** 2 + e[i + 4] ** 2)) < 1e-5
+    assert not np.array_equal(n, e)
+
+
+def test_rope_only_rotates_the_first_rope_dim_channels():
+    x = orc.rand_vec(8, 4)
+    c, s = orc.rope_tables(3, 1, 4, 10000.0)
+    y = orc.apply_rope(x, 1, 1, 8, 4, c, s, FC_ROPE_NEOX)
+    assert np.array_equal(y[4:], x[4:]) and not np.array_equal(y[:4], x[:4])
+
+
+def test_rope_scaling_divides_frequencies_and_positions_by_hand():
+    c, s = orc.rope_tables(8, 1, 4, 100.0, [2.0, 1.0], 4.0)
+    f1 = np.float32(100.0) ** np.float32(-0.5)
+    want0 = np.float32(8.0 * 1.0 / 2.0 / 4.0)
+    want1 = np.float32(np.float32(8.0) * f1 / np.float32(4.0))
+    assert abs(c[0] - math.cos(want0)) < 1e-6 and abs(s[0] - math.sin(want0)) < 1e-6
+    assert abs(c[1] - math.cos(want1)) < 1e-6 and abs(s[1] - math.sin(want1)) < 1e-6
+    a = orc.rope_tables(7, 3, 4, 1e4, [1.0, 1.0], 1.0)
+    b = orc.rope_tables(7, 3, 4, 1e4)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+
+
+def test_attention_with_one_position_returns_v():
+    heads, kv, hd = 4, 2, 3
+    q, k, v = orc.rand_vec(heads * hd, 5), orc.rand_vec(kv * hd, 6), orc.rand_vec(kv * hd, 7)
+    o = orc.attend_row(q, k, v, 1, heads, kv, hd)
+    for h in range(heads):
+        g = (h // 2) * hd
+        assert np.array_equal(o[h * hd:(h + 1) * hd], v[g:g + hd])
+
+
+def test_gqa_shares_kv_heads_between_grouped_query_heads():
+    hd = 4
+    q1 = orc.rand_vec(hd, 8)
+    q = np.concatenate([q1, q1])
+    k, v = orc.rand_vec(3 * hd, 9), orc.rand_vec(3 * hd, 10)
+    o = orc.attend_row(q, k, v, 3, 2, 1, hd)
+    assert np.array_equal(o[:hd], o[hd:])
+    o2 = orc.attend_row(q, orc.rand_vec(6 * hd, 11), orc.rand_vec(6 * hd, 12), 3, 2, 2, hd)
+    assert not np.array_equal(o2[:hd], o2[hd:])
+
+
+# ---- model properties (ferrum_ref/src/models/llama/tests.rs:L69-L111, gpt2 tests) --------------
+
+def test_tied_head_is_the_transposed_embedding():
+    t = helpers.ref_random_llama(helpers.tiny_llama_cfg(), 2, False, True)
+    assert np.array_equal(t.head, orc.transpose(t.tok, 13, 8))
+
+
+@pytest.mark.parametrize("ty,biases,kv", [(FC_ROPE_NORM, False, 2), (FC_ROPE_NEOX, True, 2),
+                                          (FC_ROPE_NORM, False, 4), (FC_ROPE_NEOX, True, 1)])
+def test_cached_decode_matches_the_full_forward_for_every_variant(ty, biases, kv):
+    cfg = helpers.tiny_llama_cfg(rope_type=ty, kv_heads=kv)
+    m = orc.OracleLlama(helpers.ref_random_llama(cfg, 3, biases, False))
+    ids = [3, 1, 4, 1, 5, 9, 2, 6]
+    full = m.forward_logits(ids)
+    for i, t in enumerate(ids):
+        step = m.feed(t)
+        assert np.abs(step - full[i]).max() < 1e-4
+    assert m.pos() == len(ids)
+
+
+def test_a_prefix_gives_the_same_logits_as_the_prefix_of_a_longer_run():
+    m = orc.OracleLlama(helpers.ref_random_llama(helpers.tiny_llama_cfg(), 4, False, False))
+    long, short = m.forward_logits([1, 2, 3, 4, 5]), m.forward_logits([1, 2, 3])
+    assert np.abs(long[:3] - short).max() < 1e-5
+
+
+def test_llama_errors():
+    cfg = helpers.tiny_llama_cfg()
+    m = orc.OracleLlama(helpers.ref_random_llama(cfg, 4, False, False))
+    with pytest.raises(ValueError, match="must be in 1..=12"):
+        m.forward_logits(list(range(13)))
+    with pytest.raises(IndexError):
+        m.feed(13)
+    for _ in range(12):
+        m.feed(1)
+    with pytest.raises(RuntimeError, match="context of 12 tokens is full"):
+        m.feed(1)
+    m.reset()
+    assert m.pos() == 0
+
+
+def test_gpt2_cached_feed_matches_forward_logits():
+    from ferrum_gpu_b200.hostmodel import Gpt2Config
+    cfg = Gpt2Config(vocab=11, ctx=10, dim=8, heads=2, layers=2, hidden=16)
+    m = orc.OracleGpt2(helpers.ref_random_gpt2(cfg, 1))
+    ids = [3, 1, 4, 1, 5, 9, 2, 6]
+    full = m.forward_logits(ids)
+    for i, t in enumerate(ids):
+        assert np.abs(m.feed(t) - full[i]).max() < 1e-4
+    with pytest.raises(RuntimeError, match="context of 10 tokens is full"):
+        m.feed(1); m.feed(1); m.feed(1)
+
+
+# ---- independent float32 numpy implementation of the Llama forward ------------------------------
+
+def _np_llama_forward(m, ids):
+    c = m.cfg
+    f = np.float32
+    d, qd, kvd, hd = c.dim, c.q_dim, c.kv_dim, c.head_dim
+    x = m.tok.reshape(c.vocab, d)[ids].astype(f)
+    n = len(ids)
+    half = c.rope_dim // 2
+    freq = (np.float64(c.rope_base) ** (-2.0 * np.arange(half) / c.rope_dim)).astype(f)
+    theta = (np.arange(n, dtype=f)[:, None] * freq[None, :]).astype(f)
+    cos, sin = np.cos(theta).astype(f), np.sin(theta).astype(f)
+
+    def rms(x, g):
+        ms = (x * x).mean(axis=1, keepdims=True, dtype=f)
+        return (x * (f(1) / np.sqrt(ms + f(c.eps))) * g).astype(f)
+
+    def rope(t, heads):
+        t = t.reshape(n, heads, hd).copy()
+        if c.rope_type == FC_ROPE_NORM:
+            a, b = t[:, :, 0:2 * half:2].copy(), t[:, :, 1:2 * half:2].copy()
+            t[:, :, 0:2 * half:2] = a * cos[:, None, :] - b * sin[:, None, :]
+            t[:, :, 1:2 * half:2] = a * sin[:, None, :] + b * cos[:, None, :]
+        else:
+            a, b = t[:, :, :half].copy(), t[:, :, half:2 * half].copy()
+            t[:, :, :half] = a * cos[:, None, :] - b * sin[:, None, :]
+            t[:, :, half:2 * half] = a * sin[:, None, :] + b * cos[:, None, :]
+        return t
+
+    for b in m.blocks:
+        h = rms(x, b.attn_norm)
+        q = h @ b.wq.reshape(d, qd)
+        k = h @ b.wk.reshape(d, kvd)
+        v = h @ b.wv.reshape(d, kvd)
+        if b.bq is not None:
+            q, k, v = q + b.bq, k + b.bk, v + b.bv
+        q, k, v = rope(q, c.heads), rope(k, c.kv_heads), v.reshape(n, c.kv_heads, hd)
+        g = c.heads // c.kv_heads
+        a = np.zeros((n, c.heads, hd), dtype=f)
+        for hh in range(c.heads):
+            s = (q[:, hh] @ k[:, hh // g].T) * f(1.0 / np.sqrt(f(hd)))
+            s = np.where(np.tril(np.ones((n, n), dtype=bool)), s, -np.inf)
+            p = np.exp(s - s.max(axis=1, keepdims=True))
+            p = p / p.sum(axis=1, keepdims=True)
+            a[:, hh] = p.astype(f) @ v[:, hh // g]
+        x = x + a.reshape(n, qd) @ b.wo.reshape(qd, d)
+        h = rms(x, b.ffn_norm)
+        gt, up = h @ b.gate.reshape(d, c.hidden), h @ b.up.reshape(d, c.hidden)
+        x = x + ((gt / (f(1) + np.exp(-gt))) * up).astype(f) @ b.down.reshape(c.hidden, d)
+    return rms(x, m.out_norm) @ m.head.reshape(d, c.vocab)
+
+
+@pytest.mark.parametrize("name,cfg,biases,tied", helpers.gpu_llama_variants())
+def test_oracle_llama_agrees_with_independent_numpy(name, cfg, biases, tied):
+    m = helpers.ref_random_llama(cfg, 7, biases, tied)
+    ids = [3, 16, 0, 9, 9, 4, 11, 2, 7, 5][:cfg.ctx]
+    got = orc.OracleLlama(m).forward_logits(ids)
+    want = _np_llama_forward(m, ids)
+    assert orc.max_rel_err(got, want) < 2e-5, name
