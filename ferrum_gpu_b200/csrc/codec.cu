@@ -1,0 +1,219 @@
+// Block codec on the device: the upload-time quantiser (bit-identical to
+// ferrum_gguf::quant::encode, ferrum_gguf/src/codec/quant.rs:L111-L133), the repack of GGUF
+// block bytes into split quant / scale planes, its inverse, and the bit-exact dequantiser
+// (codec/quant.rs:L50-L88).
+//
+// All kernels here are one-time or test-time work; they are written for exactness, with
+// explicit __fmul_rn / __fadd_rn / __fdiv_rn so the compiler can neither contract nor
+// approximate the encoder's arithmetic.
+#include "common.cuh"
+
+namespace {
+
+// Device position of element `e` (0..31) of a Q4_0 block: byte offset within the 16-byte block
+// and the shift of its nibble.
+__host__ __device__ inline void q4_dev_pos(int e, int& byte, int& shift) {
+  int w = e >> 3, j = e & 7;
+  int pos = (j >> 1) + 4 * (j & 1);
+  byte = w * 4 + (pos >> 1);
+  shift = (pos & 1) * 4;
+}
+
+// One thread per (block b, output column col); threads of a warp take consecutive columns so the
+// reads of the `[k, n]` matrix coalesce.
+template <int KIND>
+__global__ void quantise_kn_kernel(const float* __restrict__ w, uint32_t k, uint32_t n, uint8_t* __restrict__ qs,
+                                   __half* __restrict__ sc) {
+  uint32_t col = blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t b = blockIdx.y;
+  if (col >= n) return;
+  float v[QK];
+#pragma unroll
+  for (int j = 0; j < QK; j++) v[j] = w[(size_t)(b * QK + j) * n + col];
+  uint32_t nb = k / QK;
+  if (KIND == FC_Q8_0) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < QK; j++) amax = fmaxf(amax, fabsf(v[j]));
+    float d = __fdiv_rn(amax, 127.0f);
+    float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    sc[(size_t)col * nb + b] = __float2half_rn(d);
+    uint32_t words[QK / 4];
+#pragma unroll
+    for (int j = 0; j < QK; j++) {
+      float r = roundf(__fmul_rn(v[j], id)); // half away from zero
+      int q = (r != r) ? 0 : (int)fminf(fmaxf(r, -128.0f), 127.0f); // `as i8`: saturates, NaN -> 0
+      if ((j & 3) == 0) words[j >> 2] = 0;
+      words[j >> 2] |= (uint32_t)(q & 0xff) << (8 * (j & 3));
+    }
+    uint4* dst = reinterpret_cast<uint4*>(qs + (size_t)col * k + (size_t)b * QK);
+    dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+    dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+  } else {
+    float mx = 0.0f; // first element of largest magnitude, sign kept
+#pragma unroll
+    for (int j = 0; j < QK; j++)
+      if (fabsf(v[j]) > fabsf(mx)) mx = v[j];
+    float d = __fdiv_rn(mx, -8.0f);
+    float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    sc[(size_t)col * nb + b] = __float2half_rn(d);
+    uint32_t words[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int e = 0; e < QK; e++) {
+      float t = __fadd_rn(__fmul_rn(v[e], id), 8.5f);
+      // `as i32` truncates toward zero, saturates, NaN -> 0; then clamp(0, 15)
+      int q = (t != t) ? 0 : (t >= 15.0f ? 15 : (t <= 0.0f ? 0 : (int)t));
+      int byte, shift;
+      q4_dev_pos(e, byte, shift);
+      words[byte >> 2] |= (uint32_t)q << (8 * (byte & 3) + shift);
+    }
+    *reinterpret_cast<uint4*>(qs + (size_t)col * (k / 2) + (size_t)b * 16) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+// `[k, n]` -> `[n, k]` (for matrices kept in f32).
+__global__ void transpose_kn_kernel(const float* __restrict__ w, uint32_t k, uint32_t n, float* __restrict__ out) {
+  __shared__ float tile[32][33];
+  uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    uint32_t r = r0 + i, c = c0 + threadIdx.x;
+    if (r < k && c < n) tile[i][threadIdx.x] = w[(size_t)r * n + c];
+  }
+  __syncthreads();
+  for (int i = threadIdx.y; i < 32; i += blockDim.y) {
+    uint32_t c = c0 + i, r = r0 + threadIdx.x;
+    if (r < k && c < n) out[(size_t)c * k + r] = tile[threadIdx.x][i];
+  }
+}
+
+// GGUF block bytes (`n` rows of k/32 blocks of 34 or 18 bytes) -> planes. One thread per block.
+template <int KIND>
+__global__ void repack_blocks_kernel(const uint8_t* __restrict__ blocks, uint32_t k, uint32_t n,
+                                     uint8_t* __restrict__ qs, __half* __restrict__ sc) {
+  size_t nb = k / QK;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; // row * nb + b
+  if (idx >= nb * n) return;
+  constexpr int FB = KIND == FC_Q8_0 ? 34 : 18;
+  const uint8_t* p = blocks + idx * FB;
+  uint16_t h = (uint16_t)(p[0] | (p[1] << 8));
+  sc[idx] = __ushort_as_half(h);
+  if (KIND == FC_Q8_0) {
+    uint8_t* dst = qs + idx * QK;
+    for (int j = 0; j < QK; j++) dst[j] = p[2 + j];
+  } else {
+    uint32_t words[4] = {0, 0, 0, 0};
+    for (int e = 0; e < QK; e++) {
+      int q = e < 16 ? (p[2 + e] & 0x0f) : (p[2 + e - 16] >> 4);
+      int byte, shift;
+      q4_dev_pos(e, byte, shift);
+      words[byte >> 2] |= (uint32_t)q << (8 * (byte & 3) + shift);
+    }
+    *reinterpret_cast<uint4*>(qs + idx * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+// Planes -> GGUF block bytes.
+template <int KIND>
+__global__ void export_blocks_kernel(const uint8_t* __restrict__ qs, const __half* __restrict__ sc, uint32_t k,
+                                     uint32_t n, uint8_t* __restrict__ blocks) {
+  size_t nb = k / QK;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= nb * n) return;
+  constexpr int FB = KIND == FC_Q8_0 ? 34 : 18;
+  uint8_t* p = blocks + idx * FB;
+  uint16_t h = __half_as_ushort(sc[idx]);
+  p[0] = (uint8_t)(h & 0xff);
+  p[1] = (uint8_t)(h >> 8);
+  if (KIND == FC_Q8_0) {
+    for (int j = 0; j < QK; j++) p[2 + j] = qs[idx * QK + j];
+  } else {
+    const uint8_t* src = qs + idx * 16;
+    for (int j = 0; j < 16; j++) {
+      int b0, s0, b1, s1;
+      q4_dev_pos(j, b0, s0);
+      q4_dev_pos(j + 16, b1, s1);
+      p[2 + j] = (uint8_t)(((src[b0] >> s0) & 0x0f) | (((src[b1] >> s1) & 0x0f) << 4));
+    }
+  }
+}
+
+// Bit-exact decode: d * f32(q) and d * (f32(nibble) - 8), one rounding each, as the CPU decoder.
+template <int KIND>
+__global__ void dequant_kernel(const uint8_t* __restrict__ qs, const __half* __restrict__ sc, uint32_t k, uint32_t n,
+                               float* __restrict__ out) {
+  size_t nb = k / QK;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= nb * n) return;
+  float d = __half2float(sc[idx]);
+  float* o = out + idx * QK;
+  if (KIND == FC_Q8_0) {
+    const int8_t* q = reinterpret_cast<const int8_t*>(qs) + idx * QK;
+    for (int j = 0; j < QK; j++) o[j] = __fmul_rn(d, (float)q[j]);
+  } else {
+    const uint8_t* src = qs + idx * 16;
+    for (int e = 0; e < QK; e++) {
+      int byte, shift;
+      q4_dev_pos(e, byte, shift);
+      o[e] = __fmul_rn(d, (float)((src[byte] >> shift) & 0x0f) - 8.0f);
+    }
+  }
+}
+
+} // namespace
+
+int k_quantise_kn(FcDevice* dev, int kind, const float* w, uint32_t k, uint32_t n, uint8_t* qs, __half* sc) {
+  if (k == 0 || k % QK || n == 0) return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole 32-element blocks", k, n);
+  dim3 grid((n + 127) / 128, k / QK);
+  if (kind == FC_Q8_0)
+    FC_LAUNCH(dev, "quantise_q8_0", quantise_kn_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
+  else if (kind == FC_Q4_0)
+    FC_LAUNCH(dev, "quantise_q4_0", quantise_kn_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
+  else
+    return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  return FC_OK;
+}
+
+int k_transpose_kn(FcDevice* dev, const float* w, uint32_t k, uint32_t n, float* out) {
+  dim3 grid((n + 31) / 32, (k + 31) / 32), block(32, 8);
+  FC_LAUNCH(dev, "transpose_kn", transpose_kn_kernel<<<grid, block, 0, dev->stream>>>(w, k, n, out));
+  return FC_OK;
+}
+
+int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, uint32_t n, uint8_t* qs, __half* sc) {
+  size_t total = (size_t)(k / QK) * n;
+  unsigned grid = (unsigned)((total + 127) / 128);
+  if (kind == FC_Q8_0)
+    FC_LAUNCH(dev, "repack_q8_0", repack_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
+  else if (kind == FC_Q4_0)
+    FC_LAUNCH(dev, "repack_q4_0", repack_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
+  else
+    return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  return FC_OK;
+}
+
+int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
+  size_t total = (size_t)(m.k / QK) * m.n;
+  unsigned grid = (unsigned)((total + 127) / 128);
+  if (m.kind == FC_Q8_0)
+    FC_LAUNCH(dev, "export_q8_0", export_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
+  else if (m.kind == FC_Q4_0)
+    FC_LAUNCH(dev, "export_q4_0", export_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
+  else
+    return fc_fail(dev, FC_ERR_ARG, "an f32 weight has no block form");
+  return FC_OK;
+}
+
+int k_dequant(FcDevice* dev, const QMat& m, float* out) {
+  if (m.kind == FC_F32) {
+    FC_CUDA(dev, cudaMemcpyAsync(out, m.qs, (size_t)m.k * m.n * 4, cudaMemcpyDeviceToDevice, dev->stream));
+    return FC_OK;
+  }
+  size_t total = (size_t)(m.k / QK) * m.n;
+  unsigned grid = (unsigned)((total + 127) / 128);
+  if (m.kind == FC_Q8_0)
+    FC_LAUNCH(dev, "dequant_q8_0", dequant_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
+  else
+    FC_LAUNCH(dev, "dequant_q4_0", dequant_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
+  return FC_OK;
+}

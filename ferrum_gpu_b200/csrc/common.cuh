@@ -1,0 +1,122 @@
+// Shared host-side plumbing of libferrum_cuda: device handle, status/error helpers, launch
+// accounting with host-side fault injection, and the packed-weight descriptor every kernel takes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/ferrum_cuda.h"
+
+#define FC_API extern "C" __attribute__((visibility("default")))
+
+constexpr int QK = 32; // elements per quantisation block (ferrum_gguf/src/lib.rs:L55)
+
+struct FcDevice {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  std::string last_error;
+  bool lost = false;       // a CUDA call failed: sticky, like the reference's device-lost health
+  uint64_t launches = 0;   // kernels launched by this library on this device
+  int64_t fail_after = -1; // fault injection: launches left before every launch is refused
+  void* pinned = nullptr;  // pinned host staging for results and small inputs
+  size_t pinned_bytes = 0;
+  int* d_flag = nullptr;   // device int for kernels that report a status
+};
+
+// Record a message and hand back the status code.
+int fc_fail(FcDevice* dev, int code, const char* fmt, ...);
+
+// Counts one kernel launch; refuses it (before it reaches the device) when the injection hook
+// has run out. Every launch in the library goes through FC_LAUNCH.
+int fc_pre_launch(FcDevice* dev, const char* what);
+int fc_post_launch(FcDevice* dev, const char* what);
+
+#define FC_TRY(expr)            \
+  do {                          \
+    int _rc = (expr);           \
+    if (_rc != FC_OK) return _rc; \
+  } while (0)
+
+#define FC_CUDA(dev, expr)                                                                   \
+  do {                                                                                       \
+    cudaError_t _e = (expr);                                                                 \
+    if (_e != cudaSuccess) {                                                                 \
+      (dev)->lost = _e != cudaErrorMemoryAllocation;                                         \
+      return fc_fail((dev), _e == cudaErrorMemoryAllocation ? FC_ERR_OOM : FC_ERR_DEVICE,    \
+                     "%s: %s", #expr, cudaGetErrorString(_e));                               \
+    }                                                                                        \
+  } while (0)
+
+#define FC_LAUNCH(dev, what, ...)         \
+  do {                                    \
+    FC_TRY(fc_pre_launch((dev), (what))); \
+    __VA_ARGS__;                          \
+    FC_TRY(fc_post_launch((dev), (what))); \
+  } while (0)
+
+// Pinned staging buffer of at least `bytes` (grown on demand).
+int fc_pinned(FcDevice* dev, size_t bytes, void** out);
+
+// A weight matrix as the kernels see it: `n` output rows of `k` inputs.
+//  FC_Q8_0: qs = int8 [n][k];            sc = f16 [n][k/32]
+//  FC_Q4_0: qs = u8   [n][k/2], 16 bytes (four u32 words) per block; word w holds elements
+//           8w..8w+7 of the block, element j in nibble position (j>>1) + 4*(j&1), so that the
+//           mask pairs (p, p+4) of one word unpack to consecutive elements; sc as above
+//  FC_F32:  qs = f32  [n][k];            sc = nullptr
+struct QMat {
+  int kind = FC_F32;
+  uint32_t k = 0, n = 0;
+  const uint8_t* qs = nullptr;
+  const __half* sc = nullptr;
+};
+
+struct FcQWeight {
+  FcDevice* dev = nullptr;
+  QMat m;
+  void* qs_alloc = nullptr;
+  void* sc_alloc = nullptr;
+  uint64_t bytes = 0;
+  // bf16 GEMM operand descriptors are built lazily by the tensor path
+  void* tc_cache = nullptr;
+};
+
+static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
+  return kind == FC_Q8_0 ? k * n : kind == FC_Q4_0 ? k * n / 2 : k * n * 4;
+}
+static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) { return kind == FC_F32 ? 0 : (k / QK) * n * 2; }
+
+// Epilogue of a matrix product: y = act(x W + bias) (+ resid). All pointers device, nullable.
+enum { ACT_NONE = 0, ACT_GELU = 1 };
+struct Epilogue {
+  const float* bias = nullptr;  // [n]
+  const float* resid = nullptr; // [m][n]; may alias y
+  int act = ACT_NONE;
+};
+
+// ---- kernels' host entry points (each enqueues on dev->stream) --------------------------------
+// codec.cu
+int k_quantise_kn(FcDevice* dev, int kind, const float* w_kn_dev, uint32_t k, uint32_t n, uint8_t* qs, __half* sc);
+int k_transpose_kn(FcDevice* dev, const float* w_kn_dev, uint32_t k, uint32_t n, float* out_nk);
+int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks_dev, uint32_t k, uint32_t n, uint8_t* qs, __half* sc);
+int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks_dev);
+int k_dequant(FcDevice* dev, const QMat& m, float* out_nk_dev);
+// matvec.cu: m <= 8 rows
+int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
+// gemm_f32.cu: any m
+int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
+// The exact-f32 product of any m: picks matvec or tiled GEMM.
+int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
+
+// Upload helpers (weights.cu)
+int qweight_from_f32(FcDevice* dev, int kind, const float* w_in_out_host, uint32_t k, uint32_t n, FcQWeight** out);
+int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats_host, const uint32_t* ns, int count,
+                            uint32_t k, FcQWeight** out);
+void qweight_free(FcQWeight* w);

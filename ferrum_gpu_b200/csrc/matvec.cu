@@ -1,0 +1,222 @@
+// Memory-bound quantised matvec for decode: y[m, n] = x[m, k] . W[n, k]^T (+ bias, activation,
+// residual) for m = 1..8 rows of x. Replaces qgemv.wgsl / qlinear.wgsl for single rows
+// (ferrum_wgpu/src/shaders/quant, chosen by ops/quant.rs:L314-L323).
+//
+// Shape of the kernel: the weight planes are streamed once with 16-byte loads; a group of LPR
+// lanes owns R output rows at a time and walks their K axis in 16-byte chunks, so each lane has R
+// independent 16-byte loads in flight while the x chunk it needs (staged once per CTA in shared
+// memory) is read once and reused for the R rows. Integer quants are turned into floats with
+// bit tricks (no I2F), the per-block f16 scale multiplies the block's partial sum, accumulation
+// is f32, and the LPR partial sums are combined with warp shuffles.
+#include "common.cuh"
+
+namespace {
+
+template <int KIND>
+struct Chunk; // one 16-byte load of a weight row
+template <>
+struct Chunk<FC_Q8_0> {
+  static constexpr int ELEMS = 16;
+};
+template <>
+struct Chunk<FC_Q4_0> {
+  static constexpr int ELEMS = 32;
+};
+template <>
+struct Chunk<FC_F32> {
+  static constexpr int ELEMS = 4;
+};
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// sum over the chunk of x[e] * q[e] (scale not applied)
+template <int KIND>
+__device__ __forceinline__ float chunk_dot(const uint4& wq, const float* __restrict__ xs) {
+  float acc = 0.0f;
+  const uint32_t words[4] = {wq.x, wq.y, wq.z, wq.w};
+  if (KIND == FC_Q8_0) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      float4 xv = *reinterpret_cast<const float4*>(xs + 4 * w);
+      uint32_t u = words[w] ^ 0x80808080u; // int8 -> biased uint8
+      // 0x4B000000 | byte is the float 2^23 + byte; subtracting 2^23 + 128 gives the int8 exactly
+      float q0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+      float q1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+      float q2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+      float q3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+      acc = fmaf(xv.x, q0, acc);
+      acc = fmaf(xv.y, q1, acc);
+      acc = fmaf(xv.z, q2, acc);
+      acc = fmaf(xv.w, q3, acc);
+    }
+  } else if (KIND == FC_Q4_0) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      float4 xa = *reinterpret_cast<const float4*>(xs + 8 * w);
+      float4 xb = *reinterpret_cast<const float4*>(xs + 8 * w + 4);
+      const float xe[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int pos = (j >> 1) + 4 * (j & 1); // nibble position of element j
+        uint32_t nib = (words[w] >> (4 * pos)) & 0xfu;
+        float q = __uint_as_float(0x4B000000u | nib) - 8388616.0f; // (2^23 + nib) - (2^23 + 8)
+        acc = fmaf(xe[j], q, acc);
+      }
+    }
+  } else {
+    float4 xv = *reinterpret_cast<const float4*>(xs);
+    acc = fmaf(xv.x, __uint_as_float(wq.x), acc);
+    acc = fmaf(xv.y, __uint_as_float(wq.y), acc);
+    acc = fmaf(xv.z, __uint_as_float(wq.z), acc);
+    acc = fmaf(xv.w, __uint_as_float(wq.w), acc);
+  }
+  return acc;
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+  const float K = 0.7978846f; // ferrum_ref/src/kernels/nn.rs:L12-L15
+  return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
+}
+
+template <int KIND, int M, int LPR, int R>
+__global__ void __launch_bounds__(256)
+    qmatvec_kernel(QMat w, const float* __restrict__ x, float* __restrict__ y, Epilogue ep) {
+  extern __shared__ __align__(16) float xs[]; // [M][k]
+  const uint32_t k = w.k, n = w.n;
+  for (uint32_t i = threadIdx.x * 4; i < M * k; i += blockDim.x * 4)
+    *reinterpret_cast<float4*>(xs + i) = *reinterpret_cast<const float4*>(x + i);
+  __syncthreads();
+
+  constexpr int ELEMS = Chunk<KIND>::ELEMS;
+  constexpr int GROUPS_PER_WARP = 32 / LPR;
+  const uint32_t chunks = k / ELEMS;
+  const size_t row_bytes = (size_t)chunks * 16;
+  const uint32_t nb = k / QK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gl = lane % LPR, g = lane / LPR;
+  const uint32_t groups_per_block = (blockDim.x >> 5) * GROUPS_PER_WARP;
+  const uint32_t n_groups = (n + R - 1) / R;
+
+  // the loop bound is uniform across the warp (the shuffles below name every lane); a group past
+  // the end works on clamped rows and stores nothing
+  for (uint32_t base = blockIdx.x * groups_per_block + warp * GROUPS_PER_WARP; base < n_groups;
+       base += gridDim.x * groups_per_block) {
+    const uint32_t n0 = (base + g) * R;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int m = 0; m < M; m++) acc[r][m] = 0.0f;
+    uint32_t rows[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) rows[r] = min(n0 + r, n - 1); // clamped rows are computed and dropped
+
+    for (uint32_t c = gl; c < chunks; c += LPR) {
+      uint4 wq[R];
+      float d[R];
+#pragma unroll
+      for (int r = 0; r < R; r++) wq[r] = ldg_stream(w.qs + rows[r] * row_bytes + (size_t)c * 16);
+      if (KIND != FC_F32) {
+#pragma unroll
+        for (int r = 0; r < R; r++)
+          d[r] = __half2float(w.sc[(size_t)rows[r] * nb + (KIND == FC_Q8_0 ? (c >> 1) : c)]);
+      }
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        const float* xp = xs + (size_t)m * k + (size_t)c * ELEMS;
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          float s = chunk_dot<KIND>(wq[r], xp);
+          acc[r][m] = KIND == FC_F32 ? acc[r][m] + s : fmaf(d[r], s, acc[r][m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; r++)
+#pragma unroll
+      for (int m = 0; m < M; m++) {
+        float v = acc[r][m];
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        acc[r][m] = v;
+      }
+    if (gl == 0) {
+#pragma unroll
+      for (int r = 0; r < R; r++) {
+        const uint32_t row = n0 + r;
+        if (row < n) {
+#pragma unroll
+          for (int m = 0; m < M; m++) {
+            float v = acc[r][m];
+            if (ep.bias) v += ep.bias[row];
+            if (ep.act == ACT_GELU) v = gelu_f(v);
+            if (ep.resid) v = ep.resid[(size_t)m * n + row] + v;
+            y[(size_t)m * n + row] = v;
+          }
+        }
+      }
+    }
+  }
+}
+
+template <int KIND, int M, int LPR>
+int launch(FcDevice* dev, const QMat& w, const float* x, float* y, const Epilogue& ep) {
+  constexpr int R = M <= 2 ? 4 : 2;
+  const size_t smem = (size_t)M * w.k * sizeof(float);
+  auto kern = qmatvec_kernel<KIND, M, LPR, R>;
+  if (smem > 48 * 1024) FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const uint32_t groups_per_block = 8 * (32 / LPR);
+  const uint32_t n_groups = (w.n + R - 1) / R;
+  uint32_t blocks = (n_groups + groups_per_block - 1) / groups_per_block;
+  // persistent when there is more work than a few waves: x is staged once per CTA
+  const uint32_t max_blocks = (uint32_t)dev->prop.multiProcessorCount * 8;
+  if (blocks > max_blocks) blocks = max_blocks;
+  FC_LAUNCH(dev, "qmatvec", kern<<<blocks, 256, smem, dev->stream>>>(w, x, y, ep));
+  return FC_OK;
+}
+
+template <int KIND, int M>
+int pick_lpr(FcDevice* dev, const QMat& w, const float* x, float* y, const Epilogue& ep) {
+  const uint32_t chunks = w.k / Chunk<KIND>::ELEMS;
+  if (chunks % 32 == 0 || chunks > 256) return launch<KIND, M, 32>(dev, w, x, y, ep);
+  if (chunks % 16 == 0) return launch<KIND, M, 16>(dev, w, x, y, ep);
+  if (chunks % 8 == 0 || chunks > 16) return launch<KIND, M, 8>(dev, w, x, y, ep);
+  return launch<KIND, M, 4>(dev, w, x, y, ep);
+}
+
+template <int KIND>
+int pick_m(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
+  switch (m) {
+    case 1: return pick_lpr<KIND, 1>(dev, w, x, y, ep);
+    case 2: return pick_lpr<KIND, 2>(dev, w, x, y, ep);
+    case 3: return pick_lpr<KIND, 3>(dev, w, x, y, ep);
+    case 4: return pick_lpr<KIND, 4>(dev, w, x, y, ep);
+    case 5: return pick_lpr<KIND, 5>(dev, w, x, y, ep);
+    case 6: return pick_lpr<KIND, 6>(dev, w, x, y, ep);
+    case 7: return pick_lpr<KIND, 7>(dev, w, x, y, ep);
+    case 8: return pick_lpr<KIND, 8>(dev, w, x, y, ep);
+  }
+  return fc_fail(dev, FC_ERR_UNSUPPORTED, "the matvec kernel takes 1..8 rows, not %u", m);
+}
+
+} // namespace
+
+int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
+  if ((size_t)m * w.k * 4 > 200 * 1024 || w.k % 4)
+    return fc_fail(dev, FC_ERR_UNSUPPORTED, "matvec: %u rows of %u inputs do not fit the staging buffer", m, w.k);
+  if (w.kind == FC_Q8_0) return pick_m<FC_Q8_0>(dev, w, x, m, y, ep);
+  if (w.kind == FC_Q4_0) return pick_m<FC_Q4_0>(dev, w, x, m, y, ep);
+  return pick_m<FC_F32>(dev, w, x, m, y, ep);
+}
+
+int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
+  if (m == 0) return FC_OK;
+  if (m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0) return k_qmatvec(dev, w, x, m, y, ep);
+  return k_qgemm_f32(dev, w, x, m, y, ep);
+}

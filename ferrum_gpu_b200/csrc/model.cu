@@ -1,0 +1,635 @@
+// Resident-model orchestration and its C ABI: upload (quantise + pack), KV-cached decode for one or
+// many streams, batched prefill, stateless forward_all and scoring.
+//
+// Op order per layer follows the reference's resident models
+// (ferrum_wgpu/src/models/llama/mod.rs:L352-L438, forward.rs:L18-L72, models/gpt2.rs:L192-L265)
+// with the q/k/v products and the gate/up products each fused into one launch, bias / GELU /
+// residual folded into the product's epilogue, and RoPE fused with the cache store:
+//   norm -> qkv(+bias) -> rope+cache -> attention -> wo(+bias)+residual -> norm -> ff1(+bias, GELU)
+//   [-> swiglu] -> ff2(+bias)+residual;   final norm -> head.
+// That is 9 (Llama) / 8 (GPT-2) launches per layer against the reference's 18-21 / 15.
+#include <cmath>
+#include <cstring>
+
+#include "model.cuh"
+
+namespace {
+
+int dev_alloc(FcModel* m, size_t bytes, void** out) {
+  *out = nullptr;
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(out, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fc_fail(m->dev, FC_ERR_OOM, "cannot allocate %zu bytes: %s", bytes, cudaGetErrorString(e));
+  }
+  m->allocs.push_back(*out);
+  return FC_OK;
+}
+
+int upload_f32(FcModel* m, const float* host, size_t n, float** out) {
+  FC_TRY(dev_alloc(m, n * 4, (void**)out));
+  FC_CUDA(m->dev, cudaMemcpyAsync(*out, host, n * 4, cudaMemcpyHostToDevice, m->dev->stream));
+  FC_CUDA(m->dev, cudaStreamSynchronize(m->dev->stream));
+  return FC_OK;
+}
+
+// Concatenated bias of fused projections; a missing part contributes zeros; all missing = none.
+int upload_bias_concat(FcModel* m, const float* const* parts, const uint32_t* ns, int count, float** out) {
+  *out = nullptr;
+  bool any = false;
+  size_t total = 0;
+  for (int i = 0; i < count; i++) {
+    any = any || parts[i];
+    total += ns[i];
+  }
+  if (!any) return FC_OK;
+  std::vector<float> hb(total, 0.0f);
+  size_t off = 0;
+  for (int i = 0; i < count; i++) {
+    if (parts[i]) memcpy(hb.data() + off, parts[i], ns[i] * 4);
+    off += ns[i];
+  }
+  return upload_f32(m, hb.data(), total, out);
+}
+
+void model_free(FcModel* m) {
+  if (!m) return;
+  cudaSetDevice(m->dev->ordinal);
+  cudaStreamSynchronize(m->dev->stream);
+  model_tc_free(m);
+  for (auto& l : m->layers) {
+    qweight_free(l.qkv.w);
+    qweight_free(l.wo.w);
+    qweight_free(l.ff1.w);
+    qweight_free(l.ff2.w);
+  }
+  qweight_free(m->head.w);
+  for (void* p : m->allocs) cudaFree(p);
+  if (m->arena.base) cudaFree(m->arena.base);
+  delete m;
+}
+
+uint64_t matrix_bytes(int qkind, uint64_t k, uint64_t n) {
+  if (qkind != FC_F32 && k % QK == 0) return qmat_qs_bytes(qkind, k, n) + qmat_sc_bytes(qkind, k, n);
+  return k * n * 4;
+}
+
+struct Shape {
+  int arch;
+  uint64_t vocab, ctx, dim, heads, kv_heads, hd, layers, hidden, rope_dim;
+};
+
+// Named after models::llama::plan (ferrum_wgpu/src/models/llama/mod.rs:L108-L182): everything the
+// resident model allocates.
+uint64_t plan_bytes(const Shape& s, int qkind, uint64_t streams) {
+  const uint64_t d = s.dim, qd = s.heads * s.hd, kvd = s.kv_heads * s.hd, hid = s.hidden;
+  const uint64_t ff1 = s.arch == ARCH_LLAMA ? 2 * hid : hid;
+  uint64_t b = s.vocab * d * 4;                                      // token table (f32)
+  if (s.arch == ARCH_GPT2) b += s.ctx * d * 4;                       // position table
+  if (s.arch == ARCH_LLAMA) b += 2 * s.ctx * (s.rope_dim / 2) * 4;   // rope tables
+  uint64_t per = matrix_bytes(qkind, d, qd + 2 * kvd) + matrix_bytes(qkind, qd, d) + matrix_bytes(qkind, d, ff1) +
+                 matrix_bytes(qkind, hid, d);
+  per += 4 * d * 4 + (qd + 2 * kvd + d + ff1 + d) * 4;               // norms, biases (upper bound)
+  per += 2 * streams * s.ctx * kvd * 4;                              // K and V caches
+  b += per * s.layers;
+  b += 2 * d * 4 + matrix_bytes(qkind, d, s.vocab);                  // final norm, head
+  b += streams * (2 * d + (qd + 2 * kvd) + qd + ff1 + hid + s.vocab) * 4 + streams * 16; // decode scratch
+  return b;
+}
+
+int check_budget(FcDevice* dev, uint64_t need, uint64_t budget) {
+  size_t free_b = 0, total_b = 0;
+  FC_CUDA(dev, cudaMemGetInfo(&free_b, &total_b));
+  const uint64_t limit = budget ? budget : (uint64_t)free_b;
+  if (need > limit)
+    return fc_fail(dev, FC_ERR_OOM, "the model needs %llu bytes on the device, over the budget of %llu bytes",
+                   (unsigned long long)need, (unsigned long long)limit);
+  return FC_OK;
+}
+
+int alloc_common(FcModel* m) {
+  const uint32_t s = m->max_streams;
+  for (auto& l : m->layers) {
+    const size_t kvb = (size_t)s * m->ctx * m->kvd() * 4;
+    FC_TRY(dev_alloc(m, kvb, (void**)&l.kv.k));
+    FC_TRY(dev_alloc(m, kvb, (void**)&l.kv.v));
+    // caches start zeroed (models/llama/mod.rs:L266-L267)
+    FC_CUDA(m->dev, cudaMemsetAsync(l.kv.k, 0, kvb, m->dev->stream));
+    FC_CUDA(m->dev, cudaMemsetAsync(l.kv.v, 0, kvb, m->dev->stream));
+  }
+  FC_TRY(dev_alloc(m, (size_t)s * m->dim * 4, (void**)&m->x));
+  FC_TRY(dev_alloc(m, (size_t)s * m->dim * 4, (void**)&m->h));
+  FC_TRY(dev_alloc(m, (size_t)s * m->qkv_w() * 4, (void**)&m->qkv));
+  FC_TRY(dev_alloc(m, (size_t)s * m->qd() * 4, (void**)&m->attn));
+  FC_TRY(dev_alloc(m, (size_t)s * m->ff1_w() * 4, (void**)&m->ff));
+  FC_TRY(dev_alloc(m, (size_t)s * m->hidden * 4, (void**)&m->act));
+  FC_TRY(dev_alloc(m, (size_t)s * m->vocab * 4, (void**)&m->logits));
+  FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_ids));
+  FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_pos));
+  FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
+  FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
+  m->pos.assign(s, 0);
+  m->head_view = m->head.w->m;
+  m->v0 = 0;
+  m->v1 = m->vocab;
+  m->weight_bytes = m->head.w->bytes;
+  for (auto& l : m->layers) m->weight_bytes += l.qkv.w->bytes + l.wo.w->bytes + l.ff1.w->bytes + l.ff2.w->bytes;
+  FC_CUDA(m->dev, cudaStreamSynchronize(m->dev->stream));
+  return FC_OK;
+}
+
+// ---- the layer stack ------------------------------------------------------------------------------
+
+enum AttnMode { ATTN_DECODE, ATTN_STATELESS, ATTN_PREFILL_CACHE };
+
+struct PassBufs {
+  float *x, *h, *qkv, *attn, *ff, *act;
+};
+
+// Run `rows` rows through embedding and all layers in exact f32; leaves the final-norm output in
+// b.h. ATTN_DECODE: each row is its own stream (streams[] = cache slots). ATTN_STATELESS: n_seqs
+// sequences of t rows, no cache. ATTN_PREFILL_CACHE: t rows of one stream appended at `start`.
+int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32_t* positions, const int32_t* streams,
+                  uint32_t rows, AttnMode mode, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t stream) {
+  FcDevice* dev = m->dev;
+  const uint32_t d = m->dim;
+  FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, b.x));
+  for (auto& l : m->layers) {
+    if (m->arch == ARCH_LLAMA)
+      FC_TRY(k_rmsnorm(dev, b.x, l.norm1_g, rows, d, m->eps, b.h));
+    else
+      FC_TRY(k_layernorm(dev, b.x, l.norm1_g, l.norm1_b, rows, d, b.h));
+    Epilogue e_qkv;
+    e_qkv.bias = l.qkv.bias;
+    FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.h, rows, b.qkv, e_qkv));
+    const bool to_cache = mode != ATTN_STATELESS;
+    FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
+                     to_cache ? &l.kv : nullptr, m->ctx));
+    if (mode == ATTN_DECODE)
+      FC_TRY(k_attn_decode(dev, b.qkv, m->qkv_w(), rows, m->heads, m->kv_heads, m->hd, positions, streams, l.kv, m->ctx,
+                           b.attn));
+    else if (mode == ATTN_STATELESS)
+      FC_TRY(k_attn_causal_f32(dev, b.qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, b.attn));
+    else
+      FC_TRY(k_attn_prefill_cache_f32(dev, b.qkv, t, start, m->heads, m->kv_heads, m->hd, stream, l.kv, m->ctx, b.attn));
+    Epilogue e_wo;
+    e_wo.bias = l.wo.bias;
+    e_wo.resid = b.x;
+    FC_TRY(k_qlinear_f32(dev, l.wo.w->m, b.attn, rows, b.x, e_wo));
+    if (m->arch == ARCH_LLAMA)
+      FC_TRY(k_rmsnorm(dev, b.x, l.norm2_g, rows, d, m->eps, b.h));
+    else
+      FC_TRY(k_layernorm(dev, b.x, l.norm2_g, l.norm2_b, rows, d, b.h));
+    Epilogue e_ff1;
+    e_ff1.bias = l.ff1.bias;
+    e_ff1.act = m->arch == ARCH_GPT2 ? ACT_GELU : ACT_NONE;
+    FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.h, rows, b.ff, e_ff1));
+    const float* ff2_in = b.ff;
+    if (m->arch == ARCH_LLAMA) {
+      FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, b.act));
+      ff2_in = b.act;
+    }
+    Epilogue e_ff2;
+    e_ff2.bias = l.ff2.bias;
+    e_ff2.resid = b.x;
+    FC_TRY(k_qlinear_f32(dev, l.ff2.w->m, ff2_in, rows, b.x, e_ff2));
+  }
+  if (m->arch == ARCH_LLAMA)
+    FC_TRY(k_rmsnorm(dev, b.x, m->normf_g, rows, d, m->eps, b.h));
+  else
+    FC_TRY(k_layernorm(dev, b.x, m->normf_g, m->normf_b, rows, d, b.h));
+  return FC_OK;
+}
+
+int carve_pass(FcModel* m, uint32_t rows, PassBufs* b, size_t extra_bytes) {
+  auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t need = al((size_t)rows * m->dim * 4) * 2 + al((size_t)rows * m->qkv_w() * 4) + al((size_t)rows * m->qd() * 4) +
+                      al((size_t)rows * m->ff1_w() * 4) + al((size_t)rows * m->hidden * 4) + al(extra_bytes) + 4096;
+  FC_TRY(arena_reserve(m, need));
+  b->x = (float*)arena_take(m, (size_t)rows * m->dim * 4);
+  b->h = (float*)arena_take(m, (size_t)rows * m->dim * 4);
+  b->qkv = (float*)arena_take(m, (size_t)rows * m->qkv_w() * 4);
+  b->attn = (float*)arena_take(m, (size_t)rows * m->qd() * 4);
+  b->ff = (float*)arena_take(m, (size_t)rows * m->ff1_w() * 4);
+  b->act = (float*)arena_take(m, (size_t)rows * m->hidden * 4);
+  return FC_OK;
+}
+
+int check_ids(FcModel* m, const int32_t* ids, size_t n) {
+  for (size_t i = 0; i < n; i++)
+    if (ids[i] < 0 || (uint32_t)ids[i] >= m->vocab)
+      return fc_fail(m->dev, FC_ERR_RANGE, "index %d is out of range for %u entries", ids[i], m->vocab);
+  return FC_OK;
+}
+
+// positions 0..t-1 repeated n_seqs times, on the device
+int upload_positions(FcModel* m, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t* dst_dev) {
+  void* pin;
+  FC_TRY(fc_pinned(m->dev, (size_t)n_seqs * t * 4, &pin));
+  int32_t* p = (int32_t*)pin;
+  for (uint32_t s = 0; s < n_seqs; s++)
+    for (uint32_t i = 0; i < t; i++) p[(size_t)s * t + i] = (int32_t)(start + i);
+  FC_CUDA(m->dev, cudaMemcpyAsync(dst_dev, p, (size_t)n_seqs * t * 4, cudaMemcpyHostToDevice, m->dev->stream));
+  FC_CUDA(m->dev, cudaStreamSynchronize(m->dev->stream)); // the pinned buffer is reused by the caller
+  return FC_OK;
+}
+
+} // namespace
+
+int arena_reserve(FcModel* m, size_t bytes) {
+  m->arena.off = 0;
+  if (bytes <= m->arena.cap) return FC_OK;
+  FC_CUDA(m->dev, cudaStreamSynchronize(m->dev->stream));
+  if (m->arena.base) cudaFree(m->arena.base);
+  m->arena.base = nullptr;
+  m->arena.cap = 0;
+  cudaError_t e = cudaMalloc((void**)&m->arena.base, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fc_fail(m->dev, FC_ERR_OOM, "cannot allocate a %zu-byte workspace: %s", bytes, cudaGetErrorString(e));
+  }
+  m->arena.cap = bytes;
+  return FC_OK;
+}
+
+void* arena_take(FcModel* m, size_t bytes) {
+  void* p = m->arena.base + m->arena.off;
+  m->arena.off += (bytes + 255) & ~(size_t)255;
+  return p;
+}
+
+int model_trunk_f32(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, uint32_t n_seqs, uint32_t t,
+                    float* hidden_out) {
+  // the caller has reserved the arena and carved nothing else after this call's buffers
+  PassBufs b;
+  const uint32_t rows = n_seqs * t;
+  b.x = (float*)arena_take(m, (size_t)rows * m->dim * 4);
+  b.h = hidden_out ? hidden_out : (float*)arena_take(m, (size_t)rows * m->dim * 4);
+  b.qkv = (float*)arena_take(m, (size_t)rows * m->qkv_w() * 4);
+  b.attn = (float*)arena_take(m, (size_t)rows * m->qd() * 4);
+  b.ff = (float*)arena_take(m, (size_t)rows * m->ff1_w() * 4);
+  b.act = (float*)arena_take(m, (size_t)rows * m->hidden * 4);
+  return run_stack_f32(m, b, ids_dev, pos_dev, nullptr, rows, ATTN_STATELESS, n_seqs, t, 0, 0);
+}
+
+// ================================ C ABI ===========================================================
+
+static bool valid_llama(const FcLlamaConfig* c) {
+  if (!c) return false;
+  const uint32_t dims[] = {c->vocab, c->ctx, c->dim, c->heads, c->kv_heads, c->head_dim, c->layers, c->hidden, c->rope_dim};
+  for (uint32_t v : dims)
+    if (v == 0) return false;
+  if (c->heads % c->kv_heads) return false;
+  if (c->rope_dim > c->head_dim || c->rope_dim % 2) return false;
+  auto bad = [](float v) { return !std::isfinite(v) || v <= 0.0f; };
+  if (bad(c->eps) || bad(c->rope_base) || bad(c->rope_linear_factor)) return false;
+  if (c->n_freq_factors != 0 && (c->n_freq_factors != c->rope_dim / 2 || !c->freq_factors)) return false;
+  return true;
+}
+
+static bool valid_gpt2(const FcGpt2Config* c) {
+  if (!c) return false;
+  const uint32_t dims[] = {c->vocab, c->ctx, c->dim, c->heads, c->layers, c->hidden};
+  for (uint32_t v : dims)
+    if (v == 0) return false;
+  return c->dim % c->heads == 0;
+}
+
+FC_API uint64_t fc_llama_plan_bytes(const FcLlamaConfig* c, int qkind, uint32_t max_streams) {
+  if (!valid_llama(c) || max_streams == 0) return 0;
+  Shape s{ARCH_LLAMA, c->vocab, c->ctx, c->dim, c->heads, c->kv_heads, c->head_dim, c->layers, c->hidden, c->rope_dim};
+  return plan_bytes(s, qkind, max_streams);
+}
+
+FC_API uint64_t fc_gpt2_plan_bytes(const FcGpt2Config* c, int qkind, uint32_t max_streams) {
+  if (!valid_gpt2(c) || max_streams == 0) return 0;
+  Shape s{ARCH_GPT2, c->vocab, c->ctx, c->dim, c->heads, c->heads, c->dim / c->heads, c->layers, c->hidden, 0};
+  return plan_bytes(s, qkind, max_streams);
+}
+
+FC_API int fc_llama_create(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaWeights* w, int qkind,
+                           uint32_t max_streams, uint64_t budget_bytes, FcModel** out) {
+  if (!dev || !out) return FC_ERR_ARG;
+  *out = nullptr;
+  cudaSetDevice(dev->ordinal);
+  if (!valid_llama(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid Llama configuration");
+  if (!w || !w->tok || !w->blocks || !w->out_norm || !w->head) return fc_fail(dev, FC_ERR_ARG, "missing weights");
+  if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
+  if (qkind != FC_F32 && qkind != FC_Q8_0 && qkind != FC_Q4_0) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
+  FC_TRY(check_budget(dev, fc_llama_plan_bytes(c, qkind, max_streams), budget_bytes)); // before any allocation
+  FcModel* m = new FcModel();
+  m->dev = dev;
+  m->arch = ARCH_LLAMA;
+  m->qkind = qkind;
+  m->vocab = c->vocab, m->ctx = c->ctx, m->dim = c->dim, m->heads = c->heads, m->kv_heads = c->kv_heads;
+  m->hd = c->head_dim, m->n_layers = c->layers, m->hidden = c->hidden, m->eps = c->eps;
+  m->max_streams = max_streams;
+  const uint32_t d = m->dim, qd = m->qd(), kvd = m->kvd(), hid = m->hidden;
+  int rc = FC_OK;
+  auto fail = [&](int code) {
+    model_free(m);
+    return code;
+  };
+  // RoPE tables on the host in the reference's precision (ferrum_ref/src/models/llama/ops.rs:L80-L101)
+  {
+    const uint32_t half = c->rope_dim / 2;
+    std::vector<float> hc((size_t)c->ctx * half), hs((size_t)c->ctx * half);
+    for (uint32_t p = 0; p < c->ctx; p++)
+      for (uint32_t i = 0; i < half; i++) {
+        const float freq = (float)std::pow((double)c->rope_base, -2.0 * (double)i / (double)c->rope_dim);
+        const float ff = i < c->n_freq_factors ? c->freq_factors[i] : 1.0f;
+        const float theta = (float)p * freq / ff * (1.0f / c->rope_linear_factor);
+        hc[(size_t)p * half + i] = cosf(theta);
+        hs[(size_t)p * half + i] = sinf(theta);
+      }
+    if ((rc = upload_f32(m, hc.data(), hc.size(), &m->cos)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, hs.data(), hs.size(), &m->sin)) != FC_OK) return fail(rc);
+    m->rope.cos = m->cos, m->rope.sin = m->sin, m->rope.rope_dim = c->rope_dim, m->rope.type = c->rope_type;
+  }
+  if ((rc = upload_f32(m, w->tok, (size_t)c->vocab * d, &m->tok)) != FC_OK) return fail(rc);
+  if ((rc = upload_f32(m, w->out_norm, d, &m->normf_g)) != FC_OK) return fail(rc);
+  m->layers.resize(c->layers);
+  for (uint32_t li = 0; li < c->layers; li++) {
+    const FcLlamaBlock& b = w->blocks[li];
+    Layer& l = m->layers[li];
+    if (!b.attn_norm || !b.wq || !b.wk || !b.wv || !b.wo || !b.ffn_norm || !b.gate || !b.up || !b.down)
+      return fail(fc_fail(dev, FC_ERR_ARG, "block %u is missing a tensor", li));
+    if ((rc = upload_f32(m, b.attn_norm, d, &l.norm1_g)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.ffn_norm, d, &l.norm2_g)) != FC_OK) return fail(rc);
+    const float* qkv_m[3] = {b.wq, b.wk, b.wv};
+    const uint32_t qkv_n[3] = {qd, kvd, kvd};
+    if ((rc = qweight_from_f32_concat(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
+    const float* qkv_b[3] = {b.bq, b.bk, b.bv};
+    if ((rc = upload_bias_concat(m, qkv_b, qkv_n, 3, &l.qkv.bias)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_f32(dev, qkind, b.wo, qd, d, &l.wo.w)) != FC_OK) return fail(rc);
+    const float* gu_m[2] = {b.gate, b.up};
+    const uint32_t gu_n[2] = {hid, hid};
+    if ((rc = qweight_from_f32_concat(dev, qkind, gu_m, gu_n, 2, d, &l.ff1.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_f32(dev, qkind, b.down, hid, d, &l.ff2.w)) != FC_OK) return fail(rc);
+  }
+  if ((rc = qweight_from_f32(dev, qkind, w->head, d, c->vocab, &m->head.w)) != FC_OK) return fail(rc);
+  if ((rc = alloc_common(m)) != FC_OK) return fail(rc);
+  *out = m;
+  return FC_OK;
+}
+
+FC_API int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* c, const FcGpt2Weights* w, int qkind, uint32_t max_streams,
+                          uint64_t budget_bytes, FcModel** out) {
+  if (!dev || !out) return FC_ERR_ARG;
+  *out = nullptr;
+  cudaSetDevice(dev->ordinal);
+  if (!valid_gpt2(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid GPT-2 configuration");
+  if (!w || !w->tok || !w->pos || !w->blocks || !w->lnf_g || !w->lnf_b || !w->head)
+    return fc_fail(dev, FC_ERR_ARG, "missing weights");
+  if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
+  if (qkind != FC_F32 && qkind != FC_Q8_0 && qkind != FC_Q4_0) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
+  FC_TRY(check_budget(dev, fc_gpt2_plan_bytes(c, qkind, max_streams), budget_bytes));
+  FcModel* m = new FcModel();
+  m->dev = dev;
+  m->arch = ARCH_GPT2;
+  m->qkind = qkind;
+  m->vocab = c->vocab, m->ctx = c->ctx, m->dim = c->dim, m->heads = c->heads, m->kv_heads = c->heads;
+  m->hd = c->dim / c->heads, m->n_layers = c->layers, m->hidden = c->hidden;
+  m->max_streams = max_streams;
+  const uint32_t d = m->dim, hid = m->hidden;
+  int rc = FC_OK;
+  auto fail = [&](int code) {
+    model_free(m);
+    return code;
+  };
+  if ((rc = upload_f32(m, w->tok, (size_t)c->vocab * d, &m->tok)) != FC_OK) return fail(rc);
+  if ((rc = upload_f32(m, w->pos, (size_t)c->ctx * d, &m->pos_table)) != FC_OK) return fail(rc);
+  if ((rc = upload_f32(m, w->lnf_g, d, &m->normf_g)) != FC_OK) return fail(rc);
+  if ((rc = upload_f32(m, w->lnf_b, d, &m->normf_b)) != FC_OK) return fail(rc);
+  m->layers.resize(c->layers);
+  for (uint32_t li = 0; li < c->layers; li++) {
+    const FcGpt2Block& b = w->blocks[li];
+    Layer& l = m->layers[li];
+    const float* need[] = {b.ln1_g, b.ln1_b, b.wq, b.bq, b.wk, b.bk, b.wv, b.bv, b.wo, b.bo, b.ln2_g, b.ln2_b, b.w1, b.b1, b.w2, b.b2};
+    for (const float* p : need)
+      if (!p) return fail(fc_fail(dev, FC_ERR_ARG, "block %u is missing a tensor", li));
+    if ((rc = upload_f32(m, b.ln1_g, d, &l.norm1_g)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.ln1_b, d, &l.norm1_b)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.ln2_g, d, &l.norm2_g)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.ln2_b, d, &l.norm2_b)) != FC_OK) return fail(rc);
+    const float* qkv_m[3] = {b.wq, b.wk, b.wv};
+    const uint32_t qkv_n[3] = {d, d, d};
+    if ((rc = qweight_from_f32_concat(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
+    const float* qkv_b[3] = {b.bq, b.bk, b.bv};
+    if ((rc = upload_bias_concat(m, qkv_b, qkv_n, 3, &l.qkv.bias)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_f32(dev, qkind, b.wo, d, d, &l.wo.w)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.bo, d, &l.wo.bias)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_f32(dev, qkind, b.w1, d, hid, &l.ff1.w)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.b1, hid, &l.ff1.bias)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_f32(dev, qkind, b.w2, hid, d, &l.ff2.w)) != FC_OK) return fail(rc);
+    if ((rc = upload_f32(m, b.b2, d, &l.ff2.bias)) != FC_OK) return fail(rc);
+  }
+  if ((rc = qweight_from_f32(dev, qkind, w->head, d, c->vocab, &m->head.w)) != FC_OK) return fail(rc);
+  if ((rc = alloc_common(m)) != FC_OK) return fail(rc);
+  *out = m;
+  return FC_OK;
+}
+
+FC_API int fc_model_destroy(FcModel* m) {
+  if (!m) return FC_ERR_ARG;
+  model_free(m);
+  return FC_OK;
+}
+
+FC_API int fc_model_pos(FcModel* m, uint32_t stream_id, uint32_t* pos_out) {
+  if (!m || !pos_out) return FC_ERR_ARG;
+  if (stream_id >= m->max_streams) return fc_fail(m->dev, FC_ERR_RANGE, "stream %u of %u", stream_id, m->max_streams);
+  *pos_out = m->pos[stream_id];
+  return FC_OK;
+}
+
+FC_API int fc_model_reset(FcModel* m, uint32_t stream_id) {
+  if (!m) return FC_ERR_ARG;
+  if (stream_id >= m->max_streams) return fc_fail(m->dev, FC_ERR_RANGE, "stream %u of %u", stream_id, m->max_streams);
+  m->pos[stream_id] = 0;
+  return FC_OK;
+}
+
+FC_API int fc_model_info(FcModel* m, uint32_t* vocab, uint32_t* ctx, uint32_t* max_streams, int* qkind,
+                         uint64_t* weight_bytes) {
+  if (!m) return FC_ERR_ARG;
+  if (vocab) *vocab = m->vocab;
+  if (ctx) *ctx = m->ctx;
+  if (max_streams) *max_streams = m->max_streams;
+  if (qkind) *qkind = m->qkind;
+  if (weight_bytes) *weight_bytes = m->weight_bytes;
+  return FC_OK;
+}
+
+FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* tokens,
+                               float* logits_out, int32_t* argmax_out) {
+  if (!m || !stream_ids || !tokens) return FC_ERR_ARG;
+  FcDevice* dev = m->dev;
+  cudaSetDevice(dev->ordinal);
+  if (n == 0) return FC_OK;
+  if (n > m->max_streams) return fc_fail(dev, FC_ERR_SHAPE, "%u rows for a model of %u streams", n, m->max_streams);
+  if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "decode needs the whole head on this device");
+  std::vector<uint8_t> seen(m->max_streams, 0);
+  for (uint32_t i = 0; i < n; i++) {
+    if (stream_ids[i] >= m->max_streams) return fc_fail(dev, FC_ERR_RANGE, "stream %u of %u", stream_ids[i], m->max_streams);
+    if (seen[stream_ids[i]]) return fc_fail(dev, FC_ERR_ARG, "stream %u appears twice in one step", stream_ids[i]);
+    seen[stream_ids[i]] = 1;
+    if (m->pos[stream_ids[i]] >= m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
+  }
+  FC_TRY(check_ids(m, tokens, n));
+  void* pin;
+  FC_TRY(fc_pinned(dev, (size_t)n * 12 + (size_t)n * 4, &pin));
+  int32_t* p = (int32_t*)pin;
+  for (uint32_t i = 0; i < n; i++) {
+    p[i] = tokens[i];
+    p[n + i] = (int32_t)m->pos[stream_ids[i]];
+    p[2 * n + i] = (int32_t)stream_ids[i];
+  }
+  FC_CUDA(dev, cudaMemcpyAsync(m->d_ids, p, n * 4, cudaMemcpyHostToDevice, dev->stream));
+  FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
+  FC_CUDA(dev, cudaMemcpyAsync(m->d_streams, p + 2 * n, n * 4, cudaMemcpyHostToDevice, dev->stream));
+  PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
+  FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0));
+  FC_TRY(k_qlinear_f32(dev, m->head_view, m->h, n, m->logits, Epilogue()));
+  if (argmax_out) {
+    FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax));
+    FC_CUDA(dev, cudaMemcpyAsync(p + 3 * n, m->d_argmax, n * 4, cudaMemcpyDeviceToHost, dev->stream));
+  }
+  if (logits_out)
+    FC_CUDA(dev, cudaMemcpyAsync(logits_out, m->logits, (size_t)n * m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (argmax_out) memcpy(argmax_out, p + 3 * n, n * 4);
+  for (uint32_t i = 0; i < n; i++) m->pos[stream_ids[i]]++; // only a step that fully succeeded advances
+  return FC_OK;
+}
+
+FC_API int fc_model_feed(FcModel* m, uint32_t stream_id, int32_t token, float* logits_out, int32_t* argmax_out) {
+  return fc_model_feed_batch(m, 1, &stream_id, &token, logits_out, argmax_out);
+}
+
+// ids to the device workspace; returns the device pointer
+static int upload_ids(FcModel* m, const int32_t* ids, size_t n, int32_t* dst_dev) {
+  FC_CUDA(m->dev, cudaMemcpyAsync(dst_dev, ids, n * 4, cudaMemcpyHostToDevice, m->dev->stream));
+  return FC_OK;
+}
+
+FC_API int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, uint32_t n, float* logits_out,
+                            int32_t* argmax_out, int mode) {
+  if (!m || !ids) return FC_ERR_ARG;
+  FcDevice* dev = m->dev;
+  cudaSetDevice(dev->ordinal);
+  if (stream_id >= m->max_streams) return fc_fail(dev, FC_ERR_RANGE, "stream %u of %u", stream_id, m->max_streams);
+  if (n == 0) return FC_OK;
+  if (mode != FC_EXACT_F32) return fc_fail(dev, FC_ERR_UNSUPPORTED, "prefill runs in FC_EXACT_F32 only");
+  if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "prefill needs the whole head on this device");
+  const uint32_t start = m->pos[stream_id];
+  if (start + n > m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
+  FC_TRY(check_ids(m, ids, n));
+  PassBufs b;
+  FC_TRY(carve_pass(m, n, &b, (size_t)n * 12 + 768));
+  int32_t* d_ids = (int32_t*)arena_take(m, (size_t)n * 4);
+  int32_t* d_pos = (int32_t*)arena_take(m, (size_t)n * 4);
+  int32_t* d_slots = (int32_t*)arena_take(m, (size_t)n * 4); // every row writes the same stream's cache
+  void* pin;
+  FC_TRY(fc_pinned(dev, (size_t)n * 4, &pin));
+  for (uint32_t i = 0; i < n; i++) ((int32_t*)pin)[i] = (int32_t)stream_id;
+  FC_CUDA(dev, cudaMemcpyAsync(d_slots, pin, (size_t)n * 4, cudaMemcpyHostToDevice, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  FC_TRY(upload_positions(m, 1, n, start, d_pos));
+  FC_TRY(upload_ids(m, ids, n, d_ids));
+  FC_TRY(run_stack_f32(m, b, d_ids, d_pos, d_slots, n, ATTN_PREFILL_CACHE, 1, n, start, (int32_t)stream_id));
+  if (logits_out || argmax_out) {
+    FC_TRY(k_qlinear_f32(dev, m->head_view, b.h + (size_t)(n - 1) * m->dim, 1, m->logits, Epilogue()));
+    if (argmax_out) {
+      FC_TRY(k_argmax(dev, m->logits, 1, m->vocab, m->d_argmax));
+      FC_CUDA(dev, cudaMemcpyAsync(argmax_out, m->d_argmax, 4, cudaMemcpyDeviceToHost, dev->stream));
+    }
+    if (logits_out)
+      FC_CUDA(dev, cudaMemcpyAsync(logits_out, m->logits, (size_t)m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+  }
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  m->pos[stream_id] = start + n;
+  return FC_OK;
+}
+
+FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, float* logits_out, int mode) {
+  if (!m || !ids || !logits_out) return FC_ERR_ARG;
+  FcDevice* dev = m->dev;
+  cudaSetDevice(dev->ordinal);
+  if (n == 0 || n > m->ctx) return fc_fail(dev, FC_ERR_SHAPE, "sequence length %u must be in 1..=%u", n, m->ctx);
+  if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "forward_all needs the whole head on this device");
+  FC_TRY(check_ids(m, ids, n));
+  const size_t extra = (size_t)n * 8 + 512 + (size_t)n * m->vocab * 4 + 256 + (size_t)n * m->dim * 2 + 256;
+  PassBufs b;
+  FC_TRY(carve_pass(m, n, &b, extra));
+  int32_t* d_ids = (int32_t*)arena_take(m, (size_t)n * 4);
+  int32_t* d_pos = (int32_t*)arena_take(m, (size_t)n * 4);
+  float* logits = (float*)arena_take(m, (size_t)n * m->vocab * 4);
+  FC_TRY(upload_positions(m, 1, n, 0, d_pos));
+  FC_TRY(upload_ids(m, ids, n, d_ids));
+  if (mode == FC_EXACT_F32) {
+    FC_TRY(run_stack_f32(m, b, d_ids, d_pos, nullptr, n, ATTN_STATELESS, 1, n, 0, 0));
+    FC_TRY(k_qlinear_f32(dev, m->head_view, b.h, n, logits, Epilogue()));
+  } else if (mode == FC_TENSOR_BF16) {
+    __nv_bfloat16* hid = (__nv_bfloat16*)arena_take(m, (size_t)n * m->dim * 2);
+    FC_TRY(model_trunk_tc(m, d_ids, d_pos, 1, n, hid));
+    FC_TRY(model_logits_tc(m, hid, n, logits));
+  } else {
+    return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
+  }
+  FC_CUDA(dev, cudaMemcpyAsync(logits_out, logits, (size_t)n * m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FC_OK;
+}
+
+// Scoring of sequences already on the device. Sequences are processed in chunks that bound the
+// workspace; every chunk runs trunk -> head partials -> combine.
+FC_API int fc_model_score_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seqs, uint32_t seq_len, int mode,
+                              float* logprob_dev, uint8_t* greedy_dev, double* nll_sum_dev);
+
+FC_API int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint32_t seq_len, int mode,
+                          float* logprob_out, uint8_t* greedy_out, double* nll_sum_out) {
+  if (!m || !ids) return FC_ERR_ARG;
+  FcDevice* dev = m->dev;
+  cudaSetDevice(dev->ordinal);
+  if (seq_len < 2) return fc_fail(dev, FC_ERR_SHAPE, "scoring needs at least 2 tokens");
+  if (seq_len - 1 > m->ctx) return fc_fail(dev, FC_ERR_SHAPE, "sequence length %u must be in 1..=%u", seq_len - 1, m->ctx);
+  if (n_seqs == 0) return FC_OK;
+  FC_TRY(check_ids(m, ids, (size_t)n_seqs * seq_len));
+  const size_t rows = (size_t)n_seqs * (seq_len - 1);
+  int32_t* d_ids = nullptr;
+  float* d_lp = nullptr;
+  uint8_t* d_gr = nullptr;
+  double* d_nll = nullptr;
+  auto cleanup = [&]() {
+    if (d_ids) cudaFree(d_ids);
+    if (d_lp) cudaFree(d_lp);
+    if (d_gr) cudaFree(d_gr);
+    if (d_nll) cudaFree(d_nll);
+  };
+  cudaError_t e = cudaMalloc((void**)&d_ids, (size_t)n_seqs * seq_len * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&d_lp, rows * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&d_gr, rows);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&d_nll, (size_t)n_seqs * 8);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    cleanup();
+    return fc_fail(dev, FC_ERR_OOM, "cannot allocate scoring buffers: %s", cudaGetErrorString(e));
+  }
+  int rc = FC_OK;
+  if (cudaMemcpyAsync(d_ids, ids, (size_t)n_seqs * seq_len * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
+    rc = fc_fail(dev, FC_ERR_DEVICE, "upload of ids failed");
+  if (rc == FC_OK) rc = fc_model_score_dev(m, d_ids, n_seqs, seq_len, mode, d_lp, d_gr, d_nll);
+  if (rc == FC_OK) {
+    if (logprob_out) cudaMemcpyAsync(logprob_out, d_lp, rows * 4, cudaMemcpyDeviceToHost, dev->stream);
+    if (greedy_out) cudaMemcpyAsync(greedy_out, d_gr, rows, cudaMemcpyDeviceToHost, dev->stream);
+    if (nll_sum_out) cudaMemcpyAsync(nll_sum_out, d_nll, (size_t)n_seqs * 8, cudaMemcpyDeviceToHost, dev->stream);
+    if (cudaStreamSynchronize(dev->stream) != cudaSuccess) {
+      dev->lost = true;
+      rc = fc_fail(dev, FC_ERR_DEVICE, "scoring failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+  }
+  cleanup();
+  return rc;
+}

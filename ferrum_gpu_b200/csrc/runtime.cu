@@ -1,0 +1,209 @@
+// Device handle, error reporting, launch accounting / host-side fault injection, weight upload.
+// The CUDA counterpart of ferrum_wgpu::device (ferrum_wgpu/src/device/{mod,runtime,tensor}.rs):
+// errors are values, a failed CUDA call makes the handle report "lost" from then on, and the
+// fault hook refuses the k-th launch before it reaches the device.
+#include <mutex>
+
+#include "common.cuh"
+
+static std::string g_no_device_error;
+static std::mutex g_err_mutex;
+
+int fc_fail(FcDevice* dev, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (dev) {
+    dev->last_error = buf;
+  } else {
+    std::lock_guard<std::mutex> lock(g_err_mutex);
+    g_no_device_error = buf;
+  }
+  return code;
+}
+
+int fc_pre_launch(FcDevice* dev, const char* what) {
+  if (dev->lost) return fc_fail(dev, FC_ERR_DEVICE, "device lost: %s refused after an earlier CUDA failure", what);
+  if (dev->fail_after == 0) return fc_fail(dev, FC_ERR_INJECTED, "injected fault: launch of %s refused", what);
+  if (dev->fail_after > 0) dev->fail_after--;
+  dev->launches++;
+  return FC_OK;
+}
+
+int fc_post_launch(FcDevice* dev, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    dev->lost = true;
+    return fc_fail(dev, FC_ERR_DEVICE, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  }
+  return FC_OK;
+}
+
+int fc_pinned(FcDevice* dev, size_t bytes, void** out) {
+  if (bytes > dev->pinned_bytes) {
+    if (dev->pinned) {
+      FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+      cudaFreeHost(dev->pinned);
+      dev->pinned = nullptr;
+      dev->pinned_bytes = 0;
+    }
+    size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+    FC_CUDA(dev, cudaMallocHost(&dev->pinned, want));
+    dev->pinned_bytes = want;
+  }
+  *out = dev->pinned;
+  return FC_OK;
+}
+
+FC_API int fc_device_open(int ordinal, FcDevice** out) {
+  if (!out) return fc_fail(nullptr, FC_ERR_ARG, "fc_device_open: out is NULL");
+  *out = nullptr;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess) return fc_fail(nullptr, FC_ERR_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  if (ordinal < 0 || ordinal >= count)
+    return fc_fail(nullptr, FC_ERR_ARG, "no CUDA device %d (%d present)", ordinal, count);
+  FcDevice* dev = new FcDevice();
+  dev->ordinal = ordinal;
+  if ((e = cudaSetDevice(ordinal)) != cudaSuccess || (e = cudaGetDeviceProperties(&dev->prop, ordinal)) != cudaSuccess ||
+      (e = cudaStreamCreateWithFlags(&dev->stream, cudaStreamNonBlocking)) != cudaSuccess ||
+      (e = cudaMalloc(&dev->d_flag, sizeof(int))) != cudaSuccess) {
+    int rc = fc_fail(nullptr, FC_ERR_DEVICE, "cannot open CUDA device %d: %s", ordinal, cudaGetErrorString(e));
+    delete dev;
+    return rc;
+  }
+  if (dev->prop.major != 10) {
+    int rc = fc_fail(nullptr, FC_ERR_UNSUPPORTED, "device %d (%s, sm_%d%d) is not sm_100: this library is built for B200 only",
+                     ordinal, dev->prop.name, dev->prop.major, dev->prop.minor);
+    cudaStreamDestroy(dev->stream);
+    cudaFree(dev->d_flag);
+    delete dev;
+    return rc;
+  }
+  cudaMemsetAsync(dev->d_flag, 0, sizeof(int), dev->stream);
+  *out = dev;
+  return FC_OK;
+}
+
+FC_API int fc_device_close(FcDevice* dev) {
+  if (!dev) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  cudaStreamSynchronize(dev->stream);
+  if (dev->pinned) cudaFreeHost(dev->pinned);
+  if (dev->d_flag) cudaFree(dev->d_flag);
+  cudaStreamDestroy(dev->stream);
+  delete dev;
+  return FC_OK;
+}
+
+FC_API int fc_device_name(FcDevice* dev, char* buf, size_t buf_len) {
+  if (!dev || !buf || buf_len == 0) return FC_ERR_ARG;
+  snprintf(buf, buf_len, "%s (CUDA device %d, sm_%d%d, %d SMs)", dev->prop.name, dev->ordinal, dev->prop.major,
+           dev->prop.minor, dev->prop.multiProcessorCount);
+  return FC_OK;
+}
+
+FC_API int fc_device_props(FcDevice* dev, int* sm_count, uint64_t* total_mem_bytes) {
+  if (!dev) return FC_ERR_ARG;
+  if (sm_count) *sm_count = dev->prop.multiProcessorCount;
+  if (total_mem_bytes) *total_mem_bytes = dev->prop.totalGlobalMem;
+  return FC_OK;
+}
+
+FC_API const char* fc_last_error(FcDevice* dev) {
+  if (dev) return dev->last_error.c_str();
+  std::lock_guard<std::mutex> lock(g_err_mutex);
+  return g_no_device_error.c_str();
+}
+
+FC_API void* fc_device_stream(FcDevice* dev) { return dev ? (void*)dev->stream : nullptr; }
+
+FC_API int fc_device_sync(FcDevice* dev) {
+  if (!dev) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  return FC_OK;
+}
+
+FC_API uint64_t fc_device_launch_count(FcDevice* dev) { return dev ? dev->launches : 0; }
+
+FC_API int fc_debug_fail_after(FcDevice* dev, int64_t n_launches) {
+  if (!dev) return FC_ERR_ARG;
+  dev->fail_after = n_launches < 0 ? -1 : n_launches;
+  return FC_OK;
+}
+
+// ---- weight upload -------------------------------------------------------------------------------
+
+void qweight_free(FcQWeight* w) {
+  if (!w) return;
+  if (w->qs_alloc) cudaFree(w->qs_alloc);
+  if (w->sc_alloc) cudaFree(w->sc_alloc);
+  delete w;
+}
+
+// Quantise `count` host matrices `[k, ns[i]]` that share the input width and stack their output
+// rows into one device weight of n = sum(ns) rows (q, k and v, or gate and up, become one launch).
+int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, const uint32_t* ns, int count,
+                            uint32_t k, FcQWeight** out) {
+  *out = nullptr;
+  uint64_t n_total = 0;
+  uint32_t n_max = 0;
+  for (int i = 0; i < count; i++) {
+    n_total += ns[i];
+    n_max = ns[i] > n_max ? ns[i] : n_max;
+  }
+  if (k == 0 || n_total == 0 || n_total > 0x7fffffffu) return fc_fail(dev, FC_ERR_SHAPE, "empty or oversized weight");
+  if (kind != FC_F32 && k % QK) kind = FC_F32; // ineligible width stays f32 (ops/quant.rs:L125-L134, lin.rs:L54-L61)
+  if (kind != FC_F32 && kind != FC_Q8_0 && kind != FC_Q4_0) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  const uint32_t n = (uint32_t)n_total;
+  FcQWeight* w = new FcQWeight();
+  w->dev = dev;
+  const size_t qs_bytes = qmat_qs_bytes(kind, k, n), sc_bytes = qmat_sc_bytes(kind, k, n);
+  float* stage = nullptr;
+  cudaError_t e = cudaMalloc(&w->qs_alloc, qs_bytes);
+  if (e == cudaSuccess && sc_bytes) e = cudaMalloc(&w->sc_alloc, sc_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&stage, (size_t)k * n_max * 4);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    qweight_free(w);
+    if (stage) cudaFree(stage);
+    return fc_fail(dev, FC_ERR_OOM, "cannot allocate a %u x %u weight: %s", k, n, cudaGetErrorString(e));
+  }
+  w->m.kind = kind;
+  w->m.k = k;
+  w->m.n = n;
+  w->m.qs = (const uint8_t*)w->qs_alloc;
+  w->m.sc = (const __half*)w->sc_alloc;
+  w->bytes = qs_bytes + sc_bytes;
+  int rc = FC_OK;
+  size_t row0 = 0;
+  for (int i = 0; i < count && rc == FC_OK; i++) {
+    e = cudaMemcpyAsync(stage, mats[i], (size_t)k * ns[i] * 4, cudaMemcpyHostToDevice, dev->stream);
+    if (e != cudaSuccess) {
+      rc = fc_fail(dev, FC_ERR_DEVICE, "weight upload failed: %s", cudaGetErrorString(e));
+      break;
+    }
+    uint8_t* qs = (uint8_t*)w->qs_alloc + qmat_qs_bytes(kind, k, row0);
+    __half* sc = w->sc_alloc ? (__half*)w->sc_alloc + (size_t)(k / QK) * row0 : nullptr;
+    rc = kind == FC_F32 ? k_transpose_kn(dev, stage, k, ns[i], (float*)qs) : k_quantise_kn(dev, kind, stage, k, ns[i], qs, sc);
+    if (rc == FC_OK && cudaStreamSynchronize(dev->stream) != cudaSuccess) {
+      dev->lost = true;
+      rc = fc_fail(dev, FC_ERR_DEVICE, "weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    row0 += ns[i];
+  }
+  cudaFree(stage);
+  if (rc != FC_OK) {
+    qweight_free(w);
+    return rc;
+  }
+  *out = w;
+  return FC_OK;
+}
+
+int qweight_from_f32(FcDevice* dev, int kind, const float* w_host, uint32_t k, uint32_t n, FcQWeight** out) {
+  return qweight_from_f32_concat(dev, kind, &w_host, &n, 1, k, out);
+}

@@ -1,0 +1,67 @@
+"""Device handle: the host-side mirror of `ferrum_wgpu::device::Gpu`
+(ferrum_wgpu/src/device/mod.rs:L98-L176). Errors are values turned into exceptions here:
+`CudaError` carries the status code and the library's message."""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _ffi
+
+
+class CudaError(RuntimeError):
+    """`GpuError(String)` of the reference (device/mod.rs:L18-L27) plus the C status code."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message or _ffi.STATUS_NAMES.get(code, f"error {code}"))
+        self.code = code
+
+
+class Device:
+    def __init__(self, handle):
+        self._h = handle
+        self._lib = _ffi.load()
+
+    @classmethod
+    def open(cls, ordinal: int = 0) -> "Device":
+        lib = _ffi.load()
+        h = C.c_void_p()
+        rc = lib.fc_device_open(ordinal, C.byref(h))
+        if rc != _ffi.FC_OK:
+            raise CudaError(rc, lib.fc_last_error(None).decode())
+        return cls(h)
+
+    def close(self):
+        if self._h:
+            self._lib.fc_device_close(self._h)
+            self._h = None
+
+    @property
+    def handle(self):
+        return self._h
+
+    def check(self, rc: int):
+        if rc != _ffi.FC_OK:
+            raise CudaError(rc, self._lib.fc_last_error(self._h).decode())
+
+    def name(self) -> str:
+        buf = C.create_string_buffer(256)
+        self.check(self._lib.fc_device_name(self._h, buf, 256))
+        return buf.value.decode()
+
+    def props(self):
+        sm, mem = C.c_int(), C.c_uint64()
+        self.check(self._lib.fc_device_props(self._h, C.byref(sm), C.byref(mem)))
+        return sm.value, mem.value
+
+    def sync(self):
+        self.check(self._lib.fc_device_sync(self._h))
+
+    def stream(self) -> int:
+        return self._lib.fc_device_stream(self._h) or 0
+
+    def launch_count(self) -> int:
+        return self._lib.fc_device_launch_count(self._h)
+
+    def fail_after(self, n: int | None):
+        """`Gpu::fail_after` (device/runtime.rs:L214-L256): refuse launches after `n` more; None disarms."""
+        self.check(self._lib.fc_debug_fail_after(self._h, -1 if n is None else n))

@@ -1,0 +1,170 @@
+"""Resident models: the host-side mirror of `GpuLlama` / `GpuGpt2`
+(ferrum_wgpu/src/models/llama/{mod,forward}.rs, models/gpt2.rs): `feed`, `forward_all`, `score`,
+`reset`, `pos`, `config`, `quant`, with multi-stream decode and batched scoring added."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _ffi
+from .device import CudaError, Device
+from .hostmodel import Gpt2, Llama
+from .quant import Mode, QKind
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+class ResidentModel:
+    def __init__(self, dev: Device, handle, cfg, quant: QKind | None, max_streams: int):
+        self.dev, self._h, self._lib = dev, handle, _ffi.load()
+        self.cfg, self._quant, self.max_streams = cfg, quant, max_streams
+
+    # -- reference interface ------------------------------------------------------------------
+    def config(self):
+        return self.cfg
+
+    def quant(self):
+        """The quantisation requested at upload (ineligible matrices stay f32)."""
+        return self._quant
+
+    def pos(self, stream: int = 0) -> int:
+        p = C.c_uint32()
+        self.dev.check(self._lib.fc_model_pos(self._h, stream, C.byref(p)))
+        return p.value
+
+    def reset(self, stream: int = 0):
+        self.dev.check(self._lib.fc_model_reset(self._h, stream))
+
+    def feed(self, token: int, stream: int = 0) -> np.ndarray:
+        """Consume one token at the next position and return its next-token logits row."""
+        out = np.empty(self.cfg.vocab, dtype=np.float32)
+        self.dev.check(self._lib.fc_model_feed(self._h, stream, int(token), out.ctypes.data, None))
+        return out
+
+    def feed_greedy(self, token: int, stream: int = 0) -> int:
+        """`feed` with the argmax taken on the device (first maximum); no logits leave the GPU."""
+        a = C.c_int32()
+        self.dev.check(self._lib.fc_model_feed(self._h, stream, int(token), None, C.byref(a)))
+        return a.value
+
+    def feed_batch(self, tokens, streams=None, want_logits: bool = False):
+        """One decode step for several streams; returns (argmax[n], logits[n, vocab] | None)."""
+        tokens = _i32(tokens)
+        n = tokens.size
+        streams = np.arange(n, dtype=np.uint32) if streams is None else np.ascontiguousarray(streams, dtype=np.uint32)
+        am = np.empty(n, dtype=np.int32)
+        lg = np.empty((n, self.cfg.vocab), dtype=np.float32) if want_logits else None
+        self.dev.check(self._lib.fc_model_feed_batch(self._h, n, streams.ctypes.data, tokens.ctypes.data,
+                                                     lg.ctypes.data if want_logits else None, am.ctypes.data))
+        return am, lg
+
+    def prefill(self, ids, stream: int = 0, mode: Mode = Mode.EXACT_F32) -> np.ndarray:
+        """Feed a whole prompt in one batched pass; returns the last position's logits."""
+        ids = _i32(ids)
+        out = np.empty(self.cfg.vocab, dtype=np.float32)
+        self.dev.check(self._lib.fc_model_prefill(self._h, stream, ids.ctypes.data, ids.size, out.ctypes.data,
+                                                  None, int(mode)))
+        return out
+
+    def forward_all(self, ids, mode: Mode = Mode.EXACT_F32) -> np.ndarray:
+        """Stateless full causal forward; every position's logits `[len, vocab]`."""
+        ids = _i32(ids)
+        out = np.empty((ids.size, self.cfg.vocab), dtype=np.float32)
+        self.dev.check(self._lib.fc_model_forward_all(self._h, ids.ctypes.data, ids.size, out.ctypes.data, int(mode)))
+        return out
+
+    def score(self, ids, mode: Mode = Mode.EXACT_F32):
+        """For each i < len-1: (log-probability of ids[i+1] given ids[..=i], it is the first argmax)."""
+        ids = _i32(ids).reshape(1, -1)
+        lp, gr, _ = self.score_batch(ids, mode)
+        return lp[0], gr[0]
+
+    def score_batch(self, ids, mode: Mode = Mode.EXACT_F32):
+        """Scores `[n_seqs, seq_len]` ids: (logprob[n, L-1], greedy[n, L-1], nll_sum[n] in f64)."""
+        ids = _i32(ids)
+        if ids.ndim != 2:
+            raise CudaError(_ffi.FC_ERR_SHAPE, "score_batch takes [n_seqs, seq_len] ids")
+        n, L = ids.shape
+        if L < 2:
+            raise CudaError(_ffi.FC_ERR_SHAPE, "scoring needs at least 2 tokens")
+        lp = np.empty((n, L - 1), dtype=np.float32)
+        gr = np.empty((n, L - 1), dtype=np.uint8)
+        nll = np.empty(n, dtype=np.float64)
+        self.dev.check(self._lib.fc_model_score(self._h, ids.ctypes.data, n, L, int(mode), lp.ctypes.data,
+                                                gr.ctypes.data, nll.ctypes.data))
+        return lp, gr.astype(bool), nll
+
+    # -- device-pointer variants (benchmark, multi-GPU) -----------------------------------------
+    def score_dev(self, ids_ptr: int, n_seqs: int, seq_len: int, mode: Mode, logprob_ptr: int, greedy_ptr: int,
+                  nll_ptr: int):
+        self.dev.check(self._lib.fc_model_score_dev(self._h, ids_ptr, n_seqs, seq_len, int(mode), logprob_ptr or None,
+                                                    greedy_ptr or None, nll_ptr or None))
+
+    def set_head_shard(self, shard: int, n_shards: int):
+        self.dev.check(self._lib.fc_model_set_head_shard(self._h, shard, n_shards))
+
+    def trunk_dev(self, ids_ptr: int, n_seqs: int, seq_len: int, mode: Mode, hidden_ptr: int):
+        self.dev.check(self._lib.fc_model_trunk_dev(self._h, ids_ptr, n_seqs, seq_len, int(mode), hidden_ptr))
+
+    def head_partial_dev(self, hidden_ptr: int, targets_ptr: int, rows: int, mode: Mode, partial_ptr: int):
+        self.dev.check(self._lib.fc_model_head_partial_dev(self._h, hidden_ptr, targets_ptr, rows, int(mode),
+                                                           partial_ptr))
+
+    def weight_bytes(self) -> int:
+        b = C.c_uint64()
+        self.dev.check(self._lib.fc_model_info(self._h, None, None, None, None, C.byref(b)))
+        return b.value
+
+    def close(self):
+        if self._h:
+            self._lib.fc_model_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _kind(quant) -> int:
+    return int(QKind.F32 if quant is None else quant)
+
+
+class CudaLlama(ResidentModel):
+    """`GpuLlama::new(gpu, model, quant, budget)` (models/llama/mod.rs:L219-L314)."""
+
+    def __init__(self, dev: Device, model: Llama, quant: QKind | None = None, budget: int | None = None,
+                 max_streams: int = 1):
+        cfg, w = model.c_structs()
+        h = C.c_void_p()
+        dev.check(_ffi.load().fc_llama_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
+                                              budget or 0, C.byref(h)))
+        super().__init__(dev, h, model.cfg, quant, max_streams)
+
+
+class CudaGpt2(ResidentModel):
+    """`GpuGpt2::new` (models/gpt2.rs:L134-L190), with quantised weights added."""
+
+    def __init__(self, dev: Device, model: Gpt2, quant: QKind | None = None, budget: int | None = None,
+                 max_streams: int = 1):
+        cfg, w = model.c_structs()
+        h = C.c_void_p()
+        dev.check(_ffi.load().fc_gpt2_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
+                                             budget or 0, C.byref(h)))
+        super().__init__(dev, h, model.cfg, quant, max_streams)
+
+
+def plan_bytes(cfg, quant: QKind | None = None, max_streams: int = 1) -> int:
+    """`models::llama::plan` total (models/llama/mod.rs:L108-L182): device bytes a model needs."""
+    lib = _ffi.load()
+    if hasattr(cfg, "kv_heads"):
+        c = _ffi.FcLlamaConfig(cfg.vocab, cfg.ctx, cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.layers,
+                               cfg.hidden, cfg.rope_dim, cfg.rope_type, cfg.rope_base, cfg.eps,
+                               cfg.rope_linear_factor, 0, None, 0)
+        return lib.fc_llama_plan_bytes(C.byref(c), _kind(quant), max_streams)
+    c = _ffi.FcGpt2Config(cfg.vocab, cfg.ctx, cfg.dim, cfg.heads, cfg.layers, cfg.hidden)
+    return lib.fc_gpt2_plan_bytes(C.byref(c), _kind(quant), max_streams)

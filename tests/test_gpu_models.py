@@ -1,0 +1,265 @@
+"""Resident models against the CPU oracle through the C ABI. Mirrors
+ferrum_wgpu/src/models/llama/tests.rs and models/gpt2.rs tests: every variant, cached feed vs full
+forward, quantised feed vs the dequantised oracle, forward_all, score, greedy tokens, reset, plan /
+budget refusal, host-side fault sweep."""
+import numpy as np
+import pytest
+
+from ferrum_gpu_b200 import (CudaBackend, CudaError, CudaGpt2, CudaLlama, GenOpts, Mode, QKind, generate_with,
+                             plan_bytes)
+from ferrum_gpu_b200 import _ffi
+from ferrum_gpu_b200.hostmodel import Gpt2Config, config_c1, random_gpt2, random_llama, random_tokens
+from oracle import oracle as orc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+FORWARD = 1e-5  # ferrum_wgpu/src/tolerance.rs:L11
+IDS = [3, 16, 0, 9, 9, 4, 11, 2, 7, 5, 1, 8, 6, 10, 12, 15]
+
+
+def variants():
+    return helpers.gpu_llama_variants()
+
+
+@pytest.mark.parametrize("name,cfg,biases,tied", variants())
+def test_feed_matches_forward_logits_at_every_position(dev, name, cfg, biases, tied):
+    """models/llama/tests.rs:L46-L61 (f32 weights, whole context)."""
+    m = helpers.ref_random_llama(cfg, 7, biases, tied)
+    want = orc.OracleLlama(m).forward_logits(IDS[:cfg.ctx])
+    g = CudaLlama(dev, m)
+    for i, t in enumerate(IDS[:cfg.ctx]):
+        got = g.feed(t)
+        assert orc.max_rel_err(got, want[i]) < FORWARD, (name, i)
+    assert g.pos() == cfg.ctx
+    with pytest.raises(CudaError, match=f"context of {cfg.ctx} tokens is full") as e:
+        g.feed(1)
+    assert e.value.code == _ffi.FC_ERR_CONTEXT_FULL and g.pos() == cfg.ctx
+    g.close()
+
+
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
+@pytest.mark.parametrize("name,cfg,biases,tied", variants())
+def test_quantised_feed_matches_the_dequantised_oracle(dev, kind, name, cfg, biases, tied):
+    """models/llama/tests.rs:L63-L89: the oracle is the CPU model over dequantised weights."""
+    m = helpers.ref_random_llama(cfg, 8, biases, tied)
+    want_model = orc.dequantised_llama(m, int(kind), snap_embedding=False)
+    if tied:  # `dequantised` snaps the head on its own; the embedding table stays as it is
+        want_model.head = orc.snap_matrix(int(kind), m.head, cfg.dim, cfg.vocab)
+    oracle = orc.OracleLlama(want_model)
+    g = CudaLlama(dev, m, kind)
+    assert g.quant() == kind
+    for i, t in enumerate(IDS[:cfg.ctx]):
+        assert orc.max_rel_err(g.feed(t), oracle.feed(t)) < FORWARD, (name, kind, i)
+    g.close()
+
+
+@pytest.mark.parametrize("name,cfg,biases,tied", variants())
+def test_forward_all_and_prefill_match(dev, name, cfg, biases, tied):
+    """models/llama/tests.rs:L114-L130 (t in {1, 2, 7, 10}) plus batched prefill = token-by-token feed."""
+    m = helpers.ref_random_llama(cfg, 9, biases, tied)
+    oracle = orc.OracleLlama(m)
+    g = CudaLlama(dev, m, None, max_streams=2)
+    for t in (1, 2, 7, 10):
+        ids = IDS[:t]
+        assert orc.max_rel_err(g.forward_all(ids), oracle.forward_logits(ids)) < FORWARD, (name, t)
+    assert g.pos() == 0, "forward_all does not touch the cache"
+    last = g.prefill(IDS[:6], stream=1)
+    assert g.pos(1) == 6 and g.pos(0) == 0
+    want = oracle.forward_logits(IDS[:8])
+    assert orc.max_rel_err(last, want[5]) < FORWARD
+    assert orc.max_rel_err(g.feed(IDS[6], stream=1), want[6]) < FORWARD
+    assert orc.max_rel_err(g.feed(IDS[7], stream=1), want[7]) < FORWARD
+    with pytest.raises(CudaError, match="must be in 1..="):
+        g.forward_all(list(range(cfg.ctx + 1)))
+    g.close()
+
+
+@pytest.mark.parametrize("kind", [None, QKind.Q8_0, QKind.Q4_0])
+def test_score_matches_the_cpu_score(dev, kind):
+    """models/llama/tests.rs:L176-L194: log-probabilities within 1e-4, same greedy flags."""
+    name, cfg, biases, tied = variants()[1]
+    m = helpers.ref_random_llama(cfg, 10, biases, tied)
+    ref = m if kind is None else orc.dequantised_llama(m, int(kind), snap_embedding=False)
+    if kind is not None and tied:
+        ref.head = orc.snap_matrix(int(kind), m.head, cfg.dim, cfg.vocab)
+    g = CudaLlama(dev, m, kind)
+    ids = np.array([IDS[:12], IDS[4:16], IDS[2:14]], dtype=np.int32)
+    lp, gr, nll = g.score_batch(ids)
+    for s in range(ids.shape[0]):
+        wlp, wgr = orc.OracleLlama(ref).score(ids[s])
+        assert np.abs(lp[s] - wlp).max() < 1e-4
+        assert np.array_equal(gr[s], wgr)
+        assert abs(nll[s] + wlp.astype(np.float64).sum()) < 1e-3
+    one_lp, one_gr = g.score(ids[0])
+    assert np.array_equal(one_lp, lp[0]) and np.array_equal(one_gr, gr[0])
+    with pytest.raises(CudaError, match="at least 2 tokens"):
+        g.score([1])
+    g.close()
+
+
+@pytest.mark.parametrize("kind", [None, QKind.Q8_0])
+def test_greedy_decode_token_for_token(dev, kind):
+    """models/llama/tests.rs:L196-L213 and engine/tests.rs:L260-L297."""
+    name, cfg, biases, tied = variants()[0]
+    m = helpers.ref_random_llama(cfg, 11, biases, tied)
+    ref = m if kind is None else orc.dequantised_llama(m, int(kind), snap_embedding=False)
+    oracle = orc.OracleLlama(ref)
+    want = generate_with(oracle.feed, [3, 1, 4], GenOpts(max_new=10))
+    be = CudaBackend(dev, kind)
+    assert be.kind() == "cuda" and "B200" in be.name()
+    assert be.generate(m, [3, 1, 4], GenOpts(max_new=10)) == want
+    assert generate_with(be.llama_decoder(m), [3, 1, 4], GenOpts(max_new=10)) == want
+    with pytest.raises(RuntimeError, match="not available"):
+        be.train()
+
+
+def test_reset_rewinds_and_stale_cache_entries_do_not_leak(dev):
+    """models/llama/tests.rs:L215-L229: reset only rewinds pos; attention reads 0..len only."""
+    name, cfg, biases, tied = variants()[0]
+    m = helpers.ref_random_llama(cfg, 12, biases, tied)
+    g = CudaLlama(dev, m)
+    first = [g.feed(t) for t in IDS[:5]]
+    for t in IDS[5:12]:
+        g.feed(t)
+    g.reset()
+    assert g.pos() == 0
+    again = [g.feed(t) for t in IDS[:5]]
+    for a, b in zip(first, again):
+        assert np.array_equal(a, b)
+    g.close()
+
+
+def test_batched_streams_equal_single_stream_decoding(dev):
+    """Several streams per step (new work): every stream sees exactly what it would alone."""
+    name, cfg, biases, tied = variants()[1]
+    m = helpers.ref_random_llama(cfg, 13, biases, tied)
+    g = CudaLlama(dev, m, QKind.Q8_0, max_streams=5)
+    solo = CudaLlama(dev, m, QKind.Q8_0)
+    seqs = [IDS[i:i + 6] for i in range(5)]
+    want = []
+    for s in seqs:
+        solo.reset()
+        want.append([solo.feed(t) for t in s])
+    # streams advance at different rates: stream j joins at step j
+    for step in range(6 + 4):
+        live = [j for j in range(5) if 0 <= step - j < 6]
+        toks = [seqs[j][step - j] for j in live]
+        am, lg = g.feed_batch(toks, live, want_logits=True)
+        for r, j in enumerate(live):
+            assert orc.max_rel_err(lg[r], want[j][step - j]) < FORWARD
+            assert am[r] == orc.argmax(want[j][step - j]) or lg[r][am[r]] == lg[r].max()
+    with pytest.raises(CudaError, match="twice"):
+        g.feed_batch([1, 2], [0, 0])
+    g.close()
+    solo.close()
+
+
+def test_errors_leave_the_position_unchanged(dev):
+    name, cfg, biases, tied = variants()[0]
+    g = CudaLlama(dev, helpers.ref_random_llama(cfg, 14, biases, tied))
+    g.feed(1)
+    with pytest.raises(CudaError, match=f"index {cfg.vocab} is out of range for {cfg.vocab} entries") as e:
+        g.feed(cfg.vocab)
+    assert e.value.code == _ffi.FC_ERR_RANGE and g.pos() == 1
+    with pytest.raises(CudaError):
+        g.feed(-1)
+    assert g.pos() == 1
+    g.close()
+
+
+def test_plan_over_budget_refuses_before_allocating(dev):
+    """models/llama/tests.rs (budget refusal, mod.rs:L241-L243)."""
+    name, cfg, biases, tied = variants()[0]
+    m = helpers.ref_random_llama(cfg, 15, biases, tied)
+    need = plan_bytes(cfg, QKind.Q8_0)
+    assert need > 0
+    with pytest.raises(CudaError, match="over the budget") as e:
+        CudaLlama(dev, m, QKind.Q8_0, budget=need - 1)
+    assert e.value.code == _ffi.FC_ERR_OOM
+    CudaLlama(dev, m, QKind.Q8_0, budget=need).close()
+
+
+def test_fault_sweep_fails_cleanly_at_every_launch(dev):
+    """models/llama/tests.rs:L315-L352: refuse the k-th launch on the host for every k; the position
+    must not advance, and the next call must succeed with the same result."""
+    name, cfg, biases, tied = variants()[1]
+    m = helpers.ref_random_llama(cfg, 16, biases, tied)
+    g = CudaLlama(dev, m, QKind.Q4_0)
+    before = dev.launch_count()
+    want = g.feed(3)
+    per_token = dev.launch_count() - before
+    assert per_token == 1 + 9 * cfg.layers + 2, per_token  # embed, 9 per layer, final norm, head
+    g.reset()
+    for k in range(per_token):
+        dev.fail_after(k)
+        with pytest.raises(CudaError) as e:
+            g.feed(3)
+        assert e.value.code == _ffi.FC_ERR_INJECTED and "injected" in str(e.value)
+        assert g.pos() == 0
+        dev.fail_after(None)
+    assert np.array_equal(g.feed(3), want)
+    g.close()
+
+
+# ---- GPT-2 -------------------------------------------------------------------------------------
+
+def gpt2_cfg():
+    return Gpt2Config(vocab=37, ctx=12, dim=32, heads=4, layers=2, hidden=64)
+
+
+@pytest.mark.parametrize("kind", [None, QKind.Q8_0, QKind.Q4_0])
+def test_gpt2_feed_forward_all_and_score(dev, kind):
+    """models/gpt2.rs:L349-L538; quantised weights are new, their oracle is the CPU model over the
+    dequantised weights."""
+    cfg = gpt2_cfg()
+    m = helpers.ref_random_gpt2(cfg, 3)
+    ref = m if kind is None else orc.dequantised_gpt2(m, int(kind), snap_embedding=False)
+    oracle = orc.OracleGpt2(ref)
+    g = CudaGpt2(dev, m, kind)
+    ids = [i % cfg.vocab for i in IDS[:cfg.ctx]]
+    full = oracle.forward_logits(ids)
+    for i, t in enumerate(ids):
+        assert orc.max_rel_err(g.feed(t), oracle.feed(t)) < FORWARD, i
+    with pytest.raises(CudaError, match="context of 12 tokens is full"):
+        g.feed(1)
+    for t in (1, 2, 7, 10):
+        assert orc.max_rel_err(g.forward_all(ids[:t]), full[:t]) < FORWARD
+    lp, gr = g.score(ids)
+    wlp, wgr = oracle.score(ids)
+    assert np.abs(lp - wlp).max() < 1e-4 and np.array_equal(gr, wgr)
+    g.reset()
+    assert orc.max_rel_err(g.prefill(ids[:5]), full[4]) < FORWARD
+    g.close()
+
+
+def test_config1_greedy_decode_reproduces_the_oracle_tokens(dev):
+    """The GPT-2-style benchmark configuration (6 layers, d_model 384, Q8_0): a 16-token prompt then
+    128 greedy tokens must equal the CPU oracle's, and every logits row must stay within 1e-5."""
+    cfg = config_c1()
+    m = random_gpt2(cfg, seed=1)
+    ref = orc.dequantised_gpt2(m, int(QKind.Q8_0), snap_embedding=True)
+    m.tok = ref.tok  # the file convention: the embedding table is itself a round-tripped Q8_0 tensor
+    oracle = orc.OracleGpt2(ref)
+    prompt = random_tokens(2, 16, cfg.vocab).tolist()
+    g = CudaGpt2(dev, m, QKind.Q8_0)
+    worst = 0.0
+    tok_g = tok_o = None
+    for t in prompt:
+        lg, lo = g.feed(t), oracle.feed(t)
+        worst = max(worst, orc.max_rel_err(lg, lo))
+    out_g, out_o = [], []
+    tok_g, tok_o = orc.argmax(lg), orc.argmax(lo)
+    for _ in range(128):
+        out_g.append(tok_g)
+        out_o.append(tok_o)
+        if len(out_g) == 128:
+            break
+        lg, lo = g.feed(tok_g), oracle.feed(tok_o)
+        worst = max(worst, orc.max_rel_err(lg, lo))
+        tok_g, tok_o = orc.argmax(lg), orc.argmax(lo)
+    assert worst < FORWARD, worst
+    assert out_g == out_o
+    # the device-side greedy path produces the same continuation
+    assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128))[16:] == out_o
+    g.close()

@@ -1,0 +1,102 @@
+"""Parity of the device codec and the quantised products against the CPU oracle, through the C ABI.
+Mirrors ferrum_wgpu/src/ops/quant/tests.rs."""
+import numpy as np
+import pytest
+
+from ferrum_gpu_b200 import CudaError, Mode, QKind, linear_q, upload_quantised, upload_qweight
+from ferrum_gpu_b200 import _ffi
+from oracle import oracle as orc
+from tests import helpers
+
+pytestmark = pytest.mark.gpu
+
+KINDS = [QKind.Q8_0, QKind.Q4_0]
+REDUCING = 1e-5  # ferrum_wgpu/src/tolerance.rs:L7
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("k,n", [(32, 1), (32, 5), (64, 3), (96, 65), (128, 64), (768, 130)])
+def test_device_encoder_is_bit_identical_to_the_cpu_encoder(dev, kind, k, n):
+    for w in (helpers.nasty(k * n), orc.rand_vec(k * n, 4) * np.float32(0.02)):
+        qw = upload_quantised(dev, kind, w, k, n)
+        assert np.array_equal(qw.blocks(), orc.quantise_matrix(int(kind), w, k, n)), (kind, k, n)
+        assert (qw.kind(), qw.k(), qw.n()) == (kind, k, n)
+        assert qw.device_bytes() == k * n * (34 if kind == QKind.Q8_0 else 18) // 32
+        qw.close()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("k,n", [(32, 1), (32, 5), (64, 3), (96, 65), (128, 64)])
+def test_dequantised_values_are_bit_identical_to_the_cpu_decode(dev, kind, k, n):
+    """ops/quant/tests.rs:L106-L131, both by the decode kernel and by the identity-matrix read-back."""
+    raw = orc.quantise_matrix(int(kind), helpers.nasty(k * n), k, n)
+    rows = orc.decode(int(kind), raw, k * n).reshape(n, k)
+    qw = upload_qweight(dev, kind, raw, k, n)
+    assert np.array_equal(qw.blocks(), raw)
+    assert np.array_equal(qw.dequantised().view(np.uint32), rows.view(np.uint32))
+    eye = np.eye(k, dtype=np.float32)
+    got = linear_q(dev, eye, qw, k)  # y[r, col] = W[col, r]
+    assert np.array_equal(got, rows.T), (kind, k, n)
+    qw.close()
+
+
+@pytest.mark.parametrize("kind", KINDS + [QKind.F32])
+@pytest.mark.parametrize("rows,k,n", [(1, 32, 1), (1, 256, 100), (7, 96, 13), (33, 64, 65), (2, 512, 3),
+                                      (8, 2048, 37), (5, 2816, 70), (64, 1024, 200), (130, 768, 257)])
+def test_linear_matches_the_cpu_matmul_on_the_dequantised_weights(dev, kind, rows, k, n):
+    """ops/quant/tests.rs:L133-L157 and L271-L304 (every kernel x precision x awkward shapes)."""
+    w = orc.rand_vec(k * n, 4)
+    want_w = orc.snap_matrix(int(kind), w, k, n)
+    x = orc.rand_vec(rows * k, 5)
+    want = orc.matmul(x, want_w, rows, k, n)
+    qw = upload_quantised(dev, kind, w, k, n)
+    got = linear_q(dev, x, qw, rows)
+    e = orc.max_rel_err(got, want)
+    assert e < REDUCING, (kind, rows, k, n, e)
+    again = linear_q(dev, x, qw, rows)
+    assert np.array_equal(got, again), "a repeated run is bit-identical"
+    qw.close()
+
+
+def test_f32_weight_with_a_width_that_is_not_whole_blocks(dev):
+    """An ineligible width stays f32 (ferrum_wgpu/src/models/llama/lin.rs:L54-L61)."""
+    for rows, k, n in [(1, 24, 9), (3, 24, 40), (20, 50, 7)]:
+        w, x = orc.rand_vec(k * n, 6), orc.rand_vec(rows * k, 7)
+        qw = upload_quantised(dev, QKind.F32, w, k, n)
+        assert orc.max_rel_err(linear_q(dev, x, qw, rows), orc.matmul(x, w, rows, k, n)) < REDUCING
+        qw.close()
+
+
+def test_pack_and_quantise_refuse_bad_shapes(dev):
+    """ops/quant/tests.rs:L73-L87, L200-L215"""
+    for kind in KINDS:
+        with pytest.raises(CudaError) as e:
+            upload_qweight(dev, kind, np.zeros(100, dtype=np.uint8), 33, 1)
+        assert "whole" in str(e.value) and e.value.code == _ffi.FC_ERR_SHAPE
+        with pytest.raises(CudaError) as e:
+            upload_qweight(dev, kind, np.zeros(3, dtype=np.uint8), 32, 1)
+        assert "needs" in str(e.value)
+        with pytest.raises(CudaError):
+            upload_quantised(dev, kind, np.zeros(33, dtype=np.float32), 33, 1)
+        with pytest.raises(CudaError):
+            upload_quantised(dev, kind, np.zeros(63, dtype=np.float32), 32, 2)
+    qw = upload_quantised(dev, QKind.Q8_0, orc.rand_vec(64 * 4, 1), 64, 4)
+    with pytest.raises(CudaError):
+        linear_q(dev, np.zeros(65, dtype=np.float32), qw, 1)
+    qw.close()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_sweep_shapes_of_the_isolated_matmul_config(dev, kind):
+    """The decode-side rows of the isolated sweep (M in {1, 8, 64}) on its K, N corners, against
+    the oracle at 1e-5 with N(0,1) activations and N(0,0.02) weights."""
+    rng = np.random.default_rng(11)
+    for k, n in [(768, 768), (2048, 2816), (4096, 768)]:
+        w = (rng.standard_normal(k * n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+        want_w = orc.snap_matrix(int(kind), w, k, n)
+        qw = upload_quantised(dev, kind, w, k, n)
+        for m in (1, 8, 64):
+            x = rng.standard_normal(m * k, dtype=np.float32)
+            e = orc.max_rel_err(linear_q(dev, x, qw, m), orc.matmul(x, want_w, m, k, n, threads=8))
+            assert e < REDUCING, (kind, m, k, n, e)
+        qw.close()
