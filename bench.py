@@ -1,0 +1,299 @@
+"""Benchmark of the quantised scoring hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (N = 1): the Llama-style scoring configuration - 12 layers, d_model 768, 12 query / 4 KV
+heads, SwiGLU 2048, vocab 32000, Q4_0 weights drawn from N(0, 0.02) - scoring 256 sequences of 1024
+uniform-random token ids for their total log-probability (bf16 tensor-core path). One step = one pass
+over the 256 sequences of a rank. With N > 1 every rank holds a replica and scores its own 256
+sequences (no data-path collective); the per-sequence NLL sums are all-gathered at the end of each step.
+Everything is synthetic: there is no dataset and no checkpoint.
+
+Prints ONE JSON line (rank 0).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_SEQS, SEQ_LEN = 256, 1024
+METRIC, UNIT = "scoring tok/s", "scored tokens/s"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def c3_flops_per_token(cfg) -> float:
+    """2 * matrix parameters + causal attention (4 * heads * head_dim * (t + 1) / 2 per layer)."""
+    mats = cfg.layers * (cfg.dim * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * cfg.dim + 3 * cfg.dim * cfg.hidden)
+    mats += cfg.dim * cfg.vocab
+    return 2.0 * mats, 4.0 * cfg.heads * cfg.head_dim * (SEQ_LEN / 2.0) * cfg.layers
+
+
+def run_reference(args, rank: int):
+    """The reference's own CPU path for this workload, restated (no Rust toolchain exists here): the
+    f32 oracle over the dequantised weights, all host threads, on a bounded sample per step."""
+    if rank != 0:
+        return
+    from ferrum_gpu_b200 import _ffi
+    from ferrum_gpu_b200.hostmodel import config_c3, random_llama, random_tokens
+    from oracle import oracle as orc
+    cores = os.cpu_count() or 1
+    cfg = config_c3()
+    model = random_llama(cfg, seed=1)
+    ref = orc.dequantised_llama(model, _ffi.FC_Q4_0, snap_embedding=False)
+    oracle = orc.OracleLlama(ref, threads=cores)
+    sample_len = 129
+    ids = random_tokens(100, sample_len, cfg.vocab)
+    for _ in range(min(args.warmup, 1)):
+        oracle.score(ids)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.score(ids)
+    dt = (time.perf_counter() - t0) / args.steps
+    value = (sample_len - 1) / dt
+    sample = f"1 sequence x {sample_len} tokens per step (of 256 x 1024), f32 oracle, {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c3-llama-12L-d768-q4_0-scoring-256x1024", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--seqs", type=int, default=N_SEQS, help="sequences per rank (256 = the benchmark workload)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from ferrum_gpu_b200 import CudaGpt2, CudaLlama, Device, Mode, QKind
+    from ferrum_gpu_b200.hostmodel import config_c1, config_c3, random_gpt2, random_llama, random_tokens
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = Device.open(local)
+    stream = torch.cuda.ExternalStream(dev.stream(), device=local)
+    hbm, tf_burst, tf_sust, peak_src = peaks()
+
+    cfg = config_c3()
+    model = random_llama(cfg, seed=1)          # every rank holds the same replica
+    g = CudaLlama(dev, model, QKind.Q4_0)
+    n_seqs = args.seqs
+    ids_host = np.stack([random_tokens(1000 + rank * 100000 + i, SEQ_LEN, cfg.vocab) for i in range(n_seqs)])
+    rows = n_seqs * (SEQ_LEN - 1)
+
+    with torch.cuda.stream(stream):
+        ids_dev = torch.from_numpy(ids_host).to(f"cuda:{local}", non_blocking=False)
+        nll_dev = torch.zeros(n_seqs, dtype=torch.float64, device=f"cuda:{local}")
+        gathered = torch.zeros(world * n_seqs, dtype=torch.float64, device=f"cuda:{local}") if world > 1 else None
+
+        def step():
+            g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_BF16, 0, 0, nll_dev.data_ptr())
+            if world > 1:
+                dist.all_gather_into_tensor(gathered, nll_dev)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        l0 = dev.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        launches = dev.launch_count() - l0
+        clocks = sampler.stop() if rank == 0 else None
+        tms = torch.tensor([ms], dtype=torch.float64, device=f"cuda:{local}")
+        if world > 1:
+            dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+        ms_step = float(tms.item()) / args.steps
+        nll_total = float(nll_dev.sum().item())
+
+    # end to end through the public API with host buffers: ids go up, log-probs / flags / sums come back
+    g.score_batch(ids_host[:2], Mode.TENSOR_BF16)
+    t0 = time.perf_counter()
+    e2e_steps = max(1, min(args.steps, 3))
+    for _ in range(e2e_steps):
+        lp, gr, nll = g.score_batch(ids_host, Mode.TENSOR_BF16)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    te = torch.tensor([e2e_s], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
+
+    out = None
+    if rank == 0:
+        # per-kernel device time of one step (event pairs around every launch), for the roofline
+        dev.profile(True)
+        g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_BF16, 0, 0, nll_dev.data_ptr())
+        prof = dev.profile_report()
+        dev.profile(False)
+        total_ms = sum(v["ms"] for v in prof.values()) or 1.0
+        gemm = prof.get("qgemm_tc", {"launches": 0, "ms": 0.0})
+        lin_flops, attn_flops = c3_flops_per_token(cfg)
+        gemm_flops_step = lin_flops * rows          # algorithmic: 2 * M * N * K summed over the products
+        achieved = gemm_flops_step / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+        shares = {k: round(v["ms"] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
+        out = {
+            "metric": METRIC, "value": world * rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "c3-llama-12L-d768-q4_0-scoring-256x1024", "seqs_per_gpu": n_seqs, "seq_len": SEQ_LEN,
+                       "weights": "Q4_0", "arithmetic": "bf16 tcgen05, f32 accumulate",
+                       "l2": "inputs larger than L2 (activations of one chunk exceed 126 MB)", "parallelism": f"replica x{world}"},
+            "e2e": {"value": world * rows / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(ids_host.nbytes),
+                    "d2h_bytes_per_step": int(lp.nbytes + rows + nll.nbytes)},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "qgemm_tc_kernel", "achieved": achieved, "peak": tf_sust,
+                         "unit": "TFLOP/s", "frac": achieved / tf_sust, "peak_source": f"{peak_src} (sustained bf16)",
+                         "frac_of_burst": achieved / tf_burst, "traffic": None,
+                         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"], "kernel_shares": shares},
+            "model_flops_per_step": (lin_flops + attn_flops) * rows,
+            "mfu_of_sustained": (lin_flops + attn_flops) * rows / (ms_step * 1e-3) / 1e12 / tf_sust,
+            "nll_checksum": nll_total,
+        }
+        if not args.no_decode and world == 1:
+            out["decode"] = bench_decode(dev, hbm)
+        if not args.no_cpu_baseline and world == 1:
+            out["cpu_baseline"] = cpu_baseline(cfg, model)
+    g.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    dev.close()
+    if rank == 0:
+        print(json.dumps(out))
+
+
+def bench_decode(dev, hbm_gbs):
+    """KV-cached greedy decode, batch 1: the GPT-2-style configuration (6 layers, d_model 384, Q8_0),
+    a 16-token prompt then 128 decoded tokens, timed as the reference does (the decoded tokens as a whole)."""
+    from ferrum_gpu_b200 import CudaGpt2, QKind
+    from ferrum_gpu_b200.hostmodel import config_c1, random_gpt2, random_tokens
+    cfg = config_c1()
+    m = CudaGpt2(dev, random_gpt2(cfg, seed=1), QKind.Q8_0)
+    prompt = random_tokens(2, 16, cfg.vocab)
+    best = None
+    for _ in range(3):
+        m.reset()
+        tok = 0
+        for t in prompt:
+            tok = m.feed_greedy(int(t))
+        t0 = time.perf_counter()
+        for _ in range(127):
+            tok = m.feed_greedy(tok)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    wbytes = m.weight_bytes()
+    m.close()
+    tok_s = 127 / best
+    bytes_per_tok = wbytes + 2 * cfg.dim * 4 * 80 * cfg.layers  # weights + K/V read at mid-run length
+    return {"workload": "c1-gpt2-6L-d384-q8_0-b1-16+128", "tok_s": tok_s, "ms_per_token": best / 127 * 1e3,
+            "hbm_frac": bytes_per_tok * tok_s / 1e9 / hbm_gbs,
+            "note": "weights (11 MB) live in L2; the limiter is launch/dependency latency, not HBM"}
+
+
+def cpu_baseline(cfg, model):
+    """The f32 oracle (a port of the reference's CPU path) on one host thread, bounded sample."""
+    from ferrum_gpu_b200 import _ffi
+    from ferrum_gpu_b200.hostmodel import random_tokens
+    from oracle import oracle as orc
+    ref = orc.dequantised_llama(model, _ffi.FC_Q4_0, snap_embedding=False)
+    oracle = orc.OracleLlama(ref, threads=1)
+    n = 49
+    ids = random_tokens(100, n, cfg.vocab)
+    t0 = time.perf_counter()
+    oracle.score(ids)
+    dt = time.perf_counter() - t0
+    return {"value": (n - 1) / dt, "unit": UNIT, "cores": 1, "kind": "port",
+            "sample": f"1 sequence x {n} tokens (of 256 x 1024), single thread as `--device cpu` runs scoring"}
+
+
+if __name__ == "__main__":
+    main()

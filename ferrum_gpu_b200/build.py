@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose and out:
                     print(out)
     if force or jobs or _stale(OUT, objs):
-        run([NVCC] + ARCH + ["-shared", "-o", OUT] + objs + ["-lcudart", "-lcuda"])
+        run([NVCC] + ARCH + ["-shared", "-o", OUT] + objs + ["-lcudart"])
     return OUT
 
 

@@ -29,6 +29,14 @@ struct FcDevice {
   void* pinned = nullptr;  // pinned host staging for results and small inputs
   size_t pinned_bytes = 0;
   int* d_flag = nullptr;   // device int for kernels that report a status
+  // per-kernel timing (off by default): one event pair per launch, summed by name on report
+  bool profiling = false;
+  struct ProfSpan {
+    const char* name;
+    cudaEvent_t t0, t1;
+  };
+  std::vector<ProfSpan> spans;
+  std::vector<cudaEvent_t> event_pool;
 };
 
 // Record a message and hand back the status code.
@@ -86,6 +94,7 @@ struct FcQWeight {
   uint64_t bytes = 0;
   // bf16 GEMM operand descriptors are built lazily by the tensor path
   void* tc_cache = nullptr;
+  size_t tc_cache_bytes = 0;
 };
 
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {

@@ -79,11 +79,15 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 }
 
 // ferrum_ref/src/models/llama/ops.rs:L69-L76: silu(g) * u with silu(x) = x / (1 + exp(-x))
-__global__ void swiglu_kernel(const float* __restrict__ gu, uint32_t rows, uint32_t hidden, float* __restrict__ act) {
+// `group` > 0: the fused product's columns come as `group` gate columns followed by the matching
+// `group` up columns (the layout the tensor-core SwiGLU epilogue wants); 0: all gate, then all up.
+__global__ void swiglu_kernel(const float* __restrict__ gu, uint32_t rows, uint32_t hidden, uint32_t group,
+                              float* __restrict__ act) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)rows * hidden) return;
   const size_t r = i / hidden, c = i % hidden;
-  const float g = gu[r * 2 * hidden + c], u = gu[r * 2 * hidden + hidden + c];
+  const size_t gi = group ? (c / group) * 2 * group + c % group : c;
+  const float g = gu[r * 2 * hidden + gi], u = gu[r * 2 * hidden + gi + (group ? group : hidden)];
   act[i] = g / (1.0f + expf(-g)) * u;
 }
 
@@ -260,10 +264,10 @@ int k_layernorm(FcDevice* dev, const float* x, const float* g, const float* b, u
   return FC_OK;
 }
 
-int k_swiglu(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t hidden, float* act) {
+int k_swiglu(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t hidden, uint32_t group, float* act) {
   const size_t total = (size_t)rows * hidden;
   if (!total) return FC_OK;
-  FC_LAUNCH(dev, "swiglu", swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(gate_up, rows, hidden, act));
+  FC_LAUNCH(dev, "swiglu", swiglu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(gate_up, rows, hidden, group, act));
   return FC_OK;
 }
 

@@ -1,0 +1,351 @@
+// Scoring-side quantised product on the 5th-generation tensor cores:
+//   Y[m, n] = A[m, k] (bf16) . dequant(W)[n, k]^T, f32 accumulators in tensor memory.
+// Replaces qlinear_tiled.wgsl for M >= 128 (ferrum_wgpu/src/shaders/quant/qlinear_tiled.wgsl:L93-L128).
+//
+// One CTA computes a 128 x 128 output tile, K in slices of 64 through a 3-deep shared-memory ring:
+//   warp 0      TMA producer: the A slice (128 rows x 64 bf16) arrives as one 128B-swizzled box.
+//   warp 1      allocates tensor memory, then one lane issues tcgen05.mma (4 x K=16 per slice) and
+//               commits each slice back to the ring and the last one to the epilogue.
+//   warps 2-5   weight producers: each thread owns one weight row of the tile, reads its packed
+//               blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to bf16 in registers
+//               and stores the 128-byte row into the same swizzled K-major layout TMA produces.
+//               After the main loop the same four warps are the epilogue: tcgen05.ld their lane
+//               quadrant, apply bias / activation / residual / SwiGLU / online log-sum-exp, store.
+// Two CTAs fit per SM (96 KB of ring + 128 TMEM columns each), so one CTA's epilogue overlaps the
+// other's main loop.
+#include "gemm_tc.cuh"
+#include "tc_ptx.cuh"
+
+namespace {
+
+constexpr int STAGES = 3;
+constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2; // 16 KB
+constexpr uint32_t B_BYTES = TC_BN * TC_BK * 2; // 16 KB
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;
+
+enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+// One 32-element Q4_0 block (4 words, device nibble order) -> 4 chunks of 8 bf16 at `row_smem`,
+// chunk index c0..c0+3 of the 128-byte row, XOR-swizzled with the row number.
+__device__ __forceinline__ void dequant_q4_block(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+  const uint32_t dbf = pack_bf16(__half2float(d), __half2float(d));
+  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+      // nibbles p and p+4 of the word are elements 2p and 2p+1: 0x4300 | nib is the bf16 128 + nib
+      uint32_t t = ((words[w] >> (4 * p)) & 0x000f000fu) | 0x43004300u;
+      t = bf16x2_sub(t, 0x43084308u); // - 136: exact, (nib - 8)
+      o[p] = bf16x2_mul(t, dbf);
+    }
+    const uint32_t addr = row_smem + (((c0 + w) ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+  }
+}
+
+// 16 int8 quants (one uint4 = half a Q8_0 block) -> 2 chunks
+__device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+      const uint32_t u = words[2 * h + w] ^ 0x80808080u;
+      const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
+      const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
+      const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
+      const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
+      o[2 * w] = pack_bf16(f0 * d, f1 * d);
+      o[2 * w + 1] = pack_bf16(f2 * d, f3 * d);
+    }
+    const uint32_t addr = row_smem + (((c0 + h) ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+  }
+}
+
+__device__ __forceinline__ float gelu_f(float x) {
+  const float K = 0.7978846f;
+  return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
+}
+
+template <int KIND>
+struct RowRegs; // packed data of one weight row for one K slice
+template <>
+struct RowRegs<FC_Q4_0> {
+  uint4 q[2];
+  uint32_t sc;
+};
+template <>
+struct RowRegs<FC_Q8_0> {
+  uint4 q[4];
+  uint32_t sc;
+};
+template <>
+struct RowRegs<FC_F32> {
+  uint4 q[16];
+};
+
+template <int KIND>
+__device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32_t row, uint32_t it, bool valid) {
+  if (KIND == FC_Q4_0) {
+    const uint4* p = reinterpret_cast<const uint4*>(w.qs + (size_t)row * (w.k / 2) + (size_t)it * 32);
+    r.q[0] = valid ? __ldg(p) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+    r.q[1] = valid ? __ldg(p + 1) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+    *reinterpret_cast<uint32_t*>(&((RowRegs<FC_Q4_0>&)r).sc) =
+        valid ? __ldg(reinterpret_cast<const uint32_t*>(w.sc + (size_t)row * (w.k / QK) + (size_t)it * 2)) : 0u;
+  } else if (KIND == FC_Q8_0) {
+    const uint4* p = reinterpret_cast<const uint4*>(w.qs + (size_t)row * w.k + (size_t)it * 64);
+#pragma unroll
+    for (int i = 0; i < 4; i++) r.q[i] = valid ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint32_t*>(&((RowRegs<FC_Q8_0>&)r).sc) =
+        valid ? __ldg(reinterpret_cast<const uint32_t*>(w.sc + (size_t)row * (w.k / QK) + (size_t)it * 2)) : 0u;
+  } else {
+    const uint4* p = reinterpret_cast<const uint4*>(w.qs + ((size_t)row * w.k + (size_t)it * 64) * 4);
+#pragma unroll
+    for (int i = 0; i < 16; i++) r.q[i] = valid ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+template <int KIND>
+__device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_smem, uint32_t sw) {
+  if (KIND == FC_Q4_0) {
+    const RowRegs<FC_Q4_0>& rr = (const RowRegs<FC_Q4_0>&)r;
+    const __half d0 = __ushort_as_half((unsigned short)(rr.sc & 0xffff)), d1 = __ushort_as_half((unsigned short)(rr.sc >> 16));
+    dequant_q4_block(rr.q[0], d0, row_smem, sw, 0);
+    dequant_q4_block(rr.q[1], d1, row_smem, sw, 4);
+  } else if (KIND == FC_Q8_0) {
+    const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
+    const float d0 = __half2float(__ushort_as_half((unsigned short)(rr.sc & 0xffff)));
+    const float d1 = __half2float(__ushort_as_half((unsigned short)(rr.sc >> 16)));
+    dequant_q8_half(rr.q[0], d0, row_smem, sw, 0);
+    dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
+    dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
+    dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+  } else {
+    const RowRegs<FC_F32>& rr = (const RowRegs<FC_F32>&)r;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      const uint4 a = rr.q[2 * c], b = rr.q[2 * c + 1];
+      const uint32_t o0 = pack_bf16(__uint_as_float(a.x), __uint_as_float(a.y));
+      const uint32_t o1 = pack_bf16(__uint_as_float(a.z), __uint_as_float(a.w));
+      const uint32_t o2 = pack_bf16(__uint_as_float(b.x), __uint_as_float(b.y));
+      const uint32_t o3 = pack_bf16(__uint_as_float(b.z), __uint_as_float(b.w));
+      const uint32_t addr = row_smem + (((uint32_t)c ^ sw) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+    }
+  }
+}
+
+// ---- epilogues -------------------------------------------------------------------------------------
+
+// One thread's 32 consecutive accumulator columns [c, c + 32) of output row `row`.
+template <int EPI>
+__device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* acc) {
+  if (row >= a.m) return;
+  if (EPI == EPI_F32 || EPI == EPI_RESID) {
+    float* dst = a.out_f32 + (size_t)row * a.ldo + col0;
+    if (((a.ldo | a.n) & 3) != 0) { // rows are not 16-byte aligned (odd vocabularies): scalar stores
+#pragma unroll
+      for (int j = 0; j < 32; j++) {
+        if (col0 + j < a.n) {
+          float v = __uint_as_float(acc[j]);
+          if (a.bias) v += a.bias[col0 + j];
+          if (EPI == EPI_RESID) v += dst[j];
+          dst[j] = v;
+        }
+      }
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (col0 + j >= a.n) break;
+      float4 v = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]), __uint_as_float(acc[j + 2]),
+                             __uint_as_float(acc[j + 3]));
+      if (a.bias) {
+        const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + j);
+        v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+      }
+      if (EPI == EPI_RESID) {
+        const float4 r = *reinterpret_cast<const float4*>(dst + j);
+        v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
+      }
+      *reinterpret_cast<float4*>(dst + j) = v;
+    }
+  } else if (EPI == EPI_BF16) {
+    __nv_bfloat16* dst = a.out_bf16 + (size_t)row * a.ldo + col0;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      if (col0 + j >= a.n) break; // n is a multiple of 8 on this path
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        v[i] = __uint_as_float(acc[j + i]);
+        if (a.bias) v[i] += a.bias[col0 + j + i];
+        if (a.act == ACT_GELU) v[i] = gelu_f(v[i]);
+      }
+      *reinterpret_cast<uint4*>(dst + j) =
+          make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    }
+  }
+}
+
+// gate chunk g[32] and up chunk u[32] -> 32 activations
+__device__ __forceinline__ void epilogue_swiglu(const TcArgs& a, uint32_t row, uint32_t out_col0, const uint32_t* g,
+                                                const uint32_t* u) {
+  if (row >= a.m) return;
+  __nv_bfloat16* dst = a.out_bf16 + (size_t)row * a.ldo + out_col0;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float gv = __uint_as_float(g[j + i]), uv = __uint_as_float(u[j + i]);
+      v[i] = gv / (1.0f + __expf(-gv)) * uv;
+    }
+    *reinterpret_cast<uint4*>(dst + j) =
+        make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+  }
+}
+
+struct LseState {
+  float mx = -INFINITY, se = 0.0f, tl = -INFINITY;
+  int first = 0;
+};
+__device__ __forceinline__ void epilogue_lse(const TcArgs& a, LseState& s, uint32_t col0, int target, const uint32_t* acc) {
+  float cm = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    const float v = col0 + j < a.n ? __uint_as_float(acc[j]) : -INFINITY;
+    cm = fmaxf(cm, v);
+  }
+  if (cm == -INFINITY) return;
+  if (cm > s.mx) { // strictly greater: an earlier chunk keeps a tied maximum
+    s.se *= __expf(s.mx - cm);
+    s.mx = cm;
+    int f = 0;
+    bool found = false;
+#pragma unroll
+    for (int j = 0; j < 32; j++) {
+      const float v = col0 + j < a.n ? __uint_as_float(acc[j]) : -INFINITY;
+      if (!found && v == cm) {
+        f = j;
+        found = true;
+      }
+    }
+    s.first = (int)(a.v0 + col0) + f;
+  }
+#pragma unroll
+  for (int j = 0; j < 32; j++) {
+    if (col0 + j < a.n) {
+      const float v = __uint_as_float(acc[j]);
+      s.se += __expf(v - s.mx);
+      if ((int)(a.v0 + col0) + j == target) s.tl = v;
+    }
+  }
+}
+
+#include "gemm_tc_main.cuh"
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point: the library carries no link
+// dependency on libcuda, so it still loads (and exports its symbols) on a machine without a GPU.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int KIND, int EPI>
+int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, dim3 grid) {
+  auto kern = qgemm_tc_kernel<KIND, EPI>;
+  static bool attr = false; // one per instantiation
+  if (!attr) {
+    FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
+    attr = true;
+  }
+  FC_LAUNCH(dev, "qgemm_tc", kern<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmap, w, a));
+  return FC_OK;
+}
+
+template <int KIND>
+int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, int epi, dim3 grid) {
+  switch (epi) {
+    case EPI_F32: return launch_tc<KIND, EPI_F32>(dev, tmap, w, a, grid);
+    case EPI_BF16: return launch_tc<KIND, EPI_BF16>(dev, tmap, w, a, grid);
+    case EPI_RESID: return launch_tc<KIND, EPI_RESID>(dev, tmap, w, a, grid);
+    case EPI_SWIGLU: return launch_tc<KIND, EPI_SWIGLU>(dev, tmap, w, a, grid);
+    case EPI_LSE: return launch_tc<KIND, EPI_LSE>(dev, tmap, w, a, grid);
+  }
+  return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
+}
+
+} // namespace
+
+int k_qgemm_tc_bf16(FcDevice* dev, const QMat& w, const __nv_bfloat16* a_dev, int epi, TcArgs args) {
+  if (args.m == 0) return FC_OK;
+  args.n = w.n;
+  args.k = w.k;
+  args.err_flag = dev->d_flag;
+  if (w.k % TC_BK) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product needs k %% 64 == 0, not %u", w.k);
+  if ((epi == EPI_BF16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
+    return fc_fail(dev, FC_ERR_UNSUPPORTED, "a bf16 result needs n %% 8 == 0, not %u", w.n);
+  if (epi == EPI_SWIGLU && w.n % 128) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the SwiGLU epilogue needs n %% 128 == 0");
+  if ((reinterpret_cast<uintptr_t>(a_dev) & 15) != 0) return fc_fail(dev, FC_ERR_ARG, "the A operand must be 16-byte aligned");
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap tmap;
+  const cuuint64_t dims[2] = {w.k, args.m};
+  const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
+  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)a_dev, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);
+  dim3 grid((w.n + TC_BN - 1) / TC_BN, (args.m + TC_BM - 1) / TC_BM);
+  if (grid.y > 65535) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u rows exceed one launch of the tensor-core product", args.m);
+  if (w.kind == FC_Q4_0) return pick_epi<FC_Q4_0>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_Q8_0) return pick_epi<FC_Q8_0>(dev, tmap, w, args, epi, grid);
+  return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);
+}
+
+int tc_check_errors(FcDevice* dev) {
+  int flag = 0;
+  FC_CUDA(dev, cudaMemcpyAsync(&flag, dev->d_flag, sizeof(int), cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (flag != 0) {
+    cudaMemsetAsync(dev->d_flag, 0, sizeof(int), dev->stream);
+    return fc_fail(dev, FC_ERR_TIMEOUT, "a tensor-core kernel gave up a bounded wait (stage %d)", flag);
+  }
+  return FC_OK;
+}

@@ -187,7 +187,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.h, rows, b.ff, e_ff1));
     const float* ff2_in = b.ff;
     if (m->arch == ARCH_LLAMA) {
-      FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, b.act));
+      FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, m->gu_group, b.act));
       ff2_in = b.act;
     }
     Epilogue e_ff2;
@@ -366,6 +366,10 @@ FC_API int fc_llama_create(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaW
     const float* gu_m[2] = {b.gate, b.up};
     const uint32_t gu_n[2] = {hid, hid};
     if ((rc = qweight_from_f32_concat(dev, qkind, gu_m, gu_n, 2, d, &l.ff1.w)) != FC_OK) return fail(rc);
+    if (hid % 64 == 0) { // 64 gate rows then their 64 up rows: what the SwiGLU epilogue of the tensor path reads
+      if ((rc = model_interleave_gate_up(dev, l.ff1.w, hid, 64)) != FC_OK) return fail(rc);
+      m->gu_group = 64;
+    }
     if ((rc = qweight_from_f32(dev, qkind, b.down, hid, d, &l.ff2.w)) != FC_OK) return fail(rc);
   }
   if ((rc = qweight_from_f32(dev, qkind, w->head, d, c->vocab, &m->head.w)) != FC_OK) return fail(rc);
@@ -560,7 +564,8 @@ FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, floa
   if (n == 0 || n > m->ctx) return fc_fail(dev, FC_ERR_SHAPE, "sequence length %u must be in 1..=%u", n, m->ctx);
   if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "forward_all needs the whole head on this device");
   FC_TRY(check_ids(m, ids, n));
-  const size_t extra = (size_t)n * 8 + 512 + (size_t)n * m->vocab * 4 + 256 + (size_t)n * m->dim * 2 + 256;
+  const size_t extra = (size_t)n * 8 + 512 + (size_t)n * m->vocab * 4 + 256 + (size_t)n * m->dim * 2 + 256 +
+                       (mode == FC_TENSOR_BF16 ? model_tc_trunk_bytes(m, n) : 0);
   PassBufs b;
   FC_TRY(carve_pass(m, n, &b, extra));
   int32_t* d_ids = (int32_t*)arena_take(m, (size_t)n * 4);
@@ -575,6 +580,7 @@ FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, floa
     __nv_bfloat16* hid = (__nv_bfloat16*)arena_take(m, (size_t)n * m->dim * 2);
     FC_TRY(model_trunk_tc(m, d_ids, d_pos, 1, n, hid));
     FC_TRY(model_logits_tc(m, hid, n, logits));
+    FC_TRY(tc_check_errors(dev));
   } else {
     return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   }
@@ -621,6 +627,7 @@ FC_API int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint3
   if (cudaMemcpyAsync(d_ids, ids, (size_t)n_seqs * seq_len * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "upload of ids failed");
   if (rc == FC_OK) rc = fc_model_score_dev(m, d_ids, n_seqs, seq_len, mode, d_lp, d_gr, d_nll);
+  if (rc == FC_OK && mode == FC_TENSOR_BF16) rc = tc_check_errors(dev);
   if (rc == FC_OK) {
     if (logprob_out) cudaMemcpyAsync(logprob_out, d_lp, rows * 4, cudaMemcpyDeviceToHost, dev->stream);
     if (greedy_out) cudaMemcpyAsync(greedy_out, d_gr, rows, cudaMemcpyDeviceToHost, dev->stream);

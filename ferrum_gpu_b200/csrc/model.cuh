@@ -41,6 +41,7 @@ struct FcModel {
   QMat head_view;             // the rows of `head` this rank owns
   uint32_t shard = 0, n_shards = 1, v0 = 0, v1 = 0;
   std::vector<Layer> layers;
+  uint32_t gu_group = 0;      // gate/up rows of ff1 interleaved in groups of this many (0: not interleaved)
   uint32_t max_streams = 1;
   std::vector<uint32_t> pos;  // per stream
   uint64_t weight_bytes = 0;
@@ -74,3 +75,7 @@ int model_head_partial_tc(FcModel* m, const __nv_bfloat16* hidden, const int32_t
                           float* partial);
 int model_logits_tc(FcModel* m, const __nv_bfloat16* hidden, uint32_t rows, float* logits);
 void model_tc_free(FcModel* m);
+size_t model_tc_trunk_bytes(const FcModel* m, size_t rows); // workspace model_trunk_tc takes from the arena
+size_t model_tc_head_bytes(const FcModel* m, size_t rows);  // workspace model_head_partial_tc takes
+int model_interleave_gate_up(FcDevice* dev, FcQWeight* w, uint32_t hidden, uint32_t group);
+int tc_check_errors(FcDevice* dev);

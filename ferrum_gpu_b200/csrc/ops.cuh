@@ -20,7 +20,7 @@ int k_embed(FcDevice* dev, const float* tok, const float* pos_table /*nullable*/
             const int32_t* positions /*nullable unless pos_table*/, uint32_t rows, uint32_t d, float* x);
 int k_rmsnorm(FcDevice* dev, const float* x, const float* g, uint32_t rows, uint32_t d, float eps, float* y);
 int k_layernorm(FcDevice* dev, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d, float* y);
-int k_swiglu(FcDevice* dev, const float* gate_up /*[rows][2*hidden]*/, uint32_t rows, uint32_t hidden, float* act);
+int k_swiglu(FcDevice* dev, const float* gate_up /*[rows][2*hidden]*/, uint32_t rows, uint32_t hidden, uint32_t group, float* act);
 // Rotate q and k of the fused qkv rows in place (rope.type/rope_dim; skipped when rope.cos is
 // NULL) and, when `kv` is given, store each row's k and v into the cache at (stream, position).
 int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,

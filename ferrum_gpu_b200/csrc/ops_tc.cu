@@ -1,0 +1,165 @@
+// Companions of the tensor-core scoring path: f32 -> bf16 conversion, RMSNorm / LayerNorm with a
+// bf16 result (the next product's A operand), RoPE on the bf16 fused qkv rows, the merge of
+// per-tile log-sum-exp partials, and the row permutation that interleaves gate and up rows.
+#include "gemm_tc.cuh"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  return warp_sum(lane < nw ? red[lane] : 0.0f);
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, size_t n, __nv_bfloat16* __restrict__ y) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    const float4 v = *reinterpret_cast<const float4*>(x + i);
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(y + i) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+  } else {
+    for (size_t j = i; j < n; j++) y[j] = __float2bfloat16_rn(x[j]);
+  }
+}
+
+// One CTA per row; same arithmetic as the f32 norms, result rounded to bf16.
+template <bool LAYERNORM>
+__global__ void norm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+                                 uint32_t d, float eps, __nv_bfloat16* __restrict__ y) {
+  __shared__ float red[32];
+  const float* row = x + (size_t)blockIdx.x * d;
+  float mean = 0.0f, inv;
+  if (LAYERNORM) {
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) s += row[i];
+    mean = block_sum(s, red) / (float)d;
+    float vs = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+      const float dl = row[i] - mean;
+      vs = fmaf(dl, dl, vs);
+    }
+    inv = 1.0f / sqrtf(block_sum(vs, red) / (float)d + 1e-5f);
+  } else {
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    inv = 1.0f / sqrtf(block_sum(ss, red) / (float)d + eps);
+  }
+  for (uint32_t i = threadIdx.x * 2; i < d; i += blockDim.x * 2) { // d is even on this path
+    float v0, v1;
+    if (LAYERNORM) {
+      v0 = (row[i] - mean) * inv * g[i] + b[i];
+      v1 = (row[i + 1] - mean) * inv * g[i + 1] + b[i + 1];
+    } else {
+      v0 = row[i] * inv * g[i];
+      v1 = row[i + 1] * inv * g[i + 1];
+    }
+    *reinterpret_cast<__nv_bfloat162*>(y + (size_t)blockIdx.x * d + i) = __floats2bfloat162_rn(v0, v1);
+  }
+}
+
+// rope.wgsl on bf16 rows: rotate q and k heads in place, angles from the host-built f32 tables.
+__global__ void rope_bf16_kernel(__nv_bfloat16* __restrict__ qkv, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+                                 const float* __restrict__ cos, const float* __restrict__ sin, uint32_t rope_dim,
+                                 uint32_t type, const int32_t* __restrict__ positions) {
+  const uint32_t r = blockIdx.x;
+  const uint32_t stride = (heads + 2 * kv_heads) * hd;
+  __nv_bfloat16* row = qkv + (size_t)r * stride;
+  const uint32_t half = rope_dim / 2;
+  const float* cs = cos + (size_t)positions[r] * half;
+  const float* sn = sin + (size_t)positions[r] * half;
+  const uint32_t total = (heads + kv_heads) * half;
+  for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
+    const uint32_t h = i / half, p = i % half;
+    __nv_bfloat16* base = row + (size_t)h * hd;
+    const uint32_t ia = type == FC_ROPE_NORM ? 2 * p : p;
+    const uint32_t ib = type == FC_ROPE_NORM ? 2 * p + 1 : p + half;
+    const float c = cs[p], s = sn[p], a = __bfloat162float(base[ia]), b = __bfloat162float(base[ib]);
+    base[ia] = __float2bfloat16_rn(a * c - b * s);
+    base[ib] = __float2bfloat16_rn(a * s + b * c);
+  }
+}
+
+// [n_tiles][rows][4] -> [rows][4]: tiles are in ascending vocabulary order
+__global__ void partial_merge_kernel(const float* __restrict__ tiles, uint32_t n_tiles, uint32_t rows,
+                                     float* __restrict__ out) {
+  const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  float mx = -INFINITY, tl = -INFINITY;
+  for (uint32_t s = 0; s < n_tiles; s++) {
+    const float4 p = *reinterpret_cast<const float4*>(tiles + ((size_t)s * rows + r) * 4);
+    mx = fmaxf(mx, p.x);
+    tl = fmaxf(tl, p.z);
+  }
+  float se = 0.0f, first = 0.0f;
+  bool found = false;
+  for (uint32_t s = 0; s < n_tiles; s++) {
+    const float4 p = *reinterpret_cast<const float4*>(tiles + ((size_t)s * rows + r) * 4);
+    se += p.y * expf(p.x - mx);
+    if (!found && p.x == mx) {
+      first = p.w;
+      found = true;
+    }
+  }
+  *reinterpret_cast<float4*>(out + (size_t)r * 4) = make_float4(mx, se, tl, first);
+}
+
+// Rows [0, half) are gate rows, [half, 2*half) up rows; destination groups them as `group` gate
+// rows followed by the matching `group` up rows. One CTA per destination row.
+__global__ void permute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint32_t row_bytes,
+                                    uint32_t half, uint32_t group) {
+  const uint32_t dr = blockIdx.x;
+  const uint32_t blk = dr / (2 * group), in = dr % (2 * group);
+  const uint32_t sr = in < group ? blk * group + in : half + blk * group + (in - group);
+  const uint8_t* s = src + (size_t)sr * row_bytes;
+  uint8_t* d = dst + (size_t)dr * row_bytes;
+  for (uint32_t i = threadIdx.x; i < row_bytes; i += blockDim.x) d[i] = s[i];
+}
+
+} // namespace
+
+int k_f32_to_bf16(FcDevice* dev, const float* x, size_t n, __nv_bfloat16* y) {
+  if (!n) return FC_OK;
+  const size_t threads = (n + 3) / 4;
+  FC_LAUNCH(dev, "f32_to_bf16", f32_to_bf16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(x, n, y));
+  return FC_OK;
+}
+
+int k_norm_bf16(FcDevice* dev, bool layernorm, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d,
+                float eps, __nv_bfloat16* y) {
+  if (!rows) return FC_OK;
+  if (d % 2) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the bf16 norm needs an even width, not %u", d);
+  if (layernorm)
+    FC_LAUNCH(dev, "layernorm_bf16", norm_bf16_kernel<true><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
+  else
+    FC_LAUNCH(dev, "rmsnorm_bf16", norm_bf16_kernel<false><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
+  return FC_OK;
+}
+
+int k_rope_bf16(FcDevice* dev, __nv_bfloat16* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+                const float* cos, const float* sin, uint32_t rope_dim, uint32_t type, const int32_t* positions) {
+  if (!rows || !cos) return FC_OK;
+  FC_LAUNCH(dev, "rope_bf16",
+            rope_bf16_kernel<<<rows, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, cos, sin, rope_dim, type, positions));
+  return FC_OK;
+}
+
+int k_partial_merge(FcDevice* dev, const float* tiles, uint32_t n_tiles, uint32_t rows, float* out) {
+  if (!rows) return FC_OK;
+  FC_LAUNCH(dev, "partial_merge", partial_merge_kernel<<<(rows + 127) / 128, 128, 0, dev->stream>>>(tiles, n_tiles, rows, out));
+  return FC_OK;
+}
+
+int k_permute_rows(FcDevice* dev, const uint8_t* src, uint8_t* dst, uint32_t rows, uint32_t row_bytes, uint32_t half,
+                   uint32_t group) {
+  if (!rows) return FC_OK;
+  FC_LAUNCH(dev, "permute_rows", permute_rows_kernel<<<rows, 128, 0, dev->stream>>>(src, dst, row_bytes, half, group));
+  return FC_OK;
+}

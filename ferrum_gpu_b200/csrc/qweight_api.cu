@@ -2,7 +2,8 @@
 // counterpart of ferrum_wgpu::ops::quant's public functions (ferrum_wgpu/src/ops/quant.rs).
 #include "common.cuh"
 
-int k_qgemm_tc(FcDevice* dev, FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev); // gemm_tc.cu
+int k_qgemm_tc(FcDevice* dev, FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev); // model_tc.cu
+int tc_check_errors(FcDevice* dev);                                                            // gemm_tc.cu
 
 FC_API size_t fc_block_bytes(int kind, size_t n_elems) {
   if (kind == FC_F32) return n_elems * 4;
@@ -146,6 +147,7 @@ FC_API int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mo
   if (cudaMemcpyAsync(dx, x, (size_t)m * w->m.k * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "upload of x failed");
   if (rc == FC_OK) rc = fc_qmatmul_dev(w, dx, m, dy, mode);
+  if (rc == FC_OK && mode == FC_TENSOR_BF16) rc = tc_check_errors(dev);
   if (rc == FC_OK && cudaMemcpyAsync(y, dy, (size_t)m * w->m.n * 4, cudaMemcpyDeviceToHost, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "read-back of y failed");
   if (rc == FC_OK && cudaStreamSynchronize(dev->stream) != cudaSuccess) {

@@ -2,6 +2,7 @@
 // The CUDA counterpart of ferrum_wgpu::device (ferrum_wgpu/src/device/{mod,runtime,tensor}.rs):
 // errors are values, a failed CUDA call makes the handle report "lost" from then on, and the
 // fault hook refuses the k-th launch before it reaches the device.
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -29,10 +30,24 @@ int fc_pre_launch(FcDevice* dev, const char* what) {
   if (dev->fail_after == 0) return fc_fail(dev, FC_ERR_INJECTED, "injected fault: launch of %s refused", what);
   if (dev->fail_after > 0) dev->fail_after--;
   dev->launches++;
+  if (dev->profiling) {
+    FcDevice::ProfSpan s{what, nullptr, nullptr};
+    for (cudaEvent_t* ev : {&s.t0, &s.t1}) {
+      if (!dev->event_pool.empty()) {
+        *ev = dev->event_pool.back();
+        dev->event_pool.pop_back();
+      } else if (cudaEventCreate(ev) != cudaSuccess) {
+        return fc_fail(dev, FC_ERR_DEVICE, "cannot create a timing event");
+      }
+    }
+    cudaEventRecord(s.t0, dev->stream);
+    dev->spans.push_back(s);
+  }
   return FC_OK;
 }
 
 int fc_post_launch(FcDevice* dev, const char* what) {
+  if (dev->profiling && !dev->spans.empty()) cudaEventRecord(dev->spans.back().t1, dev->stream);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     dev->lost = true;
@@ -93,6 +108,11 @@ FC_API int fc_device_close(FcDevice* dev) {
   cudaStreamSynchronize(dev->stream);
   if (dev->pinned) cudaFreeHost(dev->pinned);
   if (dev->d_flag) cudaFree(dev->d_flag);
+  for (auto& s : dev->spans) {
+    cudaEventDestroy(s.t0);
+    cudaEventDestroy(s.t1);
+  }
+  for (cudaEvent_t e : dev->event_pool) cudaEventDestroy(e);
   cudaStreamDestroy(dev->stream);
   delete dev;
   return FC_OK;
@@ -132,6 +152,54 @@ FC_API uint64_t fc_device_launch_count(FcDevice* dev) { return dev ? dev->launch
 FC_API int fc_debug_fail_after(FcDevice* dev, int64_t n_launches) {
   if (!dev) return FC_ERR_ARG;
   dev->fail_after = n_launches < 0 ? -1 : n_launches;
+  return FC_OK;
+}
+
+FC_API int fc_debug_profile(FcDevice* dev, int enable) {
+  if (!dev) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  dev->profiling = enable != 0;
+  return FC_OK;
+}
+
+// JSON object {"kernel name": {"launches": n, "ms": total}, ...} of every launch timed since the last
+// report; synchronises the stream, then forgets the spans.
+FC_API int fc_debug_profile_report(FcDevice* dev, char* buf, size_t buf_len) {
+  if (!dev || !buf || buf_len < 3) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  struct Acc {
+    const char* name;
+    uint64_t n;
+    double ms;
+  };
+  std::vector<Acc> acc;
+  for (auto& s : dev->spans) {
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, s.t0, s.t1);
+    Acc* a = nullptr;
+    for (auto& e : acc)
+      if (e.name == s.name || std::string(e.name) == s.name) a = &e;
+    if (!a) {
+      acc.push_back({s.name, 0, 0.0});
+      a = &acc.back();
+    }
+    a->n++;
+    a->ms += ms;
+    dev->event_pool.push_back(s.t0);
+    dev->event_pool.push_back(s.t1);
+  }
+  dev->spans.clear();
+  std::string out = "{";
+  for (size_t i = 0; i < acc.size(); i++) {
+    char line[256];
+    snprintf(line, sizeof line, "%s\"%s\": {\"launches\": %llu, \"ms\": %.6f}", i ? ", " : "", acc[i].name,
+             (unsigned long long)acc[i].n, acc[i].ms);
+    out += line;
+  }
+  out += "}";
+  if (out.size() + 1 > buf_len) return fc_fail(dev, FC_ERR_SHAPE, "the profile report needs %zu bytes", out.size() + 1);
+  memcpy(buf, out.c_str(), out.size() + 1);
   return FC_OK;
 }
 

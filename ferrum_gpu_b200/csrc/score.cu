@@ -27,6 +27,7 @@ size_t chunk_bytes(const FcModel* m, size_t rows, int mode) {
   size_t b = al(rows * m->dim * 4) * 2 + al(rows * m->qkv_w() * 4) + al(rows * m->qd() * 4) + al(rows * m->ff1_w() * 4) +
              al(rows * m->hidden * 4) + 3 * al(rows * 4) + al(rows * 16) + al(rows * m->dim * 2) + 8192;
   if (mode == FC_EXACT_F32) b += al(rows * vs * 4); // materialised logits of the chunk
+  else b += model_tc_head_bytes(m, rows);           // per-tile log-sum-exp partials
   return b;
 }
 
@@ -138,7 +139,10 @@ FC_API int fc_model_head_partial_dev(FcModel* m, const void* hidden_dev, const i
   FcDevice* dev = m->dev;
   cudaSetDevice(dev->ordinal);
   if (rows == 0) return FC_OK;
-  if (mode == FC_TENSOR_BF16) return model_head_partial_tc(m, (const __nv_bfloat16*)hidden_dev, targets_dev, rows, partial_dev);
+  if (mode == FC_TENSOR_BF16) {
+    FC_TRY(arena_reserve(m, model_tc_head_bytes(m, rows)));
+    return model_head_partial_tc(m, (const __nv_bfloat16*)hidden_dev, targets_dev, rows, partial_dev);
+  }
   if (mode != FC_EXACT_F32) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   // chunk the rows so the materialised logits stay under 2 GiB
   const size_t vs = m->v1 - m->v0;

@@ -4,6 +4,8 @@
 from __future__ import annotations
 
 import ctypes as C
+import json
+import weakref
 
 from . import _ffi
 
@@ -20,6 +22,9 @@ class Device:
     def __init__(self, handle):
         self._h = handle
         self._lib = _ffi.load()
+        # weights and models opened on this device: closed before the device is, whatever order the
+        # interpreter drops them in
+        self._children = weakref.WeakSet()
 
     @classmethod
     def open(cls, ordinal: int = 0) -> "Device":
@@ -30,10 +35,21 @@ class Device:
             raise CudaError(rc, lib.fc_last_error(None).decode())
         return cls(h)
 
+    def adopt(self, child):
+        self._children.add(child)
+
     def close(self):
         if self._h:
+            for c in list(self._children):
+                c.close()
             self._lib.fc_device_close(self._h)
             self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
     @property
     def handle(self):
@@ -61,6 +77,16 @@ class Device:
 
     def launch_count(self) -> int:
         return self._lib.fc_device_launch_count(self._h)
+
+    def profile(self, enable: bool):
+        """Bracket every launch with CUDA events (per-kernel timing); off by default."""
+        self.check(self._lib.fc_debug_profile(self._h, 1 if enable else 0))
+
+    def profile_report(self) -> dict:
+        """{kernel: {"launches": n, "ms": total}} since the last report; synchronises."""
+        buf = C.create_string_buffer(1 << 16)
+        self.check(self._lib.fc_debug_profile_report(self._h, buf, len(buf)))
+        return json.loads(buf.value.decode())
 
     def fail_after(self, n: int | None):
         """`Gpu::fail_after` (device/runtime.rs:L214-L256): refuse launches after `n` more; None disarms."""

@@ -44,6 +44,7 @@ class QWeight:
         kind, k, n, b = C.c_int(), C.c_uint32(), C.c_uint32(), C.c_uint64()
         dev.check(self._lib.fc_qweight_info(handle, C.byref(kind), C.byref(k), C.byref(n), C.byref(b)))
         self._kind, self._k, self._n, self._bytes = QKind(kind.value), k.value, n.value, b.value
+        dev.adopt(self)
 
     def kind(self) -> QKind:
         return self._kind

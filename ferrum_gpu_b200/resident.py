@@ -21,6 +21,7 @@ class ResidentModel:
     def __init__(self, dev: Device, handle, cfg, quant: QKind | None, max_streams: int):
         self.dev, self._h, self._lib = dev, handle, _ffi.load()
         self.cfg, self._quant, self.max_streams = cfg, quant, max_streams
+        dev.adopt(self)
 
     # -- reference interface ------------------------------------------------------------------
     def config(self):

@@ -85,6 +85,13 @@ uint64_t fc_device_launch_count(FcDevice* dev);
  * further launch is refused with FC_ERR_INJECTED *before it reaches the device*; a negative
  * value disarms the hook. No GPU fault is ever produced. */
 int fc_debug_fail_after(FcDevice* dev, int64_t n_launches);
+/* Per-kernel device timing, the counterpart of the reference's one-kernel-at-a-time profiler
+ * (ferrum_wgpu/benches/profile_train.rs:L15-L25): while enabled every launch is bracketed by a pair
+ * of CUDA events on the device's stream. The report is a JSON object
+ * {"kernel": {"launches": n, "ms": total}, ...} of the launches since the previous report; it
+ * synchronises the stream. Off by default. */
+int fc_debug_profile(FcDevice* dev, int enable);
+int fc_debug_profile_report(FcDevice* dev, char* buf, size_t buf_len);
 
 /* ---- stand-alone quantised weights and products ------------------------------------------ */
 /* Bytes of a GGUF tensor of `n_elems` elements (ferrum_gguf/src/codec/quant.rs:L17-L46);

@@ -99,15 +99,15 @@ def gpu_llama_variants():
     """The four shapes of ferrum_wgpu/src/models/llama/tests.rs:L10-L42 (llama; qwen = NEOX +
     biases + tied; MQA + partial rotary; dim 24 = not whole 32-blocks), widened to dim 32/64 where
     the quantised path needs whole blocks."""
-    mk = LlamaConfig
+    def mk(**kw):
+        base = dict(vocab=17, ctx=10, dim=32, heads=4, kv_heads=2, head_dim=8, layers=2, hidden=64,
+                    rope_dim=8, rope_base=10000.0, rope_type=_ffi.FC_ROPE_NORM, eps=1e-5)
+        base.update(kw)
+        return LlamaConfig(**base)
+
     return [
-        ("llama", mk(vocab=40, ctx=16, dim=32, heads=4, kv_heads=2, head_dim=8, layers=2, hidden=64,
-                     rope_dim=8, rope_base=10000.0, rope_type=_ffi.FC_ROPE_NORM, eps=1e-5), False, False),
-        ("qwen", mk(vocab=48, ctx=16, dim=64, heads=4, kv_heads=2, head_dim=16, layers=2, hidden=96,
-                    rope_dim=16, rope_base=1e6, rope_type=_ffi.FC_ROPE_NEOX, eps=1e-6), True, True),
-        ("mqa-partial", mk(vocab=33, ctx=12, dim=32, heads=4, kv_heads=1, head_dim=8, layers=2,
-                           hidden=64, rope_dim=4, rope_base=10000.0, rope_type=_ffi.FC_ROPE_NEOX,
-                           eps=1e-5), False, False),
-        ("dim24", mk(vocab=29, ctx=10, dim=24, heads=3, kv_heads=3, head_dim=8, layers=1, hidden=40,
-                     rope_dim=8, rope_base=10000.0, rope_type=_ffi.FC_ROPE_NORM, eps=1e-5), True, False),
+        ("llama", mk(), False, False),
+        ("qwen", mk(rope_type=_ffi.FC_ROPE_NEOX), True, True),
+        ("mqa-partial", mk(kv_heads=1, rope_dim=4), False, False),
+        ("dim24", mk(dim=24, heads=3, kv_heads=3, head_dim=8, rope_dim=8), True, False),
     ]
