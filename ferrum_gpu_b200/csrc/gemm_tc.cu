@@ -1,29 +1,29 @@
 // Scoring-side quantised product on the 5th-generation tensor cores:
-//   Y[m, n] = A[m, k] (bf16) . dequant(W)[n, k]^T, f32 accumulators in tensor memory.
+//   Y[m, n] = A[m, k] (bf16) . dequant(W)[n, k]^T (fp16), f32 accumulators in tensor memory.
 // Replaces qlinear_tiled.wgsl for M >= 128 (ferrum_wgpu/src/shaders/quant/qlinear_tiled.wgsl:L93-L128).
 //
-// One CTA computes a 128 x 128 output tile, K in slices of 64 through a 3-deep shared-memory ring:
-//   warp 0      TMA producer: the A slice (128 rows x 64 bf16) arrives as one 128B-swizzled box.
-//   warp 1      allocates tensor memory, then one lane issues tcgen05.mma (4 x K=16 per slice) and
-//               commits each slice back to the ring and the last one to the epilogue.
-//   warps 2-5   weight producers: each thread owns one weight row of the tile, reads its packed
-//               blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to bf16 in registers
-//               and stores the 128-byte row into the same swizzled K-major layout TMA produces.
-//               After the main loop the same four warps are the epilogue: tcgen05.ld their lane
-//               quadrant, apply bias / activation / residual / SwiGLU / online log-sum-exp, store.
-// Two CTAs fit per SM (96 KB of ring + 128 TMEM columns each), so one CTA's epilogue overlaps the
-// other's main loop.
+// A persistent CTA per SM walks 256 x 128 output tiles, K in slices of 64 through a 4-deep
+// shared-memory ring (see gemm_tc_main.cuh for the warp roles and barriers):
+//   - the A slice (256 rows x 64 bf16) arrives by TMA as one 128B-swizzled box;
+//   - the weight slice (128 rows x 64) is produced in the kernel: each producer thread owns one weight
+//     row, reads its packed blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to bf16 in
+//     registers and stores the 128-byte row into the same swizzled K-major layout TMA produces;
+//   - one thread issues tcgen05.mma into two 128 x 128 f32 accumulators in tensor memory that share
+//     the weight slice; tensor memory holds two tiles so the epilogue of one overlaps the next;
+//   - eight epilogue warps tcgen05.ld their lane quadrants and apply bias / activation / residual /
+//     SwiGLU / online log-sum-exp before storing.
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
 
 namespace {
 
-constexpr int STAGES = 3;
-constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2; // 16 KB
+constexpr int STAGES = 4;
+constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2; // 32 KB: two 128-row halves
 constexpr uint32_t B_BYTES = TC_BN * TC_BK * 2; // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int THREADS = 192;
+constexpr int THREADS = 448;
+constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 columns
 
 enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
 
@@ -32,31 +32,38 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
-__device__ __forceinline__ uint32_t bf16x2_sub(uint32_t a, uint32_t b) {
+// The weight operand is fp16: the block scale is an f16 and a quant has at most 8 bits, so d * q
+// rounds once to 11 bits (2^-12 relative) instead of twice to 8; the activations stay bf16.
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t r;
-  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
-__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t f16x2_sub(uint32_t a, uint32_t b) {
   uint32_t r;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t f16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
 
-// One 32-element Q4_0 block (4 words, device nibble order) -> 4 chunks of 8 bf16 at `row_smem`,
+// One 32-element Q4_0 block (4 words, device nibble order) -> 4 chunks of 8 fp16 at `row_smem`,
 // chunk index c0..c0+3 of the 128-byte row, XOR-swizzled with the row number.
 __device__ __forceinline__ void dequant_q4_block(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
-  const uint32_t dbf = pack_bf16(__half2float(d), __half2float(d));
+  const uint32_t dd = (uint32_t)__half_as_ushort(d) * 0x00010001u; // the f16 scale in both halves
   const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
   for (int w = 0; w < 4; w++) {
     uint32_t o[4];
 #pragma unroll
     for (int p = 0; p < 4; p++) {
-      // nibbles p and p+4 of the word are elements 2p and 2p+1: 0x4300 | nib is the bf16 128 + nib
-      uint32_t t = ((words[w] >> (4 * p)) & 0x000f000fu) | 0x43004300u;
-      t = bf16x2_sub(t, 0x43084308u); // - 136: exact, (nib - 8)
-      o[p] = bf16x2_mul(t, dbf);
+      // nibbles p and p+4 of the word are elements 2p and 2p+1: 0x6400 | nib is the fp16 1024 + nib
+      uint32_t t = ((words[w] >> (4 * p)) & 0x000f000fu) | 0x64006400u;
+      t = f16x2_sub(t, 0x64086408u); // - 1032: exact, (nib - 8)
+      o[p] = f16x2_mul(t, dd);        // one rounding
     }
     const uint32_t addr = row_smem + (((c0 + w) ^ sw) << 4);
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
@@ -76,8 +83,8 @@ __device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_
       const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
       const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
       const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
-      o[2 * w] = pack_bf16(f0 * d, f1 * d);
-      o[2 * w + 1] = pack_bf16(f2 * d, f3 * d);
+      o[2 * w] = pack_f16(f0 * d, f1 * d);
+      o[2 * w + 1] = pack_f16(f2 * d, f3 * d);
     }
     const uint32_t addr = row_smem + (((c0 + h) ^ sw) << 4);
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
@@ -147,10 +154,10 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
 #pragma unroll
     for (int c = 0; c < 8; c++) {
       const uint4 a = rr.q[2 * c], b = rr.q[2 * c + 1];
-      const uint32_t o0 = pack_bf16(__uint_as_float(a.x), __uint_as_float(a.y));
-      const uint32_t o1 = pack_bf16(__uint_as_float(a.z), __uint_as_float(a.w));
-      const uint32_t o2 = pack_bf16(__uint_as_float(b.x), __uint_as_float(b.y));
-      const uint32_t o3 = pack_bf16(__uint_as_float(b.z), __uint_as_float(b.w));
+      const uint32_t o0 = pack_f16(__uint_as_float(a.x), __uint_as_float(a.y));
+      const uint32_t o1 = pack_f16(__uint_as_float(a.z), __uint_as_float(a.w));
+      const uint32_t o2 = pack_f16(__uint_as_float(b.x), __uint_as_float(b.y));
+      const uint32_t o3 = pack_f16(__uint_as_float(b.z), __uint_as_float(b.w));
       const uint32_t addr = row_smem + (((uint32_t)c ^ sw) << 4);
       asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
     }
@@ -332,8 +339,10 @@ int k_qgemm_tc_bf16(FcDevice* dev, const QMat& w, const __nv_bfloat16* a_dev, in
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);
-  dim3 grid((w.n + TC_BN - 1) / TC_BN, (args.m + TC_BM - 1) / TC_BM);
-  if (grid.y > 65535) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u rows exceed one launch of the tensor-core product", args.m);
+  const uint64_t tiles = (uint64_t)((w.n + TC_BN - 1) / TC_BN) * ((args.m + TC_BM - 1) / TC_BM);
+  if (tiles > 0x7fffffffull) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u rows exceed one launch of the tensor-core product", args.m);
+  const uint32_t sms = (uint32_t)dev->prop.multiProcessorCount;
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms)); // persistent: one CTA per SM walks the tiles
   if (w.kind == FC_Q4_0) return pick_epi<FC_Q4_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_Q8_0) return pick_epi<FC_Q8_0>(dev, tmap, w, args, epi, grid);
   return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);

@@ -26,7 +26,7 @@ struct TcArgs {
   int* err_flag = nullptr;
 };
 
-constexpr uint32_t TC_BM = 128, TC_BN = 128, TC_BK = 64;
+constexpr uint32_t TC_BM = 256, TC_BN = 128, TC_BK = 64; // output tile of one CTA step, K slice
 
 // y = a[m][k] (bf16, row-major, device) . W^T with the epilogue `epi`. k % 64 == 0.
 int k_qgemm_tc_bf16(FcDevice* dev, const QMat& w, const __nv_bfloat16* a, int epi, TcArgs args);

@@ -1,7 +1,30 @@
 // The kernel body of gemm_tc.cu (included there, inside its anonymous namespace).
+//
+// Persistent: one CTA per SM walks output tiles of 256 x 128 (two 128-row accumulators that share
+// one dequantised weight slice, which halves the dequantisation work per MMA). Tensor memory holds
+// two such tiles (4 x 128 columns), so the epilogue of tile i overlaps the main loop of tile i+1.
+//
+//   warp 0        TMA producer: A slice, 256 rows x 64 bf16 = one 32 KB swizzled box per K step
+//   warp 1        TMEM owner and MMA issuer: 2 accumulators x 4 MMAs (K = 16) per K step
+//   warps 2-5     weight producers: one weight row per thread, packed blocks -> bf16 swizzled slice
+//   warps 6-13    epilogue: warp w reads TMEM lane quadrant w % 4 of accumulator (w - 6) / 4
+//
+// Barriers: full[s] (TMA bytes + 4 producer-warp arrivals) / empty[s] (MMA commit) for the
+// shared-memory ring; acc_full[b] (MMA commit) / acc_empty[b] (8 epilogue-warp arrivals) for the two
+// accumulator buffers. Every wait is bounded; the first wait that gives up raises a CTA-wide abort
+// word that every loop polls, so a protocol error ends the kernel within one bounded wait.
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+  for (uint32_t i = 0; i < tc::WAIT_LIMIT; i++) {
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_word) return false;
+  }
+  *abort_word = 1;
+  return false;
+}
 
 template <int KIND, int EPI>
-__global__ void __launch_bounds__(THREADS, 2)
+__global__ void __launch_bounds__(THREADS, 1)
     qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const QMat w, const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment: the 128B swizzle is a function of the absolute shared-memory address
@@ -10,23 +33,30 @@ __global__ void __launch_bounds__(THREADS, 2)
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_word = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n0 = blockIdx.x * TC_BN, m0 = blockIdx.y * TC_BM;
   const uint32_t k_iters = a.k / TC_BK;
+  const uint32_t tiles_n = (a.n + TC_BN - 1) / TC_BN, tiles_m = (a.m + TC_BM - 1) / TC_BM;
+  const uint32_t total_tiles = tiles_n * tiles_m;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
-      tc::mbar_init(&full[s], 1 + 4); // TMA thread (with its byte count) + one arrive per weight-producer warp
-      tc::mbar_init(&empty[s], 1);    // the MMA thread's commit
+      tc::mbar_init(&full[s], 1 + 4);
+      tc::mbar_init(&empty[s], 1);
     }
-    tc::mbar_init(acc_full, 1);
+    for (int b = 0; b < 2; b++) {
+      tc::mbar_init(&acc_full[b], 1);
+      tc::mbar_init(&acc_empty[b], 8);
+    }
+    *abort_word = 0;
     tc::fence_barrier_init();
     tc::prefetch_tmap(&tmap_a);
   }
   if (warp == 1) {
-    tc::tmem_alloc(tmem_slot, TC_BN);
+    tc::tmem_alloc(tmem_slot, TMEM_COLS);
     tc::tmem_relinquish();
   }
   tc::tc_fence_before();
@@ -37,73 +67,106 @@ __global__ void __launch_bounds__(THREADS, 2)
   if (warp == 0) {
     // ---- TMA producer ----
     if (lane == 0) {
-      for (uint32_t it = 0; it < k_iters; it++) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!tc::mbar_wait(&empty[s], ph ^ 1)) {
-          atomicExch(a.err_flag, ERR_WAIT_EMPTY);
-          break;
+      uint32_t it = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x) {
+        const uint32_t m0 = (tile / tiles_n) * TC_BM;
+        for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!wait_or_abort(&empty[s], ph ^ 1, abort_word)) {
+            atomicExch(a.err_flag, ERR_WAIT_EMPTY);
+            break;
+          }
+          tc::mbar_arrive_expect_tx(&full[s], A_BYTES);
+          tc::tma_load_2d(smem + s * STAGE_BYTES, &tmap_a, &full[s], (int32_t)(kk * TC_BK), (int32_t)m0);
         }
-        tc::mbar_arrive_expect_tx(&full[s], A_BYTES);
-        tc::tma_load_2d(smem + s * STAGE_BYTES, &tmap_a, &full[s], (int32_t)(it * TC_BK), (int32_t)m0);
       }
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::idesc_bf16_f32(TC_BM, TC_BN);
-      bool ok = true;
-      for (uint32_t it = 0; it < k_iters && ok; it++) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!tc::mbar_wait(&full[s], ph)) {
-          atomicExch(a.err_flag, ERR_WAIT_FULL);
-          ok = false;
+      constexpr uint32_t idesc = tc::idesc_bf16_f32(128, TC_BN);
+      uint32_t it = 0, tcnt = 0;
+      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
+        const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
+        if (!wait_or_abort(&acc_empty[buf], aph ^ 1, abort_word)) { // the epilogue has drained this buffer
+          atomicExch(a.err_flag, ERR_WAIT_ACC);
           break;
         }
         tc::tc_fence_after();
-        const uint32_t a_addr = base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+        const uint32_t d0 = tmem_base + buf * (2 * TC_BN), d1 = d0 + TC_BN;
+        bool ok = true;
+        for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
+          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+          if (!wait_or_abort(&full[s], ph, abort_word)) {
+            atomicExch(a.err_flag, ERR_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc::tc_fence_after();
+          const uint32_t a_addr = base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
 #pragma unroll
-        for (uint32_t ks = 0; ks < TC_BK / 16; ks++) {
-          const uint64_t da = tc::smem_desc_sw128(a_addr + ks * 32);
-          const uint64_t db = tc::smem_desc_sw128(b_addr + ks * 32);
-          tc::mma_bf16(tmem_base, da, db, idesc, (it | ks) != 0 ? 1u : 0u);
+          for (uint32_t ks = 0; ks < TC_BK / 16; ks++) {
+            const uint64_t db = tc::smem_desc_sw128(b_addr + ks * 32);
+            tc::mma_bf16(d0, tc::smem_desc_sw128(a_addr + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
+            tc::mma_bf16(d1, tc::smem_desc_sw128(a_addr + A_BYTES / 2 + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
+          }
+          tc::mma_commit(&empty[s]);
         }
-        tc::mma_commit(&empty[s]); // the slice can be refilled once these MMAs have read it
+        if (!ok) break;
+        tc::mma_commit(&acc_full[buf]);
       }
-      tc::mma_commit(acc_full);    // accumulator complete (or abandoned: the epilogue must not hang)
     }
-  } else {
-    // ---- weight producers, then epilogue ----
-    const uint32_t r = threadIdx.x - 64;        // weight row of the tile owned by this thread
-    const uint32_t row = n0 + r;
-    const bool valid = row < w.n;
+  } else if (warp < 6) {
+    // ---- weight producers ----
+    const uint32_t r = threadIdx.x - 64;
     const uint32_t sw = r & 7;
     RowRegs<KIND> cur, nxt;
-    load_row<KIND>(cur, w, valid ? row : 0, 0, valid);
-    bool ok = true;
-    for (uint32_t it = 0; it < k_iters; it++) {
-      const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-      if (it + 1 < k_iters) load_row<KIND>(nxt, w, valid ? row : 0, it + 1, valid);
-      if (!tc::mbar_wait(&empty[s], ph ^ 1)) {
-        atomicExch(a.err_flag, ERR_WAIT_EMPTY);
-        ok = false;
+    uint32_t tile = blockIdx.x;
+    if (tile < total_tiles) {
+      const uint32_t row = (tile % tiles_n) * TC_BN + r;
+      load_row<KIND>(cur, w, row < w.n ? row : 0, 0, row < w.n);
+    }
+    uint32_t it = 0;
+    for (; tile < total_tiles && !*abort_word; tile += gridDim.x) {
+      const uint32_t row = (tile % tiles_n) * TC_BN + r;
+      const bool valid = row < w.n;
+      bool ok = true;
+      for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        // prefetch the packed blocks of the next K step (or of the next tile's first step)
+        if (kk + 1 < k_iters) {
+          load_row<KIND>(nxt, w, valid ? row : 0, kk + 1, valid);
+        } else if (tile + gridDim.x < total_tiles) {
+          const uint32_t nrow = ((tile + gridDim.x) % tiles_n) * TC_BN + r;
+          load_row<KIND>(nxt, w, nrow < w.n ? nrow : 0, 0, nrow < w.n);
+        }
+        if (!wait_or_abort(&empty[s], ph ^ 1, abort_word)) {
+          atomicExch(a.err_flag, ERR_WAIT_EMPTY);
+          ok = false;
+          break;
+        }
+        store_row<KIND>(cur, base + s * STAGE_BYTES + A_BYTES + r * 128, sw);
+        tc::fence_async_smem();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&full[s]);
+        cur = nxt;
+      }
+      if (!ok) break;
+    }
+  } else {
+    // ---- epilogue ----
+    const uint32_t e = warp - 6, half = e >> 2, quad = warp & 3;
+    uint32_t tcnt = 0;
+    for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
+      const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
+      const uint32_t n0 = (tile % tiles_n) * TC_BN;
+      const uint32_t out_row = (tile / tiles_n) * TC_BM + half * 128 + quad * 32 + lane;
+      if (!wait_or_abort(&acc_full[buf], aph, abort_word)) {
+        atomicExch(a.err_flag, ERR_WAIT_ACC);
         break;
       }
-      store_row<KIND>(cur, base + s * STAGE_BYTES + A_BYTES + r * 128, sw);
-      tc::fence_async_smem();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&full[s]);
-      cur = nxt;
-    }
-    // epilogue: this warp may read TMEM lanes [32 * (warp % 4), +32)
-    const uint32_t quad = warp & 3;
-    const uint32_t out_row = m0 + quad * 32 + lane;
-    if (ok && !tc::mbar_wait(acc_full, 0)) {
-      atomicExch(a.err_flag, ERR_WAIT_ACC);
-      ok = false;
-    }
-    tc::tc_fence_after();
-    if (ok) {
-      const uint32_t taddr = tmem_base + ((quad * 32) << 16);
+      tc::tc_fence_after();
+      const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * (2 * TC_BN) + half * TC_BN;
       if (EPI == EPI_SWIGLU) {
         // columns [0, 64) of the tile are gate rows, [64, 128) the matching up rows
 #pragma unroll 1
@@ -125,7 +188,7 @@ __global__ void __launch_bounds__(THREADS, 2)
           epilogue_lse(a, st, n0 + c * 32, target, acc);
         }
         if (out_row < a.m)
-          *reinterpret_cast<float4*>(a.partial + ((size_t)blockIdx.x * a.m + out_row) * 4) =
+          *reinterpret_cast<float4*>(a.partial + ((size_t)(tile % tiles_n) * a.m + out_row) * 4) =
               make_float4(st.mx, st.se, st.tl, (float)st.first);
       } else {
 #pragma unroll 1
@@ -136,12 +199,16 @@ __global__ void __launch_bounds__(THREADS, 2)
           epilogue_chunk<EPI>(a, out_row, n0 + c * 32, acc);
         }
       }
+      // this warp's reads of the buffer are complete: hand it back to the MMA issuer
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
     }
   }
   tc::tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     __syncwarp();
-    tc::tmem_dealloc(tmem_base, TC_BN);
+    tc::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }

@@ -85,11 +85,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                            // bits 61-63: SWIZZLE_128B
   return d;
 }
-// Instruction descriptor for kind::f16 with bf16 A and B (both K-major), f32 accumulate, M x N tile.
+// Instruction descriptor for kind::f16 with a bf16 A and an fp16 B (both K-major), f32 accumulate,
+// M x N tile.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(uint32_t m, uint32_t n) {
   return (1u << 4)            // D format: f32
          | (1u << 7)          // A format: bf16
-         | (1u << 10)         // B format: bf16
+         | (0u << 10)         // B format: fp16
          | (0u << 15)         // A K-major
          | (0u << 16)         // B K-major
          | ((n >> 3) << 17)   // N / 8

@@ -1,0 +1,86 @@
+"""Small, self-terminating cases of each hot kernel, sized for an `ncu` capture (inputs above the
+126 MB L2 where DRAM figures matter, a few launches, well under a GB on the device).
+
+    python -m ferrum_gpu_b200.profile_cases gemm      # tensor-core product, Q4_0, M=16384 K=768 N=1280
+    python -m ferrum_gpu_b200.profile_cases head      # fused head + log-sum-exp, M=8192 K=768 N=32000
+    python -m ferrum_gpu_b200.profile_cases matvec    # decode matvec, Q4_0 and Q8_0, K=4096 N=32000, M=1
+    python -m ferrum_gpu_b200.profile_cases decode    # batched decode step: 16 streams at cache length ~1500
+    python -m ferrum_gpu_b200.profile_cases score     # 8 sequences x 1024 of the Llama scoring configuration
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+from . import CudaLlama, Device, Mode, QKind, linear_q, upload_quantised
+from .hostmodel import LlamaConfig, config_c3, random_llama, random_tokens
+
+
+def _weights(k, n, seed=1):
+    return (np.random.default_rng(seed).standard_normal(k * n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+
+
+def gemm(dev):
+    k, n, m = 768, 1280, 16384
+    qw = upload_quantised(dev, QKind.Q4_0, _weights(k, n), k, n)
+    x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
+    for _ in range(3):
+        linear_q(dev, x, qw, m, Mode.TENSOR_BF16)
+    qw.close()
+
+
+def matvec(dev):
+    k, n = 4096, 32000
+    x = np.random.default_rng(2).standard_normal(k, dtype=np.float32)
+    for kind in (QKind.Q4_0, QKind.Q8_0):
+        qw = upload_quantised(dev, kind, _weights(k, n), k, n)
+        for _ in range(3):
+            linear_q(dev, x, qw, 1)
+        qw.close()
+
+
+def _c3_model(dev, layers=None, max_streams=1, ctx=None):
+    cfg = config_c3()
+    if layers:
+        cfg.layers = layers
+    if ctx:
+        cfg.ctx = ctx
+    return cfg, CudaLlama(dev, random_llama(cfg, seed=1), QKind.Q4_0, max_streams=max_streams)
+
+
+def score(dev):
+    cfg, g = _c3_model(dev, layers=2)
+    ids = np.stack([random_tokens(10 + i, 1024, cfg.vocab) for i in range(8)])
+    for _ in range(2):
+        g.score_batch(ids, Mode.TENSOR_BF16)
+    g.close()
+
+
+def head(dev):
+    score(dev)
+
+
+def decode(dev):
+    cfg = LlamaConfig(vocab=32000, ctx=2048, dim=1024, heads=16, kv_heads=2, head_dim=64, layers=2, hidden=2816,
+                      rope_dim=64, rope_base=1e6, rope_type=1, eps=1e-6)
+    g = CudaLlama(dev, random_llama(cfg, seed=1, biases=True), QKind.Q8_0, max_streams=16)
+    for s in range(16):
+        g.prefill(random_tokens(s, 1500, cfg.vocab), stream=s)
+    toks = random_tokens(99, 16, cfg.vocab)
+    for _ in range(3):
+        g.feed_batch(toks)
+    g.close()
+
+
+CASES = {"gemm": gemm, "head": head, "matvec": matvec, "decode": decode, "score": score}
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    d = Device.open(0)
+    try:
+        CASES[name](d)
+        d.sync()
+        print("case", name, "done;", d.launch_count(), "launches")
+    finally:
+        d.close()

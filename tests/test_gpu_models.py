@@ -27,10 +27,15 @@ def test_feed_matches_forward_logits_at_every_position(dev, name, cfg, biases, t
     """models/llama/tests.rs:L46-L61 (f32 weights, whole context)."""
     m = helpers.ref_random_llama(cfg, 7, biases, tied)
     want = orc.OracleLlama(m).forward_logits(IDS[:cfg.ctx])
+    # The f32 oracle sums serially and is itself up to 9e-6 away from exact arithmetic on these models
+    # (float64 restatement below); a kernel that sums in another order can only be held to 1e-5 against
+    # exact arithmetic, and to the sum of both roundings against the oracle.
+    exact = helpers.np_llama_forward(m, IDS[:cfg.ctx], np.float64)
     g = CudaLlama(dev, m)
     for i, t in enumerate(IDS[:cfg.ctx]):
         got = g.feed(t)
-        assert orc.max_rel_err(got, want[i]) < FORWARD, (name, i)
+        assert orc.max_rel_err(got, exact[i]) < FORWARD, (name, i)
+        assert orc.max_rel_err(got, want[i]) < 2 * FORWARD, (name, i)
     assert g.pos() == cfg.ctx
     with pytest.raises(CudaError, match=f"context of {cfg.ctx} tokens is full") as e:
         g.feed(1)

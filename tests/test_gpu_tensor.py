@@ -78,7 +78,7 @@ def test_llama_tensor_forward_and_score_match_the_f32_oracle(dev, kind, variant)
     cfg = {"norm-gqa": llama_tc_cfg(), "neox-bias-tied": llama_tc_cfg(rope_type=_ffi.FC_ROPE_NEOX, rope_base=1e6, vocab=104),
            "mha": llama_tc_cfg(kv_heads=2, hidden=128)}[variant]
     biases, tied = variant == "neox-bias-tied", variant == "neox-bias-tied"
-    m = random_llama(cfg, seed=5, biases=biases, tied=tied, std=0.08, gain_jitter=0.1)
+    m = random_llama(cfg, seed=5, biases=biases, tied=tied, std=0.05, gain_jitter=0.1)
     ref = orc.dequantised_llama(m, int(kind), snap_embedding=False)
     if tied:
         ref.head = orc.snap_matrix(int(kind), m.head, cfg.dim, cfg.vocab)
@@ -87,8 +87,9 @@ def test_llama_tensor_forward_and_score_match_the_f32_oracle(dev, kind, variant)
     ids = random_tokens(9, 150, cfg.vocab)
     want = oracle.forward_logits(ids)
     got = g.forward_all(ids, Mode.TENSOR_BF16)
-    err, scale = np.abs(got - want).max(), np.abs(want).max()
-    assert err < LOGIT_TOL and err < 0.05 * scale, (variant, kind, err, scale)
+    # the reference's metric |g - w| / max(|w|, 1): these test weights give logits up to ~4
+    err, scale = orc.max_rel_err(got, want), np.abs(want).max()
+    assert err < LOGIT_TOL and np.abs(got - want).max() < 0.03 * scale, (variant, kind, err, scale)
     # the exact path on the same (gate/up interleaved) weights stays at 1e-5
     assert orc.max_rel_err(g.forward_all(ids[:40]), want[:40]) < 1e-5
     seqs = np.stack([random_tokens(20 + i, 131, cfg.vocab) for i in range(3)])
@@ -105,15 +106,15 @@ def test_llama_tensor_forward_and_score_match_the_f32_oracle(dev, kind, variant)
 @pytest.mark.parametrize("kind", [QKind.Q4_0, QKind.Q8_0])
 def test_gpt2_tensor_forward_and_score_match_the_f32_oracle(dev, kind):
     cfg = Gpt2Config(vocab=80, ctx=200, dim=128, heads=2, layers=2, hidden=256)
-    m = random_gpt2(cfg, seed=6, std=0.08, bias_std=0.05, gain_jitter=0.1)
+    m = random_gpt2(cfg, seed=6, std=0.05, bias_std=0.05, gain_jitter=0.1)
     ref = orc.dequantised_gpt2(m, int(kind), snap_embedding=False)
     oracle = orc.OracleGpt2(ref, threads=8)
     g = CudaGpt2(dev, m, kind)
     ids = random_tokens(10, 140, cfg.vocab)
     want = oracle.forward_logits(ids)
     got = g.forward_all(ids, Mode.TENSOR_BF16)
-    err, scale = np.abs(got - want).max(), np.abs(want).max()
-    assert err < LOGIT_TOL and err < 0.05 * scale, (kind, err, scale)
+    err, scale = orc.max_rel_err(got, want), np.abs(want).max()
+    assert err < LOGIT_TOL and np.abs(got - want).max() < 0.03 * scale, (kind, err, scale)
     lp, gr = g.score(ids, Mode.TENSOR_BF16)
     wlp, _ = oracle.score(ids)
     assert abs(float(np.mean(lp - wlp))) < NLL_TOL

@@ -447,54 +447,7 @@ def test_gpt2_cached_feed_matches_forward_logits():
 
 # ---- independent float32 numpy implementation of the Llama forward ------------------------------
 
-def _np_llama_forward(m, ids):
-    c = m.cfg
-    f = np.float32
-    d, qd, kvd, hd = c.dim, c.q_dim, c.kv_dim, c.head_dim
-    x = m.tok.reshape(c.vocab, d)[ids].astype(f)
-    n = len(ids)
-    half = c.rope_dim // 2
-    freq = (np.float64(c.rope_base) ** (-2.0 * np.arange(half) / c.rope_dim)).astype(f)
-    theta = (np.arange(n, dtype=f)[:, None] * freq[None, :]).astype(f)
-    cos, sin = np.cos(theta).astype(f), np.sin(theta).astype(f)
-
-    def rms(x, g):
-        ms = (x * x).mean(axis=1, keepdims=True, dtype=f)
-        return (x * (f(1) / np.sqrt(ms + f(c.eps))) * g).astype(f)
-
-    def rope(t, heads):
-        t = t.reshape(n, heads, hd).copy()
-        if c.rope_type == FC_ROPE_NORM:
-            a, b = t[:, :, 0:2 * half:2].copy(), t[:, :, 1:2 * half:2].copy()
-            t[:, :, 0:2 * half:2] = a * cos[:, None, :] - b * sin[:, None, :]
-            t[:, :, 1:2 * half:2] = a * sin[:, None, :] + b * cos[:, None, :]
-        else:
-            a, b = t[:, :, :half].copy(), t[:, :, half:2 * half].copy()
-            t[:, :, :half] = a * cos[:, None, :] - b * sin[:, None, :]
-            t[:, :, half:2 * half] = a * sin[:, None, :] + b * cos[:, None, :]
-        return t
-
-    for b in m.blocks:
-        h = rms(x, b.attn_norm)
-        q = h @ b.wq.reshape(d, qd)
-        k = h @ b.wk.reshape(d, kvd)
-        v = h @ b.wv.reshape(d, kvd)
-        if b.bq is not None:
-            q, k, v = q + b.bq, k + b.bk, v + b.bv
-        q, k, v = rope(q, c.heads), rope(k, c.kv_heads), v.reshape(n, c.kv_heads, hd)
-        g = c.heads // c.kv_heads
-        a = np.zeros((n, c.heads, hd), dtype=f)
-        for hh in range(c.heads):
-            s = (q[:, hh] @ k[:, hh // g].T) * f(1.0 / np.sqrt(f(hd)))
-            s = np.where(np.tril(np.ones((n, n), dtype=bool)), s, -np.inf)
-            p = np.exp(s - s.max(axis=1, keepdims=True))
-            p = p / p.sum(axis=1, keepdims=True)
-            a[:, hh] = p.astype(f) @ v[:, hh // g]
-        x = x + a.reshape(n, qd) @ b.wo.reshape(qd, d)
-        h = rms(x, b.ffn_norm)
-        gt, up = h @ b.gate.reshape(d, c.hidden), h @ b.up.reshape(d, c.hidden)
-        x = x + ((gt / (f(1) + np.exp(-gt))) * up).astype(f) @ b.down.reshape(c.hidden, d)
-    return rms(x, m.out_norm) @ m.head.reshape(d, c.vocab)
+_np_llama_forward = helpers.np_llama_forward
 
 
 @pytest.mark.parametrize("name,cfg,biases,tied", helpers.gpu_llama_variants())
