@@ -162,7 +162,7 @@ def main():
         gathered = torch.zeros(world * n_seqs, dtype=torch.float64, device=f"cuda:{local}") if world > 1 else None
 
         def step():
-            g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_BF16, 0, 0, nll_dev.data_ptr())
+            g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_F16, 0, 0, nll_dev.data_ptr())
             if world > 1:
                 dist.all_gather_into_tensor(gathered, nll_dev)
 
@@ -195,11 +195,11 @@ def main():
         nll_total = float(nll_dev.sum().item())
 
     # end to end through the public API with host buffers: ids go up, log-probs / flags / sums come back
-    g.score_batch(ids_host[:2], Mode.TENSOR_BF16)
+    g.score_batch(ids_host[:2], Mode.TENSOR_F16)
     t0 = time.perf_counter()
     e2e_steps = max(1, min(args.steps, 3))
     for _ in range(e2e_steps):
-        lp, gr, nll = g.score_batch(ids_host, Mode.TENSOR_BF16)
+        lp, gr, nll = g.score_batch(ids_host, Mode.TENSOR_F16)
     e2e_s = (time.perf_counter() - t0) / e2e_steps
     te = torch.tensor([e2e_s], dtype=torch.float64, device=f"cuda:{local}")
     if world > 1:
@@ -210,7 +210,7 @@ def main():
     if rank == 0:
         # per-kernel device time of one step (event pairs around every launch), for the roofline
         dev.profile(True)
-        g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_BF16, 0, 0, nll_dev.data_ptr())
+        g.score_dev(ids_dev.data_ptr(), n_seqs, SEQ_LEN, Mode.TENSOR_F16, 0, 0, nll_dev.data_ptr())
         prof = dev.profile_report()
         dev.profile(False)
         total_ms = sum(v["ms"] for v in prof.values()) or 1.0

@@ -1,4 +1,4 @@
-// Causal attention for the scoring path, bf16 operands with f32 softmax and accumulation, never
+// Causal attention for the scoring path, f16 operands with f32 softmax and accumulation, never
 // materialising the [t, t] probabilities. Replaces attn_gqa_scores.wgsl + attn_softmax.wgsl +
 // attn_gqa_pv.wgsl and their MHA twins (ferrum_wgpu/src/ops/llama.rs:L119-L146,
 // ops/mod.rs:L108-L127), which write and re-read a [batch * heads * t, t] buffer.
@@ -34,23 +34,23 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
 }
 __device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
 
-// address of 16-byte chunk `ch` of row `row` in a [64][64] bf16 tile with the XOR swizzle
+// address of 16-byte chunk `ch` of row `row` in a [64][64] f16 tile with the XOR swizzle
 __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t row, uint32_t ch) {
   return tile + row * 128 + ((ch ^ (row & 7)) << 4);
 }
 
-// 64 rows x 64 bf16 from `src` (row stride `stride` elements; rows clamped to max_row) into a tile
-__device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* src, uint32_t row0, uint32_t max_row,
+// 64 rows x 64 f16 from `src` (row stride `stride` elements; rows clamped to max_row) into a tile
+__device__ __forceinline__ void load_tile(uint32_t tile, const __half* src, uint32_t row0, uint32_t max_row,
                                           size_t stride) {
 #pragma unroll
   for (int i = 0; i < 4; i++) {
@@ -62,8 +62,8 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const __nv_bfloat16* sr
 }
 
 __global__ void __launch_bounds__(128)
-    attn_causal_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, uint32_t t, uint32_t heads, uint32_t kv_heads,
-                            __nv_bfloat16* __restrict__ out) {
+    attn_causal_f16_kernel(const __half* __restrict__ qkv, uint32_t t, uint32_t heads, uint32_t kv_heads,
+                            __half* __restrict__ out) {
   __shared__ __align__(1024) uint8_t sm[BQ * 128 + 2 * 2 * BKV * 128];
   const uint32_t q_tile = smem_u32(sm);
   const uint32_t kv_tiles = q_tile + BQ * 128;
@@ -73,10 +73,10 @@ __global__ void __launch_bounds__(128)
   const uint32_t qb = gridDim.x - 1 - blockIdx.x; // heaviest (latest) query blocks first
   const uint32_t h = blockIdx.y, seq = blockIdx.z;
   const uint32_t kvh = h / (heads / kv_heads);
-  const __nv_bfloat16* base = qkv + (size_t)seq * t * stride;
-  const __nv_bfloat16* qsrc = base + (size_t)h * HD;
-  const __nv_bfloat16* ksrc = base + qd + (size_t)kvh * HD;
-  const __nv_bfloat16* vsrc = ksrc + kvd;
+  const __half* base = qkv + (size_t)seq * t * stride;
+  const __half* qsrc = base + (size_t)h * HD;
+  const __half* ksrc = base + qd + (size_t)kvh * HD;
+  const __half* vsrc = ksrc + kvd;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const uint32_t q0 = qb * BQ;
   const uint32_t n_kv = qb + 1; // causal: key blocks 0..qb
@@ -168,8 +168,8 @@ __global__ void __launch_bounds__(128)
       const float p2 = exp2f(s[nb][2] * sl2 - msc[1]), p3 = exp2f(s[nb][3] * sl2 - msc[1]);
       ls[0] += p0 + p1;
       ls[1] += p2 + p3;
-      pf[nb >> 1][(nb & 1) * 2] = pack_bf16(p0, p1);     // row g
-      pf[nb >> 1][(nb & 1) * 2 + 1] = pack_bf16(p2, p3); // row g + 8
+      pf[nb >> 1][(nb & 1) * 2] = pack_f16(p0, p1);     // row g
+      pf[nb >> 1][(nb & 1) * 2 + 1] = pack_f16(p2, p3); // row g + 8
     }
     l_run[0] += ls[0];
     l_run[1] += ls[1];
@@ -205,19 +205,19 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
   for (int db = 0; db < 8; db++) {
     const uint32_t col = h * HD + db * 8 + 2 * tq;
-    if (r0 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r0) * qd + col) = pack_bf16(o[db][0] * inv0, o[db][1] * inv0);
-    if (r1 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r1) * qd + col) = pack_bf16(o[db][2] * inv1, o[db][3] * inv1);
+    if (r0 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r0) * qd + col) = pack_f16(o[db][0] * inv0, o[db][1] * inv0);
+    if (r1 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r1) * qd + col) = pack_f16(o[db][2] * inv1, o[db][3] * inv1);
   }
 }
 
 } // namespace
 
-int k_attn_causal_bf16(FcDevice* dev, const __nv_bfloat16* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads,
-                       uint32_t kv_heads, uint32_t hd, __nv_bfloat16* out) {
+int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads,
+                       uint32_t kv_heads, uint32_t hd, __half* out) {
   if (!n_seqs || !t) return FC_OK;
   if (hd != HD) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core attention is built for head_dim 64, not %u", hd);
   dim3 grid((t + BQ - 1) / BQ, heads, n_seqs);
   if (n_seqs > 65535) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u sequences exceed one attention launch", n_seqs);
-  FC_LAUNCH(dev, "attn_causal_bf16", attn_causal_bf16_kernel<<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
+  FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
   return FC_OK;
 }

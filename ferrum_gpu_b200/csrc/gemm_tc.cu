@@ -1,12 +1,12 @@
 // Scoring-side quantised product on the 5th-generation tensor cores:
-//   Y[m, n] = A[m, k] (bf16) . dequant(W)[n, k]^T (fp16), f32 accumulators in tensor memory.
+//   Y[m, n] = A[m, k] (f16) . dequant(W)[n, k]^T (fp16), f32 accumulators in tensor memory.
 // Replaces qlinear_tiled.wgsl for M >= 128 (ferrum_wgpu/src/shaders/quant/qlinear_tiled.wgsl:L93-L128).
 //
 // A persistent CTA per SM walks 256 x 128 output tiles, K in slices of 64 through a 4-deep
 // shared-memory ring (see gemm_tc_main.cuh for the warp roles and barriers):
-//   - the A slice (256 rows x 64 bf16) arrives by TMA as one 128B-swizzled box;
+//   - the A slice (256 rows x 64 f16) arrives by TMA as one 128B-swizzled box;
 //   - the weight slice (128 rows x 64) is produced in the kernel: each producer thread owns one weight
-//     row, reads its packed blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to bf16 in
+//     row, reads its packed blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to f16 in
 //     registers and stores the 128-byte row into the same swizzled K-major layout TMA produces;
 //   - one thread issues tcgen05.mma into two 128 x 128 f32 accumulators in tensor memory that share
 //     the weight slice; tensor memory holds two tiles so the epilogue of one overlaps the next;
@@ -27,16 +27,13 @@ constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 column
 
 enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
-}
-// The weight operand is fp16: the block scale is an f16 and a quant has at most 8 bits, so d * q
-// rounds once to 11 bits (2^-12 relative) instead of twice to 8; the activations stay bf16.
+// Both operands are fp16 (f32 accumulation). The block scale is an f16 and a quant has at most 8
+// bits, so d * q rounds once to 11 bits; bf16 operands (8 bits) miss the 2e-2 per-logit bound of this
+// path by a factor of 1.6 on the 12-layer scoring model, fp16 operands meet it with a 6x margin.
+// Activations saturate at the fp16 range instead of overflowing to infinity.
 __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   uint32_t r;
-  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
 __device__ __forceinline__ uint32_t f16x2_sub(uint32_t a, uint32_t b) {
@@ -200,7 +197,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, ui
       *reinterpret_cast<float4*>(dst + j) = v;
     }
   } else if (EPI == EPI_BF16) {
-    __nv_bfloat16* dst = a.out_bf16 + (size_t)row * a.ldo + col0;
+    __half* dst = a.out_f16 + (size_t)row * a.ldo + col0;
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
       if (col0 + j >= a.n) break; // n is a multiple of 8 on this path
@@ -212,7 +209,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, ui
         if (a.act == ACT_GELU) v[i] = gelu_f(v[i]);
       }
       *reinterpret_cast<uint4*>(dst + j) =
-          make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+          make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
     }
   }
 }
@@ -221,7 +218,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, ui
 __device__ __forceinline__ void epilogue_swiglu(const TcArgs& a, uint32_t row, uint32_t out_col0, const uint32_t* g,
                                                 const uint32_t* u) {
   if (row >= a.m) return;
-  __nv_bfloat16* dst = a.out_bf16 + (size_t)row * a.ldo + out_col0;
+  __half* dst = a.out_f16 + (size_t)row * a.ldo + out_col0;
 #pragma unroll
   for (int j = 0; j < 32; j += 8) {
     float v[8];
@@ -231,8 +228,56 @@ __device__ __forceinline__ void epilogue_swiglu(const TcArgs& a, uint32_t row, u
       v[i] = gv / (1.0f + __expf(-gv)) * uv;
     }
     *reinterpret_cast<uint4*>(dst + j) =
-        make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
   }
+}
+
+// One 64-column head of a fused qkv row: lo = columns [0, 32), hi = [32, 64). Adds the bias, rotates
+// the head when it is a q or k head (rope.wgsl: NORM pairs (2i, 2i+1), NEOX pairs (i, i + 32); NEOX is
+// fused only for a full rotary of 64), rounds to f16 and stores 128 bytes.
+__device__ __forceinline__ void epilogue_qkv(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* lo,
+                                             const uint32_t* hi) {
+  if (row >= a.m || col0 >= a.n) return;
+  float v[64];
+#pragma unroll
+  for (int i = 0; i < 32; i++) {
+    v[i] = __uint_as_float(lo[i]);
+    v[32 + i] = __uint_as_float(hi[i]);
+  }
+  if (a.bias) {
+#pragma unroll
+    for (int i = 0; i < 64; i += 4) {
+      const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + i);
+      v[i] += b.x, v[i + 1] += b.y, v[i + 2] += b.z, v[i + 3] += b.w;
+    }
+  }
+  if (a.rope_cos && col0 < a.rope_cols) {
+    const uint32_t half = a.rope_dim / 2;
+    const float* cs = a.rope_cos + (size_t)a.positions[row] * half;
+    const float* sn = a.rope_sin + (size_t)a.positions[row] * half;
+    if (a.rope_type == FC_ROPE_NORM) {
+#pragma unroll
+      for (int p = 0; p < 32; p++) {
+        if ((uint32_t)p < half) {
+          const float c = cs[p], s = sn[p], x = v[2 * p], y = v[2 * p + 1];
+          v[2 * p] = x * c - y * s;
+          v[2 * p + 1] = x * s + y * c;
+        }
+      }
+    } else { // NEOX with rope_dim == 64 (checked on the host)
+#pragma unroll
+      for (int p = 0; p < 32; p++) {
+        const float c = cs[p], s = sn[p], x = v[p], y = v[p + 32];
+        v[p] = x * c - y * s;
+        v[p + 32] = x * s + y * c;
+      }
+    }
+  }
+  __half* dst = a.out_f16 + (size_t)row * a.ldo + col0;
+#pragma unroll
+  for (int j = 0; j < 64; j += 8)
+    *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
+                                                    pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
 }
 
 struct LseState {
@@ -312,20 +357,24 @@ int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs
     case EPI_RESID: return launch_tc<KIND, EPI_RESID>(dev, tmap, w, a, grid);
     case EPI_SWIGLU: return launch_tc<KIND, EPI_SWIGLU>(dev, tmap, w, a, grid);
     case EPI_LSE: return launch_tc<KIND, EPI_LSE>(dev, tmap, w, a, grid);
+    case EPI_QKV: return launch_tc<KIND, EPI_QKV>(dev, tmap, w, a, grid);
   }
   return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
 }
 
 } // namespace
 
-int k_qgemm_tc_bf16(FcDevice* dev, const QMat& w, const __nv_bfloat16* a_dev, int epi, TcArgs args) {
+int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, TcArgs args) {
   if (args.m == 0) return FC_OK;
   args.n = w.n;
   args.k = w.k;
   args.err_flag = dev->d_flag;
   if (w.k % TC_BK) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product needs k %% 64 == 0, not %u", w.k);
+  if (epi == EPI_QKV && (w.n % 64 || args.ldo % 8 || args.rope_cols % 64 ||
+                         (args.rope_cos && args.rope_type != FC_ROPE_NORM && args.rope_dim != 64) || args.rope_dim > 64))
+    return fc_fail(dev, FC_ERR_UNSUPPORTED, "the fused qkv epilogue needs heads of 64 columns and, for NEOX, rope_dim 64");
   if ((epi == EPI_BF16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
-    return fc_fail(dev, FC_ERR_UNSUPPORTED, "a bf16 result needs n %% 8 == 0, not %u", w.n);
+    return fc_fail(dev, FC_ERR_UNSUPPORTED, "a f16 result needs n %% 8 == 0, not %u", w.n);
   if (epi == EPI_SWIGLU && w.n % 128) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the SwiGLU epilogue needs n %% 128 == 0");
   if ((reinterpret_cast<uintptr_t>(a_dev) & 15) != 0) return fc_fail(dev, FC_ERR_ARG, "the A operand must be 16-byte aligned");
   EncodeTiledFn enc = encode_fn();
@@ -335,7 +384,7 @@ int k_qgemm_tc_bf16(FcDevice* dev, const QMat& w, const __nv_bfloat16* a_dev, in
   const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
   const cuuint32_t box[2] = {TC_BK, TC_BM};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)a_dev, dims, strides, box, estr,
+  CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a_dev, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);

@@ -4,9 +4,9 @@
 // one dequantised weight slice, which halves the dequantisation work per MMA). Tensor memory holds
 // two such tiles (4 x 128 columns), so the epilogue of tile i overlaps the main loop of tile i+1.
 //
-//   warp 0        TMA producer: A slice, 256 rows x 64 bf16 = one 32 KB swizzled box per K step
+//   warp 0        TMA producer: A slice, 256 rows x 64 f16 = one 32 KB swizzled box per K step
 //   warp 1        TMEM owner and MMA issuer: 2 accumulators x 4 MMAs (K = 16) per K step
-//   warps 2-5     weight producers: one weight row per thread, packed blocks -> bf16 swizzled slice
+//   warps 2-5     weight producers: one weight row per thread, packed blocks -> f16 swizzled slice
 //   warps 6-13    epilogue: warp w reads TMEM lane quadrant w % 4 of accumulator (w - 6) / 4
 //
 // Barriers: full[s] (TMA bytes + 4 producer-warp arrivals) / empty[s] (MMA commit) for the
@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
-      constexpr uint32_t idesc = tc::idesc_bf16_f32(128, TC_BN);
+      constexpr uint32_t idesc = tc::idesc_f16_f32(128, TC_BN);
       uint32_t it = 0, tcnt = 0;
       for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
         const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
@@ -107,8 +107,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 #pragma unroll
           for (uint32_t ks = 0; ks < TC_BK / 16; ks++) {
             const uint64_t db = tc::smem_desc_sw128(b_addr + ks * 32);
-            tc::mma_bf16(d0, tc::smem_desc_sw128(a_addr + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
-            tc::mma_bf16(d1, tc::smem_desc_sw128(a_addr + A_BYTES / 2 + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
+            tc::mma_f16(d0, tc::smem_desc_sw128(a_addr + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
+            tc::mma_f16(d1, tc::smem_desc_sw128(a_addr + A_BYTES / 2 + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
           }
           tc::mma_commit(&empty[s]);
         }
@@ -176,6 +176,16 @@ __global__ void __launch_bounds__(THREADS, 1)
           tc::tmem_ld_32x32(taddr + 64 + c * 32, u);
           tc::tmem_ld_wait();
           epilogue_swiglu(a, out_row, (n0 / 2) + c * 32, g, u);
+        }
+      } else if (EPI == EPI_QKV) {
+        // two heads of 64 columns per tile
+#pragma unroll 1
+        for (uint32_t c = 0; c < 2; c++) {
+          uint32_t lo[32], hi[32];
+          tc::tmem_ld_32x32(taddr + c * 64, lo);
+          tc::tmem_ld_32x32(taddr + c * 64 + 32, hi);
+          tc::tmem_ld_wait();
+          epilogue_qkv(a, out_row, n0 + c * 64, lo, hi);
         }
       } else if (EPI == EPI_LSE) {
         LseState st;

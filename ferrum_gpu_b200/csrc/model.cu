@@ -565,7 +565,7 @@ FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, floa
   if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "forward_all needs the whole head on this device");
   FC_TRY(check_ids(m, ids, n));
   const size_t extra = (size_t)n * 8 + 512 + (size_t)n * m->vocab * 4 + 256 + (size_t)n * m->dim * 2 + 256 +
-                       (mode == FC_TENSOR_BF16 ? model_tc_trunk_bytes(m, n) : 0);
+                       (mode == FC_TENSOR_F16 ? model_tc_trunk_bytes(m, n) : 0);
   PassBufs b;
   FC_TRY(carve_pass(m, n, &b, extra));
   int32_t* d_ids = (int32_t*)arena_take(m, (size_t)n * 4);
@@ -576,8 +576,8 @@ FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, floa
   if (mode == FC_EXACT_F32) {
     FC_TRY(run_stack_f32(m, b, d_ids, d_pos, nullptr, n, ATTN_STATELESS, 1, n, 0, 0));
     FC_TRY(k_qlinear_f32(dev, m->head_view, b.h, n, logits, Epilogue()));
-  } else if (mode == FC_TENSOR_BF16) {
-    __nv_bfloat16* hid = (__nv_bfloat16*)arena_take(m, (size_t)n * m->dim * 2);
+  } else if (mode == FC_TENSOR_F16) {
+    __half* hid = (__half*)arena_take(m, (size_t)n * m->dim * 2);
     FC_TRY(model_trunk_tc(m, d_ids, d_pos, 1, n, hid));
     FC_TRY(model_logits_tc(m, hid, n, logits));
     FC_TRY(tc_check_errors(dev));
@@ -627,7 +627,7 @@ FC_API int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint3
   if (cudaMemcpyAsync(d_ids, ids, (size_t)n_seqs * seq_len * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "upload of ids failed");
   if (rc == FC_OK) rc = fc_model_score_dev(m, d_ids, n_seqs, seq_len, mode, d_lp, d_gr, d_nll);
-  if (rc == FC_OK && mode == FC_TENSOR_BF16) rc = tc_check_errors(dev);
+  if (rc == FC_OK && mode == FC_TENSOR_F16) rc = tc_check_errors(dev);
   if (rc == FC_OK) {
     if (logprob_out) cudaMemcpyAsync(logprob_out, d_lp, rows * 4, cudaMemcpyDeviceToHost, dev->stream);
     if (greedy_out) cudaMemcpyAsync(greedy_out, d_gr, rows, cudaMemcpyDeviceToHost, dev->stream);

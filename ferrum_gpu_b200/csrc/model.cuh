@@ -70,10 +70,10 @@ int model_trunk_f32(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, 
 
 // bf16 tensor-core passes (model_tc.cu)
 int model_trunk_tc(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, uint32_t n_seqs, uint32_t t,
-                   __nv_bfloat16* hidden_out);
-int model_head_partial_tc(FcModel* m, const __nv_bfloat16* hidden, const int32_t* targets_dev, uint32_t rows,
+                   __half* hidden_out);
+int model_head_partial_tc(FcModel* m, const __half* hidden, const int32_t* targets_dev, uint32_t rows,
                           float* partial);
-int model_logits_tc(FcModel* m, const __nv_bfloat16* hidden, uint32_t rows, float* logits);
+int model_logits_tc(FcModel* m, const __half* hidden, uint32_t rows, float* logits);
 void model_tc_free(FcModel* m);
 size_t model_tc_trunk_bytes(const FcModel* m, size_t rows); // workspace model_trunk_tc takes from the arena
 size_t model_tc_head_bytes(const FcModel* m, size_t rows);  // workspace model_head_partial_tc takes

@@ -1,7 +1,7 @@
-// bf16 tensor-core passes of the resident model (scoring / forward_all with FC_TENSOR_BF16).
+// f16 tensor-core passes of the resident model (scoring / forward_all with FC_TENSOR_F16).
 //
-// Per layer: norm (f32 residual stream -> bf16) -> fused qkv product (bf16 out, bias) -> RoPE on the
-// bf16 rows -> causal flash attention -> output product with the residual add in its epilogue ->
+// Per layer: norm (f32 residual stream -> f16) -> fused qkv product (f16 out, bias) -> RoPE on the
+// f16 rows -> causal flash attention -> output product with the residual add in its epilogue ->
 // norm -> feed-forward product with SwiGLU (gate/up rows interleaved at upload) or bias+GELU in its
 // epilogue -> down product with the residual add. The residual stream stays f32. The head never
 // writes logits for scoring: its epilogue reduces each 128-column tile to (max, sum exp, target
@@ -75,67 +75,74 @@ int k_qgemm_tc(FcDevice* dev, FcQWeight* w, const float* x_dev, uint32_t m, floa
     FC_CUDA(dev, cudaMalloc(&w->tc_cache, need));
     w->tc_cache_bytes = need;
   }
-  __nv_bfloat16* a = (__nv_bfloat16*)w->tc_cache;
-  FC_TRY(k_f32_to_bf16(dev, x_dev, (size_t)m * w->m.k, a));
+  __half* a = (__half*)w->tc_cache;
+  FC_TRY(k_f32_to_f16(dev, x_dev, (size_t)m * w->m.k, a));
   TcArgs t;
   t.m = m;
   t.out_f32 = y_dev;
   t.ldo = w->m.n;
-  return k_qgemm_tc_bf16(dev, w->m, a, EPI_F32, t);
+  return k_qgemm_tc_f16(dev, w->m, a, EPI_F32, t);
 }
 
 int model_trunk_tc(FcModel* m, const int32_t* ids, const int32_t* positions, uint32_t n_seqs, uint32_t t,
-                   __nv_bfloat16* hidden_out) {
+                   __half* hidden_out) {
   FcDevice* dev = m->dev;
   FC_TRY(check_tc_shapes(m));
   const uint32_t rows = n_seqs * t, d = m->dim;
   float* x = (float*)arena_take(m, (size_t)rows * d * 4);
-  __nv_bfloat16* h = (__nv_bfloat16*)arena_take(m, (size_t)rows * d * 2);
-  __nv_bfloat16* qkv = (__nv_bfloat16*)arena_take(m, (size_t)rows * m->qkv_w() * 2);
-  __nv_bfloat16* attn = (__nv_bfloat16*)arena_take(m, (size_t)rows * m->qd() * 2);
-  __nv_bfloat16* act = (__nv_bfloat16*)arena_take(m, (size_t)rows * m->hidden * 2);
+  __half* h = (__half*)arena_take(m, (size_t)rows * d * 2);
+  __half* qkv = (__half*)arena_take(m, (size_t)rows * m->qkv_w() * 2);
+  __half* attn = (__half*)arena_take(m, (size_t)rows * m->qd() * 2);
+  __half* act = (__half*)arena_take(m, (size_t)rows * m->hidden * 2);
   const bool ln = m->arch == ARCH_GPT2;
   FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, x));
   for (auto& l : m->layers) {
-    FC_TRY(k_norm_bf16(dev, ln, x, l.norm1_g, l.norm1_b, rows, d, m->eps, h));
+    FC_TRY(k_norm_f16(dev, ln, x, l.norm1_g, l.norm1_b, rows, d, m->eps, h));
     TcArgs a_qkv;
-    a_qkv.m = rows, a_qkv.bias = l.qkv.bias, a_qkv.out_bf16 = qkv, a_qkv.ldo = m->qkv_w();
-    FC_TRY(k_qgemm_tc_bf16(dev, l.qkv.w->m, h, EPI_BF16, a_qkv));
-    FC_TRY(k_rope_bf16(dev, qkv, rows, m->heads, m->kv_heads, m->hd, m->rope.cos, m->rope.sin, m->rope.rope_dim,
-                       m->rope.type, positions));
-    FC_TRY(k_attn_causal_bf16(dev, qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, attn));
+    a_qkv.m = rows, a_qkv.bias = l.qkv.bias, a_qkv.out_f16 = qkv, a_qkv.ldo = m->qkv_w();
+    const bool fuse_rope = !m->rope.cos || m->rope.type == FC_ROPE_NORM || m->rope.rope_dim == 64;
+    if (fuse_rope) { // RoPE on the f32 accumulators, in the product's epilogue
+      a_qkv.rope_cos = m->rope.cos, a_qkv.rope_sin = m->rope.sin, a_qkv.positions = positions;
+      a_qkv.rope_dim = m->rope.rope_dim, a_qkv.rope_type = m->rope.type, a_qkv.rope_cols = m->qd() + m->kvd();
+      FC_TRY(k_qgemm_tc_f16(dev, l.qkv.w->m, h, EPI_QKV, a_qkv));
+    } else {         // NEOX with a partial rotary: pairs straddle the epilogue's register chunks
+      FC_TRY(k_qgemm_tc_f16(dev, l.qkv.w->m, h, EPI_BF16, a_qkv));
+      FC_TRY(k_rope_f16(dev, qkv, rows, m->heads, m->kv_heads, m->hd, m->rope.cos, m->rope.sin, m->rope.rope_dim,
+                         m->rope.type, positions));
+    }
+    FC_TRY(k_attn_causal_f16(dev, qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, attn));
     TcArgs a_wo;
     a_wo.m = rows, a_wo.bias = l.wo.bias, a_wo.out_f32 = x, a_wo.ldo = d;
-    FC_TRY(k_qgemm_tc_bf16(dev, l.wo.w->m, attn, EPI_RESID, a_wo));
-    FC_TRY(k_norm_bf16(dev, ln, x, l.norm2_g, l.norm2_b, rows, d, m->eps, h));
+    FC_TRY(k_qgemm_tc_f16(dev, l.wo.w->m, attn, EPI_RESID, a_wo));
+    FC_TRY(k_norm_f16(dev, ln, x, l.norm2_g, l.norm2_b, rows, d, m->eps, h));
     TcArgs a_ff1;
-    a_ff1.m = rows, a_ff1.bias = l.ff1.bias, a_ff1.out_bf16 = act, a_ff1.ldo = m->hidden;
+    a_ff1.m = rows, a_ff1.bias = l.ff1.bias, a_ff1.out_f16 = act, a_ff1.ldo = m->hidden;
     if (m->arch == ARCH_LLAMA) {
-      FC_TRY(k_qgemm_tc_bf16(dev, l.ff1.w->m, h, EPI_SWIGLU, a_ff1));
+      FC_TRY(k_qgemm_tc_f16(dev, l.ff1.w->m, h, EPI_SWIGLU, a_ff1));
     } else {
       a_ff1.act = ACT_GELU;
-      FC_TRY(k_qgemm_tc_bf16(dev, l.ff1.w->m, h, EPI_BF16, a_ff1));
+      FC_TRY(k_qgemm_tc_f16(dev, l.ff1.w->m, h, EPI_BF16, a_ff1));
     }
     TcArgs a_ff2;
     a_ff2.m = rows, a_ff2.bias = l.ff2.bias, a_ff2.out_f32 = x, a_ff2.ldo = d;
-    FC_TRY(k_qgemm_tc_bf16(dev, l.ff2.w->m, act, EPI_RESID, a_ff2));
+    FC_TRY(k_qgemm_tc_f16(dev, l.ff2.w->m, act, EPI_RESID, a_ff2));
   }
-  return k_norm_bf16(dev, ln, x, m->normf_g, m->normf_b, rows, d, m->eps, hidden_out);
+  return k_norm_f16(dev, ln, x, m->normf_g, m->normf_b, rows, d, m->eps, hidden_out);
 }
 
-int model_head_partial_tc(FcModel* m, const __nv_bfloat16* hidden, const int32_t* targets, uint32_t rows, float* partial) {
+int model_head_partial_tc(FcModel* m, const __half* hidden, const int32_t* targets, uint32_t rows, float* partial) {
   const uint32_t tiles = (m->v1 - m->v0 + TC_BN - 1) / TC_BN;
   float* tile_partials = (float*)arena_take(m, (size_t)rows * tiles * 16);
   TcArgs a;
   a.m = rows, a.targets = targets, a.v0 = m->v0, a.partial = tile_partials;
-  FC_TRY(k_qgemm_tc_bf16(m->dev, m->head_view, hidden, EPI_LSE, a));
+  FC_TRY(k_qgemm_tc_f16(m->dev, m->head_view, hidden, EPI_LSE, a));
   return k_partial_merge(m->dev, tile_partials, tiles, rows, partial);
 }
 
-int model_logits_tc(FcModel* m, const __nv_bfloat16* hidden, uint32_t rows, float* logits) {
+int model_logits_tc(FcModel* m, const __half* hidden, uint32_t rows, float* logits) {
   TcArgs a;
   a.m = rows, a.out_f32 = logits, a.ldo = m->v1 - m->v0;
-  return k_qgemm_tc_bf16(m->dev, m->head_view, hidden, EPI_F32, a);
+  return k_qgemm_tc_f16(m->dev, m->head_view, hidden, EPI_F32, a);
 }
 
 void model_tc_free(FcModel*) {}

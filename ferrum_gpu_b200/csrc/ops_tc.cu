@@ -1,5 +1,5 @@
-// Companions of the tensor-core scoring path: f32 -> bf16 conversion, RMSNorm / LayerNorm with a
-// bf16 result (the next product's A operand), RoPE on the bf16 fused qkv rows, the merge of
+// Companions of the tensor-core scoring path: f32 -> f16 conversion, RMSNorm / LayerNorm with a
+// f16 result (the next product's A operand), RoPE on the f16 fused qkv rows, the merge of
 // per-tile log-sum-exp partials, and the row permutation that interleaves gate and up rows.
 #include "gemm_tc.cuh"
 
@@ -19,21 +19,79 @@ __device__ float block_sum(float v, float* red) {
   return warp_sum(lane < nw ? red[lane] : 0.0f);
 }
 
-__global__ void f32_to_bf16_kernel(const float* __restrict__ x, size_t n, __nv_bfloat16* __restrict__ y) {
+__global__ void f32_to_f16_kernel(const float* __restrict__ x, size_t n, __half* __restrict__ y) {
   const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i + 3 < n) {
     const float4 v = *reinterpret_cast<const float4*>(x + i);
-    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
     *reinterpret_cast<uint2*>(y + i) = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
   } else {
-    for (size_t j = i; j < n; j++) y[j] = __float2bfloat16_rn(x[j]);
+    for (size_t j = i; j < n; j++) y[j] = __float2half_rn(x[j]);
   }
 }
 
-// One CTA per row; same arithmetic as the f32 norms, result rounded to bf16.
+// One warp per row, the row held in registers (NV float4 per lane, d <= 128 * NV): the row is read
+// from HBM exactly once and written once as f16. Same arithmetic as the f32 norms.
+template <bool LAYERNORM, int NV>
+__global__ void __launch_bounds__(128)
+    norm_f16_warp_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+                          uint32_t rows, uint32_t d, float eps, __half* __restrict__ y) {
+  const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const uint32_t d4 = d / 4;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)row * d);
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const uint32_t c = lane + 32 * i;
+    v[i] = c < d4 ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float mean = 0.0f, inv;
+  if (LAYERNORM) {
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    mean = warp_sum(s) / (float)d;
+    float vs = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) {
+      if ((uint32_t)(lane + 32 * i) < d4) {
+        const float a0 = v[i].x - mean, a1 = v[i].y - mean, a2 = v[i].z - mean, a3 = v[i].w - mean;
+        vs += a0 * a0 + a1 * a1 + a2 * a2 + a3 * a3;
+      }
+    }
+    inv = 1.0f / sqrtf(warp_sum(vs) / (float)d + 1e-5f);
+  } else {
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; i++) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    inv = 1.0f / sqrtf(warp_sum(ss) / (float)d + eps);
+  }
+  uint2* dst = reinterpret_cast<uint2*>(y + (size_t)row * d);
+#pragma unroll
+  for (int i = 0; i < NV; i++) {
+    const uint32_t c = lane + 32 * i;
+    if (c < d4) {
+      const float4 gg = reinterpret_cast<const float4*>(g)[c];
+      float o0, o1, o2, o3;
+      if (LAYERNORM) {
+        const float4 bb = reinterpret_cast<const float4*>(b)[c];
+        o0 = (v[i].x - mean) * inv * gg.x + bb.x, o1 = (v[i].y - mean) * inv * gg.y + bb.y;
+        o2 = (v[i].z - mean) * inv * gg.z + bb.z, o3 = (v[i].w - mean) * inv * gg.w + bb.w;
+      } else {
+        o0 = v[i].x * inv * gg.x, o1 = v[i].y * inv * gg.y, o2 = v[i].z * inv * gg.z, o3 = v[i].w * inv * gg.w;
+      }
+      __half2 p0 = __floats2half2_rn(o0, o1), p1 = __floats2half2_rn(o2, o3);
+      dst[c] = make_uint2(*reinterpret_cast<uint32_t*>(&p0), *reinterpret_cast<uint32_t*>(&p1));
+    }
+  }
+}
+
+// Fallback for wide or oddly sized rows: one CTA per row, the row re-read from cache.
 template <bool LAYERNORM>
-__global__ void norm_bf16_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
-                                 uint32_t d, float eps, __nv_bfloat16* __restrict__ y) {
+__global__ void norm_f16_kernel(const float* __restrict__ x, const float* __restrict__ g, const float* __restrict__ b,
+                                 uint32_t d, float eps, __half* __restrict__ y) {
   __shared__ float red[32];
   const float* row = x + (size_t)blockIdx.x * d;
   float mean = 0.0f, inv;
@@ -61,29 +119,29 @@ __global__ void norm_bf16_kernel(const float* __restrict__ x, const float* __res
       v0 = row[i] * inv * g[i];
       v1 = row[i + 1] * inv * g[i + 1];
     }
-    *reinterpret_cast<__nv_bfloat162*>(y + (size_t)blockIdx.x * d + i) = __floats2bfloat162_rn(v0, v1);
+    *reinterpret_cast<__half2*>(y + (size_t)blockIdx.x * d + i) = __floats2half2_rn(v0, v1);
   }
 }
 
-// rope.wgsl on bf16 rows: rotate q and k heads in place, angles from the host-built f32 tables.
-__global__ void rope_bf16_kernel(__nv_bfloat16* __restrict__ qkv, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+// rope.wgsl on f16 rows: rotate q and k heads in place, angles from the host-built f32 tables.
+__global__ void rope_f16_kernel(__half* __restrict__ qkv, uint32_t heads, uint32_t kv_heads, uint32_t hd,
                                  const float* __restrict__ cos, const float* __restrict__ sin, uint32_t rope_dim,
                                  uint32_t type, const int32_t* __restrict__ positions) {
   const uint32_t r = blockIdx.x;
   const uint32_t stride = (heads + 2 * kv_heads) * hd;
-  __nv_bfloat16* row = qkv + (size_t)r * stride;
+  __half* row = qkv + (size_t)r * stride;
   const uint32_t half = rope_dim / 2;
   const float* cs = cos + (size_t)positions[r] * half;
   const float* sn = sin + (size_t)positions[r] * half;
   const uint32_t total = (heads + kv_heads) * half;
   for (uint32_t i = threadIdx.x; i < total; i += blockDim.x) {
     const uint32_t h = i / half, p = i % half;
-    __nv_bfloat16* base = row + (size_t)h * hd;
+    __half* base = row + (size_t)h * hd;
     const uint32_t ia = type == FC_ROPE_NORM ? 2 * p : p;
     const uint32_t ib = type == FC_ROPE_NORM ? 2 * p + 1 : p + half;
-    const float c = cs[p], s = sn[p], a = __bfloat162float(base[ia]), b = __bfloat162float(base[ib]);
-    base[ia] = __float2bfloat16_rn(a * c - b * s);
-    base[ib] = __float2bfloat16_rn(a * s + b * c);
+    const float c = cs[p], s = sn[p], a = __half2float(base[ia]), b = __half2float(base[ib]);
+    base[ia] = __float2half_rn(a * c - b * s);
+    base[ib] = __float2half_rn(a * s + b * c);
   }
 }
 
@@ -125,29 +183,44 @@ __global__ void permute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __
 
 } // namespace
 
-int k_f32_to_bf16(FcDevice* dev, const float* x, size_t n, __nv_bfloat16* y) {
+int k_f32_to_f16(FcDevice* dev, const float* x, size_t n, __half* y) {
   if (!n) return FC_OK;
   const size_t threads = (n + 3) / 4;
-  FC_LAUNCH(dev, "f32_to_bf16", f32_to_bf16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(x, n, y));
+  FC_LAUNCH(dev, "f32_to_f16", f32_to_f16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, dev->stream>>>(x, n, y));
   return FC_OK;
 }
 
-int k_norm_bf16(FcDevice* dev, bool layernorm, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d,
-                float eps, __nv_bfloat16* y) {
+int k_norm_f16(FcDevice* dev, bool layernorm, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d,
+                float eps, __half* y) {
   if (!rows) return FC_OK;
-  if (d % 2) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the bf16 norm needs an even width, not %u", d);
+  if (d % 2) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the f16 norm needs an even width, not %u", d);
+  if (d % 4 == 0 && d <= 1024) {
+    const unsigned grid = (rows + 3) / 4;
+    if (d <= 512) {
+      if (layernorm)
+        FC_LAUNCH(dev, "layernorm_f16", norm_f16_warp_kernel<true, 4><<<grid, 128, 0, dev->stream>>>(x, g, b, rows, d, eps, y));
+      else
+        FC_LAUNCH(dev, "rmsnorm_f16", norm_f16_warp_kernel<false, 4><<<grid, 128, 0, dev->stream>>>(x, g, b, rows, d, eps, y));
+    } else {
+      if (layernorm)
+        FC_LAUNCH(dev, "layernorm_f16", norm_f16_warp_kernel<true, 8><<<grid, 128, 0, dev->stream>>>(x, g, b, rows, d, eps, y));
+      else
+        FC_LAUNCH(dev, "rmsnorm_f16", norm_f16_warp_kernel<false, 8><<<grid, 128, 0, dev->stream>>>(x, g, b, rows, d, eps, y));
+    }
+    return FC_OK;
+  }
   if (layernorm)
-    FC_LAUNCH(dev, "layernorm_bf16", norm_bf16_kernel<true><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
+    FC_LAUNCH(dev, "layernorm_f16", norm_f16_kernel<true><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
   else
-    FC_LAUNCH(dev, "rmsnorm_bf16", norm_bf16_kernel<false><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
+    FC_LAUNCH(dev, "rmsnorm_f16", norm_f16_kernel<false><<<rows, 128, 0, dev->stream>>>(x, g, b, d, eps, y));
   return FC_OK;
 }
 
-int k_rope_bf16(FcDevice* dev, __nv_bfloat16* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+int k_rope_f16(FcDevice* dev, __half* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
                 const float* cos, const float* sin, uint32_t rope_dim, uint32_t type, const int32_t* positions) {
   if (!rows || !cos) return FC_OK;
-  FC_LAUNCH(dev, "rope_bf16",
-            rope_bf16_kernel<<<rows, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, cos, sin, rope_dim, type, positions));
+  FC_LAUNCH(dev, "rope_f16",
+            rope_f16_kernel<<<rows, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, cos, sin, rope_dim, type, positions));
   return FC_OK;
 }
 

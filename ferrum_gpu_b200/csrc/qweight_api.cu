@@ -126,7 +126,7 @@ FC_API int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y
   FcDevice* dev = w->dev;
   cudaSetDevice(dev->ordinal);
   if (mode == FC_EXACT_F32) return k_qlinear_f32(dev, w->m, x_dev, m, y_dev, Epilogue());
-  if (mode == FC_TENSOR_BF16) return k_qgemm_tc(dev, w, x_dev, m, y_dev);
+  if (mode == FC_TENSOR_F16) return k_qgemm_tc(dev, w, x_dev, m, y_dev);
   return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
 }
 
@@ -147,7 +147,7 @@ FC_API int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mo
   if (cudaMemcpyAsync(dx, x, (size_t)m * w->m.k * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "upload of x failed");
   if (rc == FC_OK) rc = fc_qmatmul_dev(w, dx, m, dy, mode);
-  if (rc == FC_OK && mode == FC_TENSOR_BF16) rc = tc_check_errors(dev);
+  if (rc == FC_OK && mode == FC_TENSOR_F16) rc = tc_check_errors(dev);
   if (rc == FC_OK && cudaMemcpyAsync(y, dy, (size_t)m * w->m.n * 4, cudaMemcpyDeviceToHost, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "read-back of y failed");
   if (rc == FC_OK && cudaStreamSynchronize(dev->stream) != cudaSuccess) {

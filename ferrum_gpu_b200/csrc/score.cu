@@ -48,7 +48,7 @@ FC_API int fc_model_score_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seq
   cudaSetDevice(dev->ordinal);
   if (seq_len < 2) return fc_fail(dev, FC_ERR_SHAPE, "scoring needs at least 2 tokens");
   if (seq_len - 1 > m->ctx) return fc_fail(dev, FC_ERR_SHAPE, "sequence length %u must be in 1..=%u", seq_len - 1, m->ctx);
-  if (mode != FC_EXACT_F32 && mode != FC_TENSOR_BF16) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
+  if (mode != FC_EXACT_F32 && mode != FC_TENSOR_F16) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   if (m->n_shards != 1)
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "this model holds one vocabulary shard: use the trunk / head_partial / combine calls");
   if (n_seqs == 0) return FC_OK;
@@ -81,8 +81,8 @@ FC_API int fc_model_score_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seq
       FC_TRY(model_trunk_f32(m, in_ids, positions, ns, t, (float*)hidden));
       FC_TRY(head_partial_f32(m, (const float*)hidden, targets, rows, logits_ws, partial));
     } else {
-      FC_TRY(model_trunk_tc(m, in_ids, positions, ns, t, (__nv_bfloat16*)hidden));
-      FC_TRY(model_head_partial_tc(m, (const __nv_bfloat16*)hidden, targets, rows, partial));
+      FC_TRY(model_trunk_tc(m, in_ids, positions, ns, t, (__half*)hidden));
+      FC_TRY(model_head_partial_tc(m, (const __half*)hidden, targets, rows, partial));
     }
     FC_TRY(k_score_combine(dev, partial, 1, rows, targets, lp, gr));
   }
@@ -117,7 +117,7 @@ FC_API int fc_model_trunk_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seq
   if (seq_len == 0 || seq_len > m->ctx) return fc_fail(dev, FC_ERR_SHAPE, "sequence length %u must be in 1..=%u", seq_len, m->ctx);
   if (n_seqs == 0) return FC_OK;
   const size_t rows = (size_t)n_seqs * seq_len;
-  FC_TRY(arena_reserve(m, chunk_bytes(m, rows, FC_TENSOR_BF16)));
+  FC_TRY(arena_reserve(m, chunk_bytes(m, rows, FC_TENSOR_F16)));
   int32_t* positions = (int32_t*)arena_take(m, rows * 4);
   // positions 0..seq_len-1 per sequence (score_prep with a virtual extra token would drop the
   // last row; here every row is kept)
@@ -129,7 +129,7 @@ FC_API int fc_model_trunk_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seq
     FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
   }
   if (mode == FC_EXACT_F32) return model_trunk_f32(m, ids_dev, positions, n_seqs, seq_len, (float*)hidden_dev);
-  if (mode == FC_TENSOR_BF16) return model_trunk_tc(m, ids_dev, positions, n_seqs, seq_len, (__nv_bfloat16*)hidden_dev);
+  if (mode == FC_TENSOR_F16) return model_trunk_tc(m, ids_dev, positions, n_seqs, seq_len, (__half*)hidden_dev);
   return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
 }
 
@@ -139,9 +139,9 @@ FC_API int fc_model_head_partial_dev(FcModel* m, const void* hidden_dev, const i
   FcDevice* dev = m->dev;
   cudaSetDevice(dev->ordinal);
   if (rows == 0) return FC_OK;
-  if (mode == FC_TENSOR_BF16) {
+  if (mode == FC_TENSOR_F16) {
     FC_TRY(arena_reserve(m, model_tc_head_bytes(m, rows)));
-    return model_head_partial_tc(m, (const __nv_bfloat16*)hidden_dev, targets_dev, rows, partial_dev);
+    return model_head_partial_tc(m, (const __half*)hidden_dev, targets_dev, rows, partial_dev);
   }
   if (mode != FC_EXACT_F32) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   // chunk the rows so the materialised logits stay under 2 GiB

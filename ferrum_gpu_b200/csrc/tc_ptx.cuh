@@ -85,11 +85,11 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                            // bits 61-63: SWIZZLE_128B
   return d;
 }
-// Instruction descriptor for kind::f16 with a bf16 A and an fp16 B (both K-major), f32 accumulate,
+// Instruction descriptor for kind::f16 with a f16 A and an fp16 B (both K-major), f32 accumulate,
 // M x N tile.
-__host__ __device__ constexpr uint32_t idesc_bf16_f32(uint32_t m, uint32_t n) {
+__host__ __device__ constexpr uint32_t idesc_f16_f32(uint32_t m, uint32_t n) {
   return (1u << 4)            // D format: f32
-         | (1u << 7)          // A format: bf16
+         | (0u << 7)          // A format: fp16 (1 would be bf16)
          | (0u << 10)         // B format: fp16
          | (0u << 15)         // A K-major
          | (0u << 16)         // B K-major
@@ -98,7 +98,7 @@ __host__ __device__ constexpr uint32_t idesc_bf16_f32(uint32_t m, uint32_t n) {
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.
-__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)

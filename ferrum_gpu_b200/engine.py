@@ -97,7 +97,7 @@ class CudaBackend:
         finally:
             m.close()
 
-    def score(self, model, ids, mode: Mode = Mode.TENSOR_BF16):
+    def score(self, model, ids, mode: Mode = Mode.TENSOR_F16):
         """Scoring at the engine layer (the reference routes it to the CPU oracle,
         serving/decoder.rs:L141-L149): (logprob, greedy) per position of one or many sequences."""
         cls = CudaLlama if isinstance(model, Llama) else CudaGpt2

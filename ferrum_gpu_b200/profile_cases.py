@@ -26,7 +26,7 @@ def gemm(dev):
     qw = upload_quantised(dev, QKind.Q4_0, _weights(k, n), k, n)
     x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
     for _ in range(3):
-        linear_q(dev, x, qw, m, Mode.TENSOR_BF16)
+        linear_q(dev, x, qw, m, Mode.TENSOR_F16)
     qw.close()
 
 
@@ -53,7 +53,7 @@ def score(dev):
     cfg, g = _c3_model(dev, layers=2)
     ids = np.stack([random_tokens(10 + i, 1024, cfg.vocab) for i in range(8)])
     for _ in range(2):
-        g.score_batch(ids, Mode.TENSOR_BF16)
+        g.score_batch(ids, Mode.TENSOR_F16)
     g.close()
 
 

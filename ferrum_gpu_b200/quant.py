@@ -24,7 +24,7 @@ class QKind(IntEnum):
 
 class Mode(IntEnum):
     EXACT_F32 = _ffi.FC_EXACT_F32
-    TENSOR_BF16 = _ffi.FC_TENSOR_BF16
+    TENSOR_F16 = _ffi.FC_TENSOR_F16
 
 
 def eligible(k: int) -> bool:

@@ -52,9 +52,9 @@ enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };
 
 /* Arithmetic of the batched (scoring / forward_all) matrix products.
  * FC_EXACT_F32: f32 FMA with f32 accumulation, same path as decode (parity <= 1e-5).
- * FC_TENSOR_BF16: weights dequantised to bf16 in shared memory, tcgen05 MMA with fp32
+ * FC_TENSOR_F16: weights dequantised to bf16 in shared memory, tcgen05 MMA with fp32
  * accumulators in tensor memory (parity <= 2e-2 max-abs per logit, 1e-3 mean NLL). */
-enum { FC_EXACT_F32 = 0, FC_TENSOR_BF16 = 1 };
+enum { FC_EXACT_F32 = 0, FC_TENSOR_F16 = 1 };
 
 typedef struct FcDevice FcDevice;
 typedef struct FcQWeight FcQWeight;
@@ -121,7 +121,7 @@ int fc_qweight_blocks(FcQWeight* w, uint8_t* out, size_t out_bytes);
 int fc_dequant(FcQWeight* w, float* out_n_k, size_t out_elems);
 
 /* `y[m, n] = x[m, k] * W` with host buffers (copies inside). Replaces ops::quant::linear_q
- * (ferrum_wgpu/src/ops/quant.rs:L326-L381). `mode` is FC_EXACT_F32 or FC_TENSOR_BF16. */
+ * (ferrum_wgpu/src/ops/quant.rs:L326-L381). `mode` is FC_EXACT_F32 or FC_TENSOR_F16. */
 int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mode);
 /* The same on device buffers, enqueued on the device's stream, no synchronisation. */
 int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, int mode);
@@ -239,7 +239,7 @@ int fc_model_score_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seqs, uint
 /* Restrict the resident model's head to one vocabulary shard (call once, after create). */
 int fc_model_set_head_shard(FcModel* m, uint32_t shard, uint32_t n_shards);
 /* Trunk only: final-norm hidden states of every position, `[n_seqs*seq_len, dim]` bf16 (mode
- * FC_TENSOR_BF16) or f32 (FC_EXACT_F32), written to `hidden_dev`. */
+ * FC_TENSOR_F16) or f32 (FC_EXACT_F32), written to `hidden_dev`. */
 int fc_model_trunk_dev(FcModel* m, const int32_t* ids_dev, uint32_t n_seqs, uint32_t seq_len,
                        int mode, void* hidden_dev);
 /* Head over this rank's vocabulary shard for `rows` hidden rows: per row the local maximum, the

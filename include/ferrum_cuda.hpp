@@ -28,7 +28,7 @@ struct Error : std::runtime_error {
 };
 
 enum class QKind { F32 = FC_F32, Q8_0 = FC_Q8_0, Q4_0 = FC_Q4_0 };
-enum class Mode { ExactF32 = FC_EXACT_F32, TensorBf16 = FC_TENSOR_BF16 };
+enum class Mode { ExactF32 = FC_EXACT_F32, TensorF16 = FC_TENSOR_F16 };
 
 class Gpu {
  public:

@@ -43,7 +43,7 @@ def test_tensor_product_is_exact_on_exactly_representable_inputs(dev, kind, m, k
     qw = upload_quantised(dev, kind, w, k, n)
     if kind != QKind.F32:
         assert np.array_equal(qw.dequantised().T.reshape(-1), w), "the weights must survive quantisation exactly"
-    got = linear_q(dev, x, qw, m, Mode.TENSOR_BF16)
+    got = linear_q(dev, x, qw, m, Mode.TENSOR_F16)
     want = orc.matmul(x, w, m, k, n, threads=8).reshape(m, n)
     bad = np.argwhere(got != want)
     assert bad.size == 0, (kind, m, k, n, bad[:5], got[tuple(bad[0])], want[tuple(bad[0])])
@@ -58,7 +58,7 @@ def test_tensor_product_within_tolerance_on_gaussian_inputs(dev, kind, m, k, n):
     w = (rng.standard_normal(k * n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
     x = rng.standard_normal(m * k, dtype=np.float32)
     qw = upload_quantised(dev, kind, w, k, n)
-    got = linear_q(dev, x, qw, m, Mode.TENSOR_BF16)
+    got = linear_q(dev, x, qw, m, Mode.TENSOR_F16)
     want = orc.matmul(x, orc.snap_matrix(int(kind), w, k, n), m, k, n, threads=8).reshape(m, n)
     err = np.abs(got - want).max()
     assert err < LOGIT_TOL and err < 0.02 * np.abs(want).max(), (kind, m, k, n, err, np.abs(want).max())
@@ -86,14 +86,14 @@ def test_llama_tensor_forward_and_score_match_the_f32_oracle(dev, kind, variant)
     g = CudaLlama(dev, m, kind)
     ids = random_tokens(9, 150, cfg.vocab)
     want = oracle.forward_logits(ids)
-    got = g.forward_all(ids, Mode.TENSOR_BF16)
+    got = g.forward_all(ids, Mode.TENSOR_F16)
     # the reference's metric |g - w| / max(|w|, 1): these test weights give logits up to ~4
     err, scale = orc.max_rel_err(got, want), np.abs(want).max()
     assert err < LOGIT_TOL and np.abs(got - want).max() < 0.03 * scale, (variant, kind, err, scale)
     # the exact path on the same (gate/up interleaved) weights stays at 1e-5
     assert orc.max_rel_err(g.forward_all(ids[:40]), want[:40]) < 1e-5
     seqs = np.stack([random_tokens(20 + i, 131, cfg.vocab) for i in range(3)])
-    lp, gr, nll = g.score_batch(seqs, Mode.TENSOR_BF16)
+    lp, gr, nll = g.score_batch(seqs, Mode.TENSOR_F16)
     for s in range(3):
         wlp, wgr = oracle.score(seqs[s])
         assert abs(float(np.mean(lp[s] - wlp))) < NLL_TOL, (variant, kind, s)
@@ -112,10 +112,10 @@ def test_gpt2_tensor_forward_and_score_match_the_f32_oracle(dev, kind):
     g = CudaGpt2(dev, m, kind)
     ids = random_tokens(10, 140, cfg.vocab)
     want = oracle.forward_logits(ids)
-    got = g.forward_all(ids, Mode.TENSOR_BF16)
+    got = g.forward_all(ids, Mode.TENSOR_F16)
     err, scale = orc.max_rel_err(got, want), np.abs(want).max()
     assert err < LOGIT_TOL and np.abs(got - want).max() < 0.03 * scale, (kind, err, scale)
-    lp, gr = g.score(ids, Mode.TENSOR_BF16)
+    lp, gr = g.score(ids, Mode.TENSOR_F16)
     wlp, _ = oracle.score(ids)
     assert abs(float(np.mean(lp - wlp))) < NLL_TOL
     g.close()
@@ -132,10 +132,10 @@ def test_config3_shape_scoring_within_tolerance(dev):
     g = CudaLlama(dev, m, QKind.Q4_0)
     ids = random_tokens(3, 193, cfg.vocab)
     want = oracle.forward_logits(ids[:-1])
-    got = g.forward_all(ids[:-1], Mode.TENSOR_BF16)
+    got = g.forward_all(ids[:-1], Mode.TENSOR_F16)
     assert np.abs(got - want).max() < LOGIT_TOL
     wlp, _ = orc.score(want, ids[1:], cfg.vocab)
-    lp, _ = g.score(ids, Mode.TENSOR_BF16)
+    lp, _ = g.score(ids, Mode.TENSOR_F16)
     assert abs(float(np.mean(lp - wlp))) < NLL_TOL
     lp32, _ = g.score(ids, Mode.EXACT_F32)
     assert np.abs(lp32 - wlp).max() < 1e-4
