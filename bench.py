@@ -222,9 +222,9 @@ def main():
         out = {
             "metric": METRIC, "value": world * rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "c3-llama-12L-d768-q4_0-scoring-256x1024", "seqs_per_gpu": n_seqs, "seq_len": SEQ_LEN,
-                       "weights": "Q4_0", "arithmetic": "bf16 tcgen05, f32 accumulate",
+                       "weights": "Q4_0", "arithmetic": "fp16 operands on tcgen05 (kind::f16), f32 accumulate",
                        "l2": "inputs larger than L2 (activations of one chunk exceed 126 MB)", "parallelism": f"replica x{world}"},
             "e2e": {"value": world * rows / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(ids_host.nbytes),
                     "d2h_bytes_per_step": int(lp.nbytes + rows + nll.nbytes)},

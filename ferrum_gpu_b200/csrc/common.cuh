@@ -95,6 +95,7 @@ struct FcQWeight {
   // bf16 GEMM operand descriptors are built lazily by the tensor path
   void* tc_cache = nullptr;
   size_t tc_cache_bytes = 0;
+  void* mma_scratch = nullptr; // scratch of the batched-decode product for stand-alone use
 };
 
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
@@ -108,7 +109,15 @@ struct Epilogue {
   const float* bias = nullptr;  // [n]
   const float* resid = nullptr; // [m][n]; may alias y
   int act = ACT_NONE;
+  // device scratch of at least qmatvec_mma_scratch_bytes(k, n): lets products of 9..64 rows run on the
+  // tensor-core batched-decode kernel; without it they take the tiled f32 kernel
+  void* scratch = nullptr;
 };
+
+// matvec_mma.cu: 9 <= m <= 64 rows at f32-class accuracy on mma.sync
+bool qmatvec_mma_supports(const QMat& w, uint32_t m);
+size_t qmatvec_mma_scratch_bytes(uint32_t k, uint32_t n);
+int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch);
 
 // ---- kernels' host entry points (each enqueues on dev->stream) --------------------------------
 // codec.cu

@@ -170,7 +170,11 @@ int launch(FcDevice* dev, const QMat& w, const float* x, float* y, const Epilogu
   constexpr int R = M <= 2 ? 4 : 2;
   const size_t smem = (size_t)M * w.k * sizeof(float);
   auto kern = qmatvec_kernel<KIND, M, LPR, R>;
-  if (smem > 48 * 1024) FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  static bool attr = false; // once per instantiation: the largest staging buffer the host entry admits
+  if (!attr) {
+    FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
   const uint32_t groups_per_block = 8 * (32 / LPR);
   const uint32_t n_groups = (w.n + R - 1) / R;
   uint32_t blocks = (n_groups + groups_per_block - 1) / groups_per_block;
@@ -218,5 +222,6 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
 int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
   if (m == 0) return FC_OK;
   if (m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0) return k_qmatvec(dev, w, x, m, y, ep);
+  if (ep.scratch && qmatvec_mma_supports(w, m)) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
   return k_qgemm_f32(dev, w, x, m, y, ep);
 }

@@ -58,6 +58,9 @@ void model_free(FcModel* m) {
   cudaSetDevice(m->dev->ordinal);
   cudaStreamSynchronize(m->dev->stream);
   model_tc_free(m);
+  for (cudaGraphExec_t g : m->graphs)
+    if (g) cudaGraphExecDestroy(g);
+  if (m->pin_dec) cudaFreeHost(m->pin_dec);
   for (auto& l : m->layers) {
     qweight_free(l.qkv.w);
     qweight_free(l.wo.w);
@@ -129,6 +132,16 @@ int alloc_common(FcModel* m) {
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_pos));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
+  // scratch of the batched-decode tensor product (x split + split-K partials), sized for the widest matrix
+  if (s > 8) {
+    size_t need = qmatvec_mma_scratch_bytes(m->head.w->m.k, m->head.w->m.n);
+    for (auto& l : m->layers)
+      for (const FcQWeight* q : {l.qkv.w, l.wo.w, l.ff1.w, l.ff2.w}) {
+        const size_t b = qmatvec_mma_scratch_bytes(q->m.k, q->m.n);
+        need = b > need ? b : need;
+      }
+    FC_TRY(dev_alloc(m, need, &m->mma_scratch));
+  }
   m->pos.assign(s, 0);
   m->head_view = m->head.w->m;
   m->v0 = 0;
@@ -161,6 +174,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     else
       FC_TRY(k_layernorm(dev, b.x, l.norm1_g, l.norm1_b, rows, d, b.h));
     Epilogue e_qkv;
+    e_qkv.scratch = m->mma_scratch;
     e_qkv.bias = l.qkv.bias;
     FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.h, rows, b.qkv, e_qkv));
     const bool to_cache = mode != ATTN_STATELESS;
@@ -174,6 +188,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     else
       FC_TRY(k_attn_prefill_cache_f32(dev, b.qkv, t, start, m->heads, m->kv_heads, m->hd, stream, l.kv, m->ctx, b.attn));
     Epilogue e_wo;
+    e_wo.scratch = m->mma_scratch;
     e_wo.bias = l.wo.bias;
     e_wo.resid = b.x;
     FC_TRY(k_qlinear_f32(dev, l.wo.w->m, b.attn, rows, b.x, e_wo));
@@ -182,6 +197,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     else
       FC_TRY(k_layernorm(dev, b.x, l.norm2_g, l.norm2_b, rows, d, b.h));
     Epilogue e_ff1;
+    e_ff1.scratch = m->mma_scratch;
     e_ff1.bias = l.ff1.bias;
     e_ff1.act = m->arch == ARCH_GPT2 ? ACT_GELU : ACT_NONE;
     FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.h, rows, b.ff, e_ff1));
@@ -191,6 +207,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
       ff2_in = b.act;
     }
     Epilogue e_ff2;
+    e_ff2.scratch = m->mma_scratch;
     e_ff2.bias = l.ff2.bias;
     e_ff2.resid = b.x;
     FC_TRY(k_qlinear_f32(dev, l.ff2.w->m, ff2_in, rows, b.x, e_ff2));
@@ -482,23 +499,61 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
     if (m->pos[stream_ids[i]] >= m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
   }
   FC_TRY(check_ids(m, tokens, n));
-  void* pin;
-  FC_TRY(fc_pinned(dev, (size_t)n * 12 + (size_t)n * 4, &pin));
-  int32_t* p = (int32_t*)pin;
+  // The step's variable inputs (token, position, cache slot per row) travel through one pinned
+  // buffer owned by the model, so the whole step is a fixed sequence of launches and copies: after
+  // one eager step per batch width it is captured into a CUDA graph and replayed (a decode step is
+  // ~50-220 dependent launches of a few microseconds each, so launch overhead, not bandwidth, sets
+  // its time at small widths). Fault injection and per-kernel profiling use the eager path.
+  if (!m->pin_dec) FC_CUDA(dev, cudaMallocHost((void**)&m->pin_dec, (size_t)m->max_streams * 16));
+  int32_t* p = m->pin_dec;
   for (uint32_t i = 0; i < n; i++) {
     p[i] = tokens[i];
     p[n + i] = (int32_t)m->pos[stream_ids[i]];
     p[2 * n + i] = (int32_t)stream_ids[i];
   }
-  FC_CUDA(dev, cudaMemcpyAsync(m->d_ids, p, n * 4, cudaMemcpyHostToDevice, dev->stream));
-  FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
-  FC_CUDA(dev, cudaMemcpyAsync(m->d_streams, p + 2 * n, n * 4, cudaMemcpyHostToDevice, dev->stream));
-  PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
-  FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0));
-  FC_TRY(k_qlinear_f32(dev, m->head_view, m->h, n, m->logits, Epilogue()));
-  if (argmax_out) {
+  auto enqueue_step = [&]() -> int {
+    FC_CUDA(dev, cudaMemcpyAsync(m->d_ids, p, n * 4, cudaMemcpyHostToDevice, dev->stream));
+    FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
+    FC_CUDA(dev, cudaMemcpyAsync(m->d_streams, p + 2 * n, n * 4, cudaMemcpyHostToDevice, dev->stream));
+    PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
+    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0));
+    Epilogue e_head;
+    e_head.scratch = m->mma_scratch;
+    FC_TRY(k_qlinear_f32(dev, m->head_view, m->h, n, m->logits, e_head));
     FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax));
     FC_CUDA(dev, cudaMemcpyAsync(p + 3 * n, m->d_argmax, n * 4, cudaMemcpyDeviceToHost, dev->stream));
+    return FC_OK;
+  };
+  if (m->graphs.size() <= n) {
+    m->graphs.resize(n + 1, nullptr);
+    m->graph_launches.resize(n + 1, 0);
+    m->graph_warm.resize(n + 1, 0);
+  }
+  const bool graph_mode = m->graph_ok && dev->fail_after < 0 && !dev->profiling;
+  if (graph_mode && m->graphs[n]) {
+    FC_CUDA(dev, cudaGraphLaunch(m->graphs[n], dev->stream));
+    dev->launches += m->graph_launches[n];
+  } else if (graph_mode && m->graph_warm[n]) {
+    const uint64_t l0 = dev->launches;
+    cudaGraph_t graph = nullptr;
+    bool ok = cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+    int rc = ok ? enqueue_step() : FC_OK;
+    if (ok) ok = cudaStreamEndCapture(dev->stream, &graph) == cudaSuccess && rc == FC_OK && graph;
+    if (ok) ok = cudaGraphInstantiate(&m->graphs[n], graph, 0) == cudaSuccess;
+    if (graph) cudaGraphDestroy(graph);
+    if (ok) {
+      m->graph_launches[n] = dev->launches - l0;
+      FC_CUDA(dev, cudaGraphLaunch(m->graphs[n], dev->stream));
+    } else { // capture is an optimisation: without it the step runs as plain launches
+      cudaGetLastError();
+      m->graphs[n] = nullptr;
+      m->graph_ok = false;
+      dev->launches = l0;
+      FC_TRY(enqueue_step());
+    }
+  } else {
+    FC_TRY(enqueue_step());
+    m->graph_warm[n] = 1;
   }
   if (logits_out)
     FC_CUDA(dev, cudaMemcpyAsync(logits_out, m->logits, (size_t)n * m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));

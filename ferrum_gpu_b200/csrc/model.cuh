@@ -49,6 +49,13 @@ struct FcModel {
   // decode scratch, sized for max_streams rows
   float *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *ff = nullptr, *act = nullptr, *logits = nullptr;
   int32_t *d_ids = nullptr, *d_pos = nullptr, *d_streams = nullptr, *d_argmax = nullptr;
+  // decode-step replay: one instantiated CUDA graph per batch width, inputs through a pinned buffer
+  void* mma_scratch = nullptr; // batched-decode product scratch (models of more than 8 streams)
+  int32_t* pin_dec = nullptr;
+  std::vector<cudaGraphExec_t> graphs;
+  std::vector<uint64_t> graph_launches;
+  std::vector<uint8_t> graph_warm;
+  bool graph_ok = true;
   Arena arena;
   void* tc = nullptr; // state of the bf16 tensor-core path (built on first use)
 

@@ -75,6 +75,7 @@ FC_API int fc_qweight_destroy(FcQWeight* w) {
   cudaSetDevice(w->dev->ordinal);
   cudaStreamSynchronize(w->dev->stream);
   if (w->tc_cache) cudaFree(w->tc_cache);
+  if (w->mma_scratch) cudaFree(w->mma_scratch);
   qweight_free(w);
   return FC_OK;
 }
@@ -125,7 +126,14 @@ FC_API int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y
   if (!w || !x_dev || !y_dev) return FC_ERR_ARG;
   FcDevice* dev = w->dev;
   cudaSetDevice(dev->ordinal);
-  if (mode == FC_EXACT_F32) return k_qlinear_f32(dev, w->m, x_dev, m, y_dev, Epilogue());
+  if (mode == FC_EXACT_F32) {
+    Epilogue ep;
+    if (qmatvec_mma_supports(w->m, m)) { // 9..64 rows: the batched-decode tensor product needs scratch
+      if (!w->mma_scratch) FC_CUDA(dev, cudaMalloc(&w->mma_scratch, qmatvec_mma_scratch_bytes(w->m.k, w->m.n)));
+      ep.scratch = w->mma_scratch;
+    }
+    return k_qlinear_f32(dev, w->m, x_dev, m, y_dev, ep);
+  }
   if (mode == FC_TENSOR_F16) return k_qgemm_tc(dev, w, x_dev, m, y_dev);
   return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
 }

@@ -194,7 +194,7 @@ def test_fault_sweep_fails_cleanly_at_every_launch(dev):
     before = dev.launch_count()
     want = g.feed(3)
     per_token = dev.launch_count() - before
-    assert per_token == 1 + 9 * cfg.layers + 2, per_token  # embed, 9 per layer, final norm, head
+    assert per_token == 1 + 9 * cfg.layers + 3, per_token  # embed, 9 per layer, final norm, head, argmax
     g.reset()
     for k in range(per_token):
         dev.fail_after(k)
