@@ -86,6 +86,7 @@ EXPORTS = (
     "fc_debug_profile", "fc_debug_profile_report",
     "fc_block_bytes", "fc_qweight_create", "fc_qweight_create_from_blocks", "fc_qweight_destroy",
     "fc_qweight_info", "fc_qweight_blocks", "fc_dequant", "fc_qmatmul", "fc_qmatmul_dev",
+    "fc_qmatmul_dev_noalloc",
     "fc_llama_plan_bytes", "fc_gpt2_plan_bytes", "fc_llama_create", "fc_gpt2_create",
     "fc_model_destroy", "fc_model_pos", "fc_model_reset", "fc_model_info", "fc_model_feed",
     "fc_model_feed_batch", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
@@ -137,6 +138,7 @@ def load() -> C.CDLL:
         "fc_dequant": (C.c_int, [vp, vp, sz]),
         "fc_qmatmul": (C.c_int, [vp, vp, u32, vp, C.c_int]),
         "fc_qmatmul_dev": (C.c_int, [vp, vp, u32, vp, C.c_int]),
+        "fc_qmatmul_dev_noalloc": (C.c_int, [vp, vp, u32, vp]),
         "fc_llama_plan_bytes": (u64, [P(FcLlamaConfig), C.c_int, u32]),
         "fc_gpt2_plan_bytes": (u64, [P(FcGpt2Config), C.c_int, u32]),
         "fc_llama_create": (C.c_int, [vp, P(FcLlamaConfig), P(FcLlamaWeights), C.c_int, u32, u64, P(vp)]),

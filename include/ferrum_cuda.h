@@ -126,6 +126,19 @@ int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mode);
 /* The same on device buffers, enqueued on the device's stream, no synchronisation. */
 int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, int mode);
 
+/* The tensor-core product of fc_qmatmul_dev (mode FC_TENSOR_F16) for callers that must not trigger a
+ * device allocation. This entry point has no counterpart in the reference. fc_qmatmul_dev keeps its
+ * fp16 copy of `x` in a buffer it cudaMalloc's and grows per weight; that is unusable from inside a
+ * stream capture, under a memory plan that was checked once and may not grow, or in a loop that
+ * cannot afford the device-wide synchronisation an allocation implies. Here the copy lives in a
+ * fixed 8 MiB array inside the library's device image (every GPU that loads the library carries it
+ * until the process exits), so `m * k` may be at most 4 Mi elements (4 194 304); larger products are
+ * refused with FC_ERR_SHAPE. `x_dev` and `y_dev` are the caller's. The first call on a device looks
+ * up the array's device address; make that call before starting any stream capture. All calls share
+ * the one array: two of them overlapping on the GPU (different streams or devices' handles on the
+ * same GPU) race, and the array keeps the previous call's contents between calls. */
+int fc_qmatmul_dev_noalloc(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev);
+
 /* ---- resident models ---------------------------------------------------------------------- */
 /* ferrum_ref::llama::Config + RopeScaling (ferrum_ref/src/models/llama/mod.rs:L24-L52,
  * ops.rs:L17-L35). */
