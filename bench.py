@@ -129,6 +129,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=N_SEQS, help="sequences per rank (256 = the benchmark workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode64", action="store_true",
+                    help="also time the 64-stream Qwen2-style decode configuration (about a minute of set-up)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -214,10 +216,19 @@ def main():
         prof = dev.profile_report()
         dev.profile(False)
         total_ms = sum(v["ms"] for v in prof.values()) or 1.0
-        gemm = prof.get("qgemm_tc", {"launches": 0, "ms": 0.0})
+        gemm = {"launches": sum(v["launches"] for k, v in prof.items() if k.startswith("qgemm_tc")),
+                "ms": sum(v["ms"] for k, v in prof.items() if k.startswith("qgemm_tc"))}
         lin_flops, attn_flops = c3_flops_per_token(cfg)
         gemm_flops_step = lin_flops * rows          # algorithmic: 2 * M * N * K summed over the products
         achieved = gemm_flops_step / (gemm["ms"] * 1e-3) / 1e12 if gemm["ms"] else 0.0
+        # the same per role of the product (its epilogue names it): flops of that role / its device time
+        role_flops = {"qgemm_tc_qkv": 2.0 * cfg.layers * cfg.dim * (cfg.q_dim + 2 * cfg.kv_dim),
+                      "qgemm_tc_resid": 2.0 * cfg.layers * (cfg.q_dim * cfg.dim + cfg.hidden * cfg.dim),
+                      "qgemm_tc_swiglu": 2.0 * cfg.layers * cfg.dim * 2 * cfg.hidden,
+                      "qgemm_tc_lse": 2.0 * cfg.dim * cfg.vocab}
+        by_role = {k: round(f * rows / (prof[k]["ms"] * 1e-3) / 1e12, 1) for k, f in role_flops.items()
+                   if k in prof and prof[k]["ms"] > 0}
+        attn_tf = attn_flops * rows / (prof["attn_causal_f16"]["ms"] * 1e-3) / 1e12 if "attn_causal_f16" in prof else None
         shares = {k: round(v["ms"] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
         out = {
             "metric": METRIC, "value": world * rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,
@@ -233,13 +244,16 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "qgemm_tc_kernel", "achieved": achieved, "peak": tf_sust,
                          "unit": "TFLOP/s", "frac": achieved / tf_sust, "peak_source": f"{peak_src} (sustained bf16)",
                          "frac_of_burst": achieved / tf_burst, "traffic": None,
-                         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"], "kernel_shares": shares},
+                         "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"], "kernel_shares": shares,
+                         "tflops_by_role": by_role, "attention_tflops": attn_tf},
             "model_flops_per_step": (lin_flops + attn_flops) * rows,
             "mfu_of_sustained": (lin_flops + attn_flops) * rows / (ms_step * 1e-3) / 1e12 / tf_sust,
             "nll_checksum": nll_total,
         }
         if not args.no_decode and world == 1:
             out["decode"] = bench_decode(dev, hbm)
+            if args.decode64:
+                out["decode64"] = bench_decode64(dev, hbm)
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(cfg, model)
     g.close()
@@ -277,6 +291,44 @@ def bench_decode(dev, hbm_gbs):
     return {"workload": "c1-gpt2-6L-d384-q8_0-b1-16+128", "tok_s": tok_s, "ms_per_token": best / 127 * 1e3,
             "hbm_frac": bytes_per_tok * tok_s / 1e9 / hbm_gbs,
             "note": "weights (11 MB) live in L2; the limiter is launch/dependency latency, not HBM"}
+
+
+def bench_decode64(dev, hbm_gbs, streams=64, prefill=1536, steps=32):
+    """Batched KV-cached decode: the Qwen2-style configuration (24 layers, d_model 1024, 16 q / 2 kv heads,
+    SwiGLU 2816, vocab 151936, tied head, q/k/v biases, Q8_0, f32 KV cache), 64 streams each with a
+    1536-token prefill, then `steps` greedy steps of all streams together (of the configuration's 512;
+    the cache length grows from 1536, the step cost with it)."""
+    from ferrum_gpu_b200 import CudaLlama, QKind
+    from ferrum_gpu_b200.hostmodel import config_c4, random_llama, random_tokens
+    cfg = config_c4()
+    model = random_llama(cfg, seed=2, biases=True, tied=True)
+    g = CudaLlama(dev, model, QKind.Q8_0, max_streams=streams)
+    t0 = time.perf_counter()
+    for s in range(streams):
+        g.prefill(random_tokens(500 + s, prefill, cfg.vocab), stream=s)
+    prefill_s = time.perf_counter() - t0
+    toks = random_tokens(7, streams, cfg.vocab)
+    for _ in range(3):  # eager step, graph capture, first replay
+        toks, _ = g.feed_batch(toks)
+    dev.sync()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        toks, _ = g.feed_batch(toks)
+    dt = (time.perf_counter() - t0) / steps
+    dev.profile(True)
+    g.feed_batch(toks)
+    prof = dev.profile_report()
+    dev.profile(False)
+    wbytes = g.weight_bytes()
+    mean_len = prefill + 3 + steps / 2
+    kv_bytes = 2 * cfg.kv_dim * 4 * mean_len * cfg.layers * streams
+    g.close()
+    total = sum(v["ms"] for v in prof.values()) or 1.0
+    return {"workload": f"c4-qwen2-24L-d1024-q8_0-{streams}streams-{prefill}+{steps}", "tok_s": streams / dt,
+            "ms_per_step": dt * 1e3, "prefill_s": prefill_s, "bytes_per_step": wbytes + kv_bytes,
+            "hbm_frac": (wbytes + kv_bytes) / dt / 1e9 / hbm_gbs,
+            "kernel_shares": {k: round(v["ms"] / total, 3) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])[:6]},
+            "profiled_step_ms": total}
 
 
 def cpu_baseline(cfg, model):

@@ -17,11 +17,12 @@
 
 namespace {
 
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2; // 32 KB: two 128-row halves
 constexpr uint32_t B_BYTES = TC_BN * TC_BK * 2; // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t STG_WORDS = 32 * 36;          // per epilogue warp: a 32 x 32 f32 chunk, rows padded to 36
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * STG_WORDS * 4;
 constexpr int THREADS = 448;
 constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 columns
 
@@ -196,7 +197,7 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, ui
       }
       *reinterpret_cast<float4*>(dst + j) = v;
     }
-  } else if (EPI == EPI_BF16) {
+  } else if (EPI == EPI_F16) {
     __half* dst = a.out_f16 + (size_t)row * a.ldo + col0;
 #pragma unroll
     for (int j = 0; j < 32; j += 8) {
@@ -211,6 +212,31 @@ __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, ui
       *reinterpret_cast<uint4*>(dst + j) =
           make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
     }
+  }
+}
+
+// Residual epilogue in two halves so the loads of the residual stream are in flight while the MMAs of
+// the tile finish and while the previous chunk is being stored: 32 f32 of row `row` at column col0.
+__device__ __forceinline__ void resid_load(const TcArgs& a, uint32_t row, uint32_t col0, float4* r) {
+  const bool ok = row < a.m;
+  const float* src = a.out_f32 + (size_t)row * a.ldo + col0;
+#pragma unroll
+  for (int j = 0; j < 8; j++)
+    r[j] = ok && col0 + 4 * j < a.n ? *reinterpret_cast<const float4*>(src + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+__device__ __forceinline__ void resid_store(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* acc, const float4* r) {
+  if (row >= a.m) return;
+  float* dst = a.out_f32 + (size_t)row * a.ldo + col0;
+#pragma unroll
+  for (int j = 0; j < 8; j++) {
+    if (col0 + 4 * j >= a.n) break;
+    float4 v = make_float4(__uint_as_float(acc[4 * j]) + r[j].x, __uint_as_float(acc[4 * j + 1]) + r[j].y,
+                           __uint_as_float(acc[4 * j + 2]) + r[j].z, __uint_as_float(acc[4 * j + 3]) + r[j].w);
+    if (a.bias) {
+      const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + 4 * j);
+      v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+    }
+    *reinterpret_cast<float4*>(dst + 4 * j) = v;
   }
 }
 
@@ -345,7 +371,9 @@ int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArg
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr = true;
   }
-  FC_LAUNCH(dev, "qgemm_tc", kern<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmap, w, a));
+  static const char* const names[] = {"qgemm_tc_f32", "qgemm_tc_f16", "qgemm_tc_resid", "qgemm_tc_swiglu", "qgemm_tc_lse",
+                                      "qgemm_tc_qkv"};
+  FC_LAUNCH(dev, names[EPI], kern<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmap, w, a));
   return FC_OK;
 }
 
@@ -353,7 +381,7 @@ template <int KIND>
 int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, int epi, dim3 grid) {
   switch (epi) {
     case EPI_F32: return launch_tc<KIND, EPI_F32>(dev, tmap, w, a, grid);
-    case EPI_BF16: return launch_tc<KIND, EPI_BF16>(dev, tmap, w, a, grid);
+    case EPI_F16: return launch_tc<KIND, EPI_F16>(dev, tmap, w, a, grid);
     case EPI_RESID: return launch_tc<KIND, EPI_RESID>(dev, tmap, w, a, grid);
     case EPI_SWIGLU: return launch_tc<KIND, EPI_SWIGLU>(dev, tmap, w, a, grid);
     case EPI_LSE: return launch_tc<KIND, EPI_LSE>(dev, tmap, w, a, grid);
@@ -373,7 +401,7 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   if (epi == EPI_QKV && (w.n % 64 || args.ldo % 8 || args.rope_cols % 64 ||
                          (args.rope_cos && args.rope_type != FC_ROPE_NORM && args.rope_dim != 64) || args.rope_dim > 64))
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "the fused qkv epilogue needs heads of 64 columns and, for NEOX, rope_dim 64");
-  if ((epi == EPI_BF16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
+  if ((epi == EPI_F16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "a f16 result needs n %% 8 == 0, not %u", w.n);
   if (epi == EPI_SWIGLU && w.n % 128) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the SwiGLU epilogue needs n %% 128 == 0");
   if ((reinterpret_cast<uintptr_t>(a_dev) & 15) != 0) return fc_fail(dev, FC_ERR_ARG, "the A operand must be 16-byte aligned");

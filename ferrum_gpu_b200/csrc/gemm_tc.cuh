@@ -7,7 +7,7 @@
 // What the epilogue does with the 128 x 128 f32 accumulator tile.
 enum {
   EPI_F32 = 0,    // out_f32[m][ldo]  = acc + bias
-  EPI_BF16 = 1,   // out_f16[m][ldo] = f16(act(acc + bias))
+  EPI_F16 = 1,   // out_f16[m][ldo] = f16(act(acc + bias))
   EPI_RESID = 2,  // out_f32[m][ldo] += acc + bias          (residual stream, in place)
   EPI_SWIGLU = 3, // out_f16[m][n/2] = f16(silu(gate) * up); weight rows interleaved 64 gate / 64 up
   EPI_LSE = 4,    // partial[tile][m][4] = (max, sum exp, target logit | -inf, first argmax)

@@ -156,18 +156,75 @@ __global__ void __launch_bounds__(THREADS, 1)
   } else {
     // ---- epilogue ----
     const uint32_t e = warp - 6, half = e >> 2, quad = warp & 3;
+    float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + e * STG_WORDS; // this warp's 32 x 36 tile
     uint32_t tcnt = 0;
     for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
       const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
       const uint32_t n0 = (tile % tiles_n) * TC_BN;
       const uint32_t out_row = (tile / tiles_n) * TC_BM + half * 128 + quad * 32 + lane;
+      const bool staged = (EPI == EPI_RESID || EPI == EPI_F32 || EPI == EPI_F16) && ((a.ldo | a.n) & 7) == 0;
+      const uint32_t wrow0 = (tile / tiles_n) * TC_BM + half * 128 + quad * 32; // first of this warp's 32 rows
+      const uint32_t tr = lane >> 3, tc4 = (lane & 7) * 4; // store mapping: rows tr + 4i, columns tc4..tc4+3
+      float4 rcur[8], rnext[8];
+      auto load_resid = [&](uint32_t col0, float4* r) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint32_t row = wrow0 + tr + 4 * i;
+          r[i] = (row < a.m && col0 + tc4 < a.n) ? *reinterpret_cast<const float4*>(a.out_f32 + (size_t)row * a.ldo + col0 + tc4)
+                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      };
+      if (staged && EPI == EPI_RESID) load_resid(n0, rnext); // in flight while the tile's MMAs finish
       if (!wait_or_abort(&acc_full[buf], aph, abort_word)) {
         atomicExch(a.err_flag, ERR_WAIT_ACC);
         break;
       }
       tc::tc_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * (2 * TC_BN) + half * TC_BN;
-      if (EPI == EPI_SWIGLU) {
+      if (staged) {
+        // tcgen05.ld hands each lane one output row; storing that way touches 32 rows per instruction.
+        // The 32 x 32 chunk goes through a padded shared-memory tile instead and leaves with 8 lanes on
+        // each row: every global access of the warp is then 4 rows x 128 contiguous bytes.
+#pragma unroll 1
+        for (uint32_t c = 0; c < TC_BN / 32; c++) {
+          uint32_t acc[32];
+          tc::tmem_ld_32x32(taddr + c * 32, acc);
+          if (EPI == EPI_RESID) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) rcur[j] = rnext[j];
+            if (c + 1 < TC_BN / 32) load_resid(n0 + (c + 1) * 32, rnext);
+          }
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; j++)
+            *reinterpret_cast<float4*>(stg + lane * 36 + 4 * j) =
+                make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]), __uint_as_float(acc[4 * j + 2]),
+                            __uint_as_float(acc[4 * j + 3]));
+          __syncwarp();
+          const uint32_t col = n0 + c * 32 + tc4;
+          if (col < a.n) {
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a.bias) b4 = *reinterpret_cast<const float4*>(a.bias + col);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const uint32_t row = wrow0 + tr + 4 * i;
+              float4 v = *reinterpret_cast<const float4*>(stg + (tr + 4 * i) * 36 + tc4);
+              v.x += b4.x, v.y += b4.y, v.z += b4.z, v.w += b4.w;
+              if (EPI == EPI_RESID) v.x += rcur[i].x, v.y += rcur[i].y, v.z += rcur[i].z, v.w += rcur[i].w;
+              if (row < a.m) {
+                if (EPI == EPI_F16) {
+                  if (a.act == ACT_GELU) v.x = gelu_f(v.x), v.y = gelu_f(v.y), v.z = gelu_f(v.z), v.w = gelu_f(v.w);
+                  *reinterpret_cast<uint2*>(a.out_f16 + (size_t)row * a.ldo + col) =
+                      make_uint2(pack_f16(v.x, v.y), pack_f16(v.z, v.w));
+                } else {
+                  *reinterpret_cast<float4*>(a.out_f32 + (size_t)row * a.ldo + col) = v;
+                }
+              }
+            }
+          }
+          __syncwarp();
+        }
+      } else if (EPI == EPI_SWIGLU) {
         // columns [0, 64) of the tile are gate rows, [64, 128) the matching up rows
 #pragma unroll 1
         for (uint32_t c = 0; c < 2; c++) {

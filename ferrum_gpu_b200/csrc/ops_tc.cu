@@ -145,6 +145,47 @@ __global__ void rope_f16_kernel(__half* __restrict__ qkv, uint32_t heads, uint32
   }
 }
 
+// The same with 16-byte accesses: one thread rotates 8 pairs of one head (NORM: 16 consecutive
+// values; NEOX: 8 values and the 8 that sit rope_dim / 2 further). rope_dim % 16 == 0.
+__global__ void __launch_bounds__(256)
+    rope_f16_vec_kernel(__half* __restrict__ qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+                        const float* __restrict__ cos, const float* __restrict__ sin, uint32_t rope_dim, uint32_t type,
+                        const int32_t* __restrict__ positions) {
+  const uint32_t half = rope_dim / 2, groups = half / 8, per_row = (heads + kv_heads) * groups;
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)rows * per_row) return;
+  const uint32_t r = (uint32_t)(idx / per_row), rem = (uint32_t)(idx % per_row), h = rem / groups, gidx = rem % groups;
+  __half* base = qkv + (size_t)r * (heads + 2 * kv_heads) * hd + (size_t)h * hd;
+  const float* cs = cos + (size_t)positions[r] * half + 8 * gidx;
+  const float* sn = sin + (size_t)positions[r] * half + 8 * gidx;
+  const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(sn), s1 = *reinterpret_cast<const float4*>(sn + 4);
+  const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float s[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  __half* pa = type == FC_ROPE_NORM ? base + 16 * gidx : base + 8 * gidx;
+  __half* pb = type == FC_ROPE_NORM ? pa + 8 : pa + half;
+  uint4 va = *reinterpret_cast<const uint4*>(pa), vb = *reinterpret_cast<const uint4*>(pb);
+  __half2* ha = reinterpret_cast<__half2*>(&va);
+  __half2* hb = reinterpret_cast<__half2*>(&vb);
+  if (type == FC_ROPE_NORM) { // pairs are the half2 lanes themselves: va holds pairs 0..3, vb pairs 4..7
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float2 x = __half22float2(ha[i]), y = __half22float2(hb[i]);
+      ha[i] = __floats2half2_rn(x.x * c[i] - x.y * s[i], x.x * s[i] + x.y * c[i]);
+      hb[i] = __floats2half2_rn(y.x * c[4 + i] - y.y * s[4 + i], y.x * s[4 + i] + y.y * c[4 + i]);
+    }
+  } else { // element i of va pairs with element i of vb
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float2 x = __half22float2(ha[i]), y = __half22float2(hb[i]);
+      ha[i] = __floats2half2_rn(x.x * c[2 * i] - y.x * s[2 * i], x.y * c[2 * i + 1] - y.y * s[2 * i + 1]);
+      hb[i] = __floats2half2_rn(x.x * s[2 * i] + y.x * c[2 * i], x.y * s[2 * i + 1] + y.y * c[2 * i + 1]);
+    }
+  }
+  *reinterpret_cast<uint4*>(pa) = va;
+  *reinterpret_cast<uint4*>(pb) = vb;
+}
+
 // [n_tiles][rows][4] -> [rows][4]: tiles are in ascending vocabulary order
 __global__ void partial_merge_kernel(const float* __restrict__ tiles, uint32_t n_tiles, uint32_t rows,
                                      float* __restrict__ out) {
@@ -219,6 +260,13 @@ int k_norm_f16(FcDevice* dev, bool layernorm, const float* x, const float* g, co
 int k_rope_f16(FcDevice* dev, __half* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
                 const float* cos, const float* sin, uint32_t rope_dim, uint32_t type, const int32_t* positions) {
   if (!rows || !cos) return FC_OK;
+  if (rope_dim % 16 == 0 && hd % 8 == 0) {
+    const size_t total = (size_t)rows * (heads + kv_heads) * (rope_dim / 16);
+    FC_LAUNCH(dev, "rope_f16",
+              rope_f16_vec_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(qkv, rows, heads, kv_heads, hd, cos,
+                                                                                             sin, rope_dim, type, positions));
+    return FC_OK;
+  }
   FC_LAUNCH(dev, "rope_f16",
             rope_f16_kernel<<<rows, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, cos, sin, rope_dim, type, positions));
   return FC_OK;

@@ -268,3 +268,29 @@ def test_config1_greedy_decode_reproduces_the_oracle_tokens(dev):
     # the device-side greedy path produces the same continuation
     assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128))[16:] == out_o
     g.close()
+
+
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
+def test_many_streams_take_the_tensor_decode_path_and_match_the_oracle(dev, kind):
+    """More than 8 concurrent streams (the 64-stream decode configuration in small): the products run
+    on the batched-decode tensor kernel, the step is replayed from a CUDA graph, and every stream still
+    sees the logits the CPU oracle computes for it alone."""
+    from ferrum_gpu_b200.hostmodel import LlamaConfig
+    cfg = LlamaConfig(vocab=200, ctx=24, dim=128, heads=2, kv_heads=1, head_dim=64, layers=2, hidden=256, rope_dim=64,
+                      rope_base=1e6, rope_type=_ffi.FC_ROPE_NEOX, eps=1e-6)
+    m = random_llama(cfg, seed=4, biases=True, std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_llama(m, int(kind), snap_embedding=False)
+    n_streams, steps = 12, 6
+    toks = np.stack([random_tokens(50 + s, steps, cfg.vocab) for s in range(n_streams)])
+    want = []
+    for s in range(n_streams):
+        o = orc.OracleLlama(ref)
+        want.append([o.feed(int(t)) for t in toks[s]])
+    g = CudaLlama(dev, m, kind, max_streams=n_streams)
+    for i in range(steps):  # the first step runs eagerly, the second is captured, later ones are replays
+        am, lg = g.feed_batch(toks[:, i], want_logits=True)
+        for s in range(n_streams):
+            assert orc.max_rel_err(lg[s], want[s][i]) < 2 * FORWARD, (kind, i, s)
+            assert am[s] == orc.argmax(lg[s])
+    assert all(g.pos(s) == steps for s in range(n_streams))
+    g.close()

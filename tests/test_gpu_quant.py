@@ -105,3 +105,24 @@ def test_sweep_shapes_of_the_isolated_matmul_config(dev, kind):
             e = orc.max_rel_err(linear_q(dev, x, qw, m), orc.matmul(x, want_w, m, k, n, threads=8))
             assert e < REDUCING, (kind, m, k, n, e)
         qw.close()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("rows,k,n", [(9, 128, 8), (16, 256, 70), (33, 1024, 200), (64, 2816, 130), (40, 384, 1536)])
+def test_batched_decode_tensor_product_keeps_f32_accuracy(dev, kind, rows, k, n):
+    """9..64 rows (concurrent decode streams) run on mma.sync with x split into two fp16 terms and the
+    block scale applied in f32: the result must stay within the f32 bound of the oracle, be exact on
+    the identity (bit-identical dequantisation), and repeat bit for bit (split-K without atomics)."""
+    w = orc.rand_vec(k * n, 4) * np.float32(1.0 / np.sqrt(k))
+    want_w = orc.snap_matrix(int(kind), w, k, n)
+    x = orc.rand_vec(rows * k, 5)
+    qw = upload_quantised(dev, kind, w, k, n)
+    got = linear_q(dev, x, qw, rows)
+    assert orc.max_rel_err(got, orc.matmul(x, want_w, rows, k, n)) < REDUCING, (kind, rows, k, n)
+    assert np.array_equal(got, linear_q(dev, x, qw, rows))
+    if rows * 2 <= k:  # one-hot rows read weight columns back exactly
+        eye = np.zeros((rows, k), dtype=np.float32)
+        eye[np.arange(rows), np.arange(rows) * 2] = 1.0
+        cols = linear_q(dev, eye, qw, rows)
+        assert np.array_equal(cols, want_w.reshape(k, n)[np.arange(rows) * 2])
+    qw.close()
