@@ -1,0 +1,235 @@
+// Decode attention, head_dim 64: one query row per stream against that stream's f32 K/V cache,
+// split along the context so that every SM streams cache (flash-decoding).
+//
+// Grid (split, kv-head, row). A CTA of 4 warps owns a contiguous range of cached positions of one
+// (stream, kv-head) and serves all G query heads that share the kv-head from one pass over K and V,
+// so the cache - the dominant HBM traffic of batched decode - is read exactly once per step.
+// A warp works on 4 positions at a time: 8 lanes per position, each lane holding 8 of the 64
+// channels (two 16-byte loads of K, two of V; a position's 256-byte row is one coalesced segment).
+// Scores are reduced over the 8 lanes with shuffles; the softmax is online with one rescale per
+// block of 4 positions per lane group. Lane groups, warps and finally splits are merged with the
+// usual (max, sum, weighted output) rule; with one split the CTA writes the result directly.
+// Replaces attn_gqd_probs.wgsl + attn_gqd_pv.wgsl (ferrum_wgpu/src/ops/llama.rs:L150-L179).
+#include "ops.cuh"
+
+namespace {
+
+constexpr int HD = 64;
+constexpr int POS_PER_ITER = 64; // positions a CTA consumes per loop iteration (4 warps x 4 groups x 4)
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// partial layout per (row, kv-head, split): [G] max (log2 domain), [G] sum, [G][64] weighted output
+template <int G>
+__global__ void __launch_bounds__(128)
+    attn_decode_split_kernel(const float* __restrict__ qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
+                             const int32_t* __restrict__ positions, const int32_t* __restrict__ streams, KvLayer kv,
+                             uint32_t ctx, uint32_t split_len, uint32_t n_splits, float* __restrict__ partial,
+                             float* __restrict__ out) {
+  __shared__ float sm_m[4][G], sm_l[4][G];
+  __shared__ __align__(16) float sm_o[4][G][HD];
+  const uint32_t split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
+  const uint32_t len = (uint32_t)positions[r] + 1;
+  const uint32_t p0 = split * split_len, p1 = min(len, p0 + split_len);
+  const uint32_t slot = streams ? (uint32_t)streams[r] : 0;
+  const float* kbase = kv.k + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
+  const float* vbase = kv.v + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
+
+  // this lane's 8 channels of each query head, pre-scaled by log2(e) / sqrt(64): scores live in the
+  // log2 domain so the exponentials are single ex2 instructions
+  float q[G][8];
+  const float qs = 0.125f * 1.4426950408889634f;
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    const float* qp = qkv + (size_t)r * q_stride + (size_t)(kvh * G + g) * HD + sub * 8;
+    const float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
+    q[g][0] = a.x * qs, q[g][1] = a.y * qs, q[g][2] = a.z * qs, q[g][3] = a.w * qs;
+    q[g][4] = b.x * qs, q[g][5] = b.y * qs, q[g][6] = b.z * qs, q[g][7] = b.w * qs;
+  }
+  float m[G], l[G], acc[G][8];
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    m[g] = -INFINITY, l[g] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[g][i] = 0.0f;
+  }
+
+  for (uint32_t j0 = p0; j0 < p1; j0 += POS_PER_ITER) {
+    // this lane group's 4 positions of the iteration
+    float s[4][G];
+    float4 vv[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t j = j0 + warp * 16 + i * 4 + grp;
+      const bool ok = j < p1;
+      const size_t off = (size_t)(ok ? j : p0) * HD;
+      const float4 k0 = *reinterpret_cast<const float4*>(kbase + off), k1 = *reinterpret_cast<const float4*>(kbase + off + 4);
+      vv[i][0] = *reinterpret_cast<const float4*>(vbase + off);
+      vv[i][1] = *reinterpret_cast<const float4*>(vbase + off + 4);
+#pragma unroll
+      for (int g = 0; g < G; g++) {
+        float d = q[g][0] * k0.x;
+        d = fmaf(q[g][1], k0.y, d), d = fmaf(q[g][2], k0.z, d), d = fmaf(q[g][3], k0.w, d);
+        d = fmaf(q[g][4], k1.x, d), d = fmaf(q[g][5], k1.y, d), d = fmaf(q[g][6], k1.z, d), d = fmaf(q[g][7], k1.w, d);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        s[i][g] = ok ? d : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+      const float bm = fmaxf(fmaxf(s[0][g], s[1][g]), fmaxf(s[2][g], s[3][g]));
+      const float mn = fmaxf(m[g], bm);
+      if (mn == -INFINITY) continue; // nothing valid yet for this group
+      const float corr = ex2(m[g] - mn);
+      m[g] = mn;
+      float p[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) p[i] = ex2(s[i][g] - mn);
+      l[g] = fmaf(l[g], corr, (p[0] + p[1]) + (p[2] + p[3]));
+#pragma unroll
+      for (int c = 0; c < 8; c++) {
+        float a = acc[g][c] * corr;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const float v = c < 4 ? (&vv[i][0].x)[c] : (&vv[i][1].x)[c - 4];
+          a = fmaf(p[i], v, a);
+        }
+        acc[g][c] = a;
+      }
+    }
+  }
+
+  // merge the 4 lane groups of the warp (lanes with equal `sub`)
+#pragma unroll
+  for (int g = 0; g < G; g++) {
+    float mm = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], 8));
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
+    const float sc = m[g] == -INFINITY ? 0.0f : ex2(m[g] - mm);
+    float ll = l[g] * sc;
+    ll += __shfl_xor_sync(0xffffffffu, ll, 8);
+    ll += __shfl_xor_sync(0xffffffffu, ll, 16);
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      float a = acc[g][c] * sc;
+      a += __shfl_xor_sync(0xffffffffu, a, 8);
+      a += __shfl_xor_sync(0xffffffffu, a, 16);
+      acc[g][c] = a;
+    }
+    m[g] = mm, l[g] = ll;
+    if (grp == 0) {
+      if (sub == 0) sm_m[warp][g] = mm, sm_l[warp][g] = ll;
+#pragma unroll
+      for (int c = 0; c < 8; c++) sm_o[warp][g][sub * 8 + c] = acc[g][c];
+    }
+  }
+  __syncthreads();
+  // merge the 4 warps: thread t handles channel t % 64 of heads g = t / 64, t / 64 + 2, ...
+  for (int g = threadIdx.x / HD; g < G; g += 2) {
+    const int c = threadIdx.x % HD;
+    float mm = fmaxf(fmaxf(sm_m[0][g], sm_m[1][g]), fmaxf(sm_m[2][g], sm_m[3][g]));
+    float ll = 0.0f, o = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float sc = sm_m[w][g] == -INFINITY ? 0.0f : ex2(sm_m[w][g] - mm);
+      ll = fmaf(sm_l[w][g], sc, ll);
+      o = fmaf(sm_o[w][g][c], sc, o);
+    }
+    if (n_splits == 1) {
+      out[(size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c] = o / ll;
+    } else {
+      float* p = partial + (((size_t)r * kv_heads + kvh) * n_splits + split) * (size_t)(G * (2 + HD));
+      if (c == 0) p[g] = mm, p[G + g] = ll;
+      p[2 * G + g * HD + c] = o;
+    }
+  }
+}
+
+// out[row][head][c] = merge over splits
+template <int G>
+__global__ void attn_decode_merge_kernel(const float* __restrict__ partial, uint32_t heads, uint32_t kv_heads,
+                                         uint32_t n_splits, float* __restrict__ out) {
+  const uint32_t kvh = blockIdx.x, r = blockIdx.y;
+  const float* base = partial + ((size_t)r * kv_heads + kvh) * n_splits * (size_t)(G * (2 + HD));
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    const int g = idx / HD, c = idx % HD;
+    float mm = -INFINITY;
+    for (uint32_t s = 0; s < n_splits; s++) mm = fmaxf(mm, base[(size_t)s * G * (2 + HD) + g]);
+    float ll = 0.0f, o = 0.0f;
+    for (uint32_t s = 0; s < n_splits; s++) {
+      const float* p = base + (size_t)s * G * (2 + HD);
+      const float sc = p[g] == -INFINITY ? 0.0f : ex2(p[g] - mm);
+      ll = fmaf(p[G + g], sc, ll);
+      o = fmaf(p[2 * G + g * HD + c], sc, o);
+    }
+    out[(size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c] = o / ll;
+  }
+}
+
+template <int G>
+int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+           const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t split_len,
+           uint32_t n_splits, float* scratch, float* out) {
+  dim3 grid(n_splits, kv_heads, rows);
+  FC_LAUNCH(dev, "attn_decode",
+            attn_decode_split_kernel<G><<<grid, 128, 0, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
+                                                                       split_len, n_splits, scratch, out));
+  if (n_splits > 1) {
+    dim3 mg(kv_heads, rows);
+    FC_LAUNCH(dev, "attn_decode_merge",
+              attn_decode_merge_kernel<G><<<mg, 128, 0, dev->stream>>>(scratch, heads, kv_heads, n_splits, out));
+  }
+  return FC_OK;
+}
+
+} // namespace
+
+// How the context is cut for `rows` streams: enough CTAs to cover the SMs about twice, ranges a
+// multiple of 64 positions. The grid depends only on (rows, ctx), never on the current positions, so a
+// captured decode step can be replayed; a CTA whose range lies beyond the row's length contributes
+// an empty partial.
+void attn_decode_plan(const FcDevice* dev, uint32_t rows, uint32_t kv_heads, uint32_t ctx, uint32_t* split_len,
+                      uint32_t* n_splits) {
+  const uint32_t want = 2 * (uint32_t)dev->prop.multiProcessorCount;
+  uint32_t base = rows * kv_heads, s = (want + base - 1) / base;
+  const uint32_t max_s = (ctx + POS_PER_ITER - 1) / POS_PER_ITER;
+  if (s > max_s) s = max_s;
+  if (s < 1) s = 1;
+  uint32_t sl = ((ctx + s - 1) / s + POS_PER_ITER - 1) / POS_PER_ITER * POS_PER_ITER;
+  *split_len = sl;
+  *n_splits = (ctx + sl - 1) / sl;
+}
+
+size_t attn_decode_scratch_bytes(const FcDevice* dev, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t ctx) {
+  uint32_t sl, ns;
+  attn_decode_plan(dev, rows, kv_heads, ctx, &sl, &ns);
+  return (size_t)rows * kv_heads * ns * (heads / kv_heads) * (2 + HD) * 4 + 256;
+}
+
+bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd) {
+  const uint32_t G = heads / kv_heads;
+  return hd == HD && (G == 1 || G == 2 || G == 3 || G == 4 || G == 6 || G == 8);
+}
+
+int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
+                        const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
+                        float* out) {
+  if (!rows) return FC_OK;
+  uint32_t sl, ns;
+  attn_decode_plan(dev, rows, kv_heads, ctx, &sl, &ns);
+  switch (heads / kv_heads) {
+    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+  }
+  return fc_fail(dev, FC_ERR_UNSUPPORTED, "split decode attention: group size %u", heads / kv_heads);
+}

@@ -132,6 +132,15 @@ int alloc_common(FcModel* m) {
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_pos));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
+  // partial results of the context-split decode attention: the largest need over every batch width
+  if (attn_decode_split_supports(m->heads, m->kv_heads, m->hd)) {
+    size_t need = 0;
+    for (uint32_t rows = 1; rows <= s; rows++) {
+      const size_t b = attn_decode_scratch_bytes(m->dev, rows, m->heads, m->kv_heads, m->ctx);
+      need = b > need ? b : need;
+    }
+    FC_TRY(dev_alloc(m, need, (void**)&m->attn_scratch));
+  }
   // scratch of the batched-decode tensor product (x split + split-K partials), sized for the widest matrix
   if (s > 8) {
     size_t need = qmatvec_mma_scratch_bytes(m->head.w->m.k, m->head.w->m.n);
@@ -182,7 +191,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
                      to_cache ? &l.kv : nullptr, m->ctx));
     if (mode == ATTN_DECODE)
       FC_TRY(k_attn_decode(dev, b.qkv, m->qkv_w(), rows, m->heads, m->kv_heads, m->hd, positions, streams, l.kv, m->ctx,
-                           b.attn));
+                           b.attn, m->attn_scratch));
     else if (mode == ATTN_STATELESS)
       FC_TRY(k_attn_causal_f32(dev, b.qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, b.attn));
     else
