@@ -1,17 +1,18 @@
-// Causal attention for the scoring path, f16 operands with f32 softmax and accumulation, never
+// Causal attention for the scoring path, fp16 operands with f32 softmax and accumulation, never
 // materialising the [t, t] probabilities. Replaces attn_gqa_scores.wgsl + attn_softmax.wgsl +
 // attn_gqa_pv.wgsl and their MHA twins (ferrum_wgpu/src/ops/llama.rs:L119-L146,
 // ops/mod.rs:L108-L127), which write and re-read a [batch * heads * t, t] buffer.
 //
-// One CTA of 4 warps owns 64 query rows of one (sequence, head); each warp 16 of them. K and V
-// tiles of 64 keys stream through a double-buffered, XOR-swizzled shared-memory ring (cp.async);
+// One CTA of 4 warps owns 64 * MT query rows of one (sequence, head); each warp MT tiles of 16 rows,
+// which share every K / V fragment it loads (MT = 2 halves the shared-memory traffic per MMA). K and
+// V tiles of 64 keys stream through a double-buffered, XOR-swizzled shared-memory ring (cp.async);
 // S = Q K^T and O += P V run on mma.sync m16n8k16 with ldmatrix-fed fragments, the running row
 // maximum and sum live in registers (online softmax). head_dim is 64.
 #include "gemm_tc.cuh"
 
 namespace {
 
-constexpr int BQ = 64, BKV = 64, HD = 64;
+constexpr int BKV = 64, HD = 64;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -43,15 +44,19 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
-// address of 16-byte chunk `ch` of row `row` in a [64][64] f16 tile with the XOR swizzle
+// address of 16-byte chunk `ch` of row `row` in a [rows][64] fp16 tile with the XOR swizzle
 __device__ __forceinline__ uint32_t tile_addr(uint32_t tile, uint32_t row, uint32_t ch) {
   return tile + row * 128 + ((ch ^ (row & 7)) << 4);
 }
 
-// 64 rows x 64 f16 from `src` (row stride `stride` elements; rows clamped to max_row) into a tile
-__device__ __forceinline__ void load_tile(uint32_t tile, const __half* src, uint32_t row0, uint32_t max_row,
-                                          size_t stride) {
+// 64 rows x 64 fp16 from `src` (row stride `stride` elements; rows clamped to max_row) into a tile
+__device__ __forceinline__ void load_tile(uint32_t tile, const __half* src, uint32_t row0, uint32_t max_row, size_t stride) {
 #pragma unroll
   for (int i = 0; i < 4; i++) {
     const uint32_t c = threadIdx.x + 128 * i;
@@ -61,9 +66,11 @@ __device__ __forceinline__ void load_tile(uint32_t tile, const __half* src, uint
   }
 }
 
+template <int MT>
 __global__ void __launch_bounds__(128)
     attn_causal_f16_kernel(const __half* __restrict__ qkv, uint32_t t, uint32_t heads, uint32_t kv_heads,
-                            __half* __restrict__ out) {
+                           __half* __restrict__ out) {
+  constexpr int BQ = 64 * MT;
   __shared__ __align__(1024) uint8_t sm[BQ * 128 + 2 * 2 * BKV * 128];
   const uint32_t q_tile = smem_u32(sm);
   const uint32_t kv_tiles = q_tile + BQ * 128;
@@ -79,18 +86,25 @@ __global__ void __launch_bounds__(128)
   const __half* vsrc = ksrc + kvd;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
   const uint32_t q0 = qb * BQ;
-  const uint32_t n_kv = qb + 1; // causal: key blocks 0..qb
+  const uint32_t wrow0 = q0 + warp * 16 * MT;                        // first query row of this warp
+  const uint32_t n_kv = min((q0 + BQ + BKV - 1) / BKV, (t + BKV - 1) / BKV); // causal: key blocks up to the last row's
 
-  load_tile(q_tile, qsrc, q0, t - 1, stride);
+#pragma unroll
+  for (int i = 0; i < MT; i++) load_tile(q_tile + i * 64 * 128, qsrc, q0 + i * 64, t - 1, stride);
   load_tile(kv_tiles, ksrc, 0, t - 1, stride);
   load_tile(kv_tiles + BKV * 128, vsrc, 0, t - 1, stride);
   cp_async_commit();
 
-  float o[8][4];
+  float o[MT][8][4];
+  float m_run[MT][2], l_run[MT][2];
 #pragma unroll
-  for (int i = 0; i < 8; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
-  uint32_t qf[4][4];
+  for (int mt = 0; mt < MT; mt++) {
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
+  }
+  uint32_t qf[MT][4][4];
   const float sl2 = 0.125f * 1.4426950408889634f; // 1/sqrt(64) * log2(e)
 
   for (uint32_t kb = 0; kb < n_kv; kb++) {
@@ -108,116 +122,141 @@ __global__ void __launch_bounds__(128)
     __syncthreads();
     if (kb == 0) {
 #pragma unroll
+      for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int ks = 0; ks < 4; ks++) {
+          const uint32_t row = warp * 16 * MT + mt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          ldmatrix_x4(tile_addr(q_tile, row, 2 * ks + (lane >> 4)), qf[mt][ks][0], qf[mt][ks][1], qf[mt][ks][2], qf[mt][ks][3]);
+        }
+    }
+    // every key of this block lies after every row of this warp: nothing to do but keep the barriers
+    if (kb * BKV <= wrow0 + 16 * MT - 1) {
+      // S = Q K^T: MT x (16 x 64) per warp, each K fragment used by all MT row tiles
+      float s[MT][8][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) s[mt][i][0] = s[mt][i][1] = s[mt][i][2] = s[mt][i][3] = 0.0f;
+#pragma unroll
       for (int ks = 0; ks < 4; ks++) {
-        const uint32_t row = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-        ldmatrix_x4(tile_addr(q_tile, row, 2 * ks + (lane >> 4)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+#pragma unroll
+        for (int nb = 0; nb < 8; nb += 2) {
+          uint32_t b0, b1, b2, b3;
+          const uint32_t key = nb * 8 + (lane & 7) + 8 * (lane >> 4);
+          ldmatrix_x4(tile_addr(k_tile, key, 2 * ks + ((lane >> 3) & 1)), b0, b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < MT; mt++) {
+            mma_16816(s[mt][nb], qf[mt][ks], b0, b1);
+            mma_16816(s[mt][nb + 1], qf[mt][ks], b2, b3);
+          }
+        }
       }
-    }
-    // S = Q K^T: 16 x 64 per warp
-    float s[8][4];
+      uint32_t pf[MT][4][4]; // P as A fragments: k-step ks covers keys 16ks..16ks+15 = n-blocks 2ks, 2ks+1
 #pragma unroll
-    for (int i = 0; i < 8; i++) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+      for (int mt = 0; mt < MT; mt++) {
+        // causal mask where the block reaches past the tile's first row, then online softmax
+        const uint32_t qi0 = wrow0 + mt * 16 + g;
+        if (kb * BKV + BKV - 1 > wrow0 + mt * 16) {
 #pragma unroll
-    for (int ks = 0; ks < 4; ks++) {
+          for (int nb = 0; nb < 8; nb++) {
+            const uint32_t kj = kb * BKV + nb * 8 + 2 * tq;
+            if (kj > qi0) s[mt][nb][0] = -INFINITY;
+            if (kj + 1 > qi0) s[mt][nb][1] = -INFINITY;
+            if (kj > qi0 + 8) s[mt][nb][2] = -INFINITY;
+            if (kj + 1 > qi0 + 8) s[mt][nb][3] = -INFINITY;
+          }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int nb = 0; nb < 8; nb += 2) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t key = nb * 8 + (lane & 7) + 8 * (lane >> 4);
-        ldmatrix_x4(tile_addr(k_tile, key, 2 * ks + ((lane >> 3) & 1)), b0, b1, b2, b3);
-        mma_16816(s[nb], qf[ks], b0, b1);
-        mma_16816(s[nb + 1], qf[ks], b2, b3);
+        for (int nb = 0; nb < 8; nb++) {
+          mx[0] = fmaxf(mx[0], fmaxf(s[mt][nb][0], s[mt][nb][1]));
+          mx[1] = fmaxf(mx[1], fmaxf(s[mt][nb][2], s[mt][nb][3]));
+        }
+        float corr[2], msc[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+          mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+          // key 0 is never masked and block 0 is never skipped, so the running maximum is finite from
+          // the first processed block on; a fully masked row of a later block keeps it
+          const float m_new = fmaxf(m_run[mt][r], mx[r]);
+          corr[r] = ex2((m_run[mt][r] - m_new) * sl2);
+          m_run[mt][r] = m_new;
+          msc[r] = m_new * sl2;
+          l_run[mt][r] *= corr[r];
+        }
+        float ls[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int nb = 0; nb < 8; nb++) {
+          const float p0 = ex2(s[mt][nb][0] * sl2 - msc[0]), p1 = ex2(s[mt][nb][1] * sl2 - msc[0]);
+          const float p2 = ex2(s[mt][nb][2] * sl2 - msc[1]), p3 = ex2(s[mt][nb][3] * sl2 - msc[1]);
+          ls[0] += p0 + p1;
+          ls[1] += p2 + p3;
+          pf[mt][nb >> 1][(nb & 1) * 2] = pack_f16(p0, p1);     // row g
+          pf[mt][nb >> 1][(nb & 1) * 2 + 1] = pack_f16(p2, p3); // row g + 8
+        }
+        l_run[mt][0] += ls[0];
+        l_run[mt][1] += ls[1];
+#pragma unroll
+        for (int db = 0; db < 8; db++) {
+          o[mt][db][0] *= corr[0];
+          o[mt][db][1] *= corr[0];
+          o[mt][db][2] *= corr[1];
+          o[mt][db][3] *= corr[1];
+        }
       }
-    }
-    // causal mask on the diagonal block, then online softmax (rows g and g + 8 of the warp's 16)
-    const uint32_t qi0 = q0 + warp * 16 + g;
-    if (kb == qb) {
+      // O += P V, each V fragment used by all MT row tiles
 #pragma unroll
-      for (int nb = 0; nb < 8; nb++) {
-        const uint32_t kj = kb * BKV + nb * 8 + 2 * tq;
-        if (kj > qi0) s[nb][0] = -INFINITY;
-        if (kj + 1 > qi0) s[nb][1] = -INFINITY;
-        if (kj > qi0 + 8) s[nb][2] = -INFINITY;
-        if (kj + 1 > qi0 + 8) s[nb][3] = -INFINITY;
-      }
-    }
-    float mx[2] = {-INFINITY, -INFINITY};
+      for (int ks = 0; ks < 4; ks++) {
 #pragma unroll
-    for (int nb = 0; nb < 8; nb++) {
-      mx[0] = fmaxf(mx[0], fmaxf(s[nb][0], s[nb][1]));
-      mx[1] = fmaxf(mx[1], fmaxf(s[nb][2], s[nb][3]));
-    }
+        for (int db = 0; db < 8; db += 2) {
+          uint32_t b0, b1, b2, b3;
+          const uint32_t key = ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          ldmatrix_x4_trans(tile_addr(v_tile, key, db + (lane >> 4)), b0, b1, b2, b3);
 #pragma unroll
-    for (int r = 0; r < 2; r++) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-    }
-    float corr[2], msc[2];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      const float m_new = fmaxf(m_run[r], mx[r]); // key 0 is never masked, so m_new is finite
-      corr[r] = exp2f((m_run[r] - m_new) * sl2);
-      m_run[r] = m_new;
-      msc[r] = m_new * sl2;
-      l_run[r] *= corr[r];
-    }
-    uint32_t pf[4][4]; // P as A fragments: k-step ks covers keys 16ks..16ks+15 = n-blocks 2ks, 2ks+1
-    float ls[2] = {0.0f, 0.0f};
-#pragma unroll
-    for (int nb = 0; nb < 8; nb++) {
-      const float p0 = exp2f(s[nb][0] * sl2 - msc[0]), p1 = exp2f(s[nb][1] * sl2 - msc[0]);
-      const float p2 = exp2f(s[nb][2] * sl2 - msc[1]), p3 = exp2f(s[nb][3] * sl2 - msc[1]);
-      ls[0] += p0 + p1;
-      ls[1] += p2 + p3;
-      pf[nb >> 1][(nb & 1) * 2] = pack_f16(p0, p1);     // row g
-      pf[nb >> 1][(nb & 1) * 2 + 1] = pack_f16(p2, p3); // row g + 8
-    }
-    l_run[0] += ls[0];
-    l_run[1] += ls[1];
-#pragma unroll
-    for (int db = 0; db < 8; db++) {
-      o[db][0] *= corr[0];
-      o[db][1] *= corr[0];
-      o[db][2] *= corr[1];
-      o[db][3] *= corr[1];
-    }
-    // O += P V
-#pragma unroll
-    for (int ks = 0; ks < 4; ks++) {
-#pragma unroll
-      for (int db = 0; db < 8; db += 2) {
-        uint32_t b0, b1, b2, b3;
-        const uint32_t key = ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-        ldmatrix_x4_trans(tile_addr(v_tile, key, db + (lane >> 4)), b0, b1, b2, b3);
-        mma_16816(o[db], pf[ks], b0, b1);
-        mma_16816(o[db + 1], pf[ks], b2, b3);
+          for (int mt = 0; mt < MT; mt++) {
+            mma_16816(o[mt][db], pf[mt][ks], b0, b1);
+            mma_16816(o[mt][db + 1], pf[mt][ks], b2, b3);
+          }
+        }
       }
     }
     __syncthreads(); // everyone is done with this buffer before the next prefetch overwrites it
   }
   // row sums live per thread: combine the 4 threads of a row, normalise, store
 #pragma unroll
-  for (int r = 0; r < 2; r++) {
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
-  }
-  const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
-  const uint32_t r0 = q0 + warp * 16 + g, r1 = r0 + 8;
+  for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
-  for (int db = 0; db < 8; db++) {
-    const uint32_t col = h * HD + db * 8 + 2 * tq;
-    if (r0 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r0) * qd + col) = pack_f16(o[db][0] * inv0, o[db][1] * inv0);
-    if (r1 < t) *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r1) * qd + col) = pack_f16(o[db][2] * inv1, o[db][3] * inv1);
+    for (int r = 0; r < 2; r++) {
+      l_run[mt][r] += __shfl_xor_sync(0xffffffffu, l_run[mt][r], 1);
+      l_run[mt][r] += __shfl_xor_sync(0xffffffffu, l_run[mt][r], 2);
+    }
+    const float inv0 = 1.0f / l_run[mt][0], inv1 = 1.0f / l_run[mt][1];
+    const uint32_t r0 = wrow0 + mt * 16 + g, r1 = r0 + 8;
+#pragma unroll
+    for (int db = 0; db < 8; db++) {
+      const uint32_t col = h * HD + db * 8 + 2 * tq;
+      if (r0 < t)
+        *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r0) * qd + col) = pack_f16(o[mt][db][0] * inv0, o[mt][db][1] * inv0);
+      if (r1 < t)
+        *reinterpret_cast<uint32_t*>(out + ((size_t)seq * t + r1) * qd + col) = pack_f16(o[mt][db][2] * inv1, o[mt][db][3] * inv1);
+    }
   }
 }
 
 } // namespace
 
-int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads,
-                       uint32_t kv_heads, uint32_t hd, __half* out) {
+int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
+                      uint32_t hd, __half* out) {
   if (!n_seqs || !t) return FC_OK;
   if (hd != HD) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core attention is built for head_dim 64, not %u", hd);
-  dim3 grid((t + BQ - 1) / BQ, heads, n_seqs);
   if (n_seqs > 65535) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u sequences exceed one attention launch", n_seqs);
-  FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
+  if (t > 64) { // two 16-row tiles per warp
+    dim3 grid((t + 127) / 128, heads, n_seqs);
+    FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<2><<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
+  } else {
+    dim3 grid((t + 63) / 64, heads, n_seqs);
+    FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<1><<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
+  }
   return FC_OK;
 }
