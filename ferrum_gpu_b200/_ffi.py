@@ -83,7 +83,7 @@ class FcGpt2Weights(C.Structure):
 EXPORTS = (
     "fc_device_open", "fc_device_close", "fc_device_name", "fc_device_props", "fc_last_error",
     "fc_device_stream", "fc_device_sync", "fc_device_launch_count", "fc_debug_fail_after",
-    "fc_debug_profile", "fc_debug_profile_report",
+    "fc_debug_profile", "fc_debug_profile_report", "fc_debug_attention_f16",
     "fc_block_bytes", "fc_qweight_create", "fc_qweight_create_from_blocks", "fc_qweight_destroy",
     "fc_qweight_info", "fc_qweight_blocks", "fc_dequant", "fc_qmatmul", "fc_qmatmul_dev",
     "fc_qmatmul_dev_noalloc",
@@ -129,6 +129,7 @@ def load() -> C.CDLL:
         "fc_debug_fail_after": (C.c_int, [vp, i64]),
         "fc_debug_profile": (C.c_int, [vp, C.c_int]),
         "fc_debug_profile_report": (C.c_int, [vp, C.c_char_p, sz]),
+        "fc_debug_attention_f16": (C.c_int, [vp, vp, u32, u32, u32, u32, vp, C.c_int, C.c_int, P(C.c_float)]),
         "fc_block_bytes": (sz, [C.c_int, sz]),
         "fc_qweight_create": (C.c_int, [vp, C.c_int, vp, u32, u32, P(vp)]),
         "fc_qweight_create_from_blocks": (C.c_int, [vp, C.c_int, vp, sz, u32, u32, P(vp)]),

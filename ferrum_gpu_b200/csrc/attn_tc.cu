@@ -246,12 +246,22 @@ __global__ void __launch_bounds__(128)
 
 } // namespace
 
-int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
-                      uint32_t hd, __half* out) {
+// attn_tmem.cu
+bool attn_tmem_supports(uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads, uint32_t hd);
+int k_attn_causal_tmem(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
+                       uint32_t hd, __half* out);
+
+// variant: 0 picks by sequence length, 1 / 2 the mma.sync kernel with one / two row tiles per warp,
+// 3 the tcgen05 kernel
+int k_attn_causal_f16_variant(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads,
+                              uint32_t kv_heads, uint32_t hd, __half* out, int variant) {
   if (!n_seqs || !t) return FC_OK;
   if (hd != HD) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core attention is built for head_dim 64, not %u", hd);
   if (n_seqs > 65535) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u sequences exceed one attention launch", n_seqs);
-  if (t > 64) { // two 16-row tiles per warp
+  if (!kv_heads || heads % kv_heads) return fc_fail(dev, FC_ERR_SHAPE, "%u query heads over %u kv heads", heads, kv_heads);
+  if (variant == 0) variant = (t > 128 && attn_tmem_supports(n_seqs, t, heads, kv_heads, hd)) ? 3 : 1;
+  if (variant == 3) return k_attn_causal_tmem(dev, qkv, n_seqs, t, heads, kv_heads, hd, out);
+  if (variant == 2) {
     dim3 grid((t + 127) / 128, heads, n_seqs);
     FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<2><<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
   } else {
@@ -259,4 +269,50 @@ int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_
     FC_LAUNCH(dev, "attn_causal_f16", attn_causal_f16_kernel<1><<<grid, 128, 0, dev->stream>>>(qkv, t, heads, kv_heads, out));
   }
   return FC_OK;
+}
+
+int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
+                      uint32_t hd, __half* out) {
+  return k_attn_causal_f16_variant(dev, qkv, n_seqs, t, heads, kv_heads, hd, out, 0);
+}
+
+// Stand-alone causal attention over a packed fp16 [n_seqs * t][(heads + 2 kv_heads) * 64] host buffer
+// (q heads | k heads | v heads per row); the result is fp16 [n_seqs * t][heads * 64]. Test and
+// measurement hook: `iters` back-to-back launches, the average device time of one is returned.
+FC_API int fc_debug_attention_f16(FcDevice* dev, const uint16_t* qkv_host, uint32_t n_seqs, uint32_t t, uint32_t heads,
+                                  uint32_t kv_heads, uint16_t* out_host, int variant, int iters, float* ms_out) {
+  if (!dev || !qkv_host || !out_host) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  if (!n_seqs || !t || !heads || !kv_heads) return fc_fail(dev, FC_ERR_SHAPE, "empty attention problem");
+  const size_t rows = (size_t)n_seqs * t, in_elems = rows * (heads + 2 * kv_heads) * HD, out_elems = rows * heads * HD;
+  __half *d_in = nullptr, *d_out = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  int rc = FC_OK;
+  auto body = [&]() -> int {
+    FC_CUDA(dev, cudaMalloc(&d_in, in_elems * 2));
+    FC_CUDA(dev, cudaMalloc(&d_out, out_elems * 2));
+    FC_CUDA(dev, cudaMemcpyAsync(d_in, qkv_host, in_elems * 2, cudaMemcpyHostToDevice, dev->stream));
+    FC_CUDA(dev, cudaMemsetAsync(d_out, 0, out_elems * 2, dev->stream));
+    FC_CUDA(dev, cudaEventCreate(&e0));
+    FC_CUDA(dev, cudaEventCreate(&e1));
+    FC_TRY(k_attn_causal_f16_variant(dev, d_in, n_seqs, t, heads, kv_heads, HD, d_out, variant)); // warm-up, checked below
+    FC_CUDA(dev, cudaEventRecord(e0, dev->stream));
+    for (int i = 0; i < iters; i++) FC_TRY(k_attn_causal_f16_variant(dev, d_in, n_seqs, t, heads, kv_heads, HD, d_out, variant));
+    FC_CUDA(dev, cudaEventRecord(e1, dev->stream));
+    FC_CUDA(dev, cudaMemcpyAsync(out_host, d_out, out_elems * 2, cudaMemcpyDeviceToHost, dev->stream));
+    FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    FC_TRY(tc_check_errors(dev));
+    if (ms_out) {
+      float ms = 0.0f;
+      FC_CUDA(dev, cudaEventElapsedTime(&ms, e0, e1));
+      *ms_out = iters > 0 ? ms / (float)iters : 0.0f;
+    }
+    return FC_OK;
+  };
+  rc = body();
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (d_in) cudaFree(d_in);
+  if (d_out) cudaFree(d_out);
+  return rc;
 }

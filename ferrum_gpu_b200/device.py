@@ -88,6 +88,23 @@ class Device:
         self.check(self._lib.fc_debug_profile_report(self._h, buf, len(buf)))
         return json.loads(buf.value.decode())
 
+    def attention_f16(self, qkv, n_seqs: int, t: int, heads: int, kv_heads: int, variant: int = 0, iters: int = 0):
+        """Causal attention over packed fp16 rows (q heads | k heads | v heads, head_dim 64).
+
+        Returns (out fp16 [n_seqs * t, heads * 64], mean milliseconds of `iters` timed launches).
+        variant 0 = the kernel the model passes pick, 1 / 2 = mma.sync with one / two row tiles per
+        warp, 3 = tcgen05 with tensor-memory accumulators."""
+        import numpy as np
+        qkv = np.ascontiguousarray(qkv, dtype=np.float16)
+        rows = n_seqs * t
+        if qkv.size != rows * (heads + 2 * kv_heads) * 64:
+            raise ValueError("qkv must hold n_seqs * t rows of (heads + 2 * kv_heads) * 64 values")
+        out = np.empty((rows, heads * 64), dtype=np.float16)
+        ms = C.c_float(0.0)
+        self.check(self._lib.fc_debug_attention_f16(self._h, qkv.ctypes.data, n_seqs, t, heads, kv_heads,
+                                                    out.ctypes.data, variant, iters, C.byref(ms)))
+        return out, ms.value
+
     def fail_after(self, n: int | None):
         """`Gpu::fail_after` (device/runtime.rs:L214-L256): refuse launches after `n` more; None disarms."""
         self.check(self._lib.fc_debug_fail_after(self._h, -1 if n is None else n))

@@ -92,6 +92,16 @@ int fc_debug_fail_after(FcDevice* dev, int64_t n_launches);
  * synchronises the stream. Off by default. */
 int fc_debug_profile(FcDevice* dev, int enable);
 int fc_debug_profile_report(FcDevice* dev, char* buf, size_t buf_len);
+/* The scoring path's causal attention on its own: the fused replacement of the reference's
+ * attn_gqa_scores + attn_softmax + attn_gqa_pv dispatches (ferrum_wgpu/src/ops/llama.rs:L119-L146;
+ * MHA when kv_heads == heads, ops/mod.rs:L108-L127). `qkv_host` is fp16 (IEEE binary16 bit patterns)
+ * [n_seqs * t][(heads + 2 * kv_heads) * 64], each row q heads | k heads | v heads, head_dim 64;
+ * `out_host` receives fp16 [n_seqs * t][heads * 64]. `variant`: 0 = what the model passes use,
+ * 1 / 2 = the mma.sync kernel with one / two row tiles per warp, 3 = the tcgen05 / tensor-memory
+ * kernel. After one warm-up launch `iters` launches are timed with CUDA events and their mean
+ * (milliseconds) is written to `ms_out` when it is not NULL. Test and measurement hook. */
+int fc_debug_attention_f16(FcDevice* dev, const uint16_t* qkv_host, uint32_t n_seqs, uint32_t t, uint32_t heads,
+                           uint32_t kv_heads, uint16_t* out_host, int variant, int iters, float* ms_out);
 
 /* ---- stand-alone quantised weights and products ------------------------------------------ */
 /* Bytes of a GGUF tensor of `n_elems` elements (ferrum_gguf/src/codec/quant.rs:L17-L46);
