@@ -241,7 +241,8 @@ def main():
                       "qgemm_tc_lse": 2.0 * cfg.dim * cfg.vocab}
         by_role = {k: round(f * rows / (prof[k]["ms"] * 1e-3) / 1e12, 1) for k, f in role_flops.items()
                    if k in prof and prof[k]["ms"] > 0}
-        attn_tf = attn_flops * rows / (prof["attn_causal_f16"]["ms"] * 1e-3) / 1e12 if "attn_causal_f16" in prof else None
+        attn_ms = sum(prof[k]["ms"] for k in ("attn_causal_tmem", "attn_causal_f16") if k in prof)
+        attn_tf = attn_flops * rows / (attn_ms * 1e-3) / 1e12 if attn_ms > 0 else None
         shares = {k: round(v["ms"] / total_ms, 4) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])}
         out = {
             "metric": METRIC, "value": world * rows / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world,

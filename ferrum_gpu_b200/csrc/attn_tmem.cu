@@ -5,26 +5,31 @@
 // replaces attn_gqa_scores.wgsl + attn_softmax.wgsl + attn_gqa_pv.wgsl
 // (ferrum_wgpu/src/ops/llama.rs:L119-L146) without materialising the [t, t] probabilities.
 //
-// One CTA owns 256 query rows of one (sequence, head) as two 128-row halves that leapfrog: while the
-// softmax warps of one half turn S into P, the tensor pipe runs the other half's MMAs.
+// Persistent: one CTA per SM walks work items (sequence, head, block of 256 query rows), heaviest
+// blocks first. An item's rows are two 128-row halves with their own accumulators, so the tensor pipe
+// always has the other half's MMAs to run while one half's softmax warps are busy.
 //
-//   warp 0      TMA: Q halves once, then the K and V tiles of 128 keys through a ring of KS stages
-//   warp 1      TMEM owner and MMA issuer (one elected lane), per key tile j:
-//                 O0 += P0 V_j | S0 = Q0 K_{j+1}^T | O1 += P1 V_j | S1 = Q1 K_{j+1}^T
+//   warp 0      TMA: the item's two Q halves, then its K and V tiles of 128 keys through a ring of KS
+//               stages; runs ahead into the next item
+//   warp 1      TMEM owner and MMA issuer (the warp walks the schedule, one elected lane issues), per
+//               key tile j:  S0 = Q0 K_{j+1}^T | S1 = Q1 K_{j+1}^T  as soon as the scores of tile j are
+//               in registers (they run under the softmax of tile j), then O0 += P0 V_j | O1 += P1 V_j
 //   warps 4-7   softmax of half 0 (thread = query row): row max, p = 2^(s*c - m*c) as fp16 back into
 //               tensor memory (the A operand of the P V product is read from there, so the
 //               probabilities never touch shared memory), running sum,
 //   warps 8-11  the same for half 1.   O accumulates in tensor memory over the key tiles; when a
 //               row's maximum has moved by more than 2^8 the row's thread rescales its O row in
-//               place (tcgen05.ld / st) before it publishes P - it owns S, P and O of its half
-//               between s_full and p_full, so no further barrier is needed.
+//               place (tcgen05.ld / st) once the previous P V has landed (pv_done).
+//   setmaxnreg moves registers from warps 0-3 (56) to the softmax warps (224): a row's 128 scores
+//   stay in registers from the maximum to the packed probabilities.
 //
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,320) O1 [320,384) P0 [384,448) P1 [448,512)
 // (P: two fp16 per 32-bit column).
-// Barriers: q_full[2], k_full/k_empty[KS], v_full/v_empty[KS] (TMA bytes / MMA commits), s_full[h]
-// (commit after S_h; the in-order tensor pipe makes it also mean "P_h V of the previous tile is
-// complete"), p_full[h] (4 softmax warps: S_h consumed, O_h rescaled, P_h written), o_full[h]
-// (commit after the last P V). Every wait is bounded and raises a CTA-wide abort word.
+// Barriers: q_full / q_empty[2] (TMA bytes / commit after the item's last S of the half),
+// k_full / k_empty[KS], v_full / v_empty[KS] (TMA bytes / MMA commits), s_full[h] (commit after S_h),
+// s_free[h] (4 softmax warps: the scores are in registers), p_full[h] (4 softmax warps: P_h written,
+// O_h rescaled), pv_done[h] (commit after O_h += P_h V: P_h may be overwritten, O_h read or rescaled).
+// Phases run on across items. Every wait is bounded and raises a CTA-wide abort word.
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
 
