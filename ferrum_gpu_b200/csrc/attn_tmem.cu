@@ -43,6 +43,11 @@ constexpr uint32_t OFF_BAR = OFF_V + KS * TILE_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_BAR + 512 + 1024; // + alignment slack
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
+// setmaxnreg targets (4 control warps, 8 softmax warps). The pool is what the CTA was launched with
+// (threads x registers per thread as compiled); an increase that does not fit waits forever, so the
+// launch code checks the sum against the compiled register count first.
+constexpr int REGS_CTRL = 56, REGS_SOFTMAX = 224;
+constexpr int REGS_NEEDED = 32 * (4 * REGS_CTRL + 8 * REGS_SOFTMAX);
 enum { ERR_ATTN_LOAD = 11, ERR_ATTN_MMA = 12, ERR_ATTN_SOFTMAX = 13 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
@@ -142,7 +147,7 @@ __global__ void __launch_bounds__(THREADS, 1)
   // 12 warps share the register file at 168 each; the softmax rows want their 128 scores in
   // registers, the copy and MMA warps need few: move the budget (56 + 2 x 224 <= 512 per lane slot)
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CTRL));
     if (warp == 0) {
       // ---- TMA: runs ahead of the MMAs by the depth of the K / V ring, across work items ----
       if (lane == 0 && !*abort_word) {
@@ -273,7 +278,7 @@ __global__ void __launch_bounds__(THREADS, 1)
       }
     }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
     // ---- softmax, one query row per thread ----
     const uint32_t half = (warp - 4) >> 2, quad = warp & 3;
     const uint32_t r = quad * 32 + lane;             // row within the half = TMEM lane
@@ -447,6 +452,11 @@ int k_attn_causal_tmem(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32
   if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);
   static bool attr = false;
   if (!attr) {
+    cudaFuncAttributes fa;
+    FC_CUDA(dev, cudaFuncGetAttributes(&fa, attn_tmem_kernel));
+    if (fa.numRegs * THREADS < REGS_NEEDED)
+      return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-memory attention was compiled with %d registers per thread; its "
+                     "register rebalancing needs %d", fa.numRegs, (REGS_NEEDED + THREADS - 1) / THREADS);
     FC_CUDA(dev, cudaFuncSetAttribute(attn_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr = true;
   }

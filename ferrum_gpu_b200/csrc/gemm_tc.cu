@@ -2,7 +2,7 @@
 //   Y[m, n] = A[m, k] (f16) . dequant(W)[n, k]^T (fp16), f32 accumulators in tensor memory.
 // Replaces qlinear_tiled.wgsl for M >= 128 (ferrum_wgpu/src/shaders/quant/qlinear_tiled.wgsl:L93-L128).
 //
-// A persistent CTA per SM walks 256 x 128 output tiles, K in slices of 64 through a 4-deep
+// A persistent CTA per SM walks 256 x 128 output tiles, K in slices of 64 through a 3-deep
 // shared-memory ring (see gemm_tc_main.cuh for the warp roles and barriers):
 //   - the A slice (256 rows x 64 f16) arrives by TMA as one 128B-swizzled box;
 //   - the weight slice (128 rows x 64) is produced in the kernel: each producer thread owns one weight
@@ -23,8 +23,14 @@ constexpr uint32_t B_BYTES = TC_BN * TC_BK * 2; // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr uint32_t STG_WORDS = 32 * 36;          // per epilogue warp: a 32 x 32 f32 chunk, rows padded to 36
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * STG_WORDS * 4;
-constexpr int THREADS = 448;
+constexpr int THREADS = 640; // 20 warps: TMA, MMA, 2 idle, 8 producers, 8 epilogue
 constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 columns
+// setmaxnreg targets of the three warp classes (4 control, 8 producer, 8 epilogue warps). The pool
+// they draw on is what the CTA was launched with (threads x registers per thread as compiled), and
+// an increase that does not fit waits forever, so the launch code checks the sum against the compiled
+// register count before the first launch.
+constexpr int REGS_CTRL = 40, REGS_PROD = 64, REGS_EPI = 152;
+constexpr int REGS_NEEDED = 32 * (4 * REGS_CTRL + 8 * REGS_PROD + 8 * REGS_EPI);
 
 enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
 
@@ -164,6 +170,12 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
 
 // ---- epilogues -------------------------------------------------------------------------------------
 
+__device__ __forceinline__ float ex2f_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // One thread's 32 consecutive accumulator columns [c, c + 32) of output row `row`.
 template <int EPI>
 __device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* acc) {
@@ -251,7 +263,7 @@ __device__ __forceinline__ void epilogue_swiglu(const TcArgs& a, uint32_t row, u
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const float gv = __uint_as_float(g[j + i]), uv = __uint_as_float(u[j + i]);
-      v[i] = gv / (1.0f + __expf(-gv)) * uv;
+      v[i] = __fdividef(gv, 1.0f + ex2f_approx(gv * -1.4426950408889634f)) * uv;
     }
     *reinterpret_cast<uint4*>(dst + j) =
         make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
@@ -310,37 +322,50 @@ struct LseState {
   float mx = -INFINITY, se = 0.0f, tl = -INFINITY;
   int first = 0;
 };
-__device__ __forceinline__ void epilogue_lse(const TcArgs& a, LseState& s, uint32_t col0, int target, const uint32_t* acc) {
-  float cm = -INFINITY;
+// Folds 32 consecutive logits of one row (columns [col0, col0 + 32) of this rank's vocabulary slice)
+// into the row's running (max, sum of exp, target logit, first argmax).
+__device__ __forceinline__ void epilogue_lse(const TcArgs& a, LseState& s, uint32_t col0, int target, uint32_t* acc) {
+  constexpr float LOG2E = 1.4426950408889634f;
+  if (col0 >= a.n) return;
+  if (col0 + 32 > a.n) { // ragged last chunk: columns past the vocabulary never win and add nothing
 #pragma unroll
-  for (int j = 0; j < 32; j++) {
-    const float v = col0 + j < a.n ? __uint_as_float(acc[j]) : -INFINITY;
-    cm = fmaxf(cm, v);
+    for (int j = 0; j < 32; j++)
+      if (col0 + j >= a.n) acc[j] = 0xff800000u;
   }
-  if (cm == -INFINITY) return;
-  if (cm > s.mx) { // strictly greater: an earlier chunk keeps a tied maximum
-    s.se *= __expf(s.mx - cm);
-    s.mx = cm;
-    int f = 0;
-    bool found = false;
+  float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int j = 0; j < 32; j++) {
-      const float v = col0 + j < a.n ? __uint_as_float(acc[j]) : -INFINITY;
-      if (!found && v == cm) {
-        f = j;
-        found = true;
-      }
-    }
+  for (int j = 0; j < 32; j += 4) {
+    m4[0] = fmaxf(m4[0], __uint_as_float(acc[j]));
+    m4[1] = fmaxf(m4[1], __uint_as_float(acc[j + 1]));
+    m4[2] = fmaxf(m4[2], __uint_as_float(acc[j + 2]));
+    m4[3] = fmaxf(m4[3], __uint_as_float(acc[j + 3]));
+  }
+  const float cm = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+  if (cm > s.mx) { // strictly greater: an earlier chunk keeps a tied maximum
+    s.se *= ex2f_approx((s.mx - cm) * LOG2E);
+    s.mx = cm;
+    int f = 31;
+#pragma unroll
+    for (int j = 30; j >= 0; j--)
+      if (__uint_as_float(acc[j]) == cm) f = j; // descending: the first occurrence is written last
     s.first = (int)(a.v0 + col0) + f;
   }
+  const int tj = target - (int)(a.v0 + col0);
+  if (tj >= 0 && tj < 32) {
 #pragma unroll
-  for (int j = 0; j < 32; j++) {
-    if (col0 + j < a.n) {
-      const float v = __uint_as_float(acc[j]);
-      s.se += __expf(v - s.mx);
-      if ((int)(a.v0 + col0) + j == target) s.tl = v;
-    }
+    for (int j = 0; j < 32; j++)
+      if (j == tj) s.tl = __uint_as_float(acc[j]);
   }
+  const float msc = s.mx * LOG2E;
+  float e4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    e4[0] += ex2f_approx(fmaf(__uint_as_float(acc[j]), LOG2E, -msc));
+    e4[1] += ex2f_approx(fmaf(__uint_as_float(acc[j + 1]), LOG2E, -msc));
+    e4[2] += ex2f_approx(fmaf(__uint_as_float(acc[j + 2]), LOG2E, -msc));
+    e4[3] += ex2f_approx(fmaf(__uint_as_float(acc[j + 3]), LOG2E, -msc));
+  }
+  s.se += (e4[0] + e4[1]) + (e4[2] + e4[3]);
 }
 
 #include "gemm_tc_main.cuh"
@@ -368,6 +393,11 @@ int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArg
   auto kern = qgemm_tc_kernel<KIND, EPI>;
   static bool attr = false; // one per instantiation
   if (!attr) {
+    cudaFuncAttributes fa;
+    FC_CUDA(dev, cudaFuncGetAttributes(&fa, kern));
+    if (fa.numRegs * THREADS < REGS_NEEDED)
+      return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product was compiled with %d registers per thread; its register "
+                     "rebalancing needs %d", fa.numRegs, (REGS_NEEDED + THREADS - 1) / THREADS);
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr = true;
   }

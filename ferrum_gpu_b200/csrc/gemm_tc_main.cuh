@@ -6,8 +6,13 @@
 //
 //   warp 0        TMA producer: A slice, 256 rows x 64 f16 = one 32 KB swizzled box per K step
 //   warp 1        TMEM owner and MMA issuer: 2 accumulators x 4 MMAs (K = 16) per K step
-//   warps 2-5     weight producers: one weight row per thread, packed blocks -> f16 swizzled slice
-//   warps 6-13    epilogue: warp w reads TMEM lane quadrant w % 4 of accumulator (w - 6) / 4
+//   warps 4-7     weight producers of the even K steps: one weight row per thread, packed blocks ->
+//   warps 8-11    f16 swizzled slice; the same for the odd K steps. A producer's step is a chain of
+//                 latencies (wait for the stage, dequantise, proxy fence, arrive) longer than the MMAs
+//                 of a step, so two sets leapfrog.
+//   warps 12-19   epilogue: warp w reads TMEM lane quadrant w % 4 of accumulator (w - 12) / 4
+//   (warps 2-3 idle: roles are aligned to groups of four warps so that setmaxnreg can move registers
+//   from the copy / MMA / producer warps to the epilogue warps)
 //
 // Barriers: full[s] (TMA bytes + 4 producer-warp arrivals) / empty[s] (MMA commit) for the
 // shared-memory ring; acc_full[b] (MMA commit) / acc_empty[b] (8 epilogue-warp arrivals) for the two
@@ -64,6 +69,8 @@ __global__ void __launch_bounds__(THREADS, 1)
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CTRL));
   if (warp == 0) {
     // ---- TMA producer ----
     if (lane == 0) {
@@ -83,79 +90,101 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
-    if (lane == 0) {
-      constexpr uint32_t idesc = tc::idesc_f16_f32(128, TC_BN);
-      uint32_t it = 0, tcnt = 0;
-      for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
-        const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
-        if (!wait_or_abort(&acc_empty[buf], aph ^ 1, abort_word)) { // the epilogue has drained this buffer
-          atomicExch(a.err_flag, ERR_WAIT_ACC);
-          break;
+    // The whole warp walks the tiles and waits (addresses and descriptors stay warp-uniform, which
+    // keeps the per-instruction issue cost low); one elected lane issues the MMAs and the commits.
+    const bool leader = tc::elect_one();
+    constexpr uint32_t idesc = tc::idesc_f16_f32(128, TC_BN);
+    constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128B swizzle
+    uint32_t it = 0, tcnt = 0;
+    bool ok = true;
+    for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word && ok; tile += gridDim.x, tcnt++) {
+      const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
+      if (!wait_or_abort(&acc_empty[buf], aph ^ 1, abort_word)) { // the epilogue has drained this buffer
+        atomicExch(a.err_flag, ERR_WAIT_ACC);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc::tc_fence_after();
+      const uint32_t d0 = tmem_base + buf * (2 * TC_BN), d1 = d0 + TC_BN;
+      for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        if (!wait_or_abort(&full[s], ph, abort_word)) {
+          atomicExch(a.err_flag, ERR_WAIT_FULL);
+          ok = false;
         }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
         tc::tc_fence_after();
-        const uint32_t d0 = tmem_base + buf * (2 * TC_BN), d1 = d0 + TC_BN;
-        bool ok = true;
-        for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
-          const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-          if (!wait_or_abort(&full[s], ph, abort_word)) {
-            atomicExch(a.err_flag, ERR_WAIT_FULL);
-            ok = false;
-            break;
-          }
-          tc::tc_fence_after();
-          const uint32_t a_addr = base + s * STAGE_BYTES, b_addr = a_addr + A_BYTES;
+        const uint32_t a_addr = base + s * STAGE_BYTES;
+        const uint64_t da0 = ((uint64_t)desc_hi << 32) | (a_addr >> 4);
+        const uint64_t da1 = ((uint64_t)desc_hi << 32) | ((a_addr + A_BYTES / 2) >> 4);
+        const uint64_t db = ((uint64_t)desc_hi << 32) | ((a_addr + A_BYTES) >> 4);
+        if (leader) {
 #pragma unroll
-          for (uint32_t ks = 0; ks < TC_BK / 16; ks++) {
-            const uint64_t db = tc::smem_desc_sw128(b_addr + ks * 32);
-            tc::mma_f16(d0, tc::smem_desc_sw128(a_addr + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
-            tc::mma_f16(d1, tc::smem_desc_sw128(a_addr + A_BYTES / 2 + ks * 32), db, idesc, (kk | ks) != 0 ? 1u : 0u);
+          for (uint32_t ks = 0; ks < TC_BK / 16; ks++) { // 32 bytes = 16 f16 along K inside the swizzled row
+            tc::mma_f16(d0, da0 + 2 * ks, db + 2 * ks, idesc, (kk | ks) != 0 ? 1u : 0u);
+            tc::mma_f16(d1, da1 + 2 * ks, db + 2 * ks, idesc, (kk | ks) != 0 ? 1u : 0u);
           }
           tc::mma_commit(&empty[s]);
         }
-        if (!ok) break;
-        tc::mma_commit(&acc_full[buf]);
-      }
-    }
-  } else if (warp < 6) {
-    // ---- weight producers ----
-    const uint32_t r = threadIdx.x - 64;
-    const uint32_t sw = r & 7;
-    RowRegs<KIND> cur, nxt;
-    uint32_t tile = blockIdx.x;
-    if (tile < total_tiles) {
-      const uint32_t row = (tile % tiles_n) * TC_BN + r;
-      load_row<KIND>(cur, w, row < w.n ? row : 0, 0, row < w.n);
-    }
-    uint32_t it = 0;
-    for (; tile < total_tiles && !*abort_word; tile += gridDim.x) {
-      const uint32_t row = (tile % tiles_n) * TC_BN + r;
-      const bool valid = row < w.n;
-      bool ok = true;
-      for (uint32_t kk = 0; kk < k_iters; kk++, it++) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        // prefetch the packed blocks of the next K step (or of the next tile's first step)
-        if (kk + 1 < k_iters) {
-          load_row<KIND>(nxt, w, valid ? row : 0, kk + 1, valid);
-        } else if (tile + gridDim.x < total_tiles) {
-          const uint32_t nrow = ((tile + gridDim.x) % tiles_n) * TC_BN + r;
-          load_row<KIND>(nxt, w, nrow < w.n ? nrow : 0, 0, nrow < w.n);
-        }
-        if (!wait_or_abort(&empty[s], ph ^ 1, abort_word)) {
-          atomicExch(a.err_flag, ERR_WAIT_EMPTY);
-          ok = false;
-          break;
-        }
-        store_row<KIND>(cur, base + s * STAGE_BYTES + A_BYTES + r * 128, sw);
-        tc::fence_async_smem();
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&full[s]);
-        cur = nxt;
       }
       if (!ok) break;
+      if (leader) tc::mma_commit(&acc_full[buf]);
+      __syncwarp();
+    }
+  }
+  } else if (warp < 12) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PROD));
+    // ---- weight producers ----
+    const uint32_t pset = (uint32_t)(warp - 4) >> 2;     // 0: even K steps, 1: odd K steps
+    const uint32_t r = ((uint32_t)(warp & 3) << 5) + lane; // row of the 128-row weight slice
+    const uint32_t sw = r & 7;
+    // this set's position in the CTA's sequence of (tile, K step) pairs
+    uint32_t tile = blockIdx.x, kk = 0, it = 0;
+    auto step = [&](uint32_t& t_, uint32_t& k_) {
+      if (++k_ == k_iters) {
+        k_ = 0;
+        t_ += gridDim.x;
+      }
+    };
+    if (pset) {
+      step(tile, kk);
+      it = 1;
+    }
+    RowRegs<KIND> cur, nxt;
+    if (tile < total_tiles) {
+      const uint32_t row = (tile % tiles_n) * TC_BN + r;
+      load_row<KIND>(cur, w, row < w.n ? row : 0, kk, row < w.n);
+    }
+    while (tile < total_tiles && !*abort_word) {
+      const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+      // prefetch the packed blocks of this set's next K step (two steps on, possibly in a later tile)
+      uint32_t ntile = tile, nkk = kk;
+      step(ntile, nkk);
+      step(ntile, nkk);
+      if (ntile < total_tiles) {
+        const uint32_t nrow = (ntile % tiles_n) * TC_BN + r;
+        load_row<KIND>(nxt, w, nrow < w.n ? nrow : 0, nkk, nrow < w.n);
+      }
+      if (!wait_or_abort(&empty[s], ph ^ 1, abort_word)) {
+        atomicExch(a.err_flag, ERR_WAIT_EMPTY);
+        break;
+      }
+      store_row<KIND>(cur, base + s * STAGE_BYTES + A_BYTES + r * 128, sw);
+      tc::fence_async_smem();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&full[s]);
+      cur = nxt;
+      tile = ntile;
+      kk = nkk;
+      it += 2;
     }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_EPI));
     // ---- epilogue ----
-    const uint32_t e = warp - 6, half = e >> 2, quad = warp & 3;
+    const uint32_t e = warp - 12, half = e >> 2, quad = warp & 3;
     float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + e * STG_WORDS; // this warp's 32 x 36 tile
     uint32_t tcnt = 0;
     for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
