@@ -4,7 +4,7 @@
 
 Workload (N = 1): the Llama-style scoring configuration - 12 layers, d_model 768, 12 query / 4 KV
 heads, SwiGLU 2048, vocab 32000, Q4_0 weights drawn from N(0, 0.02) - scoring 256 sequences of 1024
-uniform-random token ids for their total log-probability (bf16 tensor-core path). One step = one pass
+uniform-random token ids for their total log-probability (fp16 tensor-core path, f32 accumulation). One step = one pass
 over the 256 sequences of a rank. With N > 1 every rank holds a replica and scores its own 256
 sequences (no data-path collective); the per-sequence NLL sums are all-gathered at the end of each step.
 Everything is synthetic: there is no dataset and no checkpoint.
@@ -30,6 +30,13 @@ if ROOT not in sys.path:
 N_SEQS, SEQ_LEN = 256, 1024
 METRIC, UNIT = "scoring tok/s", "scored tokens/s"
 
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest product (gate/up with the
+# SwiGLU epilogue, M = 131072 rows, K = 768, N = 4096) from an ncu capture of a quarter-size launch
+# (32 x 1024 rows: 52.1 MB read + 76.5 MB written), scaled by 4; see profiles/.
+NCU_TRAFFIC_BYTES = 4 * (52.11e6 + 76.48e6)
+NCU_TRAFFIC_NOTE = ("gate/up product, per launch; algorithmic bytes are 740 MB (201 MB f16 rows in, 537 MB f16 out, "
+                    "1.8 MB weights) - part of the output is still in L2 when the launch ends")
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -257,7 +264,8 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "qgemm_tc_kernel", "achieved": achieved, "peak": tf_sust,
                          "unit": "TFLOP/s", "frac": achieved / tf_sust, "peak_source": f"{peak_src} (sustained bf16)",
-                         "frac_of_burst": achieved / tf_burst, "traffic": None,
+                         "frac_of_burst": achieved / tf_burst, "traffic": NCU_TRAFFIC_BYTES,
+                         "traffic_note": NCU_TRAFFIC_NOTE,
                          "launches_per_step": gemm["launches"], "ms_per_step": gemm["ms"], "kernel_shares": shares,
                          "tflops_by_role": by_role, "attention_tflops": attn_tf},
             "model_flops_per_step": (lin_flops + attn_flops) * rows,

@@ -6,6 +6,8 @@
     python -m ferrum_gpu_b200.profile_cases matvec    # decode matvec, Q4_0 and Q8_0, K=4096 N=32000, M=1
     python -m ferrum_gpu_b200.profile_cases decode    # batched decode step: 16 streams at cache length ~1500
     python -m ferrum_gpu_b200.profile_cases score     # 8 sequences x 1024 of the Llama scoring configuration
+    python -m ferrum_gpu_b200.profile_cases chunk     # 32 sequences x 1024, one layer: activations above L2
+    python -m ferrum_gpu_b200.profile_cases attention # the causal attention kernels alone, 16 x 1024 x 12 heads
 """
 from __future__ import annotations
 
@@ -61,6 +63,23 @@ def head(dev):
     score(dev)
 
 
+def chunk(dev):
+    """A quarter of one bench chunk (the bench launches its products on 128 x 1024 rows): per-launch
+    DRAM traffic scales with the rows, the weights being a few MB."""
+    cfg, g = _c3_model(dev, layers=1)
+    ids = np.stack([random_tokens(10 + i, 1024, cfg.vocab) for i in range(32)])
+    for _ in range(2):
+        g.score_batch(ids, Mode.TENSOR_F16)
+    g.close()
+
+
+def attention(dev):
+    n_seqs, t, heads, kv = 16, 1024, 12, 4
+    qkv = np.random.default_rng(0).standard_normal((n_seqs * t, (heads + 2 * kv) * 64)).astype(np.float16)
+    for variant in (1, 3):
+        dev.attention_f16(qkv, n_seqs, t, heads, kv, variant=variant, iters=1)
+
+
 def decode(dev):
     cfg = LlamaConfig(vocab=32000, ctx=2048, dim=1024, heads=16, kv_heads=2, head_dim=64, layers=2, hidden=2816,
                       rope_dim=64, rope_base=1e6, rope_type=1, eps=1e-6)
@@ -73,7 +92,8 @@ def decode(dev):
     g.close()
 
 
-CASES = {"gemm": gemm, "head": head, "matvec": matvec, "decode": decode, "score": score}
+CASES = {"gemm": gemm, "head": head, "matvec": matvec, "decode": decode, "score": score, "chunk": chunk,
+         "attention": attention}
 
 if __name__ == "__main__":
     name = sys.argv[1] if len(sys.argv) > 1 else "gemm"
