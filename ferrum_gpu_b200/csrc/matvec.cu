@@ -8,6 +8,9 @@
 // memory) is read once and reused for the R rows. Integer quants are turned into floats with
 // bit tricks (no I2F), the per-block f16 scale multiplies the block's partial sum, accumulation
 // is f32, and the LPR partial sums are combined with warp shuffles.
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace {
@@ -219,9 +222,27 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
   return pick_m<FC_F32>(dev, w, x, m, y, ep);
 }
 
+// Which kernel multiplies m rows by a packed matrix in exact-f32 mode:
+//   - 2..64 rows of a Q8_0 / Q4_0 matrix whose scratch is at hand: the tensor-core decode product
+//     (x as two fp16 terms, integer quants exact in fp16, scales applied in f32) - its cost does not
+//     grow with the rows, the FMA kernel's does (8 rows of K = 4096, N = 32000 Q4_0: 74 us against 540);
+//   - one row: the f32 FMA matvec (49 us against 71 on that matrix); 1..8 rows without scratch or of
+//     another kind likewise; everything else: the tiled f32 product.
+// FERRUM_CUDA_MATVEC=fma|mma overrides the choice for 1..8 rows (measurement aid).
 int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
   if (m == 0) return FC_OK;
-  if (m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0) return k_qmatvec(dev, w, x, m, y, ep);
-  if (ep.scratch && qmatvec_mma_supports(w, m)) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
+  static const int forced = [] {
+    const char* e = getenv("FERRUM_CUDA_MATVEC");
+    return !e ? 0 : !strcmp(e, "fma") ? 1 : !strcmp(e, "mma") ? 2 : 0;
+  }();
+  const bool fma_ok = m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0;
+  // (the tensor-core kernels stage x with 16-byte asynchronous copies)
+  const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  if (mma_ok && fma_ok) {
+    if (forced == 2 || (forced == 0 && m >= 2)) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
+    return k_qmatvec(dev, w, x, m, y, ep);
+  }
+  if (fma_ok) return k_qmatvec(dev, w, x, m, y, ep);
+  if (mma_ok) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
   return k_qgemm_f32(dev, w, x, m, y, ep);
 }

@@ -187,6 +187,167 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+
+// The same product for 1..8 rows of x (plain and small-batch decode): one 8-column n-block, and the
+// weight stream is the whole cost, so it gets a real pipeline: the CTA's 64 rows x 128 k of packed
+// quants, their scales and the f32 x slice arrive by cp.async in coalesced 16-byte pieces through a
+// 4-stage shared-memory ring (four-byte loads straight from global touch 16 cache lines per warp
+// instruction and run into the L1 tag rate at a seventh of the HBM bandwidth). x is split into its two
+// fp16 terms from the staged f32 slice, inside the kernel.
+template <int KIND>
+struct Mma8 {
+  static constexpr int ST = 4;
+  static constexpr int WBYTES = KIND == FC_Q8_0 ? 128 : 64;  // packed bytes of one row of a 128-k slice
+  static constexpr int WROW = KIND == FC_Q8_0 ? 160 : 80;    // padded: lanes (g, t) read conflict-free
+  static constexpr int W_STAGE = 64 * WROW;
+  static constexpr int SC_STAGE = 64 * 8;                    // 4 f16 scales per row
+  static constexpr int XF_STAGE = 8 * XS * 4;                // f32 x slice
+  static constexpr int XS_BYTES = 2 * 8 * XSTRIDE * 2;       // hi, lo as fp16
+  static constexpr int SMEM = ST * (W_STAGE + SC_STAGE + XF_STAGE) + 2 * XS_BYTES;
+};
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u; // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async8(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(src) : "memory");
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(128)
+    qmatvec_mma8_kernel(QMat w, const float* __restrict__ x, uint32_t m, float* __restrict__ y, float* __restrict__ partial,
+                        uint32_t blocks_per_split, Epilogue ep) {
+  using C = Mma8<KIND>;
+  extern __shared__ __align__(16) uint8_t sm8[];
+  uint8_t* wq = sm8;
+  uint8_t* scs = wq + C::ST * C::W_STAGE;
+  uint8_t* xf = scs + C::ST * C::SC_STAGE;
+  __half* xs = reinterpret_cast<__half*>(xf + C::ST * C::XF_STAGE);
+  constexpr int PART = 8 * XSTRIDE;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t n = w.n, k = w.k, nblocks = k / QK;
+  const uint32_t cta_row0 = blockIdx.x * ROWS_PER_CTA;
+  const uint32_t kb_begin = blockIdx.y * blocks_per_split;         // whole 4-block slices (checked on the host)
+  const uint32_t n_slices = blocks_per_split / 4;
+
+  auto issue = [&](uint32_t slice) {
+    const uint32_t st = slice % C::ST, kb0 = kb_begin + slice * 4;
+    // packed quants: 64 rows x WBYTES in 16-byte pieces
+    constexpr int PER_ROW = C::WBYTES / 16;
+#pragma unroll
+    for (int j = 0; j < PER_ROW * 64 / 128; j++) {
+      const uint32_t c = threadIdx.x + 128 * j, row = c / PER_ROW, ch = c % PER_ROW;
+      const uint32_t grow = min(cta_row0 + row, n - 1); // rows past the end are computed and dropped
+      const uint8_t* src = w.qs + (size_t)grow * (KIND == FC_Q8_0 ? k : k / 2) + (size_t)kb0 * (C::WBYTES / 4) + ch * 16;
+      cp_async16(smem_u32(wq + st * C::W_STAGE + row * C::WROW + ch * 16), src);
+    }
+    if (threadIdx.x < 64) {
+      const uint32_t grow = min(cta_row0 + threadIdx.x, n - 1);
+      cp_async8(smem_u32(scs + st * C::SC_STAGE + threadIdx.x * 8), w.sc + (size_t)grow * nblocks + kb0);
+    }
+    // x slice: 8 rows x 128 f32, rows >= m zero-filled
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const uint32_t c = threadIdx.x + 128 * j, row = c >> 5, ch = c & 31;
+      const bool valid = row < m;
+      cp_async16_zfill(smem_u32(xf + st * C::XF_STAGE + (row * XS + ch * 4) * 4),
+                       x + (size_t)(valid ? row : 0) * k + (size_t)kb0 * QK + ch * 4, valid);
+    }
+  };
+
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int p = 0; p < C::ST - 1; p++) { // one commit group per slice position, empty past the end
+    if ((uint32_t)p < n_slices) issue(p);
+    cp_async_commit();
+  }
+  const uint32_t r0 = warp * 16 + g, r1 = r0 + 8; // this lane's two weight rows within the CTA
+  const uint32_t xr = threadIdx.x >> 4, xk = (threadIdx.x & 15) * 8; // x conversion: 8 consecutive k of one row
+  for (uint32_t sl = 0; sl < n_slices; sl++) {
+    const uint32_t st = sl % C::ST;
+    cp_async_wait<C::ST - 2>();
+    __syncthreads(); // slice sl has landed for every thread; everyone is done with slice sl - 1
+    if (sl + C::ST - 1 < n_slices) issue(sl + C::ST - 1); // into the stage slice sl - 1 used
+    cp_async_commit();
+    { // split this slice of x into two fp16 terms
+      const float* src = reinterpret_cast<const float*>(xf + st * C::XF_STAGE) + xr * XS + xk;
+      const float4 xa = *reinterpret_cast<const float4*>(src), xb = *reinterpret_cast<const float4*>(src + 4);
+      const float v[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+      __half2 hi[4], lo[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const float c0 = fminf(fmaxf(v[2 * i], -65504.0f), 65504.0f), c1 = fminf(fmaxf(v[2 * i + 1], -65504.0f), 65504.0f);
+        hi[i] = __floats2half2_rn(c0, c1); // saturated instead of overflowing to infinity
+        const float2 back = __half22float2(hi[i]);
+        lo[i] = __floats2half2_rn(c0 - back.x, c1 - back.y);
+      }
+      __half* dst = xs + (size_t)(sl & 1) * 2 * PART + xr * XSTRIDE + xk;
+      *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hi);
+      *reinterpret_cast<uint4*>(dst + PART) = *reinterpret_cast<const uint4*>(lo);
+    }
+    __syncthreads();
+    const __half* xhb = xs + (size_t)(sl & 1) * 2 * PART;
+    const __half* xlb = xhb + PART;
+    const uint8_t* wst = wq + st * C::W_STAGE;
+    const __half* sst = reinterpret_cast<const __half*>(scs + st * C::SC_STAGE);
+#pragma unroll
+    for (int bi = 0; bi < 4; bi++) {
+      uint32_t a[2][4];
+      if (KIND == FC_Q8_0) {
+        const uint2 qa = *reinterpret_cast<const uint2*>(wst + r0 * C::WROW + bi * 32 + 8 * t);
+        const uint2 qb = *reinterpret_cast<const uint2*>(wst + r1 * C::WROW + bi * 32 + 8 * t);
+        const uint32_t wa[2] = {qa.x ^ 0x80808080u, qa.y ^ 0x80808080u}, wb[2] = {qb.x ^ 0x80808080u, qb.y ^ 0x80808080u};
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          a[s][0] = h2sub(__byte_perm(wa[s], 0x64646464u, 0x5140), 0x64806480u);
+          a[s][2] = h2sub(__byte_perm(wa[s], 0x64646464u, 0x5342), 0x64806480u);
+          a[s][1] = h2sub(__byte_perm(wb[s], 0x64646464u, 0x5140), 0x64806480u);
+          a[s][3] = h2sub(__byte_perm(wb[s], 0x64646464u, 0x5342), 0x64806480u);
+        }
+      } else {
+        const uint32_t wa = *reinterpret_cast<const uint32_t*>(wst + r0 * C::WROW + bi * 16 + 4 * t);
+        const uint32_t wb = *reinterpret_cast<const uint32_t*>(wst + r1 * C::WROW + bi * 16 + 4 * t);
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          a[s][0] = h2sub(((wa >> (8 * s)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
+          a[s][2] = h2sub(((wa >> (8 * s + 4)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
+          a[s][1] = h2sub(((wb >> (8 * s)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
+          a[s][3] = h2sub(((wb >> (8 * s + 4)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
+        }
+      }
+      const float dg = __half2float(sst[r0 * 4 + bi]), dg8 = __half2float(sst[r1 * 4 + bi]);
+      float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const uint32_t off = g * XSTRIDE + bi * QK + 8 * t;
+#pragma unroll
+      for (int s = 0; s < 2; s++) {
+        const uint2 bh = *reinterpret_cast<const uint2*>(xhb + off + 4 * s);
+        const uint2 bl = *reinterpret_cast<const uint2*>(xlb + off + 4 * s);
+        mma_16816(c, a[s], bh.x, bh.y);
+        mma_16816(c, a[s], bl.x, bl.y);
+      }
+      acc[0] = fmaf(dg, c[0], acc[0]);
+      acc[1] = fmaf(dg, c[1], acc[1]);
+      acc[2] = fmaf(dg8, c[2], acc[2]);
+      acc[3] = fmaf(dg8, c[3], acc[3]);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint32_t row = cta_row0 + warp * 16 + g + (j >> 1) * 8, col = 2 * t + (j & 1);
+    if (row >= n || col >= m) continue;
+    float v = acc[j];
+    if (partial) {
+      partial[((size_t)blockIdx.y * m + col) * n + row] = v;
+    } else {
+      if (ep.bias) v += ep.bias[row];
+      if (ep.act == ACT_GELU) v = gelu_f(v);
+      if (ep.resid) v = ep.resid[(size_t)col * n + row] + v;
+      y[(size_t)col * n + row] = v;
+    }
+  }
+}
+
 // y = epilogue(sum over splits, ascending split index)
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t splits, uint32_t m, uint32_t n,
                                      float* __restrict__ y, Epilogue ep) {
@@ -227,18 +388,50 @@ int pick_nb(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, ui
 } // namespace
 
 bool qmatvec_mma_supports(const QMat& w, uint32_t m) {
-  return (w.kind == FC_Q8_0 || w.kind == FC_Q4_0) && m > 8 && m <= 64 && w.k % XS == 0;
+  return (w.kind == FC_Q8_0 || w.kind == FC_Q4_0) && m >= 1 && m <= 64 && w.k % XS == 0;
 }
 
 // Device scratch the product needs: the two fp16 terms of x and the split-K partial sums.
 size_t qmatvec_mma_scratch_bytes(uint32_t k, uint32_t n) {
   const uint32_t row_ctas = (n + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
   uint32_t splits = 1; // an upper bound of what k_qmatvec_mma picks on any device of up to 160 SMs
-  while (splits < 16 && row_ctas * splits < 2 * 160) splits *= 2;
+  while (splits < 16 && row_ctas * splits < 8 * 160) splits *= 2;
   return (size_t)2 * 64 * k * 2 + (size_t)splits * 64 * n * 4 + 512;
 }
 
+// 1..8 rows: x is converted inside the kernel; more CTAs than the wide variant wants (each holds few
+// bytes in flight), so K is split until the grid covers the SMs about eight times
+static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
+  const uint32_t row_ctas = (w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, slices = w.k / XS;
+  uint32_t splits = 1;
+  const uint32_t want = 8 * (uint32_t)dev->prop.multiProcessorCount;
+  while (splits < 16 && row_ctas * splits < want && slices / (splits * 2) >= 1 && slices % (splits * 2) == 0) splits *= 2;
+  const uint32_t bps = (w.k / QK) / splits;
+  float* partial = (float*)(((uintptr_t)scratch + (size_t)2 * 64 * w.k * 2 + 255) & ~(uintptr_t)255);
+  float* part = splits > 1 ? partial : nullptr;
+  dim3 grid(row_ctas, splits);
+  static bool attr = false;
+  if (!attr) {
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q8_0>::SMEM));
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q4_0>::SMEM));
+    attr = true;
+  }
+  if (w.kind == FC_Q8_0)
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_Q8_0><<<grid, 128, Mma8<FC_Q8_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  else
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_Q4_0><<<grid, 128, Mma8<FC_Q4_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  if (splits > 1) {
+    const size_t tot = (size_t)m * w.n;
+    FC_LAUNCH(dev, "splitk_reduce",
+              splitk_reduce_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, dev->stream>>>(partial, splits, m, w.n, y, ep));
+  }
+  return FC_OK;
+}
+
 int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
+  if (m <= 8) return k_qmatvec_mma8(dev, w, x, m, y, ep, scratch);
   const uint32_t mp = m <= 16 ? 16 : m <= 32 ? 32 : 64;
   __half* xh = (__half*)scratch;
   __half* xl = xh + (size_t)mp * w.k;

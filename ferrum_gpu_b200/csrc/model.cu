@@ -141,8 +141,8 @@ int alloc_common(FcModel* m) {
     }
     FC_TRY(dev_alloc(m, need, (void**)&m->attn_scratch));
   }
-  // scratch of the batched-decode tensor product (x split + split-K partials), sized for the widest matrix
-  if (s > 8) {
+  // scratch of the decode tensor product (x split + split-K partials), sized for the widest matrix
+  {
     size_t need = qmatvec_mma_scratch_bytes(m->head.w->m.k, m->head.w->m.n);
     for (auto& l : m->layers)
       for (const FcQWeight* q : {l.qkv.w, l.wo.w, l.ff1.w, l.ff2.w}) {

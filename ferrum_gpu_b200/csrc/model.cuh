@@ -50,7 +50,7 @@ struct FcModel {
   float *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *ff = nullptr, *act = nullptr, *logits = nullptr;
   int32_t *d_ids = nullptr, *d_pos = nullptr, *d_streams = nullptr, *d_argmax = nullptr;
   // decode-step replay: one instantiated CUDA graph per batch width, inputs through a pinned buffer
-  void* mma_scratch = nullptr; // batched-decode product scratch (models of more than 8 streams)
+  void* mma_scratch = nullptr; // scratch of the decode tensor product
   float* attn_scratch = nullptr; // per-split partials of the decode attention
   int32_t* pin_dec = nullptr;
   std::vector<cudaGraphExec_t> graphs;

@@ -128,7 +128,7 @@ FC_API int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y
   cudaSetDevice(dev->ordinal);
   if (mode == FC_EXACT_F32) {
     Epilogue ep;
-    if (qmatvec_mma_supports(w->m, m)) { // 9..64 rows: the batched-decode tensor product needs scratch
+    if (qmatvec_mma_supports(w->m, m)) { // 1..64 rows: the decode tensor product needs scratch
       if (!w->mma_scratch) FC_CUDA(dev, cudaMalloc(&w->mma_scratch, qmatvec_mma_scratch_bytes(w->m.k, w->m.n)));
       ep.scratch = w->mma_scratch;
     }

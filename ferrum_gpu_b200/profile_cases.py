@@ -4,6 +4,7 @@
     python -m ferrum_gpu_b200.profile_cases gemm      # tensor-core product, Q4_0, M=16384 K=768 N=1280
     python -m ferrum_gpu_b200.profile_cases head      # fused head + log-sum-exp, M=8192 K=768 N=32000
     python -m ferrum_gpu_b200.profile_cases matvec    # decode matvec, Q4_0 and Q8_0, K=4096 N=32000, M=1
+    python -m ferrum_gpu_b200.profile_cases matvec8   # tensor-core decode product, 8 rows, K=4096 N=32000
     python -m ferrum_gpu_b200.profile_cases decode    # batched decode step: 16 streams at cache length ~1500
     python -m ferrum_gpu_b200.profile_cases score     # 8 sequences x 1024 of the Llama scoring configuration
     python -m ferrum_gpu_b200.profile_cases chunk     # 32 sequences x 1024, one layer: activations above L2
@@ -39,6 +40,17 @@ def matvec(dev):
         qw = upload_quantised(dev, kind, _weights(k, n), k, n)
         for _ in range(3):
             linear_q(dev, x, qw, 1)
+        qw.close()
+
+
+def matvec8(dev):
+    """The tensor-core decode product at 8 rows (small-batch decode)."""
+    k, n = 4096, 32000
+    x = np.random.default_rng(2).standard_normal(8 * k, dtype=np.float32)
+    for kind in (QKind.Q4_0, QKind.Q8_0):
+        qw = upload_quantised(dev, kind, _weights(k, n), k, n)
+        for _ in range(3):
+            linear_q(dev, x, qw, 8)
         qw.close()
 
 
@@ -92,7 +104,7 @@ def decode(dev):
     g.close()
 
 
-CASES = {"gemm": gemm, "head": head, "matvec": matvec, "decode": decode, "score": score, "chunk": chunk,
+CASES = {"gemm": gemm, "head": head, "matvec": matvec, "matvec8": matvec8, "decode": decode, "score": score, "chunk": chunk,
          "attention": attention}
 
 if __name__ == "__main__":
