@@ -140,3 +140,21 @@ def test_config3_shape_scoring_within_tolerance(dev):
     lp32, _ = g.score(ids, Mode.EXACT_F32)
     assert np.abs(lp32 - wlp).max() < 1e-4
     g.close()
+
+
+def test_long_sequences_cross_several_query_blocks_and_key_tiles(dev):
+    """520 tokens: three blocks of 256 query rows (the last one ragged, its second half idle) and up to five
+    key tiles per block in the tcgen05 attention kernel, two sequences and two KV groups per launch."""
+    cfg = llama_tc_cfg(ctx=600, heads=4, kv_heads=2, dim=256, hidden=256)
+    m = random_llama(cfg, seed=8, std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_llama(m, int(QKind.Q8_0), snap_embedding=False)
+    oracle = orc.OracleLlama(ref, threads=8)
+    g = CudaLlama(dev, m, QKind.Q8_0)
+    seqs = np.stack([random_tokens(40 + i, 520, cfg.vocab) for i in range(2)])
+    lp, gr, nll = g.score_batch(seqs, Mode.TENSOR_F16)
+    for s in range(2):
+        wlp, wgr = oracle.score(seqs[s])
+        assert abs(float(np.mean(lp[s] - wlp))) < NLL_TOL, s
+        assert np.abs(lp[s] - wlp).max() < 2 * LOGIT_TOL
+        assert (gr[s] != wgr).mean() < 0.05
+    g.close()
