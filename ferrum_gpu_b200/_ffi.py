@@ -89,7 +89,7 @@ EXPORTS = (
     "fc_qmatmul_dev_noalloc",
     "fc_llama_plan_bytes", "fc_gpt2_plan_bytes", "fc_llama_create", "fc_gpt2_create",
     "fc_model_destroy", "fc_model_pos", "fc_model_reset", "fc_model_info", "fc_model_feed",
-    "fc_model_feed_batch", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
+    "fc_model_feed_batch", "fc_model_topk", "fc_topk_dev", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
     "fc_model_score_dev", "fc_model_set_head_shard", "fc_model_trunk_dev",
     "fc_model_head_partial_dev", "fc_score_combine_dev",
 )
@@ -129,6 +129,8 @@ def load() -> C.CDLL:
         "fc_debug_fail_after": (C.c_int, [vp, i64]),
         "fc_debug_profile": (C.c_int, [vp, C.c_int]),
         "fc_debug_profile_report": (C.c_int, [vp, C.c_char_p, sz]),
+        "fc_model_topk": (C.c_int, [vp, u32, u32, C.c_float, vp, u32, vp, vp, P(u32)]),
+        "fc_topk_dev": (C.c_int, [vp, vp, u32, u32, C.c_float, vp, u32, vp, vp, P(u32)]),
         "fc_debug_attention_f16": (C.c_int, [vp, vp, u32, u32, u32, u32, vp, C.c_int, C.c_int, P(C.c_float)]),
         "fc_block_bytes": (sz, [C.c_int, sz]),
         "fc_qweight_create": (C.c_int, [vp, C.c_int, vp, u32, u32, P(vp)]),

@@ -19,8 +19,9 @@ class CudaError(RuntimeError):
 
 
 class Device:
-    def __init__(self, handle):
+    def __init__(self, handle, ordinal: int = 0):
         self._h = handle
+        self.ordinal = ordinal
         self._lib = _ffi.load()
         # weights and models opened on this device: closed before the device is, whatever order the
         # interpreter drops them in
@@ -33,7 +34,7 @@ class Device:
         rc = lib.fc_device_open(ordinal, C.byref(h))
         if rc != _ffi.FC_OK:
             raise CudaError(rc, lib.fc_last_error(None).decode())
-        return cls(h)
+        return cls(h, ordinal)
 
     def adopt(self, child):
         self._children.add(child)
@@ -104,6 +105,22 @@ class Device:
         self.check(self._lib.fc_debug_attention_f16(self._h, qkv.ctypes.data, n_seqs, t, heads, kv_heads,
                                                     out.ctypes.data, variant, iters, C.byref(ms)))
         return out, ms.value
+
+    def topk(self, logits, k: int, repetition_penalty: float = 1.0, recent=()):
+        """`fc_topk_dev` on a host row (uploaded for the call): the top-k candidates in `sampling::sample`'s order."""
+        import numpy as np
+        import torch
+        row = np.ascontiguousarray(logits, dtype=np.float32).reshape(-1)
+        d = torch.from_numpy(row).to(f"cuda:{self.ordinal}")
+        torch.cuda.synchronize(self.ordinal)
+        idx = np.empty(k, dtype=np.int32)
+        val = np.empty(k, dtype=np.float32)
+        rec = np.ascontiguousarray(np.asarray(list(recent), dtype=np.int32))
+        n = C.c_uint32()
+        self.check(self._lib.fc_topk_dev(self._h, d.data_ptr(), row.size, k, float(repetition_penalty),
+                                         rec.ctypes.data if rec.size else None, rec.size, idx.ctypes.data,
+                                         val.ctypes.data, C.byref(n)))
+        return idx[:n.value], val[:n.value]
 
     def fail_after(self, n: int | None):
         """`Gpu::fail_after` (device/runtime.rs:L214-L256): refuse launches after `n` more; None disarms."""

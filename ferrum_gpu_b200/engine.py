@@ -3,6 +3,7 @@
 `Session::new_with` would build for `--device cuda`."""
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 
 import numpy as np
@@ -14,9 +15,75 @@ from .resident import CudaGpt2, CudaLlama
 
 
 @dataclass
+class SampleParams:
+    """`sampling::Params` (ferrum_model/src/sampling.rs:L8-L30)."""
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+
+
+@dataclass
 class GenOpts:
-    """The fields of `GenOpts` this path uses (engine/mod.rs:L189-L202): greedy decoding."""
+    """The fields of `GenOpts` this path uses (engine/mod.rs:L189-L202): how many tokens, how to pick them, the
+    seed of the draw and how many recent tokens the repetition penalty looks at."""
     max_new: int = 16
+    sampling: SampleParams | None = None
+    seed: int = 1
+    penalty_window: int = 64
+
+
+class Rng:
+    """`ferrum_ref::rng::Rng` (ferrum_ref/src/kernels/rng.rs:L7-L41): xorshift64*, `next_f32` = top 24 bits."""
+
+    def __init__(self, seed: int):
+        self.s = (seed or 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+
+    def next_u64(self) -> int:
+        s = self.s
+        s ^= s >> 12
+        s ^= (s << 25) & 0xFFFFFFFFFFFFFFFF
+        s ^= s >> 27
+        self.s = s
+        return (s * 0x2545F4914F6CDD1D) & 0xFFFFFFFFFFFFFFFF
+
+    def next_f32(self) -> np.float32:
+        return np.float32(self.next_u64() >> 40) / np.float32(1 << 24)
+
+
+def sample_candidates(idx, val, p: SampleParams, rng: Rng) -> int:
+    """The tail of `sampling::sample` (sampling.rs:L67-L100) over candidates that are already penalised, sorted
+    and cut to top_k (what `topk` returns): softmax of (l - max) / temperature with sequential f32 sums, the
+    nucleus cut with renormalisation, one draw, the last candidate as the fallback."""
+    if len(idx) == 0:
+        return 0
+    f = np.float32
+    t = f(p.temperature)
+    probs = [f(math.exp(float((f(v) - f(val[0])) / t))) for v in val]  # expf, correctly rounded
+    total = f(0.0)
+    for x in probs:
+        total = f(total + x)
+    probs = [f(x / total) for x in probs]
+    idx = list(idx)
+    if p.top_p < 1.0:
+        acc, keep = f(0.0), len(probs)
+        for i, x in enumerate(probs):
+            acc = f(acc + x)
+            if acc >= f(p.top_p):
+                keep = i + 1
+                break
+        idx, probs = idx[:keep], probs[:keep]
+        s2 = f(0.0)
+        for x in probs:
+            s2 = f(s2 + x)
+        probs = [f(x / s2) for x in probs]
+    r = rng.next_f32()
+    acc = f(0.0)
+    for i, x in zip(idx, probs):
+        acc = f(acc + x)
+        if r < acc:
+            return int(i)
+    return int(idx[-1])
 
 
 def argmax(logits) -> int:
@@ -79,13 +146,29 @@ class CudaBackend:
         return lambda token: m.feed(token)
 
     def generate(self, model, prompt, opts: GenOpts):
-        """`Backend::generate`: greedy continuation with the argmax taken on the device."""
+        """`Backend::generate`: the argmax, or the top-k candidates of a sampled draw, are taken on the device;
+        a logits row is read back only for sampling without a top_k (1..1024)."""
         if len(prompt) == 0:
             raise ValueError("the prompt is empty")
         cls = CudaLlama if isinstance(model, Llama) else CudaGpt2
         m = cls(self.dev, model, self.weights)
         try:
             out = [int(t) for t in prompt]
+            sp = opts.sampling
+            if sp is not None and sp.temperature > 0.0:
+                if not 1 <= sp.top_k <= 1024:
+                    raise ValueError("sampled decoding on the device needs 1 <= top_k <= 1024")
+                rng = Rng(opts.seed)
+                for t in out:
+                    m.feed_greedy(t)
+                for i in range(opts.max_new):
+                    recent = out[-opts.penalty_window:] if sp.repetition_penalty != 1.0 else ()
+                    idx, val = m.topk(sp.top_k, 0, sp.repetition_penalty, recent)
+                    nxt = sample_candidates(idx, val, sp, rng)
+                    out.append(nxt)
+                    if i + 1 < opts.max_new:
+                        m.feed_greedy(nxt)
+                return out
             nxt = None
             for t in out:
                 nxt = m.feed_greedy(t)

@@ -51,6 +51,19 @@ class ResidentModel:
         self.dev.check(self._lib.fc_model_feed(self._h, stream, int(token), None, C.byref(a)))
         return a.value
 
+    def topk(self, k: int, row: int = 0, repetition_penalty: float = 1.0, recent=()):
+        """The candidates `sampling::sample` keeps for top_k = k from the logits row the last decode step left on
+        the device, in its order (descending, ties lower index first, NaN dropped), after its repetition
+        penalty over `recent`: (indices int32[n], values float32[n]) with n <= k. No logits row is read back."""
+        idx = np.empty(k, dtype=np.int32)
+        val = np.empty(k, dtype=np.float32)
+        rec = np.ascontiguousarray(np.asarray(list(recent), dtype=np.int32))
+        n = C.c_uint32()
+        self.dev.check(self._lib.fc_model_topk(self._h, row, k, float(repetition_penalty),
+                                               rec.ctypes.data if rec.size else None, rec.size, idx.ctypes.data,
+                                               val.ctypes.data, C.byref(n)))
+        return idx[:n.value], val[:n.value]
+
     def feed_batch(self, tokens, streams=None, want_logits: bool = False):
         """One decode step for several streams; returns (argmax[n], logits[n, vocab] | None)."""
         tokens = _i32(tokens)

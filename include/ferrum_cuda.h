@@ -52,7 +52,7 @@ enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };
 
 /* Arithmetic of the batched (scoring / forward_all) matrix products.
  * FC_EXACT_F32: f32 FMA with f32 accumulation, same path as decode (parity <= 1e-5).
- * FC_TENSOR_F16: weights dequantised to bf16 in shared memory, tcgen05 MMA with fp32
+ * FC_TENSOR_F16: weights dequantised to fp16 in shared memory, fp16 activations, tcgen05 MMA with fp32
  * accumulators in tensor memory (parity <= 2e-2 max-abs per logit, 1e-3 mean NLL). */
 enum { FC_EXACT_F32 = 0, FC_TENSOR_F16 = 1 };
 
@@ -232,6 +232,20 @@ int fc_model_feed(FcModel* m, uint32_t stream_id, int32_t token, float* logits_o
  * NULL. */
 int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* tokens,
                         float* logits_out, int32_t* argmax_out);
+/* Candidates for sampled decoding, selected on the device (new: the reference reads the whole logits
+ * row back for every sampled token, engine/mod.rs:L230-L240). Applies the repetition penalty of
+ * `sampling::sample` over `recent` (in order, a repeated token is penalised again,
+ * ferrum_model/src/sampling.rs:L44-L54; 1.0 = off) and returns the at most `k` (1..1024) non-NaN logits
+ * that `sample` would keep for top_k = k, in its order: descending by f32::total_cmp, ties lower index
+ * first (sampling.rs:L57-L66). `idx_out` / `val_out` hold `k` entries, `n_out` receives the count
+ * (fewer than k only when the row has fewer non-NaN logits). The caller runs its own softmax / top_p /
+ * draw over these candidates, which reproduces `sample(row, top_k = k, ...)` exactly. The row is row
+ * `row` of the last fc_model_feed_batch call (row 0 after fc_model_feed; after fc_model_prefill only if
+ * that call was asked for logits or the argmax). fc_topk_dev does the same for any device row. */
+int fc_model_topk(FcModel* m, uint32_t row, uint32_t k, float repetition_penalty, const int32_t* recent,
+                  uint32_t n_recent, int32_t* idx_out, float* val_out, uint32_t* n_out);
+int fc_topk_dev(FcDevice* dev, const float* logits_dev, uint32_t vocab, uint32_t k, float repetition_penalty,
+                const int32_t* recent, uint32_t n_recent, int32_t* idx_out, float* val_out, uint32_t* n_out);
 /* Feed `n` prompt tokens of one stream in one batched pass (new: the reference feeds a prompt
  * token by token, engine/mod.rs:L226-L229). Equivalent to n calls of fc_model_feed; returns
  * the last position's logits / argmax when asked. */

@@ -125,6 +125,19 @@ class ResidentModel {
     gpu_.check(fc_model_feed(h_, stream, token, nullptr, &a));
     return a;
   }
+  // The candidates sampling::sample keeps for top_k = k (ferrum_model/src/sampling.rs:L44-L66) from the
+  // logits row of the last decode step, selected on the device: (token, penalised logit) pairs in its order.
+  std::vector<std::pair<int32_t, float>> topk(uint32_t k, uint32_t row = 0, float repetition_penalty = 1.0f,
+                                              const std::vector<int32_t>& recent = {}) {
+    std::vector<int32_t> idx(k);
+    std::vector<float> val(k);
+    uint32_t n = 0;
+    gpu_.check(fc_model_topk(h_, row, k, repetition_penalty, recent.empty() ? nullptr : recent.data(),
+                             (uint32_t)recent.size(), idx.data(), val.data(), &n));
+    std::vector<std::pair<int32_t, float>> out(n);
+    for (uint32_t i = 0; i < n; i++) out[i] = {idx[i], val[i]};
+    return out;
+  }
   // forward_all (models/llama/forward.rs:L13-L17)
   std::vector<float> forward_all(const std::vector<int32_t>& ids, Mode mode = Mode::ExactF32) {
     std::vector<float> logits(ids.size() * (size_t)vocab_);

@@ -712,6 +712,66 @@ OR_API void or_logprobs_f64(const float* logits, const int32_t* targets, size_t 
 }
 OR_API int32_t or_argmax(const float* v, size_t n) { return argmax(v, n); }
 
+static float or_rng_next_f32_fwd(uint64_t* state);
+// ferrum_model/src/sampling.rs:L42-L100 `sample`: repetition penalty over `recent` in order (a token
+// listed twice is penalised twice), temperature <= 0 -> argmax, else candidates = non-NaN logits in
+// descending `total_cmp` order (stable: ties keep the lower index first), truncated to top_k, softmax
+// of (l - max) / temperature with sequential f32 sums, nucleus cut at top_p with renormalisation, one
+// `next_f32` draw, the last candidate as the fallback. `rng_state` advances only when a draw is made.
+static inline uint32_t total_order_key(float v) {  // ascending key order == f32::total_cmp order
+  uint32_t b;
+  memcpy(&b, &v, 4);
+  return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+OR_API int32_t or_sample(const float* logits, size_t n, float temperature, size_t top_k, float top_p, float rep_penalty,
+                         const int64_t* recent, size_t n_recent, uint64_t* rng_state) {
+  std::vector<float> l(logits, logits + n);
+  if (rep_penalty != 1.0f) {
+    for (size_t i = 0; i < n_recent; i++) {
+      if (recent[i] >= 0 && (size_t)recent[i] < n) {
+        float& v = l[(size_t)recent[i]];
+        v = v > 0.0f ? v / rep_penalty : v * rep_penalty;
+      }
+    }
+  }
+  if (temperature <= 0.0f) return argmax(l.data(), n);
+  std::vector<size_t> idx;
+  for (size_t i = 0; i < n; i++)
+    if (!std::isnan(l[i])) idx.push_back(i);
+  if (idx.empty()) return 0;
+  std::stable_sort(idx.begin(), idx.end(), [&](size_t a, size_t b) { return total_order_key(l[a]) > total_order_key(l[b]); });
+  if (top_k > 0 && idx.size() > top_k) idx.resize(top_k);
+  const float mx = l[idx[0]];
+  std::vector<float> probs(idx.size());
+  for (size_t i = 0; i < idx.size(); i++) probs[i] = expf((l[idx[i]] - mx) / temperature);
+  float sum = 0.0f;
+  for (float x : probs) sum += x;
+  for (float& x : probs) x /= sum;
+  if (top_p < 1.0f) {
+    float acc = 0.0f;
+    size_t keep = probs.size();
+    for (size_t i = 0; i < probs.size(); i++) {
+      acc += probs[i];
+      if (acc >= top_p) {
+        keep = i + 1;
+        break;
+      }
+    }
+    idx.resize(keep);
+    probs.resize(keep);
+    float s2 = 0.0f;
+    for (float x : probs) s2 += x;
+    for (float& x : probs) x /= s2;
+  }
+  const float r = or_rng_next_f32_fwd(rng_state);
+  float acc = 0.0f;
+  for (size_t i = 0; i < idx.size(); i++) {
+    acc += probs[i];
+    if (r < acc) return (int32_t)idx[i];
+  }
+  return (int32_t)idx.back();
+}
+
 // ferrum_ref/src/kernels/rng.rs:L7-L41 (xorshift64*): `state` is the caller's generator
 OR_API uint64_t or_rng_new(uint64_t seed) { return seed == 0 ? 0x9e3779b97f4a7c15ull : seed; }
 OR_API uint64_t or_rng_next_u64(uint64_t* state) {
@@ -723,6 +783,7 @@ OR_API uint64_t or_rng_next_u64(uint64_t* state) {
   return s * 0x2545f4914f6cdd1dull;
 }
 OR_API float or_rng_next_f32(uint64_t* state) { return (float)(or_rng_next_u64(state) >> 40) / (float)(1ull << 24); }
+static float or_rng_next_f32_fwd(uint64_t* state) { return or_rng_next_f32(state); }
 OR_API uint64_t or_rng_below(uint64_t* state, uint64_t n) {
   uint64_t zone = UINT64_MAX - (UINT64_MAX % n);
   for (;;) {

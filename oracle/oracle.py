@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
         "or_score": (None, [vp, vp, sz, sz, vp, vp]),
         "or_logprobs_f64": (None, [vp, vp, sz, sz, vp, vp]),
         "or_argmax": (i32, [vp, sz]),
+        "or_sample": (i32, [vp, sz, f, sz, f, f, vp, sz, P(u64)]),
         "or_rng_new": (u64, [u64]), "or_rng_next_u64": (u64, [P(u64)]),
         "or_rng_next_f32": (f, [P(u64)]), "or_rng_below": (u64, [P(u64), u64]),
         "or_llama_create": (vp, [P(_ffi.FcLlamaConfig), P(_ffi.FcLlamaWeights), C.c_int]),
@@ -249,6 +250,16 @@ def logprobs_f64(logits, targets, vocab: int):
 def argmax(v) -> int:
     v = _f32(v).reshape(-1)
     return lib().or_argmax(_p(v), v.size)
+
+
+def sample(logits, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0, recent=(), rng=None) -> int:
+    """`ferrum_model::sampling::sample` (sampling.rs:L42-L100); `rng` is an `Rng` and advances by one draw
+    unless the call is greedy or has no candidate."""
+    v = _f32(logits).reshape(-1)
+    rec = np.ascontiguousarray(np.asarray(list(recent), dtype=np.int64))
+    state = rng.s if rng is not None else C.c_uint64(lib().or_rng_new(1))
+    return lib().or_sample(_p(v), v.size, float(temperature), int(top_k), float(top_p), float(repetition_penalty),
+                           rec.ctypes.data if rec.size else None, rec.size, C.byref(state))
 
 
 class Rng:

@@ -457,3 +457,60 @@ def test_oracle_llama_agrees_with_independent_numpy(name, cfg, biases, tied):
     got = orc.OracleLlama(m).forward_logits(ids)
     want = _np_llama_forward(m, ids)
     assert orc.max_rel_err(got, want) < 2e-5, name
+
+
+# ---- sampling (ferrum_model/src/sampling.rs:L102-L200, the reference's own cases) --------------------
+_L = [1.0, 3.0, 3.0, 0.5, -2.0]
+
+
+def test_sample_temperature_zero_is_greedy_whatever_the_rng():
+    r = orc.Rng(1)
+    assert all(orc.sample(_L, rng=r) == 1 for _ in range(10))
+
+
+def test_sample_top_k_one_equals_greedy():
+    r = orc.Rng(2)
+    assert all(orc.sample(_L, temperature=1.5, top_k=1, rng=r) == 1 for _ in range(20))
+
+
+def test_sample_seeded_draws_are_reproducible_and_cover_the_support():
+    def run(seed):
+        r = orc.Rng(seed)
+        return [orc.sample(_L, temperature=1.0, rng=r) for _ in range(200)]
+    draws = run(9)
+    assert draws == run(9)
+    assert 1 in draws and 2 in draws and all(t < 5 for t in draws)
+    assert sum(1 for t in draws if t in (1, 2)) > 120
+
+
+def test_sample_top_p_cuts_the_tail():
+    r = orc.Rng(3)
+    assert all(orc.sample(_L, temperature=1.0, top_p=0.5, rng=r) in (1, 2) for _ in range(200))
+
+
+def test_sample_repetition_penalty_demotes_recent_tokens():
+    r = orc.Rng(4)
+    assert orc.sample(_L, repetition_penalty=4.0, recent=[1], rng=r) == 2   # 3.0 / 4 < 3.0: the tied twin wins
+    assert orc.sample([-1.0, -1.5], repetition_penalty=4.0, recent=[0], rng=r) == 1  # negatives go further down
+    assert orc.sample(_L, repetition_penalty=4.0, recent=[99], rng=r) == 1  # out-of-range ids are ignored
+
+
+def test_sample_degenerate_inputs():
+    r = orc.Rng(5)
+    assert orc.sample([float("nan"), float("nan")], temperature=1.0, rng=r) == 0
+    assert orc.sample([0.0], temperature=1.0, rng=r) == 0
+
+
+def test_host_rng_and_candidate_draw_mirror_the_oracle():
+    """The engine mirror's generator and its draw over pre-sorted candidates against `sample` on the full row."""
+    from ferrum_gpu_b200.engine import Rng, SampleParams, sample_candidates
+    a, b = Rng(9), orc.Rng(9)
+    assert [float(a.next_f32()) for _ in range(50)] == [b.next_f32() for _ in range(50)]
+    rng = np.random.default_rng(1)
+    row = (rng.standard_normal(500) * 2).astype(np.float32)
+    for p in (SampleParams(0.7, 20, 1.0, 1.0), SampleParams(1.2, 50, 0.8, 1.0)):
+        order = np.argsort(-row, kind="stable")[:p.top_k]
+        ours, theirs = Rng(3), orc.Rng(3)
+        for _ in range(200):
+            assert sample_candidates(order, row[order], p, ours) == orc.sample(row, p.temperature, p.top_k, p.top_p,
+                                                                               rng=theirs)
