@@ -216,7 +216,8 @@ def main():
         dev.check(lib.fc_model_score(g._h, ids_pin.data_ptr(), n_seqs, SEQ_LEN, int(Mode.TENSOR_F16), lp.data_ptr(),
                                      gr.data_ptr(), nll.data_ptr()))
 
-    e2e_step()
+    for _ in range(2):  # the first calls size the library's workspace and pinned staging
+        e2e_step()
     t0 = time.perf_counter()
     e2e_steps = max(1, args.steps)
     for _ in range(e2e_steps):

@@ -61,30 +61,43 @@ __global__ void x_split_kernel(const float* __restrict__ x, uint32_t m, uint32_t
 }
 
 // Fragments of one 32-wide block for rows g and g + 8: a[s] = {a0, a1, a2, a3} of k16 step s.
+// The packed quants and scales of one block for rows g and g + 8, as loaded; kept apart from the
+// conversion so that the next block's loads are in flight while the current one is multiplied.
 template <int KIND>
-__device__ __forceinline__ void load_a(const QMat& w, uint32_t row_g, uint32_t row_g8, uint32_t kb, int t, uint32_t a[2][4],
-                                       float& dg, float& dg8) {
+struct BlockRegs {
+  uint32_t q[KIND == FC_Q8_0 ? 4 : 2];
+  __half d[2];
+};
+template <int KIND>
+__device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, uint32_t row_g, uint32_t row_g8, uint32_t kb, int t) {
   const uint32_t nb = w.k / QK;
-  dg = __half2float(w.sc[(size_t)row_g * nb + kb]);
-  dg8 = __half2float(w.sc[(size_t)row_g8 * nb + kb]);
+  r.d[0] = w.sc[(size_t)row_g * nb + kb];
+  r.d[1] = w.sc[(size_t)row_g8 * nb + kb];
   if (KIND == FC_Q8_0) {
     const uint2 qa = __ldg(reinterpret_cast<const uint2*>(w.qs + (size_t)row_g * w.k + (size_t)kb * QK + 8 * t));
     const uint2 qb = __ldg(reinterpret_cast<const uint2*>(w.qs + (size_t)row_g8 * w.k + (size_t)kb * QK + 8 * t));
-    const uint32_t wa[2] = {qa.x ^ 0x80808080u, qa.y ^ 0x80808080u}, wb[2] = {qb.x ^ 0x80808080u, qb.y ^ 0x80808080u};
+    r.q[0] = qa.x, r.q[1] = qa.y, r.q[KIND == FC_Q8_0 ? 2 : 0] = qb.x, r.q[KIND == FC_Q8_0 ? 3 : 1] = qb.y;
+  } else {
+    r.q[0] = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g * (w.k / 2) + (size_t)kb * 16 + 4 * t));
+    r.q[1] = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g8 * (w.k / 2) + (size_t)kb * 16 + 4 * t));
+  }
+}
+template <int KIND>
+__device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a[2][4]) {
+  if (KIND == FC_Q8_0) {
+    const uint32_t wa[2] = {r.q[0] ^ 0x80808080u, r.q[1] ^ 0x80808080u};
+    const uint32_t wb[2] = {r.q[KIND == FC_Q8_0 ? 2 : 0] ^ 0x80808080u, r.q[KIND == FC_Q8_0 ? 3 : 1] ^ 0x80808080u};
 #pragma unroll
     for (int s = 0; s < 2; s++) {
-      // bytes (0,1) and (2,3) of the step's word become fp16 pairs 1024 + u, minus 1152 = the int8
       a[s][0] = h2sub(__byte_perm(wa[s], 0x64646464u, 0x5140), 0x64806480u);
       a[s][2] = h2sub(__byte_perm(wa[s], 0x64646464u, 0x5342), 0x64806480u);
       a[s][1] = h2sub(__byte_perm(wb[s], 0x64646464u, 0x5140), 0x64806480u);
       a[s][3] = h2sub(__byte_perm(wb[s], 0x64646464u, 0x5342), 0x64806480u);
     }
   } else {
-    const uint32_t wa = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g * (w.k / 2) + (size_t)kb * 16 + 4 * t));
-    const uint32_t wb = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g8 * (w.k / 2) + (size_t)kb * 16 + 4 * t));
+    const uint32_t wa = r.q[0], wb = r.q[1];
 #pragma unroll
     for (int s = 0; s < 2; s++) {
-      // mask pair p of the word = elements (2p, 2p + 1); 0x6400 | nib = 1024 + nib, minus 1032 = nib - 8
       a[s][0] = h2sub(((wa >> (8 * s)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
       a[s][2] = h2sub(((wa >> (8 * s + 4)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
       a[s][1] = h2sub(((wb >> (8 * s)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
@@ -126,9 +139,11 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
   for (int i = 0; i < NB; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
 
+  BlockRegs<KIND> cur, nxt;
   if (n_slices > 0) {
     stage(0, 0);
     cp_async_commit();
+    load_block<KIND>(cur, w, row_g, row_g8, kb_begin, t);
   }
   for (uint32_t sl = 0; sl < n_slices; sl++) {
     const uint32_t buf = sl & 1;
@@ -145,9 +160,10 @@ __global__ void __launch_bounds__(128)
     const uint32_t kb0 = kb_begin + sl * 4;
 #pragma unroll 1
     for (uint32_t bi = 0; bi < 4 && kb0 + bi < kb_end; bi++) {
+      if (kb0 + bi + 1 < kb_end) load_block<KIND>(nxt, w, row_g, row_g8, kb0 + bi + 1, t); // in flight under this block's MMAs
       uint32_t a[2][4];
-      float dg, dg8;
-      load_a<KIND>(w, row_g, row_g8, kb0 + bi, t, a, dg, dg8);
+      block_frags<KIND>(cur, a);
+      const float dg = __half2float(cur.d[0]), dg8 = __half2float(cur.d[1]);
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
         float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -164,6 +180,7 @@ __global__ void __launch_bounds__(128)
         acc[nb][2] = fmaf(dg8, c[2], acc[nb][2]);
         acc[nb][3] = fmaf(dg8, c[3], acc[nb][3]);
       }
+      cur = nxt;
     }
     __syncthreads();
   }
