@@ -112,7 +112,17 @@ struct Epilogue {
   // device scratch of at least qmatvec_mma_scratch_bytes(k, n): lets products of 9..64 rows run on the
   // tensor-core batched-decode kernel; without it they take the tiled f32 kernel
   void* scratch = nullptr;
+  // "x is the raw residual stream: normalise each row first" (NORM_RMS: y = x / sqrt(mean(x^2) + eps) * g,
+  // NORM_LAYER: (x - mean) / sqrt(var + 1e-5) * g + b). The one-row FMA matvec does it while it stages x
+  // in shared memory (one launch less per product); the other kernels run the norm kernel into
+  // `norm_tmp` ([m][k] floats) first.
+  int norm = 0;
+  const float* norm_g = nullptr;
+  const float* norm_b = nullptr;
+  float norm_eps = 0.0f;
+  float* norm_tmp = nullptr;
 };
+enum { NORM_NONE = 0, NORM_RMS = 1, NORM_LAYER = 2 };
 
 // matvec_mma.cu: 9 <= m <= 64 rows at f32-class accuracy on mma.sync
 bool qmatvec_mma_supports(const QMat& w, uint32_t m);

@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "ops.cuh"
 
 namespace {
 
@@ -87,14 +88,58 @@ __device__ __forceinline__ float gelu_f(float x) {
   return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
 }
 
+// Sum over the CTA, the same order as the stand-alone norm kernels use (elementwise.cu), so the fused
+// prologue below reproduces them bit for bit.
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
 template <int KIND, int M, int LPR, int R>
 __global__ void __launch_bounds__(256)
     qmatvec_kernel(QMat w, const float* __restrict__ x, float* __restrict__ y, Epilogue ep) {
   extern __shared__ __align__(16) float xs[]; // [M][k]
+  __shared__ float red[32];
   const uint32_t k = w.k, n = w.n;
   for (uint32_t i = threadIdx.x * 4; i < M * k; i += blockDim.x * 4)
     *reinterpret_cast<float4*>(xs + i) = *reinterpret_cast<const float4*>(x + i);
   __syncthreads();
+  if (ep.norm != NORM_NONE) {
+    // RMSNorm / LayerNorm of the staged rows, in place (every CTA repeats it: k is a few hundred to a
+    // few thousand floats, against a launch and a round trip through global memory saved)
+#pragma unroll 1
+    for (int m = 0; m < M; m++) {
+      float* row = xs + (size_t)m * k;
+      if (ep.norm == NORM_RMS) {
+        float ss = 0.0f;
+        for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+        ss = block_sum_256(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)k + ep.norm_eps);
+        for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) row[i] = row[i] * inv * ep.norm_g[i];
+      } else {
+        float s = 0.0f;
+        for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) s += row[i];
+        const float mean = block_sum_256(s, red) / (float)k;
+        float vs = 0.0f;
+        for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+          const float dl = row[i] - mean;
+          vs = fmaf(dl, dl, vs);
+        }
+        const float var = block_sum_256(vs, red) / (float)k;
+        const float is = 1.0f / sqrtf(var + 1e-5f);
+        for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) row[i] = (row[i] - mean) * is * ep.norm_g[i] + ep.norm_b[i];
+      }
+    }
+    __syncthreads();
+  }
 
   constexpr int ELEMS = Chunk<KIND>::ELEMS;
   constexpr int GROUPS_PER_WARP = 32 / LPR;
@@ -229,20 +274,27 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
 //   - one row: the f32 FMA matvec (49 us against 71 on that matrix); 1..8 rows without scratch or of
 //     another kind likewise; everything else: the tiled f32 product.
 // FERRUM_CUDA_MATVEC=fma|mma overrides the choice for 1..8 rows (measurement aid).
-int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep) {
+int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep_in) {
   if (m == 0) return FC_OK;
   static const int forced = [] {
     const char* e = getenv("FERRUM_CUDA_MATVEC");
     return !e ? 0 : !strcmp(e, "fma") ? 1 : !strcmp(e, "mma") ? 2 : 0;
   }();
+  Epilogue ep = ep_in;
   const bool fma_ok = m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0;
   // (the tensor-core kernels stage x with 16-byte asynchronous copies)
   const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-  if (mma_ok && fma_ok) {
-    if (forced == 2 || (forced == 0 && m >= 2)) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
-    return k_qmatvec(dev, w, x, m, y, ep);
+  const bool use_fma = fma_ok && (!mma_ok || forced == 1 || (forced == 0 && m < 2));
+  if (ep.norm != NORM_NONE && !use_fma) { // only the FMA matvec normalises while it stages x
+    if (!ep.norm_tmp) return fc_fail(dev, FC_ERR_ARG, "a fused norm needs a temporary for the kernels that cannot fuse it");
+    if (ep.norm == NORM_RMS)
+      FC_TRY(k_rmsnorm(dev, x, ep.norm_g, m, w.k, ep.norm_eps, ep.norm_tmp));
+    else
+      FC_TRY(k_layernorm(dev, x, ep.norm_g, ep.norm_b, m, w.k, ep.norm_tmp));
+    x = ep.norm_tmp;
+    ep.norm = NORM_NONE;
   }
-  if (fma_ok) return k_qmatvec(dev, w, x, m, y, ep);
+  if (use_fma) return k_qmatvec(dev, w, x, m, y, ep);
   if (mma_ok) return k_qmatvec_mma(dev, w, x, m, y, ep, ep.scratch);
   return k_qgemm_f32(dev, w, x, m, y, ep);
 }

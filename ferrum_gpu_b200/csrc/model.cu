@@ -170,22 +170,30 @@ struct PassBufs {
 };
 
 // Run `rows` rows through embedding and all layers in exact f32; leaves the final-norm output in
-// b.h. ATTN_DECODE: each row is its own stream (streams[] = cache slots). ATTN_STATELESS: n_seqs
+// b.h (the residual stream in b.x when `final_norm` is false). ATTN_DECODE: each row is its own stream (streams[] = cache slots). ATTN_STATELESS: n_seqs
 // sequences of t rows, no cache. ATTN_PREFILL_CACHE: t rows of one stream appended at `start`.
+// "normalise the rows of x first" for a product (fused into the one-row matvec, a separate launch into
+// b.h for the other kernels)
+static void norm_before(const FcModel* m, Epilogue& e, const float* g, const float* bias, float* tmp) {
+  e.norm = m->arch == ARCH_LLAMA ? NORM_RMS : NORM_LAYER;
+  e.norm_g = g;
+  e.norm_b = bias;
+  e.norm_eps = m->eps;
+  e.norm_tmp = tmp;
+}
+
 int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32_t* positions, const int32_t* streams,
-                  uint32_t rows, AttnMode mode, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t stream) {
+                  uint32_t rows, AttnMode mode, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t stream,
+                  bool final_norm) {
   FcDevice* dev = m->dev;
   const uint32_t d = m->dim;
   FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, b.x));
   for (auto& l : m->layers) {
-    if (m->arch == ARCH_LLAMA)
-      FC_TRY(k_rmsnorm(dev, b.x, l.norm1_g, rows, d, m->eps, b.h));
-    else
-      FC_TRY(k_layernorm(dev, b.x, l.norm1_g, l.norm1_b, rows, d, b.h));
     Epilogue e_qkv;
     e_qkv.scratch = m->mma_scratch;
     e_qkv.bias = l.qkv.bias;
-    FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.h, rows, b.qkv, e_qkv));
+    norm_before(m, e_qkv, l.norm1_g, l.norm1_b, b.h);
+    FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.x, rows, b.qkv, e_qkv));
     const bool to_cache = mode != ATTN_STATELESS;
     FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
                      to_cache ? &l.kv : nullptr, m->ctx));
@@ -201,15 +209,12 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     e_wo.bias = l.wo.bias;
     e_wo.resid = b.x;
     FC_TRY(k_qlinear_f32(dev, l.wo.w->m, b.attn, rows, b.x, e_wo));
-    if (m->arch == ARCH_LLAMA)
-      FC_TRY(k_rmsnorm(dev, b.x, l.norm2_g, rows, d, m->eps, b.h));
-    else
-      FC_TRY(k_layernorm(dev, b.x, l.norm2_g, l.norm2_b, rows, d, b.h));
     Epilogue e_ff1;
     e_ff1.scratch = m->mma_scratch;
     e_ff1.bias = l.ff1.bias;
     e_ff1.act = m->arch == ARCH_GPT2 ? ACT_GELU : ACT_NONE;
-    FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.h, rows, b.ff, e_ff1));
+    norm_before(m, e_ff1, l.norm2_g, l.norm2_b, b.h);
+    FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.x, rows, b.ff, e_ff1));
     const float* ff2_in = b.ff;
     if (m->arch == ARCH_LLAMA) {
       FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, m->gu_group, b.act));
@@ -221,6 +226,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     e_ff2.resid = b.x;
     FC_TRY(k_qlinear_f32(dev, l.ff2.w->m, ff2_in, rows, b.x, e_ff2));
   }
+  if (!final_norm) return FC_OK; // the caller folds it into the head product
   if (m->arch == ARCH_LLAMA)
     FC_TRY(k_rmsnorm(dev, b.x, m->normf_g, rows, d, m->eps, b.h));
   else
@@ -296,7 +302,7 @@ int model_trunk_f32(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, 
   b.attn = (float*)arena_take(m, (size_t)rows * m->qd() * 4);
   b.ff = (float*)arena_take(m, (size_t)rows * m->ff1_w() * 4);
   b.act = (float*)arena_take(m, (size_t)rows * m->hidden * 4);
-  return run_stack_f32(m, b, ids_dev, pos_dev, nullptr, rows, ATTN_STATELESS, n_seqs, t, 0, 0);
+  return run_stack_f32(m, b, ids_dev, pos_dev, nullptr, rows, ATTN_STATELESS, n_seqs, t, 0, 0, true);
 }
 
 // ================================ C ABI ===========================================================
@@ -525,10 +531,11 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
     FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
     FC_CUDA(dev, cudaMemcpyAsync(m->d_streams, p + 2 * n, n * 4, cudaMemcpyHostToDevice, dev->stream));
     PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
-    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0));
+    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false));
     Epilogue e_head;
     e_head.scratch = m->mma_scratch;
-    FC_TRY(k_qlinear_f32(dev, m->head_view, m->h, n, m->logits, e_head));
+    norm_before(m, e_head, m->normf_g, m->normf_b, m->h);
+    FC_TRY(k_qlinear_f32(dev, m->head_view, m->x, n, m->logits, e_head));
     FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax));
     FC_CUDA(dev, cudaMemcpyAsync(p + 3 * n, m->d_argmax, n * 4, cudaMemcpyDeviceToHost, dev->stream));
     return FC_OK;
@@ -606,7 +613,7 @@ FC_API int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, 
   FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
   FC_TRY(upload_positions(m, 1, n, start, d_pos));
   FC_TRY(upload_ids(m, ids, n, d_ids));
-  FC_TRY(run_stack_f32(m, b, d_ids, d_pos, d_slots, n, ATTN_PREFILL_CACHE, 1, n, start, (int32_t)stream_id));
+  FC_TRY(run_stack_f32(m, b, d_ids, d_pos, d_slots, n, ATTN_PREFILL_CACHE, 1, n, start, (int32_t)stream_id, true));
   if (logits_out || argmax_out) {
     FC_TRY(k_qlinear_f32(dev, m->head_view, b.h + (size_t)(n - 1) * m->dim, 1, m->logits, Epilogue()));
     if (argmax_out) {
@@ -638,7 +645,7 @@ FC_API int fc_model_forward_all(FcModel* m, const int32_t* ids, uint32_t n, floa
   FC_TRY(upload_positions(m, 1, n, 0, d_pos));
   FC_TRY(upload_ids(m, ids, n, d_ids));
   if (mode == FC_EXACT_F32) {
-    FC_TRY(run_stack_f32(m, b, d_ids, d_pos, nullptr, n, ATTN_STATELESS, 1, n, 0, 0));
+    FC_TRY(run_stack_f32(m, b, d_ids, d_pos, nullptr, n, ATTN_STATELESS, 1, n, 0, 0, true));
     FC_TRY(k_qlinear_f32(dev, m->head_view, b.h, n, logits, Epilogue()));
   } else if (mode == FC_TENSOR_F16) {
     __half* hid = (__half*)arena_take(m, (size_t)n * m->dim * 2);
