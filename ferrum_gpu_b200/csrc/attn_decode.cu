@@ -200,6 +200,7 @@ void attn_decode_plan(const FcDevice* dev, uint32_t rows, uint32_t kv_heads, uin
   uint32_t base = rows * kv_heads, s = (want + base - 1) / base;
   const uint32_t max_s = (ctx + POS_PER_ITER - 1) / POS_PER_ITER;
   if (s > max_s) s = max_s;
+  if (ctx <= 512) s = 1; // a short cache is a microsecond for one CTA: the merge launch would cost more
   if (s < 1) s = 1;
   uint32_t sl = ((ctx + s - 1) / s + POS_PER_ITER - 1) / POS_PER_ITER * POS_PER_ITER;
   *split_len = sl;
