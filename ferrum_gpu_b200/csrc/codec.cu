@@ -160,10 +160,34 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ qs, const __half* __r
   }
 }
 
+// FC_F16: transpose [k, n] -> [n, k] and round to nearest even (f16::f32_to_f16, ferrum_gguf/src/f16.rs:L25-L53)
+__global__ void f16_from_kn_kernel(const float* __restrict__ w, uint32_t k, uint32_t n, __half* __restrict__ out) {
+  __shared__ float tile[32][33];
+  const uint32_t c0 = blockIdx.x * 32, r0 = blockIdx.y * 32; // columns of w (n), rows of w (k)
+  for (uint32_t j = threadIdx.y; j < 32; j += 8) {
+    const uint32_t r = r0 + j, c = c0 + threadIdx.x;
+    tile[j][threadIdx.x] = (r < k && c < n) ? w[(size_t)r * n + c] : 0.0f;
+  }
+  __syncthreads();
+  for (uint32_t j = threadIdx.y; j < 32; j += 8) {
+    const uint32_t c = c0 + j, r = r0 + threadIdx.x; // out row = column of w
+    if (c < n && r < k) out[(size_t)c * k + r] = __float2half_rn(tile[threadIdx.x][j]);
+  }
+}
+__global__ void f16_to_f32_kernel(const __half* __restrict__ src, size_t total, float* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) out[i] = __half2float(src[i]);
+}
+
 } // namespace
 
 int k_quantise_kn(FcDevice* dev, int kind, const float* w, uint32_t k, uint32_t n, uint8_t* qs, __half* sc) {
   if (k == 0 || k % QK || n == 0) return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole 32-element blocks", k, n);
+  if (kind == FC_F16) {
+    dim3 g16((n + 31) / 32, (k + 31) / 32), b16(32, 8);
+    FC_LAUNCH(dev, "quantise_f16", f16_from_kn_kernel<<<g16, b16, 0, dev->stream>>>(w, k, n, (__half*)qs));
+    return FC_OK;
+  }
   dim3 grid((n + 127) / 128, k / QK);
   if (kind == FC_Q8_0)
     FC_LAUNCH(dev, "quantise_q8_0", quantise_kn_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
@@ -181,6 +205,10 @@ int k_transpose_kn(FcDevice* dev, const float* w, uint32_t k, uint32_t n, float*
 }
 
 int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, uint32_t n, uint8_t* qs, __half* sc) {
+  if (kind == FC_F16) { // a GGUF F16 tensor is already [n][k] f16
+    FC_CUDA(dev, cudaMemcpyAsync(qs, blocks, (size_t)k * n * 2, cudaMemcpyDeviceToDevice, dev->stream));
+    return FC_OK;
+  }
   size_t total = (size_t)(k / QK) * n;
   unsigned grid = (unsigned)((total + 127) / 128);
   if (kind == FC_Q8_0)
@@ -193,6 +221,10 @@ int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, 
 }
 
 int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
+  if (m.kind == FC_F16) {
+    FC_CUDA(dev, cudaMemcpyAsync(blocks, m.qs, (size_t)m.k * m.n * 2, cudaMemcpyDeviceToDevice, dev->stream));
+    return FC_OK;
+  }
   size_t total = (size_t)(m.k / QK) * m.n;
   unsigned grid = (unsigned)((total + 127) / 128);
   if (m.kind == FC_Q8_0)
@@ -207,6 +239,11 @@ int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
 int k_dequant(FcDevice* dev, const QMat& m, float* out) {
   if (m.kind == FC_F32) {
     FC_CUDA(dev, cudaMemcpyAsync(out, m.qs, (size_t)m.k * m.n * 4, cudaMemcpyDeviceToDevice, dev->stream));
+    return FC_OK;
+  }
+  if (m.kind == FC_F16) {
+    const size_t tot = (size_t)m.k * m.n;
+    FC_LAUNCH(dev, "dequant_f16", f16_to_f32_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, dev->stream>>>((const __half*)m.qs, tot, out));
     return FC_OK;
   }
   size_t total = (size_t)(m.k / QK) * m.n;

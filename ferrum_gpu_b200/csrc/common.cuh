@@ -79,6 +79,7 @@ int fc_pinned(FcDevice* dev, size_t bytes, void** out);
 //           8w..8w+7 of the block, element j in nibble position (j>>1) + 4*(j&1), so that the
 //           mask pairs (p, p+4) of one word unpack to consecutive elements; sc as above
 //  FC_F32:  qs = f32  [n][k];            sc = nullptr
+//  FC_F16:  qs = f16  [n][k];            sc = nullptr
 struct QMat {
   int kind = FC_F32;
   uint32_t k = 0, n = 0;
@@ -99,9 +100,11 @@ struct FcQWeight {
 };
 
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
-  return kind == FC_Q8_0 ? k * n : kind == FC_Q4_0 ? k * n / 2 : k * n * 4;
+  return kind == FC_Q8_0 ? k * n : kind == FC_Q4_0 ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
 }
-static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) { return kind == FC_F32 ? 0 : (k / QK) * n * 2; }
+static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) {
+  return (kind == FC_Q8_0 || kind == FC_Q4_0) ? (k / QK) * n * 2 : 0;
+}
 
 // Epilogue of a matrix product: y = act(x W + bias) (+ resid). All pointers device, nullable.
 enum { ACT_NONE = 0, ACT_GELU = 1 };

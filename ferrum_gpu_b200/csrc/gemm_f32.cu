@@ -62,6 +62,15 @@ __global__ void __launch_bounds__(256)
             const int pos = (j >> 1) + 4 * (j & 1);
             v[j] = __fmul_rn(d, (float)((q >> (4 * pos)) & 0xf) - 8.0f);
           }
+        } else if (KIND == FC_F16) {
+          const uint4 q = *reinterpret_cast<const uint4*>(w.qs + ((size_t)row * k + k0 + part * 8) * 2);
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&qw[j]));
+            v[2 * j] = f.x;
+            v[2 * j + 1] = f.y;
+          }
         } else {
           const float* src = reinterpret_cast<const float*>(w.qs) + (size_t)row * k;
 #pragma unroll
@@ -117,6 +126,8 @@ int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float*
     FC_LAUNCH(dev, "qgemm_f32_q8_0", qgemm_f32_kernel<FC_Q8_0><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else if (w.kind == FC_Q4_0)
     FC_LAUNCH(dev, "qgemm_f32_q4_0", qgemm_f32_kernel<FC_Q4_0><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
+  else if (w.kind == FC_F16)
+    FC_LAUNCH(dev, "qgemm_f32_f16", qgemm_f32_kernel<FC_F16><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else
     FC_LAUNCH(dev, "qgemm_f32_f32", qgemm_f32_kernel<FC_F32><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   return FC_OK;

@@ -116,6 +116,10 @@ template <>
 struct RowRegs<FC_F32> {
   uint4 q[16];
 };
+template <>
+struct RowRegs<FC_F16> {
+  uint4 q[8];
+};
 
 template <int KIND>
 __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32_t row, uint32_t it, bool valid) {
@@ -131,6 +135,10 @@ __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32
     for (int i = 0; i < 4; i++) r.q[i] = valid ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint32_t*>(&((RowRegs<FC_Q8_0>&)r).sc) =
         valid ? __ldg(reinterpret_cast<const uint32_t*>(w.sc + (size_t)row * (w.k / QK) + (size_t)it * 2)) : 0u;
+  } else if (KIND == FC_F16) {
+    const uint4* p = reinterpret_cast<const uint4*>(w.qs + ((size_t)row * w.k + (size_t)it * 64) * 2);
+#pragma unroll
+    for (int i = 0; i < 8; i++) r.q[i] = valid ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
   } else {
     const uint4* p = reinterpret_cast<const uint4*>(w.qs + ((size_t)row * w.k + (size_t)it * 64) * 4);
 #pragma unroll
@@ -153,6 +161,15 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
     dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
     dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
     dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+  } else if (KIND == FC_F16) { // stored values are the operand: eight 16-byte pieces into their swizzled places
+    const RowRegs<FC_F16>& rr = (const RowRegs<FC_F16>&)r;
+#pragma unroll
+    for (int c = 0; c < 8; c++) {
+      const uint32_t addr = row_smem + (((uint32_t)c ^ sw) << 4);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(rr.q[c].x), "r"(rr.q[c].y), "r"(rr.q[c].z),
+                   "r"(rr.q[c].w)
+                   : "memory");
+    }
   } else {
     const RowRegs<FC_F32>& rr = (const RowRegs<FC_F32>&)r;
 #pragma unroll
@@ -452,6 +469,7 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   dim3 grid((unsigned)(tiles < sms ? tiles : sms)); // persistent: one CTA per SM walks the tiles
   if (w.kind == FC_Q4_0) return pick_epi<FC_Q4_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_Q8_0) return pick_epi<FC_Q8_0>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_F16) return pick_epi<FC_F16>(dev, tmap, w, args, epi, grid);
   return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);
 }
 

@@ -30,6 +30,10 @@ template <>
 struct Chunk<FC_F32> {
   static constexpr int ELEMS = 4;
 };
+template <>
+struct Chunk<FC_F16> {
+  static constexpr int ELEMS = 8;
+};
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -72,6 +76,14 @@ __device__ __forceinline__ float chunk_dot(const uint4& wq, const float* __restr
         float q = __uint_as_float(0x4B000000u | nib) - 8388616.0f; // (2^23 + nib) - (2^23 + 8)
         acc = fmaf(xe[j], q, acc);
       }
+    }
+  } else if (KIND == FC_F16) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float2 xv = *reinterpret_cast<const float2*>(xs + 2 * w);
+      const float2 wv = __half22float2(*reinterpret_cast<const __half2*>(&words[w])); // exact
+      acc = fmaf(xv.x, wv.x, acc);
+      acc = fmaf(xv.y, wv.y, acc);
     }
   } else {
     float4 xv = *reinterpret_cast<const float4*>(xs);
@@ -170,7 +182,7 @@ __global__ void __launch_bounds__(256)
       float d[R];
 #pragma unroll
       for (int r = 0; r < R; r++) wq[r] = ldg_stream(w.qs + rows[r] * row_bytes + (size_t)c * 16);
-      if (KIND != FC_F32) {
+      if (KIND == FC_Q8_0 || KIND == FC_Q4_0) {
 #pragma unroll
         for (int r = 0; r < R; r++)
           d[r] = __half2float(w.sc[(size_t)rows[r] * nb + (KIND == FC_Q8_0 ? (c >> 1) : c)]);
@@ -181,7 +193,7 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
         for (int r = 0; r < R; r++) {
           float s = chunk_dot<KIND>(wq[r], xp);
-          acc[r][m] = KIND == FC_F32 ? acc[r][m] + s : fmaf(d[r], s, acc[r][m]);
+          acc[r][m] = (KIND == FC_F32 || KIND == FC_F16) ? acc[r][m] + s : fmaf(d[r], s, acc[r][m]);
         }
       }
     }
@@ -264,6 +276,7 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "matvec: %u rows of %u inputs do not fit the staging buffer", m, w.k);
   if (w.kind == FC_Q8_0) return pick_m<FC_Q8_0>(dev, w, x, m, y, ep);
   if (w.kind == FC_Q4_0) return pick_m<FC_Q4_0>(dev, w, x, m, y, ep);
+  if (w.kind == FC_F16) return pick_m<FC_F16>(dev, w, x, m, y, ep);
   return pick_m<FC_F32>(dev, w, x, m, y, ep);
 }
 

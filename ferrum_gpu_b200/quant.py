@@ -17,9 +17,10 @@ class QKind(IntEnum):
     F32 = _ffi.FC_F32
     Q8_0 = _ffi.FC_Q8_0
     Q4_0 = _ffi.FC_Q4_0
+    F16 = _ffi.FC_F16
 
     def label(self) -> str:
-        return {0: "F32", 1: "Q8_0", 2: "Q4_0"}[int(self)]
+        return {0: "F32", 1: "Q8_0", 2: "Q4_0", 3: "F16"}[int(self)]
 
 
 class Mode(IntEnum):

@@ -45,7 +45,8 @@ enum {
 
 /* Stored precision of a weight matrix. Replaces ferrum_wgpu::ops::quant::QKind
  * (ferrum_wgpu/src/ops/quant.rs:L27-L44), restricted to the kinds on this path. */
-enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2 };
+/* FC_F16: plain f16 values, no scale, compute stays f32 - QKind::F16 (ops/quant.rs:L33-L36). */
+enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2, FC_F16 = 3 };
 
 /* RoPE pairing, ferrum_ref/src/models/llama/ops.rs:L9-L15. */
 enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };
@@ -112,10 +113,12 @@ size_t fc_block_bytes(int kind, size_t n_elems);
  * ops::quant::upload_quantised = quantise_matrix + pack + upload
  * (ferrum_wgpu/src/ops/quant.rs:L238-L288). The encoder runs on the device and produces the
  * same blocks as ferrum_gguf::quant::encode (codec/quant.rs:L111-L133). `k` must be a multiple
- * of 32 unless `kind` is FC_F32. */
+ * of 32 unless `kind` is FC_F32. FC_F16 stores the transposed matrix as f16 (round to nearest even,
+ * ferrum_gguf/src/f16.rs:L25-L53). */
 int fc_qweight_create(FcDevice* dev, int kind, const float* w_in_out, uint32_t k, uint32_t n,
                       FcQWeight** out);
-/* Same from GGUF block bytes: `n` rows of `k / 32` blocks of 34 (Q8_0) or 18 (Q4_0) bytes.
+/* Same from GGUF block bytes: `n` rows of `k / 32` blocks of 34 (Q8_0) or 18 (Q4_0) bytes, or of `k` f16
+ * values (F16).
  * Replaces ops::quant::upload_qweight (ops/quant.rs:L266-L277). */
 int fc_qweight_create_from_blocks(FcDevice* dev, int kind, const uint8_t* blocks, size_t n_bytes,
                                   uint32_t k, uint32_t n, FcQWeight** out);

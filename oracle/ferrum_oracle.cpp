@@ -102,13 +102,23 @@ int8_t rust_f32_as_i8(float v) {
 
 // ---- block codec -----------------------------------------------------------------------------
 
-size_t block_bytes(int kind) { return kind == FC_Q8_0 ? 2 + QK : 2 + QK / 2; }
+// F16 (codec/quant.rs:L30,L70,L108): two bytes per element, little endian, no scale; counted here in
+// 32-element groups like the block formats it shares the kernels with (ops/quant.rs:L86)
+size_t block_bytes(int kind) { return kind == FC_Q8_0 ? 2 + QK : kind == FC_F16 ? 2 * QK : 2 + QK / 2; }
 
 // ferrum_gguf/src/codec/quant.rs:L111-L119 (Q8_0) and L120-L133 (Q4_0)
 void encode(int kind, const float* data, size_t n, uint8_t* out) {
   for (size_t b = 0; b < n / QK; b++) {
     const float* blk = data + b * QK;
     uint8_t* o = out + b * block_bytes(kind);
+    if (kind == FC_F16) {
+      for (size_t j = 0; j < QK; j++) {
+        const uint16_t h = f32_to_f16(blk[j]);
+        o[2 * j] = (uint8_t)(h & 0xff);
+        o[2 * j + 1] = (uint8_t)(h >> 8);
+      }
+      continue;
+    }
     if (kind == FC_Q8_0) {
       float amax = 0.0f;
       for (size_t j = 0; j < QK; j++) amax = std::fmax(amax, std::fabs(blk[j])); // f32::max ignores NaN
@@ -143,8 +153,12 @@ void encode(int kind, const float* data, size_t n, uint8_t* out) {
 void decode(int kind, const uint8_t* bytes, size_t n, float* out) {
   for (size_t b = 0; b < n / QK; b++) {
     const uint8_t* p = bytes + b * block_bytes(kind);
-    float d = f16_to_f32((uint16_t)(p[0] | (p[1] << 8)));
     float* o = out + b * QK;
+    if (kind == FC_F16) {
+      for (size_t j = 0; j < QK; j++) o[j] = f16_to_f32((uint16_t)(p[2 * j] | (p[2 * j + 1] << 8)));
+      continue;
+    }
+    float d = f16_to_f32((uint16_t)(p[0] | (p[1] << 8)));
     if (kind == FC_Q8_0) {
       for (size_t j = 0; j < QK; j++) o[j] = d * (float)(int8_t)p[2 + j];
     } else {

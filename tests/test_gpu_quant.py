@@ -11,21 +11,23 @@ from tests import helpers
 pytestmark = pytest.mark.gpu
 
 KINDS = [QKind.Q8_0, QKind.Q4_0]
+STORED = KINDS + [QKind.F16]  # F16: plain f16 values, no scale (ops/quant.rs:L33-L36)
+BLOCK_BYTES = {QKind.Q8_0: 34, QKind.Q4_0: 18, QKind.F16: 64}
 REDUCING = 1e-5  # ferrum_wgpu/src/tolerance.rs:L7
 
 
-@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("kind", STORED)
 @pytest.mark.parametrize("k,n", [(32, 1), (32, 5), (64, 3), (96, 65), (128, 64), (768, 130)])
 def test_device_encoder_is_bit_identical_to_the_cpu_encoder(dev, kind, k, n):
     for w in (helpers.nasty(k * n), orc.rand_vec(k * n, 4) * np.float32(0.02)):
         qw = upload_quantised(dev, kind, w, k, n)
         assert np.array_equal(qw.blocks(), orc.quantise_matrix(int(kind), w, k, n)), (kind, k, n)
         assert (qw.kind(), qw.k(), qw.n()) == (kind, k, n)
-        assert qw.device_bytes() == k * n * (34 if kind == QKind.Q8_0 else 18) // 32
+        assert qw.device_bytes() == k * n * BLOCK_BYTES[kind] // 32
         qw.close()
 
 
-@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("kind", STORED)
 @pytest.mark.parametrize("k,n", [(32, 1), (32, 5), (64, 3), (96, 65), (128, 64)])
 def test_dequantised_values_are_bit_identical_to_the_cpu_decode(dev, kind, k, n):
     """ops/quant/tests.rs:L106-L131, both by the decode kernel and by the identity-matrix read-back."""
@@ -40,7 +42,7 @@ def test_dequantised_values_are_bit_identical_to_the_cpu_decode(dev, kind, k, n)
     qw.close()
 
 
-@pytest.mark.parametrize("kind", KINDS + [QKind.F32])
+@pytest.mark.parametrize("kind", STORED + [QKind.F32])
 @pytest.mark.parametrize("rows,k,n", [(1, 32, 1), (1, 256, 100), (7, 96, 13), (33, 64, 65), (2, 512, 3),
                                       (8, 2048, 37), (5, 2816, 70), (64, 1024, 200), (130, 768, 257)])
 def test_linear_matches_the_cpu_matmul_on_the_dequantised_weights(dev, kind, rows, k, n):

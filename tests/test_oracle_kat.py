@@ -514,3 +514,22 @@ def test_host_rng_and_candidate_draw_mirror_the_oracle():
         for _ in range(200):
             assert sample_candidates(order, row[order], p, ours) == orc.sample(row, p.temperature, p.top_k, p.top_p,
                                                                                rng=theirs)
+
+
+def test_f16_stored_weights_round_to_nearest_even_without_a_scale():
+    """QKind::F16 (ferrum_wgpu/src/ops/quant.rs:L33-L36, codec/quant.rs:L70,L108): two bytes per element, little
+    endian; the round trip is exactly IEEE binary16 rounding (numpy's float16 cast is the independent check)."""
+    from ferrum_gpu_b200._ffi import FC_F16
+    rng = np.random.default_rng(4)
+    w = np.concatenate([rng.standard_normal(200).astype(np.float32) * np.float32(3.0), helpers.nasty(56)])
+    k, n = 64, 4
+    finite = np.nan_to_num(w, nan=0.0)  # NaN payloads are not compared
+    snapped = orc.snap_matrix(FC_F16, finite, k, n)
+    with np.errstate(over="ignore"):
+        want = finite.astype(np.float16).astype(np.float32)
+    assert np.array_equal(snapped.view(np.uint32), want.view(np.uint32))
+    raw = orc.quantise_matrix(FC_F16, finite, k, n)
+    assert raw.size == k * n * 2 == orc.block_bytes(FC_F16, k * n)
+    with np.errstate(over="ignore"):
+        assert np.array_equal(raw.view(np.float16).reshape(n, k).view(np.uint16),
+                              finite.reshape(k, n).T.astype(np.float16).view(np.uint16))
