@@ -158,3 +158,27 @@ def test_long_sequences_cross_several_query_blocks_and_key_tiles(dev):
         assert np.abs(lp[s] - wlp).max() < 2 * LOGIT_TOL
         assert (gr[s] != wgr).mean() < 0.05
     g.close()
+
+
+@pytest.mark.parametrize("kind", [QKind.Q4_0, QKind.Q8_0])
+def test_largest_sweep_shapes_on_sampled_output_columns(dev, kind):
+    """The far corner of the isolated sweep (K = 4096, N in {11008, 32000}, M in {1, 8, 64, 512, 4096}) is too big
+    for the scalar oracle, so 48 sampled output columns are recomputed in float64 from the oracle's snapped weights:
+    decode-side rows (exact path) within 1e-5 by the reference's metric, scoring-side rows (tensor path) within
+    2e-2 - its per-logit bound; outputs here have standard deviation ~1.3."""
+    k = 4096
+    rng = np.random.default_rng(7)
+    for n in (11008, 32000):
+        w = (rng.standard_normal((k, n), dtype=np.float32) * np.float32(0.02))
+        cols = np.sort(rng.choice(n, 48, replace=False))
+        wq = orc.snap_matrix(int(kind), np.ascontiguousarray(w[:, cols]).reshape(-1), k, cols.size).reshape(k, cols.size)
+        qw = upload_quantised(dev, kind, w.reshape(-1), k, n)
+        del w
+        for m, mode, tol in ((1, Mode.EXACT_F32, 1e-5), (8, Mode.EXACT_F32, 1e-5), (64, Mode.EXACT_F32, 1e-5),
+                             (512, Mode.TENSOR_F16, LOGIT_TOL), (4096, Mode.TENSOR_F16, LOGIT_TOL)):
+            x = rng.standard_normal((m, k), dtype=np.float32)
+            got = linear_q(dev, x.reshape(-1), qw, m, mode).reshape(m, n)[:, cols]
+            want = x.astype(np.float64) @ wq.astype(np.float64)
+            err = (np.abs(got - want) / np.maximum(np.abs(want), 1.0)).max()
+            assert err < tol, (kind, n, m, mode, err)
+        qw.close()
