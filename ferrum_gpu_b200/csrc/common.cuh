@@ -124,6 +124,9 @@ struct Epilogue {
   const float* norm_b = nullptr;
   float norm_eps = 0.0f;
   float* norm_tmp = nullptr;
+  // the producer of x has already written its two fp16 terms where the 9..64-row tensor-core product
+  // stages them (qmatvec_mma_split_ptrs): the product skips its split launch and ignores `x`
+  bool presplit = false;
 };
 enum { NORM_NONE = 0, NORM_RMS = 1, NORM_LAYER = 2 };
 
@@ -131,6 +134,10 @@ enum { NORM_NONE = 0, NORM_RMS = 1, NORM_LAYER = 2 };
 bool qmatvec_mma_supports(const QMat& w, uint32_t m);
 size_t qmatvec_mma_scratch_bytes(uint32_t k, uint32_t n);
 int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch);
+// Whether k_qlinear_f32 will take the 9..64-row tensor-core product for (w, m) with this scratch, and where
+// that product expects the two fp16 terms of x ([mp][k] each, rows >= m zero).
+bool qlinear_takes_wide_mma(const QMat& w, uint32_t m, const void* scratch);
+void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, __half** xl, uint32_t* mp);
 
 // ---- kernels' host entry points (each enqueues on dev->stream) --------------------------------
 // codec.cu

@@ -243,7 +243,35 @@ __global__ void nll_sums_kernel(const float* __restrict__ logprob, uint32_t n_se
   nll[s] = acc;
 }
 
+// the same, written as the two fp16 terms the 9..64-row decode product multiplies (rows >= `rows` of the
+// padded block are zero): saves that product's own split launch
+__global__ void swiglu_split_kernel(const float* __restrict__ gu, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group,
+                                    __half* __restrict__ xh, __half* __restrict__ xl) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)mp * hidden) return;
+  const size_t r = i / hidden, c = i % hidden;
+  float v = 0.0f;
+  if (r < rows) {
+    const size_t gi = group ? (c / group) * 2 * group + c % group : c;
+    const float g = gu[r * 2 * hidden + gi], u = gu[r * 2 * hidden + gi + (group ? group : hidden)];
+    v = g / (1.0f + expf(-g)) * u;
+  }
+  v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+  const __half h = __float2half_rn(v);
+  xh[i] = h;
+  xl[i] = __float2half_rn(v - __half2float(h));
+}
+
 } // namespace
+
+int k_swiglu_split(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group, __half* xh,
+                   __half* xl) {
+  const size_t total = (size_t)mp * hidden;
+  if (!total) return FC_OK;
+  FC_LAUNCH(dev, "swiglu_split",
+            swiglu_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(gate_up, rows, mp, hidden, group, xh, xl));
+  return FC_OK;
+}
 
 int k_embed(FcDevice* dev, const float* tok, const float* pos_table, const int32_t* ids, const int32_t* positions,
             uint32_t rows, uint32_t d, float* x) {

@@ -287,6 +287,10 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
 //   - one row: the f32 FMA matvec (49 us against 71 on that matrix); 1..8 rows without scratch or of
 //     another kind likewise; everything else: the tiled f32 product.
 // FERRUM_CUDA_MATVEC=fma|mma overrides the choice for 1..8 rows (measurement aid).
+bool qlinear_takes_wide_mma(const QMat& w, uint32_t m, const void* scratch) {
+  return scratch && m > 8 && qmatvec_mma_supports(w, m); // (x lives in the library's own aligned buffers there)
+}
+
 int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep_in) {
   if (m == 0) return FC_OK;
   static const int forced = [] {
@@ -296,9 +300,11 @@ int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   Epilogue ep = ep_in;
   const bool fma_ok = m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0;
   // (the tensor-core kernels stage x with 16-byte asynchronous copies)
-  const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0 || ep.presplit);
+  if (ep.presplit && !(mma_ok && m > 8)) return fc_fail(dev, FC_ERR_ARG, "a pre-split x needs the 9..64-row tensor-core product");
   const bool use_fma = fma_ok && (!mma_ok || forced == 1 || (forced == 0 && m < 2));
-  if (ep.norm != NORM_NONE && !use_fma) { // only the FMA matvec normalises while it stages x
+  const bool use_mma_wide = !use_fma && mma_ok && m > 8; // its x split takes the norm along
+  if (ep.norm != NORM_NONE && !use_fma && !use_mma_wide) { // the FMA matvec normalises while it stages x
     if (!ep.norm_tmp) return fc_fail(dev, FC_ERR_ARG, "a fused norm needs a temporary for the kernels that cannot fuse it");
     if (ep.norm == NORM_RMS)
       FC_TRY(k_rmsnorm(dev, x, ep.norm_g, m, w.k, ep.norm_eps, ep.norm_tmp));

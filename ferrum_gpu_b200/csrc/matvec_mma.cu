@@ -60,6 +60,59 @@ __global__ void x_split_kernel(const float* __restrict__ x, uint32_t m, uint32_t
   xl[i] = __float2half_rn(v - __half2float(h));
 }
 
+// RMSNorm / LayerNorm of row r of x and the split of the result, in one pass: what k_rmsnorm /
+// k_layernorm followed by x_split_kernel produce (the same summation order, so the same bits), for the
+// products whose input is "the norm of the residual stream". One CTA of 256 threads per padded row.
+__device__ __forceinline__ float block_sum_mma(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+__global__ void __launch_bounds__(256)
+    norm_split_kernel(const float* __restrict__ x, uint32_t m, uint32_t k, int norm, const float* __restrict__ g,
+                      const float* __restrict__ b, float eps, __half* __restrict__ xh, __half* __restrict__ xl) {
+  __shared__ float red[32];
+  const uint32_t r = blockIdx.x;
+  __half* oh = xh + (size_t)r * k;
+  __half* ol = xl + (size_t)r * k;
+  if (r >= m) { // padding rows of the n-block
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) oh[i] = ol[i] = __float2half_rn(0.0f);
+    return;
+  }
+  const float* row = x + (size_t)r * k;
+  float mean = 0.0f, inv;
+  if (norm == NORM_RMS) {
+    float ss = 0.0f;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) ss = fmaf(row[i], row[i], ss);
+    ss = block_sum_mma(ss, red);
+    inv = 1.0f / sqrtf(ss / (float)k + eps);
+  } else {
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) s += row[i];
+    mean = block_sum_mma(s, red) / (float)k;
+    float vs = 0.0f;
+    for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+      const float dl = row[i] - mean;
+      vs = fmaf(dl, dl, vs);
+    }
+    inv = 1.0f / sqrtf(block_sum_mma(vs, red) / (float)k + 1e-5f);
+  }
+  for (uint32_t i = threadIdx.x; i < k; i += blockDim.x) {
+    float v = norm == NORM_RMS ? row[i] * inv * g[i] : (row[i] - mean) * inv * g[i] + b[i];
+    v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+    const __half h = __float2half_rn(v);
+    oh[i] = h;
+    ol[i] = __float2half_rn(v - __half2float(h));
+  }
+}
+
 // Fragments of one 32-wide block for rows g and g + 8: a[s] = {a0, a1, a2, a3} of k16 step s.
 // The packed quants and scales of one block for rows g and g + 8, as loaded; kept apart from the
 // conversion so that the next block's loads are in flight while the current one is multiplied.
@@ -447,20 +500,36 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   return FC_OK;
 }
 
+void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, __half** xl, uint32_t* mp) {
+  *mp = m <= 16 ? 16 : m <= 32 ? 32 : 64;
+  *xh = (__half*)scratch;
+  *xl = *xh + (size_t)*mp * k;
+}
+
 int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
   if (m <= 8) return k_qmatvec_mma8(dev, w, x, m, y, ep, scratch);
-  const uint32_t mp = m <= 16 ? 16 : m <= 32 ? 32 : 64;
-  __half* xh = (__half*)scratch;
-  __half* xl = xh + (size_t)mp * w.k;
+  uint32_t mp;
+  __half *xh, *xl;
+  qmatvec_mma_split_ptrs(scratch, m, w.k, &xh, &xl, &mp);
   float* partial = (float*)(((uintptr_t)(xl + (size_t)mp * w.k) + 255) & ~(uintptr_t)255);
   const size_t total = (size_t)mp * w.k;
-  FC_LAUNCH(dev, "x_split", x_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(x, m, mp, w.k, xh, xl));
-  // split K until the grid covers the SMs about twice (slices stay whole 128-k units)
+  if (ep.presplit) {
+    // the producer of x wrote xh / xl itself
+  } else if (ep.norm != NORM_NONE) // x is the raw residual stream: normalise and split in one launch
+    FC_LAUNCH(dev, "norm_split",
+              norm_split_kernel<<<mp, 256, 0, dev->stream>>>(x, m, w.k, ep.norm, ep.norm_g, ep.norm_b, ep.norm_eps, xh, xl));
+  else
+    FC_LAUNCH(dev, "x_split", x_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(x, m, mp, w.k, xh, xl));
+  // split K until the grid covers the SMs about twice: whole 128-k slices per split, the last split may be
+  // shorter (K = 2816 is 22 slices: 11 splits of 2, where a power-of-two rule stops at 2 splits of 11)
   const uint32_t row_ctas = (w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, slices = w.k / XS;
-  uint32_t splits = 1;
   const uint32_t want = 2 * (uint32_t)dev->prop.multiProcessorCount;
-  while (splits < 16 && row_ctas * splits < want && slices / (splits * 2) >= 1 && slices % (splits * 2) == 0) splits *= 2;
-  const uint32_t bps = (w.k / QK) / splits;
+  uint32_t splits = (want + row_ctas - 1) / row_ctas;
+  splits = splits < 1 ? 1 : splits > 16 ? 16 : splits;
+  splits = splits > slices ? slices : splits;
+  const uint32_t slices_per_split = (slices + splits - 1) / splits;
+  splits = (slices + slices_per_split - 1) / slices_per_split; // no empty split
+  const uint32_t bps = slices_per_split * (XS / QK);
   float* part = splits > 1 ? partial : nullptr;
   if (w.kind == FC_Q8_0)
     FC_TRY(pick_nb<FC_Q8_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));

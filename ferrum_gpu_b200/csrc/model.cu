@@ -216,11 +216,19 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     norm_before(m, e_ff1, l.norm2_g, l.norm2_b, b.h);
     FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.x, rows, b.ff, e_ff1));
     const float* ff2_in = b.ff;
+    Epilogue e_ff2;
     if (m->arch == ARCH_LLAMA) {
-      FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, m->gu_group, b.act));
+      if (qlinear_takes_wide_mma(l.ff2.w->m, rows, m->mma_scratch)) { // SwiGLU writes the product's fp16 terms itself
+        __half *xh, *xl;
+        uint32_t mp;
+        qmatvec_mma_split_ptrs(m->mma_scratch, rows, m->hidden, &xh, &xl, &mp);
+        FC_TRY(k_swiglu_split(dev, b.ff, rows, mp, m->hidden, m->gu_group, xh, xl));
+        e_ff2.presplit = true;
+      } else {
+        FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, m->gu_group, b.act));
+      }
       ff2_in = b.act;
     }
-    Epilogue e_ff2;
     e_ff2.scratch = m->mma_scratch;
     e_ff2.bias = l.ff2.bias;
     e_ff2.resid = b.x;

@@ -21,6 +21,8 @@ int k_embed(FcDevice* dev, const float* tok, const float* pos_table /*nullable*/
 int k_rmsnorm(FcDevice* dev, const float* x, const float* g, uint32_t rows, uint32_t d, float eps, float* y);
 int k_layernorm(FcDevice* dev, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d, float* y);
 int k_swiglu(FcDevice* dev, const float* gate_up /*[rows][2*hidden]*/, uint32_t rows, uint32_t hidden, uint32_t group, float* act);
+int k_swiglu_split(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group, __half* xh,
+                   __half* xl);
 // Rotate q and k of the fused qkv rows in place (rope.type/rope_dim; skipped when rope.cos is
 // NULL) and, when `kv` is given, store each row's k and v into the cache at (stream, position).
 int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
