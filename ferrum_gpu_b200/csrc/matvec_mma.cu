@@ -297,8 +297,8 @@ __global__ void __launch_bounds__(128)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const uint32_t n = w.n, k = w.k, nblocks = k / QK;
   const uint32_t cta_row0 = blockIdx.x * ROWS_PER_CTA;
-  const uint32_t kb_begin = blockIdx.y * blocks_per_split;         // whole 4-block slices (checked on the host)
-  const uint32_t n_slices = blocks_per_split / 4;
+  const uint32_t kb_begin = blockIdx.y * blocks_per_split;         // whole 4-block slices; the last split may be shorter
+  const uint32_t n_slices = (min(kb_begin + blocks_per_split, nblocks) - kb_begin) / 4;
 
   auto issue = [&](uint32_t slice) {
     const uint32_t st = slice % C::ST, kb0 = kb_begin + slice * 4;
@@ -473,10 +473,14 @@ size_t qmatvec_mma_scratch_bytes(uint32_t k, uint32_t n) {
 // bytes in flight), so K is split until the grid covers the SMs about eight times
 static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
   const uint32_t row_ctas = (w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, slices = w.k / XS;
-  uint32_t splits = 1;
   const uint32_t want = 8 * (uint32_t)dev->prop.multiProcessorCount;
-  while (splits < 16 && row_ctas * splits < want && slices / (splits * 2) >= 1 && slices % (splits * 2) == 0) splits *= 2;
-  const uint32_t bps = (w.k / QK) / splits;
+  uint32_t splits = (want + row_ctas - 1) / row_ctas;
+  splits = splits < 1 ? 1 : splits > 16 ? 16 : splits;
+  splits = splits > slices ? slices : splits;
+  if ((size_t)w.n * w.k <= ((size_t)1 << 20)) splits = 1; // a second launch costs more than a few short CTAs
+  const uint32_t slices_per_split = (slices + splits - 1) / splits; // whole slices; the last split may be shorter
+  splits = (slices + slices_per_split - 1) / slices_per_split;
+  const uint32_t bps = slices_per_split * (XS / QK);
   float* partial = (float*)(((uintptr_t)scratch + (size_t)2 * 64 * w.k * 2 + 255) & ~(uintptr_t)255);
   float* part = splits > 1 ? partial : nullptr;
   dim3 grid(row_ctas, splits);
