@@ -9,6 +9,13 @@
 // Scores are reduced over the 8 lanes with shuffles; the softmax is online with one rescale per
 // block of 4 positions per lane group. Lane groups, warps and finally splits are merged with the
 // usual (max, sum, weighted output) rule; with one split the CTA writes the result directly.
+//
+// The number of splits is fixed per batch width (a captured step can be replayed) and chosen so that
+// all CTAs are resident at once: a second, partly filled wave costs more than longer ranges (64 streams
+// x 2 kv-heads at 1550 positions: 2 splits 0.60 ms per step of 24 layers, 3 splits 0.70). The range
+// of a split is not fixed: each row's current length is cut into equal parts, so the CTAs of a row
+// carry the same load whatever the length. The merge launch writes f32 rows or, for a following
+// 9..64-row tensor-core product, directly that product's two fp16 terms.
 // Replaces attn_gqd_probs.wgsl + attn_gqd_pv.wgsl (ferrum_wgpu/src/ops/llama.rs:L150-L179).
 #include "ops.cuh"
 
@@ -23,19 +30,42 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// Where the result goes: f32 rows [rows][heads * 64], or (xh set) the two fp16 terms of the same rows,
+// saturated like the product's own split of x, in blocks of `mp` rows.
+struct DecodeOut {
+  float* out;
+  __half *xh, *xl;
+  uint32_t mp;
+  __device__ __forceinline__ void put(size_t at, float v) const {
+    if (xh) {
+      v = fminf(fmaxf(v, -65504.0f), 65504.0f);
+      const __half h = __float2half_rn(v);
+      xh[at] = h;
+      xl[at] = __float2half_rn(v - __half2float(h));
+    } else {
+      out[at] = v;
+    }
+  }
+};
+
 // partial layout per (row, kv-head, split): [G] max (log2 domain), [G] sum, [G][64] weighted output
 template <int G>
 __global__ void __launch_bounds__(128)
     attn_decode_split_kernel(const float* __restrict__ qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
                              const int32_t* __restrict__ positions, const int32_t* __restrict__ streams, KvLayer kv,
-                             uint32_t ctx, uint32_t split_len, uint32_t n_splits, float* __restrict__ partial,
-                             float* __restrict__ out) {
+                             uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst) {
   __shared__ float sm_m[4][G], sm_l[4][G];
   __shared__ __align__(16) float sm_o[4][G][HD];
   const uint32_t split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
   const uint32_t len = (uint32_t)positions[r] + 1;
-  const uint32_t p0 = split * split_len, p1 = min(len, p0 + split_len);
+  const uint32_t split_len = ((len + n_splits - 1) / n_splits + POS_PER_ITER - 1) / POS_PER_ITER * POS_PER_ITER;
+  const uint32_t p0 = min(len, split * split_len), p1 = min(len, p0 + split_len);
+  if (dst.xh && split == 0 && r + 1 == gridDim.z) // the padding rows of the product's n-block are zero
+    for (uint32_t i = threadIdx.x; i < (dst.mp - gridDim.z) * G * HD; i += blockDim.x) {
+      const size_t at = (size_t)(gridDim.z + i / (G * HD)) * heads * HD + (size_t)kvh * G * HD + i % (G * HD);
+      dst.xh[at] = dst.xl[at] = __float2half_rn(0.0f);
+    }
   const uint32_t slot = streams ? (uint32_t)streams[r] : 0;
   const float* kbase = kv.k + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
   const float* vbase = kv.v + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
@@ -142,7 +172,7 @@ __global__ void __launch_bounds__(128)
       o = fmaf(sm_o[w][g][c], sc, o);
     }
     if (n_splits == 1) {
-      out[(size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c] = o / ll;
+      dst.put((size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c, o / ll);
     } else {
       float* p = partial + (((size_t)r * kv_heads + kvh) * n_splits + split) * (size_t)(G * (2 + HD));
       if (c == 0) p[g] = mm, p[G + g] = ll;
@@ -151,10 +181,10 @@ __global__ void __launch_bounds__(128)
   }
 }
 
-// out[row][head][c] = merge over splits
+// out[row][head][c] = merge over splits, ascending
 template <int G>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, uint32_t heads, uint32_t kv_heads,
-                                         uint32_t n_splits, float* __restrict__ out) {
+                                         uint32_t n_splits, DecodeOut dst) {
   const uint32_t kvh = blockIdx.x, r = blockIdx.y;
   const float* base = partial + ((size_t)r * kv_heads + kvh) * n_splits * (size_t)(G * (2 + HD));
   for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
@@ -168,48 +198,63 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, uint
       ll = fmaf(p[G + g], sc, ll);
       o = fmaf(p[2 * G + g * HD + c], sc, o);
     }
-    out[(size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c] = o / ll;
+    dst.put((size_t)r * heads * HD + (size_t)(kvh * G + g) * HD + c, o / ll);
   }
 }
 
 template <int G>
 int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
-           const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t split_len,
-           uint32_t n_splits, float* scratch, float* out) {
+           const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t n_splits,
+           float* scratch, const DecodeOut& dst) {
   dim3 grid(n_splits, kv_heads, rows);
   FC_LAUNCH(dev, "attn_decode",
             attn_decode_split_kernel<G><<<grid, 128, 0, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
-                                                                       split_len, n_splits, scratch, out));
+                                                                       n_splits, scratch, dst));
   if (n_splits > 1) {
     dim3 mg(kv_heads, rows);
     FC_LAUNCH(dev, "attn_decode_merge",
-              attn_decode_merge_kernel<G><<<mg, 128, 0, dev->stream>>>(scratch, heads, kv_heads, n_splits, out));
+              attn_decode_merge_kernel<G><<<mg, 128, 0, dev->stream>>>(scratch, heads, kv_heads, n_splits, dst));
   }
   return FC_OK;
 }
 
 } // namespace
 
-// How the context is cut for `rows` streams: enough CTAs to cover the SMs about twice, ranges a
-// multiple of 64 positions. The grid depends only on (rows, ctx), never on the current positions, so a
-// captured decode step can be replayed; a CTA whose range lies beyond the row's length contributes
-// an empty partial.
-void attn_decode_plan(const FcDevice* dev, uint32_t rows, uint32_t kv_heads, uint32_t ctx, uint32_t* split_len,
-                      uint32_t* n_splits) {
-  const uint32_t want = 2 * (uint32_t)dev->prop.multiProcessorCount;
-  uint32_t base = rows * kv_heads, s = (want + base - 1) / base;
+// CTAs of the split kernel one SM holds (registers bound it: 2 at 8 heads per kv-head, more below).
+template <int G>
+static int resident_ctas() {
+  static int n = 0;
+  if (!n && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_split_kernel<G>, 128, 0) != cudaSuccess) {
+    cudaGetLastError();
+    n = 2;
+  }
+  return n < 1 ? 1 : n;
+}
+
+// How many ways the context is cut for `rows` streams: the most that keeps every CTA resident at
+// once, no range shorter than 64 positions of a full cache. It depends only on (rows, ctx), never on
+// the current positions, so a captured decode step can be replayed.
+static uint32_t attn_decode_splits(const FcDevice* dev, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t ctx) {
+  int per_sm = 2;
+  switch (heads / kv_heads) {
+    case 1: per_sm = resident_ctas<1>(); break;
+    case 2: per_sm = resident_ctas<2>(); break;
+    case 3: per_sm = resident_ctas<3>(); break;
+    case 4: per_sm = resident_ctas<4>(); break;
+    case 6: per_sm = resident_ctas<6>(); break;
+    case 8: per_sm = resident_ctas<8>(); break;
+  }
+  const uint32_t slots = (uint32_t)per_sm * (uint32_t)dev->prop.multiProcessorCount;
+  uint32_t s = slots / (rows * kv_heads);
   const uint32_t max_s = (ctx + POS_PER_ITER - 1) / POS_PER_ITER;
   if (s > max_s) s = max_s;
   if (ctx <= 512) s = 1; // a short cache is a microsecond for one CTA: the merge launch would cost more
-  if (s < 1) s = 1;
-  uint32_t sl = ((ctx + s - 1) / s + POS_PER_ITER - 1) / POS_PER_ITER * POS_PER_ITER;
-  *split_len = sl;
-  *n_splits = (ctx + sl - 1) / sl;
+  return s < 1 ? 1 : s;
 }
 
+// Partial results of every split.
 size_t attn_decode_scratch_bytes(const FcDevice* dev, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t ctx) {
-  uint32_t sl, ns;
-  attn_decode_plan(dev, rows, kv_heads, ctx, &sl, &ns);
+  const uint32_t ns = attn_decode_splits(dev, rows, heads, kv_heads, ctx);
   return (size_t)rows * kv_heads * ns * (heads / kv_heads) * (2 + HD) * 4 + 256;
 }
 
@@ -220,17 +265,18 @@ bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd) 
 
 int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                         const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
-                        float* out) {
+                        float* out, __half* xh, __half* xl, uint32_t mp) {
   if (!rows) return FC_OK;
-  uint32_t sl, ns;
-  attn_decode_plan(dev, rows, kv_heads, ctx, &sl, &ns);
+  const uint32_t ns = attn_decode_splits(dev, rows, heads, kv_heads, ctx);
+  DecodeOut dst;
+  dst.out = out, dst.xh = xh, dst.xl = xl, dst.mp = mp;
   switch (heads / kv_heads) {
-    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
-    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
-    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
-    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
-    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
-    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, sl, ns, scratch, out);
+    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
   }
   return fc_fail(dev, FC_ERR_UNSUPPORTED, "split decode attention: group size %u", heads / kv_heads);
 }

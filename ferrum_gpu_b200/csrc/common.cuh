@@ -108,6 +108,18 @@ static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) {
 
 // Epilogue of a matrix product: y = act(x W + bias) (+ resid). All pointers device, nullable.
 enum { ACT_NONE = 0, ACT_GELU = 1 };
+// A 9..64-row product whose split-K partial sums have not been combined yet: the consumer of its result
+// (the norm + split launch of the next product) adds them up, applies bias and residual, writes y and
+// carries on - one launch instead of two on a step that is bound by its launch chain.
+struct DeferredReduce {
+  const float* partial = nullptr; // [splits][m][n]
+  uint32_t splits = 0;            // 0: nothing pending
+  uint32_t m = 0, n = 0;
+  const float* bias = nullptr;
+  const float* resid = nullptr;
+  float* y = nullptr;
+};
+
 struct Epilogue {
   const float* bias = nullptr;  // [n]
   const float* resid = nullptr; // [m][n]; may alias y
@@ -127,6 +139,10 @@ struct Epilogue {
   // the producer of x has already written its two fp16 terms where the 9..64-row tensor-core product
   // stages them (qmatvec_mma_split_ptrs): the product skips its split launch and ignores `x`
   bool presplit = false;
+  // leave this product's split-K reduce to the consumer (filled in when the product did split)
+  DeferredReduce* defer_out = nullptr;
+  // finish this pending reduce first: its y is this product's x (same buffer, raw residual stream)
+  const DeferredReduce* pending = nullptr;
 };
 enum { NORM_NONE = 0, NORM_RMS = 1, NORM_LAYER = 2 };
 
@@ -137,6 +153,7 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
 // Whether k_qlinear_f32 will take the 9..64-row tensor-core product for (w, m) with this scratch, and where
 // that product expects the two fp16 terms of x ([mp][k] each, rows >= m zero).
 bool qlinear_takes_wide_mma(const QMat& w, uint32_t m, const void* scratch);
+int k_flush_deferred(FcDevice* dev, const DeferredReduce& d);
 void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, __half** xl, uint32_t* mp);
 
 // ---- kernels' host entry points (each enqueues on dev->stream) --------------------------------

@@ -304,6 +304,11 @@ int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   if (ep.presplit && !(mma_ok && m > 8)) return fc_fail(dev, FC_ERR_ARG, "a pre-split x needs the 9..64-row tensor-core product");
   const bool use_fma = fma_ok && (!mma_ok || forced == 1 || (forced == 0 && m < 2));
   const bool use_mma_wide = !use_fma && mma_ok && m > 8; // its x split takes the norm along
+  if (ep.pending && ep.pending->splits && !use_mma_wide) { // only that split can finish a producer's split-K sum
+    FC_TRY(k_flush_deferred(dev, *ep.pending));
+    ep.pending = nullptr;
+  }
+  if (!use_mma_wide) ep.defer_out = nullptr;
   if (ep.norm != NORM_NONE && !use_fma && !use_mma_wide) { // the FMA matvec normalises while it stages x
     if (!ep.norm_tmp) return fc_fail(dev, FC_ERR_ARG, "a fused norm needs a temporary for the kernels that cannot fuse it");
     if (ep.norm == NORM_RMS)

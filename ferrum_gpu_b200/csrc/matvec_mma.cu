@@ -76,8 +76,9 @@ __device__ __forceinline__ float block_sum_mma(float v, float* red) {
   return t;
 }
 __global__ void __launch_bounds__(256)
-    norm_split_kernel(const float* __restrict__ x, uint32_t m, uint32_t k, int norm, const float* __restrict__ g,
-                      const float* __restrict__ b, float eps, __half* __restrict__ xh, __half* __restrict__ xl) {
+    norm_split_kernel(const float* x, uint32_t m, uint32_t k, int norm, const float* __restrict__ g,
+                      const float* __restrict__ b, float eps, __half* __restrict__ xh, __half* __restrict__ xl,
+                      DeferredReduce pend) {
   __shared__ float red[32];
   const uint32_t r = blockIdx.x;
   __half* oh = xh + (size_t)r * k;
@@ -87,6 +88,33 @@ __global__ void __launch_bounds__(256)
     return;
   }
   const float* row = x + (size_t)r * k;
+  if (pend.splits) {
+    // x is the result of a product whose split-K partials are still apart: finish it exactly as
+    // splitk_reduce_kernel would (ascending split order, bias, residual) and store it; the block reads
+    // the row back below (x is pend.y, and not declared restrict for that reason).
+    float* yrow = pend.y + (size_t)r * k;
+    const size_t split_stride = (size_t)pend.m * k;
+    const float* prow = pend.partial + (size_t)r * k;
+    for (uint32_t i = threadIdx.x * 4; i < k; i += blockDim.x * 4) { // (k is a multiple of 128; rows are 16-byte aligned)
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+      for (uint32_t s = 0; s < pend.splits; s++) {
+        const float4 p = *reinterpret_cast<const float4*>(prow + s * split_stride + i);
+        v.x += p.x, v.y += p.y, v.z += p.z, v.w += p.w;
+      }
+      if (pend.bias) {
+        const float4 bb = *reinterpret_cast<const float4*>(pend.bias + i);
+        v.x += bb.x, v.y += bb.y, v.z += bb.z, v.w += bb.w;
+      }
+      if (pend.resid) {
+        const float4 rr = *reinterpret_cast<const float4*>(pend.resid + (size_t)r * k + i);
+        v.x = rr.x + v.x, v.y = rr.y + v.y, v.z = rr.z + v.z, v.w = rr.w + v.w;
+      }
+      *reinterpret_cast<float4*>(yrow + i) = v;
+    }
+    __syncthreads(); // the loops below give the elements to other threads
+    row = yrow;
+  }
   float mean = 0.0f, inv;
   if (norm == NORM_RMS) {
     float ss = 0.0f;
@@ -504,6 +532,18 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   return FC_OK;
 }
 
+// The plain reduce of a deferred product, for a consumer that cannot take it along.
+int k_flush_deferred(FcDevice* dev, const DeferredReduce& d) {
+  if (!d.splits) return FC_OK;
+  Epilogue ep;
+  ep.bias = d.bias;
+  ep.resid = d.resid;
+  const size_t tot = (size_t)d.m * d.n;
+  FC_LAUNCH(dev, "splitk_reduce",
+            splitk_reduce_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, dev->stream>>>(d.partial, d.splits, d.m, d.n, d.y, ep));
+  return FC_OK;
+}
+
 void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, __half** xl, uint32_t* mp) {
   *mp = m <= 16 ? 16 : m <= 32 ? 32 : 64;
   *xh = (__half*)scratch;
@@ -517,11 +557,22 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   qmatvec_mma_split_ptrs(scratch, m, w.k, &xh, &xl, &mp);
   float* partial = (float*)(((uintptr_t)(xl + (size_t)mp * w.k) + 255) & ~(uintptr_t)255);
   const size_t total = (size_t)mp * w.k;
+  DeferredReduce pend;
+  if (ep.pending && ep.pending->splits) {
+    // taken along by the norm + split launch when it is this product's x and its partial sums lie clear
+    // of the x terms that launch writes; finished on its own otherwise
+    const DeferredReduce& d = *ep.pending;
+    if (!ep.presplit && ep.norm != NORM_NONE && d.y == x && d.m == m && d.n == w.k &&
+        (uintptr_t)d.partial >= (uintptr_t)(xl + (size_t)mp * w.k))
+      pend = d;
+    else
+      FC_TRY(k_flush_deferred(dev, d));
+  }
   if (ep.presplit) {
     // the producer of x wrote xh / xl itself
   } else if (ep.norm != NORM_NONE) // x is the raw residual stream: normalise and split in one launch
     FC_LAUNCH(dev, "norm_split",
-              norm_split_kernel<<<mp, 256, 0, dev->stream>>>(x, m, w.k, ep.norm, ep.norm_g, ep.norm_b, ep.norm_eps, xh, xl));
+              norm_split_kernel<<<mp, 256, 0, dev->stream>>>(x, m, w.k, ep.norm, ep.norm_g, ep.norm_b, ep.norm_eps, xh, xl, pend));
   else
     FC_LAUNCH(dev, "x_split", x_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(x, m, mp, w.k, xh, xl));
   // split K until the grid covers the SMs about twice: whole 128-k slices per split, the last split may be
@@ -539,6 +590,17 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
     FC_TRY(pick_nb<FC_Q8_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else
     FC_TRY(pick_nb<FC_Q4_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
+  if (splits > 1 && ep.defer_out && ep.act == ACT_NONE) { // the consumer's norm + split launch finishes the sum
+    DeferredReduce& d = *ep.defer_out;
+    d.partial = partial;
+    d.splits = splits;
+    d.m = m;
+    d.n = w.n;
+    d.bias = ep.bias;
+    d.resid = ep.resid;
+    d.y = y;
+    return FC_OK;
+  }
   if (splits > 1) {
     const size_t tot = (size_t)m * w.n;
     FC_LAUNCH(dev, "splitk_reduce",

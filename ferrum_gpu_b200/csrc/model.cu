@@ -184,37 +184,55 @@ static void norm_before(const FcModel* m, Epilogue& e, const float* g, const flo
 
 int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32_t* positions, const int32_t* streams,
                   uint32_t rows, AttnMode mode, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t stream,
-                  bool final_norm) {
+                  bool final_norm, DeferredReduce* tail = nullptr) {
   FcDevice* dev = m->dev;
   const uint32_t d = m->dim;
   FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, b.x));
+  // The two products that write the residual stream (wo, ff2) may leave their split-K sum to the norm
+  // launch of the product that reads it next: `pend` is that unfinished sum, consumed (or finished on
+  // its own) by the very next k_qlinear_f32.
+  DeferredReduce pend, made;
   for (auto& l : m->layers) {
     Epilogue e_qkv;
     e_qkv.scratch = m->mma_scratch;
     e_qkv.bias = l.qkv.bias;
+    e_qkv.pending = &pend;
     norm_before(m, e_qkv, l.norm1_g, l.norm1_b, b.h);
     FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.x, rows, b.qkv, e_qkv));
+    pend = DeferredReduce();
     const bool to_cache = mode != ATTN_STATELESS;
     FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
                      to_cache ? &l.kv : nullptr, m->ctx));
-    if (mode == ATTN_DECODE)
+    Epilogue e_wo;
+    if (mode == ATTN_DECODE) {
+      __half *xh = nullptr, *xl = nullptr;
+      uint32_t mp = 0;
+      if (m->attn_scratch && qlinear_takes_wide_mma(l.wo.w->m, rows, m->mma_scratch)) {
+        // the attention writes the output product's fp16 terms itself
+        qmatvec_mma_split_ptrs(m->mma_scratch, rows, m->qd(), &xh, &xl, &mp);
+        e_wo.presplit = true;
+      }
       FC_TRY(k_attn_decode(dev, b.qkv, m->qkv_w(), rows, m->heads, m->kv_heads, m->hd, positions, streams, l.kv, m->ctx,
-                           b.attn, m->attn_scratch));
-    else if (mode == ATTN_STATELESS)
+                           b.attn, m->attn_scratch, xh, xl, mp));
+    } else if (mode == ATTN_STATELESS)
       FC_TRY(k_attn_causal_f32(dev, b.qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, b.attn));
     else
       FC_TRY(k_attn_prefill_cache_f32(dev, b.qkv, t, start, m->heads, m->kv_heads, m->hd, stream, l.kv, m->ctx, b.attn));
-    Epilogue e_wo;
     e_wo.scratch = m->mma_scratch;
     e_wo.bias = l.wo.bias;
     e_wo.resid = b.x;
+    made = DeferredReduce();
+    e_wo.defer_out = &made;
     FC_TRY(k_qlinear_f32(dev, l.wo.w->m, b.attn, rows, b.x, e_wo));
+    pend = made;
     Epilogue e_ff1;
     e_ff1.scratch = m->mma_scratch;
     e_ff1.bias = l.ff1.bias;
     e_ff1.act = m->arch == ARCH_GPT2 ? ACT_GELU : ACT_NONE;
+    e_ff1.pending = &pend;
     norm_before(m, e_ff1, l.norm2_g, l.norm2_b, b.h);
     FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.x, rows, b.ff, e_ff1));
+    pend = DeferredReduce();
     const float* ff2_in = b.ff;
     Epilogue e_ff2;
     if (m->arch == ARCH_LLAMA) {
@@ -232,9 +250,17 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     e_ff2.scratch = m->mma_scratch;
     e_ff2.bias = l.ff2.bias;
     e_ff2.resid = b.x;
+    made = DeferredReduce();
+    e_ff2.defer_out = &made;
     FC_TRY(k_qlinear_f32(dev, l.ff2.w->m, ff2_in, rows, b.x, e_ff2));
+    pend = made;
   }
-  if (!final_norm) return FC_OK; // the caller folds it into the head product
+  if (!final_norm && tail) { // the caller folds the norm, and the last unfinished sum, into the head product
+    *tail = pend;
+    return FC_OK;
+  }
+  FC_TRY(k_flush_deferred(dev, pend));
+  if (!final_norm) return FC_OK;
   if (m->arch == ARCH_LLAMA)
     FC_TRY(k_rmsnorm(dev, b.x, m->normf_g, rows, d, m->eps, b.h));
   else
@@ -539,9 +565,11 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
     FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
     FC_CUDA(dev, cudaMemcpyAsync(m->d_streams, p + 2 * n, n * 4, cudaMemcpyHostToDevice, dev->stream));
     PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
-    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false));
+    DeferredReduce tail;
+    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false, &tail));
     Epilogue e_head;
     e_head.scratch = m->mma_scratch;
+    e_head.pending = &tail;
     norm_before(m, e_head, m->normf_g, m->normf_b, m->h);
     FC_TRY(k_qlinear_f32(dev, m->head_view, m->x, n, m->logits, e_head));
     FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax));

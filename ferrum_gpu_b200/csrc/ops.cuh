@@ -40,16 +40,19 @@ int k_nll_sums(FcDevice* dev, const float* logprob, uint32_t n_seqs, uint32_t ro
 
 // attention.cu
 // Decode: one query row per stream against that stream's cache, positions 0..=pos[row].
-// `scratch` (attn_decode_scratch_bytes, nullable) enables the context-split kernel of attn_decode.cu.
+// `scratch` (attn_decode_scratch_bytes, nullable) enables the context-split kernel of
+// attn_decode.cu; that kernel can write the result as the two fp16 terms [mp][heads*hd] of a following
+// 9..64-row tensor-core product instead of `out` (xh, xl set).
 int k_attn_decode(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                   uint32_t hd, const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx,
-                  float* out /*[rows][heads*hd]*/, float* scratch);
+                  float* out /*[rows][heads*hd]*/, float* scratch, __half* xh = nullptr, __half* xl = nullptr,
+                  uint32_t mp = 0);
 // attn_decode.cu
 bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd);
 size_t attn_decode_scratch_bytes(const FcDevice* dev, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t ctx);
 int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                         const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
-                        float* out);
+                        float* out, __half* xh, __half* xl, uint32_t mp);
 // Stateless causal attention over `n_seqs` sequences of `t` rows in the fused qkv buffer (exact f32).
 int k_attn_causal_f32(FcDevice* dev, const float* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
                       uint32_t hd, float* out);
