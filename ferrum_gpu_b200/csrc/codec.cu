@@ -19,6 +19,26 @@ __host__ __device__ inline void q4_dev_pos(int e, int& byte, int& shift) {
   shift = (pos & 1) * 4;
 }
 
+// Fp8::encode (ferrum_gguf/src/codec/fp8.rs:L75-L109): the nearest code by bisection over the positive
+// codes (their values grow with the code), ties to the even code, saturation at the largest finite value.
+template <int KIND>
+__device__ __forceinline__ uint32_t fp8_encode_dev(float x) {
+  if (x != x) return KIND == FC_FP8_E4M3 ? 0x7f : 0x7e;
+  const uint32_t sign = (__float_as_uint(x) >> 24) & 0x80u;
+  const float a = fminf(fabsf(x), KIND == FC_FP8_E4M3 ? 448.0f : 57344.0f);
+  uint32_t lo = 0, hi = KIND == FC_FP8_E4M3 ? 0x7e : 0x7b;
+  while (lo < hi) {
+    const uint32_t mid = lo + (hi - lo) / 2;
+    if (fp8_to_f32<KIND>(mid) < a)
+      lo = mid + 1;
+    else
+      hi = mid;
+  }
+  const uint32_t up = lo, down = lo ? lo - 1 : 0;
+  const float du = fabsf(__fsub_rn(fp8_to_f32<KIND>(up), a)), dd = fabsf(__fsub_rn(a, fp8_to_f32<KIND>(down)));
+  return sign | ((du < dd || (du == dd && up % 2 == 0)) ? up : down);
+}
+
 // One thread per (block b, output column col); threads of a warp take consecutive columns so the
 // reads of the `[k, n]` matrix coalesce.
 template <int KIND>
@@ -31,7 +51,25 @@ __global__ void quantise_kn_kernel(const float* __restrict__ w, uint32_t k, uint
 #pragma unroll
   for (int j = 0; j < QK; j++) v[j] = w[(size_t)(b * QK + j) * n + col];
   uint32_t nb = k / QK;
-  if (KIND == FC_Q8_0) {
+  if (kind_is_fp8(KIND)) { // fp8.rs:L112-L124: the inverse is taken of the rounded scale
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < QK; j++) amax = fmaxf(amax, fabsf(v[j]));
+    const __half d = __float2half_rn(__fdiv_rn(amax, KIND == FC_FP8_E4M3 ? 448.0f : 57344.0f));
+    const float df = __half2float(d);
+    const float id = df != 0.0f ? __fdiv_rn(1.0f, df) : 0.0f;
+    sc[(size_t)col * nb + b] = d;
+    uint32_t words[QK / 4];
+#pragma unroll
+    for (int j = 0; j < QK; j++) { // (unrolled like the other branches: v and words stay in registers)
+      const uint32_t c = fp8_encode_dev<KIND>(__fmul_rn(v[j], id));
+      if ((j & 3) == 0) words[j >> 2] = 0;
+      words[j >> 2] |= c << (8 * (j & 3));
+    }
+    uint4* dst = reinterpret_cast<uint4*>(qs + (size_t)col * k + (size_t)b * QK);
+    dst[0] = make_uint4(words[0], words[1], words[2], words[3]);
+    dst[1] = make_uint4(words[4], words[5], words[6], words[7]);
+  } else if (KIND == FC_Q8_0) {
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < QK; j++) amax = fmaxf(amax, fabsf(v[j]));
@@ -94,7 +132,7 @@ __global__ void repack_blocks_kernel(const uint8_t* __restrict__ blocks, uint32_
   size_t nb = k / QK;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; // row * nb + b
   if (idx >= nb * n) return;
-  constexpr int FB = KIND == FC_Q8_0 ? 34 : 18;
+  constexpr int FB = KIND == FC_Q8_0 ? 34 : 18; // (the FP8 formats come through as Q8_0: the same bytes)
   const uint8_t* p = blocks + idx * FB;
   uint16_t h = (uint16_t)(p[0] | (p[1] << 8));
   sc[idx] = __ushort_as_half(h);
@@ -147,7 +185,9 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ qs, const __half* __r
   if (idx >= nb * n) return;
   float d = __half2float(sc[idx]);
   float* o = out + idx * QK;
-  if (KIND == FC_Q8_0) {
+  if (kind_is_fp8(KIND)) { // fp8.rs:L127-L134
+    for (int j = 0; j < QK; j++) o[j] = __fmul_rn(d, fp8_to_f32<KIND>(qs[idx * QK + j]));
+  } else if (KIND == FC_Q8_0) {
     const int8_t* q = reinterpret_cast<const int8_t*>(qs) + idx * QK;
     for (int j = 0; j < QK; j++) o[j] = __fmul_rn(d, (float)q[j]);
   } else {
@@ -193,6 +233,10 @@ int k_quantise_kn(FcDevice* dev, int kind, const float* w, uint32_t k, uint32_t 
     FC_LAUNCH(dev, "quantise_q8_0", quantise_kn_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
   else if (kind == FC_Q4_0)
     FC_LAUNCH(dev, "quantise_q4_0", quantise_kn_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
+  else if (kind == FC_FP8_E4M3)
+    FC_LAUNCH(dev, "quantise_fp8", quantise_kn_kernel<FC_FP8_E4M3><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
+  else if (kind == FC_FP8_E5M2)
+    FC_LAUNCH(dev, "quantise_fp8", quantise_kn_kernel<FC_FP8_E5M2><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
   else
     return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   return FC_OK;
@@ -211,7 +255,7 @@ int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, 
   }
   size_t total = (size_t)(k / QK) * n;
   unsigned grid = (unsigned)((total + 127) / 128);
-  if (kind == FC_Q8_0)
+  if (kind_byte_blocks(kind))
     FC_LAUNCH(dev, "repack_q8_0", repack_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
   else if (kind == FC_Q4_0)
     FC_LAUNCH(dev, "repack_q4_0", repack_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
@@ -227,7 +271,7 @@ int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
   }
   size_t total = (size_t)(m.k / QK) * m.n;
   unsigned grid = (unsigned)((total + 127) / 128);
-  if (m.kind == FC_Q8_0)
+  if (kind_byte_blocks(m.kind))
     FC_LAUNCH(dev, "export_q8_0", export_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
   else if (m.kind == FC_Q4_0)
     FC_LAUNCH(dev, "export_q4_0", export_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
@@ -250,6 +294,10 @@ int k_dequant(FcDevice* dev, const QMat& m, float* out) {
   unsigned grid = (unsigned)((total + 127) / 128);
   if (m.kind == FC_Q8_0)
     FC_LAUNCH(dev, "dequant_q8_0", dequant_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
+  else if (m.kind == FC_FP8_E4M3)
+    FC_LAUNCH(dev, "dequant_fp8", dequant_kernel<FC_FP8_E4M3><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
+  else if (m.kind == FC_FP8_E5M2)
+    FC_LAUNCH(dev, "dequant_fp8", dequant_kernel<FC_FP8_E5M2><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
   else
     FC_LAUNCH(dev, "dequant_q4_0", dequant_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
   return FC_OK;

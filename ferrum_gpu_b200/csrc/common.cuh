@@ -80,6 +80,7 @@ int fc_pinned(FcDevice* dev, size_t bytes, void** out);
 //           mask pairs (p, p+4) of one word unpack to consecutive elements; sc as above
 //  FC_F32:  qs = f32  [n][k];            sc = nullptr
 //  FC_F16:  qs = f16  [n][k];            sc = nullptr
+//  FC_FP8_E4M3 / FC_FP8_E5M2: Q8_0's planes, the bytes being FP8 codes instead of int8 quants
 struct QMat {
   int kind = FC_F32;
   uint32_t k = 0, n = 0;
@@ -99,12 +100,37 @@ struct FcQWeight {
   void* mma_scratch = nullptr; // scratch of the batched-decode product for stand-alone use
 };
 
+__host__ __device__ constexpr bool kind_is_fp8(int kind) { return kind == FC_FP8_E4M3 || kind == FC_FP8_E5M2; }
+// one byte per element and an f16 scale per 32: Q8_0 and the FP8 formats share planes, loads and addressing
+__host__ __device__ constexpr bool kind_byte_blocks(int kind) { return kind == FC_Q8_0 || kind_is_fp8(kind); }
+__host__ __device__ constexpr bool kind_has_scales(int kind) { return kind_byte_blocks(kind) || kind == FC_Q4_0; }
+static inline bool kind_known(int kind) { return kind >= FC_F32 && kind <= FC_FP8_E5M2; }
+
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
-  return kind == FC_Q8_0 ? k * n : kind == FC_Q4_0 ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
+  return kind_byte_blocks(kind) ? k * n : kind == FC_Q4_0 ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
 }
-static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) {
-  return (kind == FC_Q8_0 || kind == FC_Q4_0) ? (k / QK) * n * 2 : 0;
+static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) { return kind_has_scales(kind) ? (k / QK) * n * 2 : 0; }
+
+#ifdef __CUDACC__
+// Two FP8 codes (the low 16 bits of `two`) as two fp16 values, low byte in the low half. Exact: every
+// E4M3 and E5M2 value, infinities and NaNs included, is an fp16 value.
+template <int KIND>
+__device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two) {
+  uint32_t r;
+  const unsigned short v = (unsigned short)two;
+  if (KIND == FC_FP8_E4M3)
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+  else
+    asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(r) : "h"(v));
+  return r;
 }
+// One code as f32 (exact).
+template <int KIND>
+__device__ __forceinline__ float fp8_to_f32(uint32_t code) {
+  const uint32_t h2 = fp8x2_to_f16x2<KIND>(code & 0xffu);
+  return __half2float(__ushort_as_half((unsigned short)(h2 & 0xffffu)));
+}
+#endif
 
 // Epilogue of a matrix product: y = act(x W + bias) (+ resid). All pointers device, nullable.
 enum { ACT_NONE = 0, ACT_GELU = 1 };

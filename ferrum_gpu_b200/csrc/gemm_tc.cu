@@ -95,6 +95,24 @@ __device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_
   }
 }
 
+// 16 FP8 codes (half a block) -> 2 chunks: code -> fp16 exactly, times the f16 scale, one rounding
+template <int KIND>
+__device__ __forceinline__ void dequant_fp8_half(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+  const uint32_t dd = (uint32_t)__half_as_ushort(d) * 0x00010001u;
+  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint32_t o[4];
+#pragma unroll
+    for (int w = 0; w < 2; w++) {
+      o[2 * w] = f16x2_mul(fp8x2_to_f16x2<KIND>(words[2 * h + w]), dd);
+      o[2 * w + 1] = f16x2_mul(fp8x2_to_f16x2<KIND>(words[2 * h + w] >> 16), dd);
+    }
+    const uint32_t addr = row_smem + (((c0 + h) ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+  }
+}
+
 __device__ __forceinline__ float gelu_f(float x) {
   const float K = 0.7978846f;
   return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
@@ -109,6 +127,16 @@ struct RowRegs<FC_Q4_0> {
 };
 template <>
 struct RowRegs<FC_Q8_0> {
+  uint4 q[4];
+  uint32_t sc;
+};
+template <>
+struct RowRegs<FC_FP8_E4M3> {
+  uint4 q[4];
+  uint32_t sc;
+};
+template <>
+struct RowRegs<FC_FP8_E5M2> {
   uint4 q[4];
   uint32_t sc;
 };
@@ -129,7 +157,7 @@ __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32
     r.q[1] = valid ? __ldg(p + 1) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
     *reinterpret_cast<uint32_t*>(&((RowRegs<FC_Q4_0>&)r).sc) =
         valid ? __ldg(reinterpret_cast<const uint32_t*>(w.sc + (size_t)row * (w.k / QK) + (size_t)it * 2)) : 0u;
-  } else if (KIND == FC_Q8_0) {
+  } else if (kind_byte_blocks(KIND)) { // (the three records have one layout)
     const uint4* p = reinterpret_cast<const uint4*>(w.qs + (size_t)row * w.k + (size_t)it * 64);
 #pragma unroll
     for (int i = 0; i < 4; i++) r.q[i] = valid ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
@@ -161,6 +189,13 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
     dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
     dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
     dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+  } else if (kind_is_fp8(KIND)) {
+    const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
+    const __half d0 = __ushort_as_half((unsigned short)(rr.sc & 0xffff)), d1 = __ushort_as_half((unsigned short)(rr.sc >> 16));
+    dequant_fp8_half<KIND>(rr.q[0], d0, row_smem, sw, 0);
+    dequant_fp8_half<KIND>(rr.q[1], d0, row_smem, sw, 2);
+    dequant_fp8_half<KIND>(rr.q[2], d1, row_smem, sw, 4);
+    dequant_fp8_half<KIND>(rr.q[3], d1, row_smem, sw, 6);
   } else if (KIND == FC_F16) { // stored values are the operand: eight 16-byte pieces into their swizzled places
     const RowRegs<FC_F16>& rr = (const RowRegs<FC_F16>&)r;
 #pragma unroll
@@ -470,6 +505,8 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   if (w.kind == FC_Q4_0) return pick_epi<FC_Q4_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_Q8_0) return pick_epi<FC_Q8_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_F16) return pick_epi<FC_F16>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_FP8_E4M3) return pick_epi<FC_FP8_E4M3>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_FP8_E5M2) return pick_epi<FC_FP8_E5M2>(dev, tmap, w, args, epi, grid);
   return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);
 }
 

@@ -34,6 +34,14 @@ template <>
 struct Chunk<FC_F16> {
   static constexpr int ELEMS = 8;
 };
+template <>
+struct Chunk<FC_FP8_E4M3> {
+  static constexpr int ELEMS = 16;
+};
+template <>
+struct Chunk<FC_FP8_E5M2> {
+  static constexpr int ELEMS = 16;
+};
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -76,6 +84,18 @@ __device__ __forceinline__ float chunk_dot(const uint4& wq, const float* __restr
         float q = __uint_as_float(0x4B000000u | nib) - 8388616.0f; // (2^23 + nib) - (2^23 + 8)
         acc = fmaf(xe[j], q, acc);
       }
+    }
+  } else if (kind_is_fp8(KIND)) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float4 xv = *reinterpret_cast<const float4*>(xs + 4 * w);
+      const uint32_t lo = fp8x2_to_f16x2<KIND>(words[w]), hi = fp8x2_to_f16x2<KIND>(words[w] >> 16); // exact
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+      acc = fmaf(xv.x, a.x, acc);
+      acc = fmaf(xv.y, a.y, acc);
+      acc = fmaf(xv.z, b.x, acc);
+      acc = fmaf(xv.w, b.y, acc);
     }
   } else if (KIND == FC_F16) {
 #pragma unroll
@@ -182,10 +202,10 @@ __global__ void __launch_bounds__(256)
       float d[R];
 #pragma unroll
       for (int r = 0; r < R; r++) wq[r] = ldg_stream(w.qs + rows[r] * row_bytes + (size_t)c * 16);
-      if (KIND == FC_Q8_0 || KIND == FC_Q4_0) {
+      if (kind_has_scales(KIND)) {
 #pragma unroll
         for (int r = 0; r < R; r++)
-          d[r] = __half2float(w.sc[(size_t)rows[r] * nb + (KIND == FC_Q8_0 ? (c >> 1) : c)]);
+          d[r] = __half2float(w.sc[(size_t)rows[r] * nb + (kind_byte_blocks(KIND) ? (c >> 1) : c)]);
       }
 #pragma unroll
       for (int m = 0; m < M; m++) {
@@ -277,6 +297,8 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
   if (w.kind == FC_Q8_0) return pick_m<FC_Q8_0>(dev, w, x, m, y, ep);
   if (w.kind == FC_Q4_0) return pick_m<FC_Q4_0>(dev, w, x, m, y, ep);
   if (w.kind == FC_F16) return pick_m<FC_F16>(dev, w, x, m, y, ep);
+  if (w.kind == FC_FP8_E4M3) return pick_m<FC_FP8_E4M3>(dev, w, x, m, y, ep);
+  if (w.kind == FC_FP8_E5M2) return pick_m<FC_FP8_E5M2>(dev, w, x, m, y, ep);
   return pick_m<FC_F32>(dev, w, x, m, y, ep);
 }
 

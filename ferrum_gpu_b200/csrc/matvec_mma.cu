@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(256)
 // conversion so that the next block's loads are in flight while the current one is multiplied.
 template <int KIND>
 struct BlockRegs {
-  uint32_t q[KIND == FC_Q8_0 ? 4 : 2];
+  uint32_t q[kind_byte_blocks(KIND) ? 4 : 2];
   __half d[2];
 };
 template <int KIND>
@@ -154,10 +154,10 @@ __device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, ui
   const uint32_t nb = w.k / QK;
   r.d[0] = w.sc[(size_t)row_g * nb + kb];
   r.d[1] = w.sc[(size_t)row_g8 * nb + kb];
-  if (KIND == FC_Q8_0) {
+  if (kind_byte_blocks(KIND)) {
     const uint2 qa = __ldg(reinterpret_cast<const uint2*>(w.qs + (size_t)row_g * w.k + (size_t)kb * QK + 8 * t));
     const uint2 qb = __ldg(reinterpret_cast<const uint2*>(w.qs + (size_t)row_g8 * w.k + (size_t)kb * QK + 8 * t));
-    r.q[0] = qa.x, r.q[1] = qa.y, r.q[KIND == FC_Q8_0 ? 2 : 0] = qb.x, r.q[KIND == FC_Q8_0 ? 3 : 1] = qb.y;
+    r.q[0] = qa.x, r.q[1] = qa.y, r.q[kind_byte_blocks(KIND) ? 2 : 0] = qb.x, r.q[kind_byte_blocks(KIND) ? 3 : 1] = qb.y;
   } else {
     r.q[0] = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g * (w.k / 2) + (size_t)kb * 16 + 4 * t));
     r.q[1] = __ldg(reinterpret_cast<const uint32_t*>(w.qs + (size_t)row_g8 * (w.k / 2) + (size_t)kb * 16 + 4 * t));
@@ -165,7 +165,15 @@ __device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, ui
 }
 template <int KIND>
 __device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a[2][4]) {
-  if (KIND == FC_Q8_0) {
+  if (kind_is_fp8(KIND)) { // every code is an fp16 value
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      a[s][0] = fp8x2_to_f16x2<KIND>(r.q[s]);
+      a[s][2] = fp8x2_to_f16x2<KIND>(r.q[s] >> 16);
+      a[s][1] = fp8x2_to_f16x2<KIND>(r.q[kind_byte_blocks(KIND) ? 2 + s : 0]);
+      a[s][3] = fp8x2_to_f16x2<KIND>(r.q[kind_byte_blocks(KIND) ? 2 + s : 0] >> 16);
+    }
+  } else if (KIND == FC_Q8_0) {
     const uint32_t wa[2] = {r.q[0] ^ 0x80808080u, r.q[1] ^ 0x80808080u};
     const uint32_t wb[2] = {r.q[KIND == FC_Q8_0 ? 2 : 0] ^ 0x80808080u, r.q[KIND == FC_Q8_0 ? 3 : 1] ^ 0x80808080u};
 #pragma unroll
@@ -295,8 +303,8 @@ __global__ void __launch_bounds__(128)
 template <int KIND>
 struct Mma8 {
   static constexpr int ST = 4;
-  static constexpr int WBYTES = KIND == FC_Q8_0 ? 128 : 64;  // packed bytes of one row of a 128-k slice
-  static constexpr int WROW = KIND == FC_Q8_0 ? 160 : 80;    // padded: lanes (g, t) read conflict-free
+  static constexpr int WBYTES = kind_byte_blocks(KIND) ? 128 : 64;  // packed bytes of one row of a 128-k slice
+  static constexpr int WROW = kind_byte_blocks(KIND) ? 160 : 80;    // padded: lanes (g, t) read conflict-free
   static constexpr int W_STAGE = 64 * WROW;
   static constexpr int SC_STAGE = 64 * 8;                    // 4 f16 scales per row
   static constexpr int XF_STAGE = 8 * XS * 4;                // f32 x slice
@@ -336,7 +344,7 @@ __global__ void __launch_bounds__(128)
     for (int j = 0; j < PER_ROW * 64 / 128; j++) {
       const uint32_t c = threadIdx.x + 128 * j, row = c / PER_ROW, ch = c % PER_ROW;
       const uint32_t grow = min(cta_row0 + row, n - 1); // rows past the end are computed and dropped
-      const uint8_t* src = w.qs + (size_t)grow * (KIND == FC_Q8_0 ? k : k / 2) + (size_t)kb0 * (C::WBYTES / 4) + ch * 16;
+      const uint8_t* src = w.qs + (size_t)grow * (kind_byte_blocks(KIND) ? k : k / 2) + (size_t)kb0 * (C::WBYTES / 4) + ch * 16;
       cp_async16(smem_u32(wq + st * C::W_STAGE + row * C::WROW + ch * 16), src);
     }
     if (threadIdx.x < 64) {
@@ -391,7 +399,18 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int bi = 0; bi < 4; bi++) {
       uint32_t a[2][4];
-      if (KIND == FC_Q8_0) {
+      if (kind_is_fp8(KIND)) {
+        const uint2 qa = *reinterpret_cast<const uint2*>(wst + r0 * C::WROW + bi * 32 + 8 * t);
+        const uint2 qb = *reinterpret_cast<const uint2*>(wst + r1 * C::WROW + bi * 32 + 8 * t);
+        const uint32_t wa[2] = {qa.x, qa.y}, wb[2] = {qb.x, qb.y};
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          a[s][0] = fp8x2_to_f16x2<KIND>(wa[s]);
+          a[s][2] = fp8x2_to_f16x2<KIND>(wa[s] >> 16);
+          a[s][1] = fp8x2_to_f16x2<KIND>(wb[s]);
+          a[s][3] = fp8x2_to_f16x2<KIND>(wb[s] >> 16);
+        }
+      } else if (KIND == FC_Q8_0) {
         const uint2 qa = *reinterpret_cast<const uint2*>(wst + r0 * C::WROW + bi * 32 + 8 * t);
         const uint2 qb = *reinterpret_cast<const uint2*>(wst + r1 * C::WROW + bi * 32 + 8 * t);
         const uint32_t wa[2] = {qa.x ^ 0x80808080u, qa.y ^ 0x80808080u}, wb[2] = {qb.x ^ 0x80808080u, qb.y ^ 0x80808080u};
@@ -486,7 +505,7 @@ int pick_nb(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, ui
 } // namespace
 
 bool qmatvec_mma_supports(const QMat& w, uint32_t m) {
-  return (w.kind == FC_Q8_0 || w.kind == FC_Q4_0) && m >= 1 && m <= 64 && w.k % XS == 0;
+  return kind_has_scales(w.kind) && m >= 1 && m <= 64 && w.k % XS == 0;
 }
 
 // Device scratch the product needs: the two fp16 terms of x and the split-K partial sums.
@@ -516,11 +535,21 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   if (!attr) {
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q8_0>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q4_0>::SMEM));
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_FP8_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Mma8<FC_FP8_E4M3>::SMEM));
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_FP8_E5M2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Mma8<FC_FP8_E5M2>::SMEM));
     attr = true;
   }
   if (w.kind == FC_Q8_0)
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_Q8_0><<<grid, 128, Mma8<FC_Q8_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  else if (w.kind == FC_FP8_E4M3)
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_FP8_E4M3><<<grid, 128, Mma8<FC_FP8_E4M3>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  else if (w.kind == FC_FP8_E5M2)
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_FP8_E5M2><<<grid, 128, Mma8<FC_FP8_E5M2>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
   else
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_Q4_0><<<grid, 128, Mma8<FC_Q4_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
@@ -588,6 +617,10 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   float* part = splits > 1 ? partial : nullptr;
   if (w.kind == FC_Q8_0)
     FC_TRY(pick_nb<FC_Q8_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
+  else if (w.kind == FC_FP8_E4M3)
+    FC_TRY(pick_nb<FC_FP8_E4M3>(dev, w, xh, xl, m, y, part, splits, bps, ep));
+  else if (w.kind == FC_FP8_E5M2)
+    FC_TRY(pick_nb<FC_FP8_E5M2>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else
     FC_TRY(pick_nb<FC_Q4_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   if (splits > 1 && ep.defer_out && ep.act == ACT_NONE) { // the consumer's norm + split launch finishes the sum

@@ -382,7 +382,7 @@ FC_API int fc_llama_create(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaW
   if (!valid_llama(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid Llama configuration");
   if (!w || !w->tok || !w->blocks || !w->out_norm || !w->head) return fc_fail(dev, FC_ERR_ARG, "missing weights");
   if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
-  if (qkind != FC_F32 && qkind != FC_Q8_0 && qkind != FC_Q4_0 && qkind != FC_F16) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
+  if (!kind_known(qkind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
   FC_TRY(check_budget(dev, fc_llama_plan_bytes(c, qkind, max_streams), budget_bytes)); // before any allocation
   FcModel* m = new FcModel();
   m->dev = dev;
@@ -453,7 +453,7 @@ FC_API int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* c, const FcGpt2Weig
   if (!w || !w->tok || !w->pos || !w->blocks || !w->lnf_g || !w->lnf_b || !w->head)
     return fc_fail(dev, FC_ERR_ARG, "missing weights");
   if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
-  if (qkind != FC_F32 && qkind != FC_Q8_0 && qkind != FC_Q4_0 && qkind != FC_F16) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
+  if (!kind_known(qkind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
   FC_TRY(check_budget(dev, fc_gpt2_plan_bytes(c, qkind, max_streams), budget_bytes));
   FcModel* m = new FcModel();
   m->dev = dev;

@@ -8,7 +8,7 @@ int tc_check_errors(FcDevice* dev);                                             
 FC_API size_t fc_block_bytes(int kind, size_t n_elems) {
   if (kind == FC_F32) return n_elems * 4;
   if (n_elems % QK) return 0;
-  if (kind == FC_Q8_0) return n_elems / QK * 34;
+  if (kind_byte_blocks(kind)) return n_elems / QK * 34;
   if (kind == FC_Q4_0) return n_elems / QK * 18;
   if (kind == FC_F16) return n_elems * 2;
   return 0;
@@ -19,7 +19,7 @@ FC_API int fc_qweight_create(FcDevice* dev, int kind, const float* w_in_out, uin
   *out = nullptr;
   cudaSetDevice(dev->ordinal);
   if (!w_in_out) return fc_fail(dev, FC_ERR_ARG, "fc_qweight_create: NULL weights");
-  if (kind != FC_F32 && kind != FC_Q8_0 && kind != FC_Q4_0 && kind != FC_F16) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  if (!kind_known(kind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   if (k == 0 || n == 0 || (kind != FC_F32 && k % QK))
     return fc_fail(dev, FC_ERR_SHAPE, "cannot quantise %llu elements as a %u x %u weight in whole 32-blocks",
                    (unsigned long long)k * n, k, n);
@@ -32,7 +32,7 @@ FC_API int fc_qweight_create_from_blocks(FcDevice* dev, int kind, const uint8_t*
   *out = nullptr;
   cudaSetDevice(dev->ordinal);
   if (!blocks) return fc_fail(dev, FC_ERR_ARG, "fc_qweight_create_from_blocks: NULL blocks");
-  if (kind != FC_Q8_0 && kind != FC_Q4_0 && kind != FC_F16) return fc_fail(dev, FC_ERR_ARG, "block upload takes Q8_0, Q4_0 or F16, not kind %d", kind);
+  if (!kind_known(kind) || kind == FC_F32) return fc_fail(dev, FC_ERR_ARG, "block upload takes a block format or F16, not kind %d", kind);
   if (k == 0 || n == 0 || k % QK) return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole 32-element blocks", k, n);
   const size_t want = fc_block_bytes(kind, (size_t)k * n);
   if (n_bytes != want)

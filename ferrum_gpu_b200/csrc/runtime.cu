@@ -225,7 +225,7 @@ int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, c
   }
   if (k == 0 || n_total == 0 || n_total > 0x7fffffffu) return fc_fail(dev, FC_ERR_SHAPE, "empty or oversized weight");
   if (kind != FC_F32 && k % QK) kind = FC_F32; // ineligible width stays f32 (ops/quant.rs:L125-L134, lin.rs:L54-L61)
-  if (kind != FC_F32 && kind != FC_Q8_0 && kind != FC_Q4_0 && kind != FC_F16) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  if (!kind_known(kind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   const uint32_t n = (uint32_t)n_total;
   FcQWeight* w = new FcQWeight();
   w->dev = dev;

@@ -104,7 +104,54 @@ int8_t rust_f32_as_i8(float v) {
 
 // F16 (codec/quant.rs:L30,L70,L108): two bytes per element, little endian, no scale; counted here in
 // 32-element groups like the block formats it shares the kernels with (ops/quant.rs:L86)
-size_t block_bytes(int kind) { return kind == FC_Q8_0 ? 2 + QK : kind == FC_F16 ? 2 * QK : 2 + QK / 2; }
+// The FP8 formats use Q8_0's block: an f16 scale and 32 one-byte codes (ferrum_gguf/src/codec/fp8.rs:L18).
+bool is_fp8(int kind) { return kind == FC_FP8_E4M3 || kind == FC_FP8_E5M2; }
+size_t block_bytes(int kind) {
+  return (kind == FC_Q8_0 || is_fp8(kind)) ? 2 + QK : kind == FC_F16 ? 2 * QK : 2 + QK / 2;
+}
+
+// ---- FP8 (ferrum_gguf/src/codec/fp8.rs) --------------------------------------------------------
+// Largest finite magnitude (fp8.rs:L33-L38).
+float fp8_max(int kind) { return kind == FC_FP8_E4M3 ? 448.0f : 57344.0f; }
+
+// fp8.rs:L41-L70. E4M3 has no infinity and one NaN per sign (all ones); E5M2 follows IEEE.
+float fp8_decode(int kind, uint8_t code) {
+  const float sign = (code & 0x80) ? -1.0f : 1.0f;
+  const int ebits = kind == FC_FP8_E4M3 ? 4 : 5, mbits = kind == FC_FP8_E4M3 ? 3 : 2, bias = kind == FC_FP8_E4M3 ? 7 : 15;
+  const uint32_t e = ((uint32_t)code >> mbits) & ((1u << ebits) - 1), m = (uint32_t)code & ((1u << mbits) - 1);
+  const uint32_t top = (1u << ebits) - 1;
+  if (e == top) {
+    if (kind == FC_FP8_E4M3) {
+      if (m == (1u << mbits) - 1) return std::nanf("");
+    } else {
+      return m == 0 ? sign * INFINITY : std::nanf("");
+    }
+  }
+  const float frac = (float)m / (float)(1u << mbits);
+  if (e == 0) return sign * frac * std::ldexp(1.0f, 1 - bias);
+  return sign * (1.0f + frac) * std::ldexp(1.0f, (int)e - bias);
+}
+
+// fp8.rs:L75-L109: the nearest code by bisection over the (monotonic) positive codes, ties to the
+// even code, magnitudes past the largest finite value saturate to it, NaN has its own code.
+uint8_t fp8_encode(int kind, float x) {
+  if (x != x) return kind == FC_FP8_E4M3 ? 0x7f : 0x7e;
+  const uint8_t sign = std::signbit(x) ? 0x80 : 0;
+  const float a = std::fmin(std::fabs(x), fp8_max(kind));
+  const uint8_t limit = kind == FC_FP8_E4M3 ? 0x7e : 0x7b;
+  uint8_t lo = 0, hi = limit;
+  while (lo < hi) {
+    const uint8_t mid = (uint8_t)(lo + (hi - lo) / 2);
+    if (fp8_decode(kind, mid) < a)
+      lo = (uint8_t)(mid + 1);
+    else
+      hi = mid;
+  }
+  const uint8_t up = lo, down = lo ? (uint8_t)(lo - 1) : 0;
+  const float du = std::fabs(fp8_decode(kind, up) - a), dd = std::fabs(a - fp8_decode(kind, down));
+  const uint8_t pick = (du < dd || (du == dd && up % 2 == 0)) ? up : down;
+  return sign | pick;
+}
 
 // ferrum_gguf/src/codec/quant.rs:L111-L119 (Q8_0) and L120-L133 (Q4_0)
 void encode(int kind, const float* data, size_t n, uint8_t* out) {
@@ -117,6 +164,17 @@ void encode(int kind, const float* data, size_t n, uint8_t* out) {
         o[2 * j] = (uint8_t)(h & 0xff);
         o[2 * j + 1] = (uint8_t)(h >> 8);
       }
+      continue;
+    }
+    if (is_fp8(kind)) { // fp8.rs:L112-L124: the scale maps the block's largest magnitude onto the format's
+      float amax = 0.0f;
+      for (size_t j = 0; j < QK; j++) amax = std::fmax(amax, std::fabs(blk[j]));
+      const uint16_t h = f32_to_f16(amax / fp8_max(kind));
+      const float df = f16_to_f32(h);
+      const float id = df != 0.0f ? 1.0f / df : 0.0f; // (of the rounded scale, unlike Q8_0)
+      o[0] = (uint8_t)(h & 0xff);
+      o[1] = (uint8_t)(h >> 8);
+      for (size_t j = 0; j < QK; j++) o[2 + j] = fp8_encode(kind, blk[j] * id);
       continue;
     }
     if (kind == FC_Q8_0) {
@@ -159,7 +217,9 @@ void decode(int kind, const uint8_t* bytes, size_t n, float* out) {
       continue;
     }
     float d = f16_to_f32((uint16_t)(p[0] | (p[1] << 8)));
-    if (kind == FC_Q8_0) {
+    if (is_fp8(kind)) { // fp8.rs:L127-L134
+      for (size_t j = 0; j < QK; j++) o[j] = d * fp8_decode(kind, p[2 + j]);
+    } else if (kind == FC_Q8_0) {
       for (size_t j = 0; j < QK; j++) o[j] = d * (float)(int8_t)p[2 + j];
     } else {
       for (size_t j = 0; j < QK / 2; j++) {
@@ -611,6 +671,10 @@ int gpt2_feed(OrGpt2& m, int32_t token, float* logits_out) {
 
 OR_API float or_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
 OR_API uint16_t or_f32_to_f16(float x) { return f32_to_f16(x); }
+
+// One FP8 code <-> f32 (ferrum_gguf/src/codec/fp8.rs:L41-L109)
+OR_API float or_fp8_decode(int kind, uint8_t code) { return fp8_decode(kind, code); }
+OR_API uint8_t or_fp8_encode(int kind, float x) { return fp8_encode(kind, x); }
 
 OR_API size_t or_block_bytes(int kind, size_t n) {
   if (kind == FC_F32) return n * 4;

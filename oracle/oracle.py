@@ -40,6 +40,7 @@ def lib() -> C.CDLL:
     f, P = C.c_float, C.POINTER
     sig = {
         "or_f16_to_f32": (f, [C.c_uint16]), "or_f32_to_f16": (C.c_uint16, [f]),
+        "or_fp8_decode": (f, [C.c_int, C.c_uint8]), "or_fp8_encode": (C.c_uint8, [C.c_int, f]),
         "or_block_bytes": (sz, [C.c_int, sz]),
         "or_encode": (C.c_int, [C.c_int, vp, sz, vp]), "or_decode": (C.c_int, [C.c_int, vp, sz, vp]),
         "or_quantise_matrix": (C.c_int, [C.c_int, vp, sz, sz, vp]),
@@ -96,6 +97,16 @@ def f16_to_f32(h: int) -> float:
 
 def f32_to_f16(x: float) -> int:
     return lib().or_f32_to_f16(C.c_float(x))
+
+
+def fp8_decode(kind: int, code: int) -> float:
+    """`Fp8::decode` (ferrum_gguf/src/codec/fp8.rs:L41-L70); kind is FC_FP8_E4M3 or FC_FP8_E5M2."""
+    return lib().or_fp8_decode(kind, code)
+
+
+def fp8_encode(kind: int, x: float) -> int:
+    """`Fp8::encode` (fp8.rs:L75-L109)."""
+    return lib().or_fp8_encode(kind, C.c_float(x))
 
 
 def block_bytes(kind: int, n: int) -> int:

@@ -533,3 +533,91 @@ def test_f16_stored_weights_round_to_nearest_even_without_a_scale():
     with np.errstate(over="ignore"):
         assert np.array_equal(raw.view(np.float16).reshape(n, k).view(np.uint16),
                               finite.reshape(k, n).T.astype(np.float16).view(np.uint16))
+
+
+# ---- FP8 stored formats (ferrum_gguf/src/codec/fp8.rs; known answers of fp8/tests.rs) ---------------
+
+def test_fp8_codes_have_the_published_values():
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    # fp8/tests.rs:L4-L13
+    assert orc.fp8_decode(E4, 0x00) == 0.0
+    assert orc.fp8_decode(E4, 0x01) == 2.0 ** -9   # the smallest subnormal
+    assert orc.fp8_decode(E4, 0x08) == 2.0 ** -6   # the smallest normal
+    assert orc.fp8_decode(E4, 0x38) == 1.0
+    assert orc.fp8_decode(E4, 0x7e) == 448.0       # the largest finite value
+    assert math.isnan(orc.fp8_decode(E4, 0x7f)) and math.isnan(orc.fp8_decode(E4, 0xff))
+    assert orc.fp8_decode(E4, 0xb8) == -1.0
+    # fp8/tests.rs:L16-L25
+    assert orc.fp8_decode(E5, 0x01) == 2.0 ** -16
+    assert orc.fp8_decode(E5, 0x04) == 2.0 ** -14
+    assert orc.fp8_decode(E5, 0x3c) == 1.0
+    assert orc.fp8_decode(E5, 0x7b) == 57344.0
+    assert orc.fp8_decode(E5, 0x7c) == math.inf and orc.fp8_decode(E5, 0xfc) == -math.inf
+    assert math.isnan(orc.fp8_decode(E5, 0x7d))
+
+
+def test_fp8_decode_agrees_with_the_ieee_style_bit_layouts():
+    """E5M2 is the top byte of an IEEE half; E4M3 is a half with the exponent re-biased by 8 - an
+    independent statement of the two tables."""
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    for code in range(256):
+        want = np.array([code << 8], dtype=np.uint16).view(np.float16)[0]
+        got = orc.fp8_decode(E5, code)
+        assert (math.isnan(got) and np.isnan(want)) or got == float(want), hex(code)
+        if code & 0x7f == 0x7f:
+            continue  # E4M3's NaN
+        e, m = (code >> 3) & 15, code & 7
+        mag = m / 8 * 2.0 ** -6 if e == 0 else (1 + m / 8) * 2.0 ** (e - 7)
+        assert orc.fp8_decode(E4, code) == (-mag if code & 0x80 else mag), hex(code)
+
+
+def test_fp8_every_finite_code_round_trips_through_encode():
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    for kind, limit in ((E4, 0x7e), (E5, 0x7b)):  # fp8/tests.rs:L28-L38
+        for code in range(limit + 1):
+            v = orc.fp8_decode(kind, code)
+            assert orc.fp8_decode(kind, orc.fp8_encode(kind, v)) == v
+            assert orc.fp8_decode(kind, orc.fp8_encode(kind, -v)) == -v
+
+
+def test_fp8_encode_rounds_to_nearest_ties_to_even_and_saturates():
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    # fp8/tests.rs:L41-L58
+    assert orc.fp8_encode(E4, 1.0625) == 0x38      # midpoint of 1.0 and 1.125: the even code
+    assert orc.fp8_encode(E4, 1.0626) == 0x39
+    assert orc.fp8_encode(E4, 1.1875) == 0x3a      # midpoint of 1.125 and 1.25
+    assert orc.fp8_encode(E4, 1.0e9) == 0x7e and orc.fp8_encode(E4, -1.0e9) == 0xfe
+    assert orc.fp8_encode(E4, math.inf) == 0x7e
+    assert orc.fp8_encode(E4, -0.0) == 0x80
+    assert orc.fp8_encode(E4, math.nan) == 0x7f
+    assert orc.fp8_encode(E5, math.nan) == 0x7e
+    assert orc.fp8_encode(E5, 1.0e9) == 0x7b
+
+
+def test_fp8_blocks_scale_to_the_formats_range():
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    # fp8/tests.rs:L61-L82
+    data = np.array([math.sin(i * 0.31) * (1.0 + i % 5) for i in range(64)], dtype=np.float32)
+    for kind, tol in ((E4, 0.07), (E5, 0.13)):
+        raw = orc.encode(kind, data)
+        assert raw.size == 2 * 34 == orc.block_bytes(kind, 64)
+        back = orc.decode(kind, raw, 64)
+        for b in range(2):
+            blk, got = data[32 * b:32 * b + 32], back[32 * b:32 * b + 32]
+            assert np.all(np.abs(blk - got) <= tol * np.max(np.abs(blk)))
+        # the scale is f16(amax / max) and the largest element lands on (or next to) the top code
+        d = np.frombuffer(raw[:2].tobytes(), dtype=np.float16)[0]
+        assert d == np.float16(np.max(np.abs(data[:32])) / np.float32(448.0 if kind == E4 else 57344.0))
+    assert np.array_equal(orc.decode(E4, orc.encode(E4, np.zeros(32, np.float32)), 32), np.zeros(32, np.float32))
+
+
+def test_fp8_snapping_is_idempotent():
+    """Re-encoding dequantised FP8 weights gives the same values (what lets a GPU run and the oracle share one
+    dequantised model)."""
+    from ferrum_gpu_b200._ffi import FC_FP8_E4M3 as E4, FC_FP8_E5M2 as E5
+    w = orc.rand_vec(64 * 40, 21) * np.float32(0.05)
+    for kind in (E4, E5):
+        once = orc.snap_matrix(kind, w, 64, 40)
+        assert np.max(np.abs(once - w)) <= (0.07 if kind == E4 else 0.13) * np.max(np.abs(w))
+        twice = orc.snap_matrix(kind, once, 64, 40)
+        assert np.max(np.abs(twice - once)) <= 2.0 ** -10 * np.max(np.abs(w))
