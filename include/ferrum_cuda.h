@@ -47,8 +47,10 @@ enum {
  * (ferrum_wgpu/src/ops/quant.rs:L27-L44), restricted to the kinds on this path. */
 /* FC_F16: plain f16 values, no scale, compute stays f32 - QKind::F16 (ops/quant.rs:L33-L36).
  * FC_FP8_E4M3 / FC_FP8_E5M2: one-byte floats with an f16 scale per 32, in Q8_0's block layout -
- * QKind::Fp8E4M3 / Fp8E5M2 (ops/quant.rs:L38-L41, codec ferrum_gguf/src/codec/fp8.rs). */
-enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2, FC_F16 = 3, FC_FP8_E4M3 = 4, FC_FP8_E5M2 = 5 };
+ * QKind::Fp8E4M3 / Fp8E5M2 (ops/quant.rs:L38-L41, codec ferrum_gguf/src/codec/fp8.rs).
+ * FC_MXFP4: 4-bit E2M1 values with a power-of-two scale byte per 32, 17-byte blocks (ggml type 39) -
+ * QKind::Fp4 (ops/quant.rs:L36-L37, codec ferrum_gguf/src/codec/mxfp4.rs). */
+enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2, FC_F16 = 3, FC_FP8_E4M3 = 4, FC_FP8_E5M2 = 5, FC_MXFP4 = 6 };
 
 /* RoPE pairing, ferrum_ref/src/models/llama/ops.rs:L9-L15. */
 enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };
@@ -119,8 +121,8 @@ size_t fc_block_bytes(int kind, size_t n_elems);
  * ferrum_gguf/src/f16.rs:L25-L53). */
 int fc_qweight_create(FcDevice* dev, int kind, const float* w_in_out, uint32_t k, uint32_t n,
                       FcQWeight** out);
-/* Same from GGUF block bytes: `n` rows of `k / 32` blocks of 34 (Q8_0, FP8) or 18 (Q4_0) bytes, or of
- * `k` f16 values (F16).
+/* Same from GGUF block bytes: `n` rows of `k / 32` blocks of 34 (Q8_0, FP8), 18 (Q4_0) or 17 (MXFP4)
+ * bytes, or of `k` f16 values (F16).
  * Replaces ops::quant::upload_qweight (ops/quant.rs:L266-L277). */
 int fc_qweight_create_from_blocks(FcDevice* dev, int kind, const uint8_t* blocks, size_t n_bytes,
                                   uint32_t k, uint32_t n, FcQWeight** out);

@@ -107,7 +107,41 @@ int8_t rust_f32_as_i8(float v) {
 // The FP8 formats use Q8_0's block: an f16 scale and 32 one-byte codes (ferrum_gguf/src/codec/fp8.rs:L18).
 bool is_fp8(int kind) { return kind == FC_FP8_E4M3 || kind == FC_FP8_E5M2; }
 size_t block_bytes(int kind) {
+  if (kind == FC_MXFP4) return 1 + QK / 2; // ferrum_gguf/src/codec/mxfp4.rs:L12
   return (kind == FC_Q8_0 || is_fp8(kind)) ? 2 + QK : kind == FC_F16 ? 2 * QK : 2 + QK / 2;
+}
+
+// ---- MXFP4 (ferrum_gguf/src/codec/mxfp4.rs) ----------------------------------------------------
+// The sixteen codes as twice their E2M1 value; the top bit of the nibble is the sign (mxfp4.rs:L15).
+const int8_t MXFP4_VALUES[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+
+// 2^(e - 128): half of the E8M0 scale, the two smallest being subnormal f32s (mxfp4.rs:L22-L28).
+float mxfp4_half_scale(uint8_t e) {
+  const uint32_t bits = e < 2 ? (0x00200000u << e) : (((uint32_t)e - 1) << 23);
+  float f;
+  std::memcpy(&f, &bits, 4);
+  return f;
+}
+
+// mxfp4.rs:L49-L54: the scale that puts the block's largest magnitude in [4, 8) half-steps; no NaN byte.
+uint8_t mxfp4_scale_byte(float amax) {
+  if (amax <= 0.0f || !std::isfinite(amax)) return 0;
+  const int v = (int)std::floor(std::log2(amax)) - 2 + 127; // f32 log2, as `f32::log2`
+  return (uint8_t)std::min(std::max(v, 0), 254);
+}
+
+// mxfp4.rs:L57-L68: the code whose value is nearest; a tie keeps the lower index.
+uint8_t mxfp4_nearest(float x, float d) {
+  size_t best = 0;
+  float best_err = std::fabs((float)MXFP4_VALUES[0] * d - x);
+  for (size_t i = 1; i < 16; i++) {
+    const float err = std::fabs((float)MXFP4_VALUES[i] * d - x);
+    if (err < best_err) {
+      best = i;
+      best_err = err;
+    }
+  }
+  return (uint8_t)best;
 }
 
 // ---- FP8 (ferrum_gguf/src/codec/fp8.rs) --------------------------------------------------------
@@ -166,6 +200,15 @@ void encode(int kind, const float* data, size_t n, uint8_t* out) {
       }
       continue;
     }
+    if (kind == FC_MXFP4) { // mxfp4.rs:L71-L82: low nibbles are elements 0..16, high nibbles 16..32
+      float amax = 0.0f;
+      for (size_t j = 0; j < QK; j++) amax = std::fmax(amax, std::fabs(blk[j]));
+      const uint8_t e = mxfp4_scale_byte(amax);
+      const float d = mxfp4_half_scale(e);
+      o[0] = e;
+      for (size_t j = 0; j < QK / 2; j++) o[1 + j] = mxfp4_nearest(blk[j], d) | (uint8_t)(mxfp4_nearest(blk[j + QK / 2], d) << 4);
+      continue;
+    }
     if (is_fp8(kind)) { // fp8.rs:L112-L124: the scale maps the block's largest magnitude onto the format's
       float amax = 0.0f;
       for (size_t j = 0; j < QK; j++) amax = std::fmax(amax, std::fabs(blk[j]));
@@ -214,6 +257,14 @@ void decode(int kind, const uint8_t* bytes, size_t n, float* out) {
     float* o = out + b * QK;
     if (kind == FC_F16) {
       for (size_t j = 0; j < QK; j++) o[j] = f16_to_f32((uint16_t)(p[2 * j] | (p[2 * j + 1] << 8)));
+      continue;
+    }
+    if (kind == FC_MXFP4) { // mxfp4.rs:L31-L46
+      const float hs = mxfp4_half_scale(p[0]);
+      for (size_t j = 0; j < QK / 2; j++) {
+        o[j] = (float)MXFP4_VALUES[p[1 + j] & 15] * hs;
+        o[j + QK / 2] = (float)MXFP4_VALUES[p[1 + j] >> 4] * hs;
+      }
       continue;
     }
     float d = f16_to_f32((uint16_t)(p[0] | (p[1] << 8)));
@@ -671,6 +722,10 @@ int gpt2_feed(OrGpt2& m, int32_t token, float* logits_out) {
 
 OR_API float or_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
 OR_API uint16_t or_f32_to_f16(float x) { return f32_to_f16(x); }
+
+// MXFP4 pieces (ferrum_gguf/src/codec/mxfp4.rs:L22-L28, L49-L54)
+OR_API float or_mxfp4_half_scale(uint8_t e) { return mxfp4_half_scale(e); }
+OR_API uint8_t or_mxfp4_scale_byte(float amax) { return mxfp4_scale_byte(amax); }
 
 // One FP8 code <-> f32 (ferrum_gguf/src/codec/fp8.rs:L41-L109)
 OR_API float or_fp8_decode(int kind, uint8_t code) { return fp8_decode(kind, code); }

@@ -41,6 +41,7 @@ def lib() -> C.CDLL:
     sig = {
         "or_f16_to_f32": (f, [C.c_uint16]), "or_f32_to_f16": (C.c_uint16, [f]),
         "or_fp8_decode": (f, [C.c_int, C.c_uint8]), "or_fp8_encode": (C.c_uint8, [C.c_int, f]),
+        "or_mxfp4_half_scale": (f, [C.c_uint8]), "or_mxfp4_scale_byte": (C.c_uint8, [f]),
         "or_block_bytes": (sz, [C.c_int, sz]),
         "or_encode": (C.c_int, [C.c_int, vp, sz, vp]), "or_decode": (C.c_int, [C.c_int, vp, sz, vp]),
         "or_quantise_matrix": (C.c_int, [C.c_int, vp, sz, sz, vp]),
@@ -107,6 +108,16 @@ def fp8_decode(kind: int, code: int) -> float:
 def fp8_encode(kind: int, x: float) -> int:
     """`Fp8::encode` (fp8.rs:L75-L109)."""
     return lib().or_fp8_encode(kind, C.c_float(x))
+
+
+def mxfp4_half_scale(e: int) -> float:
+    """`half_scale` (ferrum_gguf/src/codec/mxfp4.rs:L22-L28): 2^(e - 128)."""
+    return lib().or_mxfp4_half_scale(e)
+
+
+def mxfp4_scale_byte(amax: float) -> int:
+    """`scale_byte` (mxfp4.rs:L49-L54)."""
+    return lib().or_mxfp4_scale_byte(C.c_float(amax))
 
 
 def block_bytes(kind: int, n: int) -> int:

@@ -621,3 +621,69 @@ def test_fp8_snapping_is_idempotent():
         assert np.max(np.abs(once - w)) <= (0.07 if kind == E4 else 0.13) * np.max(np.abs(w))
         twice = orc.snap_matrix(kind, once, 64, 40)
         assert np.max(np.abs(twice - once)) <= 2.0 ** -10 * np.max(np.abs(w))
+
+
+# ---- MXFP4 (ferrum_gguf/src/codec/mxfp4.rs; known answers of mxfp4/tests.rs) -------------------------
+
+MXFP4_VALUES = [0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12]
+
+
+def test_mxfp4_half_scale_is_two_to_the_e_minus_128_for_every_byte():
+    for e in range(255):  # mxfp4/tests.rs:L4-L8
+        assert orc.mxfp4_half_scale(e) == float(np.float32(2.0 ** (e - 128))), e
+
+
+def test_mxfp4_a_block_of_representable_values_round_trips_exactly():
+    from ferrum_gpu_b200._ffi import FC_MXFP4
+    vals = np.array([MXFP4_VALUES[i % 16] * 0.5 for i in range(32)], dtype=np.float32)  # mxfp4/tests.rs:L11-L23
+    raw = orc.encode(FC_MXFP4, vals)
+    assert raw.size == 17 == orc.block_bytes(FC_MXFP4, 32)
+    assert raw[0] == 127           # amax = 6, floor(log2 6) = 2, e = 2 - 2 + 127
+    assert raw[1] & 15 == 0 and raw[2] & 15 == 1  # the low nibble of byte j is element j
+    assert np.array_equal(orc.decode(FC_MXFP4, raw, 32), vals)
+
+
+def test_mxfp4_error_is_at_most_half_a_step_inside_the_range():
+    from ferrum_gpu_b200._ffi import FC_MXFP4
+    data = np.array([((i * 37 % 101) - 50.0) / 25.0 for i in range(64)], dtype=np.float32)  # mxfp4/tests.rs:L26-L45
+    back = orc.decode(FC_MXFP4, orc.encode(FC_MXFP4, data), 64)
+    for b in range(2):
+        blk, got = data[32 * b:32 * b + 32], back[32 * b:32 * b + 32]
+        d = orc.mxfp4_half_scale(orc.mxfp4_scale_byte(float(np.max(np.abs(blk)))))
+        for x, y in zip(blk, got):
+            limit = 2.0 * d if abs(x) <= 12.0 * d else abs(x) - 12.0 * d
+            assert abs(x - y) <= limit + 1e-6, (x, y, d)
+
+
+def test_mxfp4_zeros_tiny_and_huge_values_keep_a_valid_block():
+    from ferrum_gpu_b200._ffi import FC_MXFP4
+    zeros = np.zeros(32, dtype=np.float32)  # mxfp4/tests.rs:L48-L61
+    assert np.array_equal(orc.encode(FC_MXFP4, zeros), np.zeros(17, dtype=np.uint8))
+    assert np.array_equal(orc.decode(FC_MXFP4, orc.encode(FC_MXFP4, zeros), 32), zeros)
+    v = np.full(32, 0.5, dtype=np.float32)
+    v[3] = np.inf
+    assert orc.encode(FC_MXFP4, v)[0] == 0        # a non-finite amax falls back to scale 0
+    assert orc.encode(FC_MXFP4, np.full(32, 3.0e38, dtype=np.float32))[0] == 252
+    assert np.all(np.isfinite(orc.decode(FC_MXFP4, orc.encode(FC_MXFP4, np.full(32, 1e-38, dtype=np.float32)), 32)))
+
+
+def test_mxfp4_a_tie_between_two_codes_takes_the_lower_one():
+    from ferrum_gpu_b200._ffi import FC_MXFP4
+    v = np.zeros(32, dtype=np.float32)  # mxfp4/tests.rs:L64-L74
+    v[0], v[1] = 6.0, 2.5
+    b = orc.encode(FC_MXFP4, v)
+    assert b[1] & 15 == 7 and b[1] >> 4 == 0 and b[2] & 15 == 4
+
+
+def test_mxfp4_scale_byte_boundaries_agree_with_the_exponent_field():
+    """floor(log2(amax)) is the f32 exponent except where the f32 logarithm of a value just below a power
+    of two rounds up to the integer; the device encoder takes the logarithm in f64 and rounds it to f32,
+    and this pins that the two agree on the floats next to every power of two."""
+    for k in range(-126, 128):
+        p = np.float32(2.0) ** np.float32(k)
+        x = p
+        for _ in range(24):
+            x = np.nextafter(x, np.float32(0.0), dtype=np.float32)
+            via_f64 = int(np.floor(np.float32(np.log2(np.float64(x))))) - 2 + 127
+            assert orc.mxfp4_scale_byte(float(x)) == min(max(via_f64, 0), 254), (k, float(x))
+        assert orc.mxfp4_scale_byte(float(p)) == min(max(k - 2 + 127, 0), 254)
