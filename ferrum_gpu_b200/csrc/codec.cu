@@ -39,6 +39,39 @@ __device__ __forceinline__ uint32_t fp8_encode_dev(float x) {
   return sign | ((du < dd || (du == dd && up % 2 == 0)) ? up : down);
 }
 
+// ---- MXFP4 (ferrum_gguf/src/codec/mxfp4.rs) ---------------------------------------------------
+// The device keeps the scale byte e as the bf16 bits of 2^(e - 127): e << 7, and 0x0040 for e = 0.
+__host__ __device__ inline uint16_t mx_scale_bits(uint32_t e) { return (uint16_t)(e ? e << 7 : 0x0040u); }
+__host__ __device__ inline uint8_t mx_scale_byte(uint16_t bits) { return (uint8_t)(bits >= 0x80 ? bits >> 7 : 0); }
+// 2^(e - 128), mxfp4.rs:L22-L28
+__device__ __forceinline__ float mx_half_scale(uint32_t e) {
+  return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1) << 23));
+}
+// mxfp4.rs:L49-L54. floor(log2(amax)) of the f32 logarithm: taken in f64 and rounded to f32, which gives
+// the f32 library's answer on the floats next to every power of two (the only place the floor can differ
+// from the exponent field).
+__device__ __forceinline__ uint32_t mx_scale_of(float amax) {
+  if (!(amax > 0.0f) || isinf(amax)) return 0;
+  const int v = (int)floorf((float)log2((double)amax)) - 2 + 127;
+  return (uint32_t)min(max(v, 0), 254);
+}
+// mxfp4.rs:L57-L68: nearest of the sixteen values (twice E2M1, the nibble's top bit the sign), a tie keeps
+// the lower index.
+__device__ __forceinline__ uint32_t mx_nearest(float x, float d) {
+  const float vals[16] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f, 0.f, -1.f, -2.f, -3.f, -4.f, -6.f, -8.f, -12.f};
+  uint32_t best = 0;
+  float best_err = fabsf(__fsub_rn(__fmul_rn(vals[0], d), x));
+#pragma unroll
+  for (int i = 1; i < 16; i++) {
+    const float err = fabsf(__fsub_rn(__fmul_rn(vals[i], d), x));
+    if (err < best_err) {
+      best = i;
+      best_err = err;
+    }
+  }
+  return best;
+}
+
 // One thread per (block b, output column col); threads of a warp take consecutive columns so the
 // reads of the `[k, n]` matrix coalesce.
 template <int KIND>
@@ -51,7 +84,19 @@ __global__ void quantise_kn_kernel(const float* __restrict__ w, uint32_t k, uint
 #pragma unroll
   for (int j = 0; j < QK; j++) v[j] = w[(size_t)(b * QK + j) * n + col];
   uint32_t nb = k / QK;
-  if (kind_is_fp8(KIND)) { // fp8.rs:L112-L124: the inverse is taken of the rounded scale
+  if (KIND == FC_MXFP4) { // mxfp4.rs:L71-L82
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < QK; j++) amax = fmaxf(amax, fabsf(v[j]));
+    const uint32_t e = mx_scale_of(amax);
+    const float d = mx_half_scale(e);
+    sc[(size_t)col * nb + b] = __ushort_as_half(mx_scale_bits(e));
+    uint32_t words[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < QK; j++) words[j >> 3] |= mx_nearest(v[j], d) << (4 * (j & 7)); // element order
+    *reinterpret_cast<uint4*>(qs + (size_t)col * (k / 2) + (size_t)b * 16) =
+        make_uint4(words[0], words[1], words[2], words[3]);
+  } else if (kind_is_fp8(KIND)) { // fp8.rs:L112-L124: the inverse is taken of the rounded scale
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < QK; j++) amax = fmaxf(amax, fabsf(v[j]));
@@ -132,6 +177,17 @@ __global__ void repack_blocks_kernel(const uint8_t* __restrict__ blocks, uint32_
   size_t nb = k / QK;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; // row * nb + b
   if (idx >= nb * n) return;
+  if (KIND == FC_MXFP4) { // 17 bytes: the scale byte, then element j | element j + 16 << 4 (mxfp4.rs:L1-L3)
+    const uint8_t* p = blocks + idx * 17;
+    sc[idx] = __ushort_as_half(mx_scale_bits(p[0]));
+    uint32_t words[4] = {0, 0, 0, 0};
+    for (int e = 0; e < QK; e++) {
+      const uint32_t q = e < 16 ? (p[1 + e] & 0x0f) : (p[1 + e - 16] >> 4);
+      words[e >> 3] |= q << (4 * (e & 7));
+    }
+    *reinterpret_cast<uint4*>(qs + idx * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+    return;
+  }
   constexpr int FB = KIND == FC_Q8_0 ? 34 : 18; // (the FP8 formats come through as Q8_0: the same bytes)
   const uint8_t* p = blocks + idx * FB;
   uint16_t h = (uint16_t)(p[0] | (p[1] << 8));
@@ -158,6 +214,16 @@ __global__ void export_blocks_kernel(const uint8_t* __restrict__ qs, const __hal
   size_t nb = k / QK;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= nb * n) return;
+  if (KIND == FC_MXFP4) {
+    uint8_t* p = blocks + idx * 17;
+    p[0] = mx_scale_byte(__half_as_ushort(sc[idx]));
+    const uint8_t* src = qs + idx * 16;
+    for (int j = 0; j < 16; j++) {
+      const uint32_t lo = (src[j >> 1] >> (4 * (j & 1))) & 0x0f, hi = (src[(j + 16) >> 1] >> (4 * (j & 1))) & 0x0f;
+      p[1 + j] = (uint8_t)(lo | (hi << 4));
+    }
+    return;
+  }
   constexpr int FB = KIND == FC_Q8_0 ? 34 : 18;
   uint8_t* p = blocks + idx * FB;
   uint16_t h = __half_as_ushort(sc[idx]);
@@ -183,9 +249,20 @@ __global__ void dequant_kernel(const uint8_t* __restrict__ qs, const __half* __r
   size_t nb = k / QK;
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= nb * n) return;
-  float d = __half2float(sc[idx]);
+  float d = block_scale_f32<KIND>(sc[idx]);
   float* o = out + idx * QK;
-  if (kind_is_fp8(KIND)) { // fp8.rs:L127-L134
+  if (KIND == FC_MXFP4) { // mxfp4.rs:L31-L46: (twice the E2M1 value) x (half the scale), here value x scale
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(qs + idx * 16);
+    for (int w = 0; w < 4; w++) {
+      uint32_t h[4];
+      e2m1x8_to_f16x2(src[w], h);
+      for (int p = 0; p < 4; p++) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[p]));
+        o[8 * w + 2 * p] = __fmul_rn(d, f.x);
+        o[8 * w + 2 * p + 1] = __fmul_rn(d, f.y);
+      }
+    }
+  } else if (kind_is_fp8(KIND)) { // fp8.rs:L127-L134
     for (int j = 0; j < QK; j++) o[j] = __fmul_rn(d, fp8_to_f32<KIND>(qs[idx * QK + j]));
   } else if (KIND == FC_Q8_0) {
     const int8_t* q = reinterpret_cast<const int8_t*>(qs) + idx * QK;
@@ -237,6 +314,8 @@ int k_quantise_kn(FcDevice* dev, int kind, const float* w, uint32_t k, uint32_t 
     FC_LAUNCH(dev, "quantise_fp8", quantise_kn_kernel<FC_FP8_E4M3><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
   else if (kind == FC_FP8_E5M2)
     FC_LAUNCH(dev, "quantise_fp8", quantise_kn_kernel<FC_FP8_E5M2><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
+  else if (kind == FC_MXFP4)
+    FC_LAUNCH(dev, "quantise_mxfp4", quantise_kn_kernel<FC_MXFP4><<<grid, 128, 0, dev->stream>>>(w, k, n, qs, sc));
   else
     return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   return FC_OK;
@@ -259,6 +338,8 @@ int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, 
     FC_LAUNCH(dev, "repack_q8_0", repack_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
   else if (kind == FC_Q4_0)
     FC_LAUNCH(dev, "repack_q4_0", repack_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
+  else if (kind == FC_MXFP4)
+    FC_LAUNCH(dev, "repack_mxfp4", repack_blocks_kernel<FC_MXFP4><<<grid, 128, 0, dev->stream>>>(blocks, k, n, qs, sc));
   else
     return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   return FC_OK;
@@ -275,6 +356,8 @@ int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
     FC_LAUNCH(dev, "export_q8_0", export_blocks_kernel<FC_Q8_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
   else if (m.kind == FC_Q4_0)
     FC_LAUNCH(dev, "export_q4_0", export_blocks_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
+  else if (m.kind == FC_MXFP4)
+    FC_LAUNCH(dev, "export_mxfp4", export_blocks_kernel<FC_MXFP4><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, blocks));
   else
     return fc_fail(dev, FC_ERR_ARG, "an f32 weight has no block form");
   return FC_OK;
@@ -298,6 +381,8 @@ int k_dequant(FcDevice* dev, const QMat& m, float* out) {
     FC_LAUNCH(dev, "dequant_fp8", dequant_kernel<FC_FP8_E4M3><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
   else if (m.kind == FC_FP8_E5M2)
     FC_LAUNCH(dev, "dequant_fp8", dequant_kernel<FC_FP8_E5M2><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
+  else if (m.kind == FC_MXFP4)
+    FC_LAUNCH(dev, "dequant_mxfp4", dequant_kernel<FC_MXFP4><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
   else
     FC_LAUNCH(dev, "dequant_q4_0", dequant_kernel<FC_Q4_0><<<grid, 128, 0, dev->stream>>>(m.qs, m.sc, m.k, m.n, out));
   return FC_OK;

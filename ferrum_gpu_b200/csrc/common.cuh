@@ -81,6 +81,10 @@ int fc_pinned(FcDevice* dev, size_t bytes, void** out);
 //  FC_F32:  qs = f32  [n][k];            sc = nullptr
 //  FC_F16:  qs = f16  [n][k];            sc = nullptr
 //  FC_FP8_E4M3 / FC_FP8_E5M2: Q8_0's planes, the bytes being FP8 codes instead of int8 quants
+//  FC_MXFP4: qs = u8 [n][k/2], 16 bytes per block in element order (byte i: element 2i in the low nibble,
+//           2i+1 in the high one), each nibble an E2M1 code; sc = u16 [n][k/32], the bf16 bit pattern
+//           of the block's power-of-two scale 2^(e-127) (all 255 scale bytes fit: the smallest is a
+//           bf16 subnormal), so a kernel gets the f32 scale with one shift
 struct QMat {
   int kind = FC_F32;
   uint32_t k = 0, n = 0;
@@ -103,11 +107,13 @@ struct FcQWeight {
 __host__ __device__ constexpr bool kind_is_fp8(int kind) { return kind == FC_FP8_E4M3 || kind == FC_FP8_E5M2; }
 // one byte per element and an f16 scale per 32: Q8_0 and the FP8 formats share planes, loads and addressing
 __host__ __device__ constexpr bool kind_byte_blocks(int kind) { return kind == FC_Q8_0 || kind_is_fp8(kind); }
-__host__ __device__ constexpr bool kind_has_scales(int kind) { return kind_byte_blocks(kind) || kind == FC_Q4_0; }
-static inline bool kind_known(int kind) { return kind >= FC_F32 && kind <= FC_FP8_E5M2; }
+// half a byte per element, 16 bytes per block: Q4_0 and MXFP4 share addressing (not the nibble order)
+__host__ __device__ constexpr bool kind_nibble_blocks(int kind) { return kind == FC_Q4_0 || kind == FC_MXFP4; }
+__host__ __device__ constexpr bool kind_has_scales(int kind) { return kind_byte_blocks(kind) || kind_nibble_blocks(kind); }
+static inline bool kind_known(int kind) { return kind >= FC_F32 && kind <= FC_MXFP4; }
 
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
-  return kind_byte_blocks(kind) ? k * n : kind == FC_Q4_0 ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
+  return kind_byte_blocks(kind) ? k * n : kind_nibble_blocks(kind) ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
 }
 static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) { return kind_has_scales(kind) ? (k / QK) * n * 2 : 0; }
 
@@ -123,6 +129,20 @@ __device__ __forceinline__ uint32_t fp8x2_to_f16x2(uint32_t two) {
   else
     asm("cvt.rn.f16x2.e5m2x2 %0, %1;" : "=r"(r) : "h"(v));
   return r;
+}
+// The eight E2M1 codes of one word of an MXFP4 block (byte i: elements 2i, 2i+1) as four fp16 pairs in
+// element order. Exact: the values are 0, 0.5, 1, 1.5, 2, 3, 4, 6 and their negatives.
+__device__ __forceinline__ void e2m1x8_to_f16x2(uint32_t w, uint32_t (&o)[4]) {
+  asm("{\n.reg .b8 b0, b1, b2, b3;\nmov.b32 {b0, b1, b2, b3}, %4;\n"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\ncvt.rn.f16x2.e2m1x2 %1, b1;\ncvt.rn.f16x2.e2m1x2 %2, b2;\ncvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+      : "=r"(o[0]), "=r"(o[1]), "=r"(o[2]), "=r"(o[3])
+      : "r"(w));
+}
+// The f32 scale of a block from its 16-bit slot: an f16 for the GGUF integer / FP8 formats, the bf16 bits
+// of a power of two for MXFP4.
+template <int KIND>
+__device__ __forceinline__ float block_scale_f32(__half raw) {
+  return KIND == FC_MXFP4 ? __uint_as_float((uint32_t)__half_as_ushort(raw) << 16) : __half2float(raw);
 }
 // One code as f32 (exact).
 template <int KIND>

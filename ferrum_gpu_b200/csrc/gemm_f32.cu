@@ -54,6 +54,17 @@ __global__ void __launch_bounds__(256)
           const uint32_t qw[2] = {q.x, q.y};
 #pragma unroll
           for (int j = 0; j < 8; j++) v[j] = __fmul_rn(d, (float)(int8_t)((qw[j >> 2] >> (8 * (j & 3))) & 0xff));
+        } else if (KIND == FC_MXFP4) {
+          const uint32_t q = *reinterpret_cast<const uint32_t*>(w.qs + (size_t)row * (k / 2) + (k0 / QK) * 16 + part * 4);
+          const float d = block_scale_f32<KIND>(w.sc[(size_t)row * (k / QK) + k0 / QK]);
+          uint32_t h[4];
+          e2m1x8_to_f16x2(q, h);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[j]));
+            v[2 * j] = __fmul_rn(d, f.x);
+            v[2 * j + 1] = __fmul_rn(d, f.y);
+          }
         } else if (kind_is_fp8(KIND)) {
           const uint2 q = *reinterpret_cast<const uint2*>(w.qs + (size_t)row * k + k0 + part * 8);
           const float d = __half2float(w.sc[(size_t)row * (k / QK) + k0 / QK]);
@@ -138,6 +149,8 @@ int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float*
     FC_LAUNCH(dev, "qgemm_f32_fp8", qgemm_f32_kernel<FC_FP8_E4M3><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else if (w.kind == FC_FP8_E5M2)
     FC_LAUNCH(dev, "qgemm_f32_fp8", qgemm_f32_kernel<FC_FP8_E5M2><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
+  else if (w.kind == FC_MXFP4)
+    FC_LAUNCH(dev, "qgemm_f32_mxfp4", qgemm_f32_kernel<FC_MXFP4><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else
     FC_LAUNCH(dev, "qgemm_f32_f32", qgemm_f32_kernel<FC_F32><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   return FC_OK;

@@ -95,6 +95,24 @@ __device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_
   }
 }
 
+// One 32-element MXFP4 block (4 words, element order) -> 4 chunks: E2M1 value times the power-of-two
+// scale in f32 (the scale itself need not be an fp16 value), saturated to fp16
+__device__ __forceinline__ void dequant_mxfp4_block(const uint4& q, float d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int w = 0; w < 4; w++) {
+    uint32_t h[4], o[4];
+    e2m1x8_to_f16x2(words[w], h);
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[p]));
+      o[p] = pack_f16(f.x * d, f.y * d);
+    }
+    const uint32_t addr = row_smem + (((c0 + w) ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+  }
+}
+
 // 16 FP8 codes (half a block) -> 2 chunks: code -> fp16 exactly, times the f16 scale, one rounding
 template <int KIND>
 __device__ __forceinline__ void dequant_fp8_half(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
@@ -131,6 +149,11 @@ struct RowRegs<FC_Q8_0> {
   uint32_t sc;
 };
 template <>
+struct RowRegs<FC_MXFP4> {
+  uint4 q[2];
+  uint32_t sc;
+};
+template <>
 struct RowRegs<FC_FP8_E4M3> {
   uint4 q[4];
   uint32_t sc;
@@ -151,10 +174,11 @@ struct RowRegs<FC_F16> {
 
 template <int KIND>
 __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32_t row, uint32_t it, bool valid) {
-  if (KIND == FC_Q4_0) {
+  if (kind_nibble_blocks(KIND)) { // (rows past the end decode to zero: nibble 8 of Q4_0, code 0 of MXFP4)
+    const uint32_t zero = KIND == FC_Q4_0 ? 0x88888888u : 0u;
     const uint4* p = reinterpret_cast<const uint4*>(w.qs + (size_t)row * (w.k / 2) + (size_t)it * 32);
-    r.q[0] = valid ? __ldg(p) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-    r.q[1] = valid ? __ldg(p + 1) : make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+    r.q[0] = valid ? __ldg(p) : make_uint4(zero, zero, zero, zero);
+    r.q[1] = valid ? __ldg(p + 1) : make_uint4(zero, zero, zero, zero);
     *reinterpret_cast<uint32_t*>(&((RowRegs<FC_Q4_0>&)r).sc) =
         valid ? __ldg(reinterpret_cast<const uint32_t*>(w.sc + (size_t)row * (w.k / QK) + (size_t)it * 2)) : 0u;
   } else if (kind_byte_blocks(KIND)) { // (the three records have one layout)
@@ -189,6 +213,10 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
     dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
     dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
     dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+  } else if (KIND == FC_MXFP4) {
+    const RowRegs<FC_Q4_0>& rr = (const RowRegs<FC_Q4_0>&)r;
+    dequant_mxfp4_block(rr.q[0], __uint_as_float(rr.sc << 16), row_smem, sw, 0);
+    dequant_mxfp4_block(rr.q[1], __uint_as_float(rr.sc & 0xffff0000u), row_smem, sw, 4);
   } else if (kind_is_fp8(KIND)) {
     const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
     const __half d0 = __ushort_as_half((unsigned short)(rr.sc & 0xffff)), d1 = __ushort_as_half((unsigned short)(rr.sc >> 16));
@@ -507,6 +535,7 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   if (w.kind == FC_F16) return pick_epi<FC_F16>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_FP8_E4M3) return pick_epi<FC_FP8_E4M3>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_FP8_E5M2) return pick_epi<FC_FP8_E5M2>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_MXFP4) return pick_epi<FC_MXFP4>(dev, tmap, w, args, epi, grid);
   return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);
 }
 

@@ -35,6 +35,10 @@ struct Chunk<FC_F16> {
   static constexpr int ELEMS = 8;
 };
 template <>
+struct Chunk<FC_MXFP4> {
+  static constexpr int ELEMS = 32;
+};
+template <>
 struct Chunk<FC_FP8_E4M3> {
   static constexpr int ELEMS = 16;
 };
@@ -84,6 +88,26 @@ __device__ __forceinline__ float chunk_dot(const uint4& wq, const float* __restr
         float q = __uint_as_float(0x4B000000u | nib) - 8388616.0f; // (2^23 + nib) - (2^23 + 8)
         acc = fmaf(xe[j], q, acc);
       }
+    }
+  } else if (KIND == FC_MXFP4) {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      const float4 xa = *reinterpret_cast<const float4*>(xs + 8 * w);
+      const float4 xb = *reinterpret_cast<const float4*>(xs + 8 * w + 4);
+      uint32_t h[4];
+      e2m1x8_to_f16x2(words[w], h); // element order, exact
+      const float2 q0 = __half22float2(*reinterpret_cast<const __half2*>(&h[0]));
+      const float2 q1 = __half22float2(*reinterpret_cast<const __half2*>(&h[1]));
+      const float2 q2 = __half22float2(*reinterpret_cast<const __half2*>(&h[2]));
+      const float2 q3 = __half22float2(*reinterpret_cast<const __half2*>(&h[3]));
+      acc = fmaf(xa.x, q0.x, acc);
+      acc = fmaf(xa.y, q0.y, acc);
+      acc = fmaf(xa.z, q1.x, acc);
+      acc = fmaf(xa.w, q1.y, acc);
+      acc = fmaf(xb.x, q2.x, acc);
+      acc = fmaf(xb.y, q2.y, acc);
+      acc = fmaf(xb.z, q3.x, acc);
+      acc = fmaf(xb.w, q3.y, acc);
     }
   } else if (kind_is_fp8(KIND)) {
 #pragma unroll
@@ -205,7 +229,7 @@ __global__ void __launch_bounds__(256)
       if (kind_has_scales(KIND)) {
 #pragma unroll
         for (int r = 0; r < R; r++)
-          d[r] = __half2float(w.sc[(size_t)rows[r] * nb + (kind_byte_blocks(KIND) ? (c >> 1) : c)]);
+          d[r] = block_scale_f32<KIND>(w.sc[(size_t)rows[r] * nb + (kind_byte_blocks(KIND) ? (c >> 1) : c)]);
       }
 #pragma unroll
       for (int m = 0; m < M; m++) {
@@ -299,6 +323,7 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
   if (w.kind == FC_F16) return pick_m<FC_F16>(dev, w, x, m, y, ep);
   if (w.kind == FC_FP8_E4M3) return pick_m<FC_FP8_E4M3>(dev, w, x, m, y, ep);
   if (w.kind == FC_FP8_E5M2) return pick_m<FC_FP8_E5M2>(dev, w, x, m, y, ep);
+  if (w.kind == FC_MXFP4) return pick_m<FC_MXFP4>(dev, w, x, m, y, ep);
   return pick_m<FC_F32>(dev, w, x, m, y, ep);
 }
 

@@ -165,7 +165,18 @@ __device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, ui
 }
 template <int KIND>
 __device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a[2][4]) {
-  if (kind_is_fp8(KIND)) { // every code is an fp16 value
+  if (KIND == FC_MXFP4) { // element order: pairs (0,1) (2,3) | (4,5) (6,7) are the two k16 steps
+    uint32_t ha[4], hb[4];
+    e2m1x8_to_f16x2(r.q[0], ha);
+    e2m1x8_to_f16x2(r.q[1], hb);
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      a[s][0] = ha[2 * s];
+      a[s][2] = ha[2 * s + 1];
+      a[s][1] = hb[2 * s];
+      a[s][3] = hb[2 * s + 1];
+    }
+  } else if (kind_is_fp8(KIND)) { // every code is an fp16 value
 #pragma unroll
     for (int s = 0; s < 2; s++) {
       a[s][0] = fp8x2_to_f16x2<KIND>(r.q[s]);
@@ -252,7 +263,7 @@ __global__ void __launch_bounds__(128)
       if (kb0 + bi + 1 < kb_end) load_block<KIND>(nxt, w, row_g, row_g8, kb0 + bi + 1, t); // in flight under this block's MMAs
       uint32_t a[2][4];
       block_frags<KIND>(cur, a);
-      const float dg = __half2float(cur.d[0]), dg8 = __half2float(cur.d[1]);
+      const float dg = block_scale_f32<KIND>(cur.d[0]), dg8 = block_scale_f32<KIND>(cur.d[1]);
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
         float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -399,7 +410,18 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int bi = 0; bi < 4; bi++) {
       uint32_t a[2][4];
-      if (kind_is_fp8(KIND)) {
+      if (KIND == FC_MXFP4) {
+        uint32_t ha[4], hb[4];
+        e2m1x8_to_f16x2(*reinterpret_cast<const uint32_t*>(wst + r0 * C::WROW + bi * 16 + 4 * t), ha);
+        e2m1x8_to_f16x2(*reinterpret_cast<const uint32_t*>(wst + r1 * C::WROW + bi * 16 + 4 * t), hb);
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+          a[s][0] = ha[2 * s];
+          a[s][2] = ha[2 * s + 1];
+          a[s][1] = hb[2 * s];
+          a[s][3] = hb[2 * s + 1];
+        }
+      } else if (kind_is_fp8(KIND)) {
         const uint2 qa = *reinterpret_cast<const uint2*>(wst + r0 * C::WROW + bi * 32 + 8 * t);
         const uint2 qb = *reinterpret_cast<const uint2*>(wst + r1 * C::WROW + bi * 32 + 8 * t);
         const uint32_t wa[2] = {qa.x, qa.y}, wb[2] = {qb.x, qb.y};
@@ -432,7 +454,7 @@ __global__ void __launch_bounds__(128)
           a[s][3] = h2sub(((wb >> (8 * s + 4)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
         }
       }
-      const float dg = __half2float(sst[r0 * 4 + bi]), dg8 = __half2float(sst[r1 * 4 + bi]);
+      const float dg = block_scale_f32<KIND>(sst[r0 * 4 + bi]), dg8 = block_scale_f32<KIND>(sst[r1 * 4 + bi]);
       float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const uint32_t off = g * XSTRIDE + bi * QK + 8 * t;
 #pragma unroll
@@ -539,6 +561,7 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
                                       Mma8<FC_FP8_E4M3>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_FP8_E5M2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Mma8<FC_FP8_E5M2>::SMEM));
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_MXFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_MXFP4>::SMEM));
     attr = true;
   }
   if (w.kind == FC_Q8_0)
@@ -550,6 +573,9 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   else if (w.kind == FC_FP8_E5M2)
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_FP8_E5M2><<<grid, 128, Mma8<FC_FP8_E5M2>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  else if (w.kind == FC_MXFP4)
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_MXFP4><<<grid, 128, Mma8<FC_MXFP4>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
   else
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_Q4_0><<<grid, 128, Mma8<FC_Q4_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
@@ -621,6 +647,8 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
     FC_TRY(pick_nb<FC_FP8_E4M3>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else if (w.kind == FC_FP8_E5M2)
     FC_TRY(pick_nb<FC_FP8_E5M2>(dev, w, xh, xl, m, y, part, splits, bps, ep));
+  else if (w.kind == FC_MXFP4)
+    FC_TRY(pick_nb<FC_MXFP4>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else
     FC_TRY(pick_nb<FC_Q4_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   if (splits > 1 && ep.defer_out && ep.act == ACT_NONE) { // the consumer's norm + split launch finishes the sum

@@ -10,6 +10,7 @@ FC_API size_t fc_block_bytes(int kind, size_t n_elems) {
   if (n_elems % QK) return 0;
   if (kind_byte_blocks(kind)) return n_elems / QK * 34;
   if (kind == FC_Q4_0) return n_elems / QK * 18;
+  if (kind == FC_MXFP4) return n_elems / QK * 17;
   if (kind == FC_F16) return n_elems * 2;
   return 0;
 }

@@ -43,7 +43,7 @@ def test_feed_matches_forward_logits_at_every_position(dev, name, cfg, biases, t
     g.close()
 
 
-@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0, QKind.F16, QKind.FP8_E4M3, QKind.FP8_E5M2])
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0, QKind.F16, QKind.FP8_E4M3, QKind.FP8_E5M2, QKind.MXFP4])
 @pytest.mark.parametrize("name,cfg,biases,tied", variants())
 def test_quantised_feed_matches_the_dequantised_oracle(dev, kind, name, cfg, biases, tied):
     """models/llama/tests.rs:L63-L89: the oracle is the CPU model over dequantised weights."""

@@ -12,8 +12,10 @@ pytestmark = pytest.mark.gpu
 
 KINDS = [QKind.Q8_0, QKind.Q4_0]
 FP8 = [QKind.FP8_E4M3, QKind.FP8_E5M2]  # one-byte floats in Q8_0's block (ops/quant.rs:L38-L41)
-STORED = KINDS + [QKind.F16] + FP8  # F16: plain f16 values, no scale (ops/quant.rs:L33-L36)
-BLOCK_BYTES = {QKind.Q8_0: 34, QKind.Q4_0: 18, QKind.F16: 64, QKind.FP8_E4M3: 34, QKind.FP8_E5M2: 34}
+MX = [QKind.MXFP4]  # E2M1 nibbles with a power-of-two scale byte (ops/quant.rs:L36-L37)
+STORED = KINDS + [QKind.F16] + FP8 + MX  # F16: plain f16 values, no scale (ops/quant.rs:L33-L36)
+# device bytes per 32 elements (MXFP4: 17 in a file, 18 on the device, where the scale takes a 16-bit slot)
+BLOCK_BYTES = {QKind.Q8_0: 34, QKind.Q4_0: 18, QKind.F16: 64, QKind.FP8_E4M3: 34, QKind.FP8_E5M2: 34, QKind.MXFP4: 18}
 REDUCING = 1e-5  # ferrum_wgpu/src/tolerance.rs:L7
 
 
@@ -110,7 +112,7 @@ def test_sweep_shapes_of_the_isolated_matmul_config(dev, kind):
         qw.close()
 
 
-@pytest.mark.parametrize("kind", KINDS + FP8)
+@pytest.mark.parametrize("kind", KINDS + FP8 + MX)
 @pytest.mark.parametrize("rows,k,n", [(9, 128, 8), (16, 256, 70), (33, 1024, 200), (64, 2816, 130), (40, 384, 1536)])
 def test_batched_decode_tensor_product_keeps_f32_accuracy(dev, kind, rows, k, n):
     """9..64 rows (concurrent decode streams) run on mma.sync with x split into two fp16 terms and the

@@ -72,7 +72,7 @@ def llama_tc_cfg(**kw):
     return LlamaConfig(**base)
 
 
-@pytest.mark.parametrize("kind", [QKind.Q4_0, QKind.Q8_0, QKind.F16, QKind.FP8_E4M3, QKind.FP8_E5M2])
+@pytest.mark.parametrize("kind", [QKind.Q4_0, QKind.Q8_0, QKind.F16, QKind.FP8_E4M3, QKind.FP8_E5M2, QKind.MXFP4])
 @pytest.mark.parametrize("variant", ["norm-gqa", "neox-bias-tied", "mha"])
 def test_llama_tensor_forward_and_score_match_the_f32_oracle(dev, kind, variant):
     cfg = {"norm-gqa": llama_tc_cfg(), "neox-bias-tied": llama_tc_cfg(rope_type=_ffi.FC_ROPE_NEOX, rope_base=1e6, vocab=104),
