@@ -309,9 +309,64 @@ int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t
   return FC_OK;
 }
 
-int k_argmax(FcDevice* dev, const float* logits, uint32_t rows, uint32_t vocab, int32_t* out) {
+// The same rule with a row spread over `parts` CTAs (a 150K-entry row is 600 KB: one CTA per row leaves
+// most SMs idle). A candidate is the 64-bit key (value as an order-preserving integer, then the
+// complement of its index): the largest key is the largest value at its lowest index, whatever order the
+// CTAs arrive in. keys[row] and done[row] start at zero and are left at zero by the CTA that finishes the row.
+__global__ void __launch_bounds__(512)
+    argmax_parts_kernel(const float* __restrict__ logits, uint32_t vocab, uint32_t parts, unsigned long long* keys,
+                        uint32_t* done, int32_t* __restrict__ out) {
+  __shared__ unsigned long long bk[16];
+  const uint32_t r = blockIdx.y, per = (vocab + parts - 1) / parts;
+  const uint32_t i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
+  const float* row = logits + (size_t)r * vocab;
+  unsigned long long best = 0; // "nothing above -inf yet"
+  for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+    const float v = row[i];
+    if (v > -INFINITY) { // (false for NaN)
+      uint32_t u = __float_as_uint(v + 0.0f); // (-0 and +0 compare equal: one key)
+      u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+      const unsigned long long key = ((unsigned long long)u << 32) | (uint32_t)~i;
+      best = key > best ? key : best;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long ok = __shfl_xor_sync(0xffffffffu, best, o);
+    best = ok > best ? ok : best;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) bk[warp] = best;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (uint32_t w = 1; w < blockDim.x / 32; w++) best = bk[w] > best ? bk[w] : best;
+    if (best) atomicMax(&keys[r], best);
+    __threadfence();
+    if (atomicAdd(&done[r], 1u) == parts - 1) { // every CTA of the row has contributed
+      __threadfence();
+      const unsigned long long k = atomicExch(&keys[r], 0ull);
+      done[r] = 0;
+      out[r] = k ? (int32_t)~(uint32_t)k : 0; // nothing beat -inf: index 0
+    }
+  }
+}
+
+size_t argmax_scratch_bytes(uint32_t rows) { return (size_t)rows * 16; }
+
+// `scratch` (argmax_scratch_bytes, zeroed once; nullable) lets long rows use several CTAs each.
+int k_argmax(FcDevice* dev, const float* logits, uint32_t rows, uint32_t vocab, int32_t* out, void* scratch) {
   if (!rows) return FC_OK;
-  FC_LAUNCH(dev, "argmax", argmax_kernel<<<rows, 1024, 0, dev->stream>>>(logits, vocab, out));
+  const uint32_t sms = (uint32_t)dev->prop.multiProcessorCount;
+  uint32_t parts = (2 * sms + rows - 1) / rows;
+  const uint32_t max_parts = (vocab + 4095) / 4096; // at least 4096 entries per CTA
+  parts = parts > max_parts ? max_parts : parts;
+  if (!scratch || parts < 2) {
+    FC_LAUNCH(dev, "argmax", argmax_kernel<<<rows, 1024, 0, dev->stream>>>(logits, vocab, out));
+    return FC_OK;
+  }
+  unsigned long long* keys = (unsigned long long*)scratch;
+  uint32_t* done = (uint32_t*)(keys + rows);
+  FC_LAUNCH(dev, "argmax", argmax_parts_kernel<<<dim3(parts, rows), 512, 0, dev->stream>>>(logits, vocab, parts, keys, done, out));
   return FC_OK;
 }
 

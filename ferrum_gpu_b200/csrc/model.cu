@@ -132,6 +132,8 @@ int alloc_common(FcModel* m) {
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_pos));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
+  FC_TRY(dev_alloc(m, argmax_scratch_bytes(s), &m->argmax_scratch));
+  FC_CUDA(m->dev, cudaMemsetAsync(m->argmax_scratch, 0, argmax_scratch_bytes(s), m->dev->stream));
   // partial results of the context-split decode attention: the largest need over every batch width
   if (attn_decode_split_supports(m->heads, m->kv_heads, m->hd)) {
     size_t need = 0;
@@ -572,7 +574,7 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
     e_head.pending = &tail;
     norm_before(m, e_head, m->normf_g, m->normf_b, m->h);
     FC_TRY(k_qlinear_f32(dev, m->head_view, m->x, n, m->logits, e_head));
-    FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax));
+    FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax, m->argmax_scratch));
     FC_CUDA(dev, cudaMemcpyAsync(p + 3 * n, m->d_argmax, n * 4, cudaMemcpyDeviceToHost, dev->stream));
     return FC_OK;
   };
@@ -653,7 +655,7 @@ FC_API int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, 
   if (logits_out || argmax_out) {
     FC_TRY(k_qlinear_f32(dev, m->head_view, b.h + (size_t)(n - 1) * m->dim, 1, m->logits, Epilogue()));
     if (argmax_out) {
-      FC_TRY(k_argmax(dev, m->logits, 1, m->vocab, m->d_argmax));
+      FC_TRY(k_argmax(dev, m->logits, 1, m->vocab, m->d_argmax, m->argmax_scratch));
       FC_CUDA(dev, cudaMemcpyAsync(argmax_out, m->d_argmax, 4, cudaMemcpyDeviceToHost, dev->stream));
     }
     if (logits_out)

@@ -49,6 +49,7 @@ struct FcModel {
   // decode scratch, sized for max_streams rows
   float *x = nullptr, *h = nullptr, *qkv = nullptr, *attn = nullptr, *ff = nullptr, *act = nullptr, *logits = nullptr;
   int32_t *d_ids = nullptr, *d_pos = nullptr, *d_streams = nullptr, *d_argmax = nullptr;
+  void* argmax_scratch = nullptr; // keys and counters of the multi-CTA argmax, zero between launches
   // decode-step replay: one instantiated CUDA graph per batch width, inputs through a pinned buffer
   void* mma_scratch = nullptr; // scratch of the decode tensor product
   float* attn_scratch = nullptr; // per-split partials of the decode attention

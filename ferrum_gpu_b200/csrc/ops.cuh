@@ -28,7 +28,8 @@ int k_swiglu_split(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t 
 int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
               const RopeParams& rope, const int32_t* positions, const int32_t* streams /*nullable: row's cache slot*/,
               const KvLayer* kv, uint32_t ctx);
-int k_argmax(FcDevice* dev, const float* logits, uint32_t rows, uint32_t vocab, int32_t* out);
+size_t argmax_scratch_bytes(uint32_t rows);
+int k_argmax(FcDevice* dev, const float* logits, uint32_t rows, uint32_t vocab, int32_t* out, void* scratch = nullptr);
 // nn::score on materialised logits in two steps: per-row partials over vocabulary columns
 // [v0, v0 + vs) as (max, sum exp, target logit | -inf, first argmax), then the merge of n_shards.
 int k_score_partial(FcDevice* dev, const float* logits, const int32_t* targets, uint32_t rows, uint32_t vs, uint32_t v0,

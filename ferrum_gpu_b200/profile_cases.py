@@ -104,7 +104,21 @@ def decode(dev):
     g.close()
 
 
-CASES = {"gemm": gemm, "head": head, "matvec": matvec, "matvec8": matvec8, "decode": decode, "score": score, "chunk": chunk,
+def decode64(dev):
+    """Four layers and the 151936-row head of the 64-stream decode configuration at 1500 cached positions:
+    the per-launch times of one step (the full model repeats the layer launches 24 times)."""
+    cfg = LlamaConfig(vocab=151936, ctx=2048, dim=1024, heads=16, kv_heads=2, head_dim=64, layers=4, hidden=2816,
+                      rope_dim=64, rope_base=1e6, rope_type=1, eps=1e-6)
+    g = CudaLlama(dev, random_llama(cfg, seed=1, biases=True, tied=True), QKind.Q8_0, max_streams=64)
+    for s in range(64):
+        g.prefill(random_tokens(s, 1500, cfg.vocab), stream=s)
+    toks = random_tokens(99, 64, cfg.vocab)
+    for _ in range(3):
+        g.feed_batch(toks)
+    g.close()
+
+
+CASES = {"gemm": gemm, "head": head, "matvec": matvec, "matvec8": matvec8, "decode": decode, "decode64": decode64, "score": score, "chunk": chunk,
          "attention": attention}
 
 if __name__ == "__main__":

@@ -296,3 +296,24 @@ def test_many_streams_take_the_tensor_decode_path_and_match_the_oracle(dev, kind
             assert am[s] == orc.argmax(lg[s])
     assert all(g.pos(s) == steps for s in range(n_streams))
     g.close()
+
+
+def test_greedy_pick_over_a_long_row_keeps_the_first_maximum(dev):
+    """A long vocabulary row is searched by several CTAs; the first-maximum rule of `sampling::argmax`
+    (ferrum_model/src/sampling.rs:L32-L40) must survive that: every logit of this model appears twice, at
+    i and i + 10000 (different CTAs), so the pick has to be the lower of the two."""
+    from ferrum_gpu_b200.hostmodel import LlamaConfig
+    cfg = LlamaConfig(vocab=20000, ctx=16, dim=64, heads=1, kv_heads=1, head_dim=64, layers=1, hidden=64, rope_dim=64,
+                      rope_base=1e4, rope_type=_ffi.FC_ROPE_NORM, eps=1e-5)
+    m = random_llama(cfg, seed=6, std=0.05)
+    head = np.array(m.head, dtype=np.float32).reshape(cfg.dim, cfg.vocab)
+    head[:, 10000:] = head[:, :10000]
+    m.head = head.reshape(-1)
+    for streams in (1, 3, 12):
+        g = CudaLlama(dev, m, None, max_streams=streams)
+        for step in range(3):
+            am, lg = g.feed_batch(random_tokens(step, streams, cfg.vocab), want_logits=True)
+            for s in range(streams):
+                assert am[s] == orc.argmax(lg[s]) and am[s] < 10000, (streams, step, s)
+                assert np.array_equal(lg[s][:10000], lg[s][10000:])
+        g.close()
