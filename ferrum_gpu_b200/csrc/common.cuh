@@ -187,6 +187,9 @@ struct Epilogue {
   bool presplit = false;
   // leave this product's split-K reduce to the consumer (filled in when the product did split)
   DeferredReduce* defer_out = nullptr;
+  // where a deferring product puts its partial sums, when the place behind its own x terms would be
+  // overwritten by the consumer (nullable: that default place)
+  float* partial_at = nullptr;
   // finish this pending reduce first: its y is this product's x (same buffer, raw residual stream)
   const DeferredReduce* pending = nullptr;
 };

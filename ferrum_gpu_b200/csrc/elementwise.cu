@@ -95,10 +95,31 @@ __global__ void swiglu_kernel(const float* __restrict__ gu, uint32_t rows, uint3
 // ferrum_wgpu/src/models/llama/mod.rs:L393-L399). One CTA per row; thread i handles pair i of a head.
 __global__ void rope_kv_kernel(float* __restrict__ qkv, uint32_t heads, uint32_t kv_heads, uint32_t hd, RopeParams rope,
                                const int32_t* __restrict__ positions, const int32_t* __restrict__ streams,
-                               KvLayer kv, bool has_kv, uint32_t ctx) {
+                               KvLayer kv, bool has_kv, uint32_t ctx, DeferredReduce pend) {
   const uint32_t r = blockIdx.x;
   const uint32_t qd = heads * hd, kvd = kv_heads * hd;
   float* row = qkv + (size_t)r * (qd + 2 * kvd);
+  if (pend.splits) {
+    // the qkv product left its split-K partial sums apart: add them in ascending order and apply the bias,
+    // exactly as its own reduce launch would, then carry on with the finished row
+    const uint32_t w = qd + 2 * kvd; // (a multiple of 4: the host checks)
+    const size_t split_stride = (size_t)pend.m * w;
+    const float* prow = pend.partial + (size_t)r * w;
+    for (uint32_t i = threadIdx.x * 4; i < w; i += blockDim.x * 4) {
+      float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+      for (uint32_t s = 0; s < pend.splits; s++) {
+        const float4 p = *reinterpret_cast<const float4*>(prow + s * split_stride + i);
+        v.x += p.x, v.y += p.y, v.z += p.z, v.w += p.w;
+      }
+      if (pend.bias) {
+        const float4 bb = *reinterpret_cast<const float4*>(pend.bias + i);
+        v.x += bb.x, v.y += bb.y, v.z += bb.z, v.w += bb.w;
+      }
+      *reinterpret_cast<float4*>(row + i) = v;
+    }
+    __syncthreads();
+  }
   const uint32_t pos = (uint32_t)positions[r];
   if (rope.cos) {
     const uint32_t half = rope.rope_dim / 2;
@@ -245,15 +266,30 @@ __global__ void nll_sums_kernel(const float* __restrict__ logprob, uint32_t n_se
 
 // the same, written as the two fp16 terms the 9..64-row decode product multiplies (rows >= `rows` of the
 // padded block are zero): saves that product's own split launch
+// With `pend` the gate/up product's split-K partial sums are still apart: an element is then their sum in
+// ascending split order plus the bias (what that product's reduce launch computes), and `gu` is not read.
 __global__ void swiglu_split_kernel(const float* __restrict__ gu, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group,
-                                    __half* __restrict__ xh, __half* __restrict__ xl) {
+                                    __half* __restrict__ xh, __half* __restrict__ xl, DeferredReduce pend) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)mp * hidden) return;
   const size_t r = i / hidden, c = i % hidden;
   float v = 0.0f;
   if (r < rows) {
     const size_t gi = group ? (c / group) * 2 * group + c % group : c;
-    const float g = gu[r * 2 * hidden + gi], u = gu[r * 2 * hidden + gi + (group ? group : hidden)];
+    const size_t ui = gi + (group ? group : hidden);
+    float g, u;
+    if (pend.splits) {
+      const size_t stride = (size_t)pend.m * 2 * hidden;
+      const float* p = pend.partial + r * 2 * hidden;
+      g = 0.0f, u = 0.0f;
+      for (uint32_t s = 0; s < pend.splits; s++) {
+        g += p[s * stride + gi];
+        u += p[s * stride + ui];
+      }
+      if (pend.bias) g += pend.bias[gi], u += pend.bias[ui];
+    } else {
+      g = gu[r * 2 * hidden + gi], u = gu[r * 2 * hidden + ui];
+    }
     v = g / (1.0f + expf(-g)) * u;
   }
   v = fminf(fmaxf(v, -65504.0f), 65504.0f);
@@ -265,11 +301,20 @@ __global__ void swiglu_split_kernel(const float* __restrict__ gu, uint32_t rows,
 } // namespace
 
 int k_swiglu_split(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group, __half* xh,
-                   __half* xl) {
+                   __half* xl, const DeferredReduce* pending) {
   const size_t total = (size_t)mp * hidden;
+  DeferredReduce pend;
+  if (pending && pending->splits) {
+    // taken along when it is gate_up's own unfinished sum and lies clear of the terms written here
+    if (total && pending->y == gate_up && pending->m == rows && pending->n == 2 * hidden && !pending->resid &&
+        (uintptr_t)pending->partial >= (uintptr_t)(xl + total))
+      pend = *pending;
+    else
+      FC_TRY(k_flush_deferred(dev, *pending));
+  }
   if (!total) return FC_OK;
-  FC_LAUNCH(dev, "swiglu_split",
-            swiglu_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(gate_up, rows, mp, hidden, group, xh, xl));
+  FC_LAUNCH(dev, "swiglu_split", swiglu_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(
+                                     gate_up, rows, mp, hidden, group, xh, xl, pend));
   return FC_OK;
 }
 
@@ -300,12 +345,23 @@ int k_swiglu(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t hidden
 }
 
 int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
-              const RopeParams& rope, const int32_t* positions, const int32_t* streams, const KvLayer* kv, uint32_t ctx) {
+              const RopeParams& rope, const int32_t* positions, const int32_t* streams, const KvLayer* kv, uint32_t ctx,
+              const DeferredReduce* pending) {
+  DeferredReduce pend;
+  if (pending && pending->splits) {
+    // taken along when it is the qkv buffer's own unfinished sum (no residual: the kernel adds none)
+    const uint32_t w = (heads + 2 * kv_heads) * hd;
+    if (rows && (rope.cos || kv) && pending->y == qkv && pending->m == rows && pending->n == w && w % 4 == 0 &&
+        !pending->resid)
+      pend = *pending;
+    else
+      FC_TRY(k_flush_deferred(dev, *pending));
+  }
   if (!rows || (!rope.cos && !kv)) return FC_OK;
   KvLayer l = kv ? *kv : KvLayer();
   FC_LAUNCH(dev, "rope_kv",
             rope_kv_kernel<<<rows, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, rope, positions, streams, l,
-                                                          kv != nullptr, ctx));
+                                                          kv != nullptr, ctx, pend));
   return FC_OK;
 }
 

@@ -610,7 +610,7 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   uint32_t mp;
   __half *xh, *xl;
   qmatvec_mma_split_ptrs(scratch, m, w.k, &xh, &xl, &mp);
-  float* partial = (float*)(((uintptr_t)(xl + (size_t)mp * w.k) + 255) & ~(uintptr_t)255);
+  float* partial = ep.partial_at ? ep.partial_at : (float*)(((uintptr_t)(xl + (size_t)mp * w.k) + 255) & ~(uintptr_t)255);
   const size_t total = (size_t)mp * w.k;
   DeferredReduce pend;
   if (ep.pending && ep.pending->splits) {

@@ -151,6 +151,9 @@ int alloc_common(FcModel* m) {
         const size_t b = qmatvec_mma_scratch_bytes(q->m.k, q->m.n);
         need = b > need ? b : need;
       }
+    // (the gate/up product may keep its partial sums behind the widest x terms: run_stack_f32)
+    const size_t gu = qmatvec_mma_scratch_bytes(m->hidden > m->dim ? m->hidden : m->dim, m->ff1_w());
+    need = gu > need ? gu : need;
     FC_TRY(dev_alloc(m, need, &m->mma_scratch));
   }
   m->pos.assign(s, 0);
@@ -200,11 +203,13 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     e_qkv.bias = l.qkv.bias;
     e_qkv.pending = &pend;
     norm_before(m, e_qkv, l.norm1_g, l.norm1_b, b.h);
+    DeferredReduce qkv_sum; // the RoPE / cache launch that follows finishes the qkv product's split-K sum
+    e_qkv.defer_out = &qkv_sum;
     FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.x, rows, b.qkv, e_qkv));
     pend = DeferredReduce();
     const bool to_cache = mode != ATTN_STATELESS;
     FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
-                     to_cache ? &l.kv : nullptr, m->ctx));
+                     to_cache ? &l.kv : nullptr, m->ctx, &qkv_sum));
     Epilogue e_wo;
     if (mode == ATTN_DECODE) {
       __half *xh = nullptr, *xl = nullptr;
@@ -233,16 +238,25 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     e_ff1.act = m->arch == ARCH_GPT2 ? ACT_GELU : ACT_NONE;
     e_ff1.pending = &pend;
     norm_before(m, e_ff1, l.norm2_g, l.norm2_b, b.h);
+    // When SwiGLU writes ff2's fp16 terms (below) it also finishes the gate/up product's split-K sum; the
+    // partial sums then sit behind the widest x terms, clear of the ones SwiGLU writes.
+    const bool swiglu_splits = m->arch == ARCH_LLAMA && qlinear_takes_wide_mma(l.ff2.w->m, rows, m->mma_scratch);
+    DeferredReduce gu_sum;
+    if (swiglu_splits) {
+      e_ff1.defer_out = &gu_sum;
+      const size_t widest = m->hidden > d ? m->hidden : d;
+      e_ff1.partial_at = (float*)(((uintptr_t)m->mma_scratch + (size_t)2 * 64 * widest * 2 + 255) & ~(uintptr_t)255);
+    }
     FC_TRY(k_qlinear_f32(dev, l.ff1.w->m, b.x, rows, b.ff, e_ff1));
     pend = DeferredReduce();
     const float* ff2_in = b.ff;
     Epilogue e_ff2;
     if (m->arch == ARCH_LLAMA) {
-      if (qlinear_takes_wide_mma(l.ff2.w->m, rows, m->mma_scratch)) { // SwiGLU writes the product's fp16 terms itself
+      if (swiglu_splits) { // SwiGLU writes the product's fp16 terms itself
         __half *xh, *xl;
         uint32_t mp;
         qmatvec_mma_split_ptrs(m->mma_scratch, rows, m->hidden, &xh, &xl, &mp);
-        FC_TRY(k_swiglu_split(dev, b.ff, rows, mp, m->hidden, m->gu_group, xh, xl));
+        FC_TRY(k_swiglu_split(dev, b.ff, rows, mp, m->hidden, m->gu_group, xh, xl, &gu_sum));
         e_ff2.presplit = true;
       } else {
         FC_TRY(k_swiglu(dev, b.ff, rows, m->hidden, m->gu_group, b.act));

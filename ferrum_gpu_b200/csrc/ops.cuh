@@ -22,12 +22,13 @@ int k_rmsnorm(FcDevice* dev, const float* x, const float* g, uint32_t rows, uint
 int k_layernorm(FcDevice* dev, const float* x, const float* g, const float* b, uint32_t rows, uint32_t d, float* y);
 int k_swiglu(FcDevice* dev, const float* gate_up /*[rows][2*hidden]*/, uint32_t rows, uint32_t hidden, uint32_t group, float* act);
 int k_swiglu_split(FcDevice* dev, const float* gate_up, uint32_t rows, uint32_t mp, uint32_t hidden, uint32_t group, __half* xh,
-                   __half* xl);
+                   __half* xl, const DeferredReduce* pending = nullptr); // gate_up's unfinished split-K sum: finished here
 // Rotate q and k of the fused qkv rows in place (rope.type/rope_dim; skipped when rope.cos is
 // NULL) and, when `kv` is given, store each row's k and v into the cache at (stream, position).
 int k_rope_kv(FcDevice* dev, float* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
               const RopeParams& rope, const int32_t* positions, const int32_t* streams /*nullable: row's cache slot*/,
-              const KvLayer* kv, uint32_t ctx);
+              const KvLayer* kv, uint32_t ctx,
+              const DeferredReduce* pending = nullptr); // an unfinished split-K sum of the qkv product: finished here
 size_t argmax_scratch_bytes(uint32_t rows);
 int k_argmax(FcDevice* dev, const float* logits, uint32_t rows, uint32_t vocab, int32_t* out, void* scratch = nullptr);
 // nn::score on materialised logits in two steps: per-row partials over vocabulary columns
