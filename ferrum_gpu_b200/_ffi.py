@@ -32,7 +32,7 @@ STATUS_NAMES = {
     FC_ERR_UNSUPPORTED: "unsupported",
 }
 
-FC_F32, FC_Q8_0, FC_Q4_0, FC_F16, FC_FP8_E4M3, FC_FP8_E5M2, FC_MXFP4 = 0, 1, 2, 3, 4, 5, 6
+FC_F32, FC_Q8_0, FC_Q4_0, FC_F16, FC_FP8_E4M3, FC_FP8_E5M2, FC_MXFP4, FC_Q2_K = 0, 1, 2, 3, 4, 5, 6, 7
 FC_ROPE_NORM, FC_ROPE_NEOX = 0, 1
 FC_EXACT_F32, FC_TENSOR_F16 = 0, 1
 

@@ -21,10 +21,11 @@ class QKind(IntEnum):
     FP8_E4M3 = _ffi.FC_FP8_E4M3
     FP8_E5M2 = _ffi.FC_FP8_E5M2
     MXFP4 = _ffi.FC_MXFP4
+    Q2_K = _ffi.FC_Q2_K
 
     def label(self) -> str:
         """`QKind::label` (ops/quant.rs:L60-L70)."""
-        return {0: "F32", 1: "Q8_0", 2: "Q4_0", 3: "F16", 4: "FP8 E4M3", 5: "FP8 E5M2", 6: "MXFP4"}[int(self)]
+        return {0: "F32", 1: "Q8_0", 2: "Q4_0", 3: "F16", 4: "FP8 E4M3", 5: "FP8 E5M2", 6: "MXFP4", 7: "Q2_K"}[int(self)]
 
 
 class Mode(IntEnum):

@@ -49,8 +49,11 @@ enum {
  * FC_FP8_E4M3 / FC_FP8_E5M2: one-byte floats with an f16 scale per 32, in Q8_0's block layout -
  * QKind::Fp8E4M3 / Fp8E5M2 (ops/quant.rs:L38-L41, codec ferrum_gguf/src/codec/fp8.rs).
  * FC_MXFP4: 4-bit E2M1 values with a power-of-two scale byte per 32, 17-byte blocks (ggml type 39) -
- * QKind::Fp4 (ops/quant.rs:L36-L37, codec ferrum_gguf/src/codec/mxfp4.rs). */
-enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2, FC_F16 = 3, FC_FP8_E4M3 = 4, FC_FP8_E5M2 = 5, FC_MXFP4 = 6 };
+ * QKind::Fp4 (ops/quant.rs:L36-L37, codec ferrum_gguf/src/codec/mxfp4.rs).
+ * FC_Q2_K: 2-bit values in super-blocks of 256 with 4-bit sub-block scales and mins, 84-byte blocks -
+ * QKind::Q2K (ops/quant.rs:L42-L43, codec ferrum_gguf/src/codec/q2k.rs, decode blocks.rs:L199-L220). A width
+ * that is whole 32s but not whole 256s is stored as Q4_0 instead (`effective`, ops/quant.rs:L134-L144). */
+enum { FC_F32 = 0, FC_Q8_0 = 1, FC_Q4_0 = 2, FC_F16 = 3, FC_FP8_E4M3 = 4, FC_FP8_E5M2 = 5, FC_MXFP4 = 6, FC_Q2_K = 7 };
 
 /* RoPE pairing, ferrum_ref/src/models/llama/ops.rs:L9-L15. */
 enum { FC_ROPE_NORM = 0, FC_ROPE_NEOX = 1 };

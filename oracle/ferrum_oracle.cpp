@@ -187,8 +187,157 @@ uint8_t fp8_encode(int kind, float x) {
   return sign | pick;
 }
 
+
+// ---- Q2_K (ferrum_gguf/src/codec/q2k.rs, decode ferrum_gguf/src/codec/blocks.rs:L199-L220) -----
+constexpr size_t QK_K = 256;                       // ferrum_gguf/src/lib.rs
+constexpr size_t Q2K_BLOCK = 16 + QK_K / 4 + 4;    // scales, 2-bit quants, d, dmin (q2k.rs:L13)
+
+// q2k.rs:L17-L20: round half to even through the float's own rounding
+int32_t q2k_nearest_int(float x) {
+  const float y = x + 12582912.0f;
+  int32_t bits;
+  std::memcpy(&bits, &y, 4);
+  return (bits & 0x007fffff) - 0x00400000;
+}
+
+// q2k.rs:L25-L88: scale and min of 16 values on a 0..3 grid, searched over 16 candidate scales for
+// the smallest |x|-weighted absolute error. Returns (scale, -min); fills the levels.
+void q2k_fit(const float* x, uint8_t* l, float* scale_out, float* neg_min_out) {
+  const int NMAX = 3;
+  float weights[16];
+  for (int i = 0; i < 16; i++) weights[i] = std::fabs(x[i]);
+  float mn = x[0], mx = x[0];
+  float sum_w = weights[0];
+  float sum_x = sum_w * x[0];
+  for (int i = 1; i < 16; i++) {
+    mn = std::fmin(mn, x[i]);
+    mx = std::fmax(mx, x[i]);
+    sum_w += weights[i];
+    sum_x += weights[i] * x[i];
+  }
+  if (mn > 0.0f) mn = 0.0f;
+  if (mx == mn) {
+    for (int i = 0; i < 16; i++) l[i] = 0;
+    *scale_out = 0.0f;
+    *neg_min_out = -mn;
+    return;
+  }
+  float iscale = (float)NMAX / (mx - mn);
+  float scale = 1.0f / iscale;
+  float best_mad = 0.0f;
+  for (int i = 0; i < 16; i++) {
+    const int q = std::min(std::max(q2k_nearest_int(iscale * (x[i] - mn)), 0), NMAX);
+    l[i] = (uint8_t)q;
+    const float diff = scale * (float)q + mn - x[i];
+    best_mad += weights[i] * std::fabs(diff);
+  }
+  for (int step = 0; step <= 15; step++) {
+    iscale = (-0.5f + 0.1f * (float)step + (float)NMAX) / (mx - mn);
+    float sum_l = 0.0f, sum_l2 = 0.0f, sum_xl = 0.0f;
+    uint8_t laux[16];
+    for (int i = 0; i < 16; i++) {
+      const int q = std::min(std::max(q2k_nearest_int(iscale * (x[i] - mn)), 0), NMAX);
+      laux[i] = (uint8_t)q;
+      const float w = weights[i], qf = (float)q;
+      sum_l += w * qf;
+      sum_l2 += w * qf * qf;
+      sum_xl += w * qf * x[i];
+    }
+    const float d = sum_w * sum_l2 - sum_l * sum_l;
+    if (d > 0.0f) {
+      float this_scale = (sum_w * sum_xl - sum_x * sum_l) / d;
+      float this_min = (sum_l2 * sum_x - sum_l * sum_xl) / d;
+      if (this_min > 0.0f) {
+        this_min = 0.0f;
+        this_scale = sum_xl / sum_l2;
+      }
+      float mad = 0.0f;
+      for (int i = 0; i < 16; i++) {
+        const float diff = this_scale * (float)laux[i] + this_min - x[i];
+        mad += weights[i] * std::fabs(diff);
+      }
+      if (mad < best_mad) {
+        for (int i = 0; i < 16; i++) l[i] = laux[i];
+        best_mad = mad;
+        scale = this_scale;
+        mn = this_min;
+      }
+    }
+  }
+  *scale_out = scale;
+  *neg_min_out = -mn;
+}
+
+// q2k.rs:L91-L150: one 84-byte super-block per 256 values.
+void q2k_encode(const float* data, size_t n, uint8_t* out) {
+  for (size_t b = 0; b < n / QK_K; b++) {
+    const float* blk = data + b * QK_K;
+    uint8_t* o = out + b * Q2K_BLOCK;
+    float scales[16], mins[16];
+    uint8_t levels[QK_K];
+    for (int j = 0; j < 16; j++) q2k_fit(blk + 16 * j, levels + 16 * j, &scales[j], &mins[j]);
+    float max_scale = 0.0f, max_min = 0.0f;
+    for (int j = 0; j < 16; j++) {
+      max_scale = std::fmax(max_scale, scales[j]);
+      max_min = std::fmax(max_min, mins[j]);
+    }
+    uint8_t packed[16] = {0};
+    uint16_t d = 0, dmin = 0;
+    if (max_scale > 0.0f) {
+      const float iscale = 15.0f / max_scale;
+      for (int j = 0; j < 16; j++) packed[j] = (uint8_t)q2k_nearest_int(iscale * scales[j]);
+      d = f32_to_f16(max_scale / 15.0f);
+    }
+    if (max_min > 0.0f) {
+      const float iscale = 15.0f / max_min;
+      for (int j = 0; j < 16; j++) packed[j] |= (uint8_t)((uint8_t)q2k_nearest_int(iscale * mins[j]) << 4);
+      dmin = f32_to_f16(max_min / 15.0f);
+    }
+    const float d32 = f16_to_f32(d), dmin32 = f16_to_f32(dmin);
+    for (int j = 0; j < 16; j++) { // the levels again, against the scales as stored
+      const float sc = d32 * (float)(packed[j] & 15);
+      if (sc == 0.0f) continue;
+      const float dm = dmin32 * (float)(packed[j] >> 4);
+      for (int ii = 0; ii < 16; ii++) {
+        const int q = q2k_nearest_int((blk[16 * j + ii] + dm) / sc);
+        levels[16 * j + ii] = (uint8_t)std::min(std::max(q, 0), 3);
+      }
+    }
+    std::memcpy(o, packed, 16);
+    size_t at = 16;
+    for (size_t half = 0; half < QK_K; half += 128)
+      for (size_t l = 0; l < 32; l++)
+        o[at++] = (uint8_t)(levels[half + l] | (levels[half + l + 32] << 2) | (levels[half + l + 64] << 4) |
+                            (levels[half + l + 96] << 6));
+    o[80] = (uint8_t)(d & 0xff), o[81] = (uint8_t)(d >> 8);
+    o[82] = (uint8_t)(dmin & 0xff), o[83] = (uint8_t)(dmin >> 8);
+  }
+}
+
+// blocks.rs:L199-L220: y = d * sc * q - dmin * m over two 128-element halves, shifts 0, 2, 4, 6, two
+// 16-element runs per shift.
+void q2k_decode(const uint8_t* bytes, size_t n, float* out) {
+  for (size_t b = 0; b < n / QK_K; b++) {
+    const uint8_t* p = bytes + b * Q2K_BLOCK;
+    const uint8_t *scales = p, *qs = p + 16;
+    const float d = f16_to_f32((uint16_t)(p[80] | (p[81] << 8))), dmin = f16_to_f32((uint16_t)(p[82] | (p[83] << 8)));
+    float* o = out + b * QK_K;
+    size_t is = 0, at = 0;
+    for (size_t half = 0; half < 2; half++) {
+      const uint8_t* q = qs + 32 * half;
+      for (int shift = 0; shift < 8; shift += 2)
+        for (size_t run = 0; run < 2; run++) {
+          const uint8_t sc = scales[is++];
+          const float dl = d * (float)(sc & 0x0f), ml = dmin * (float)(sc >> 4);
+          for (size_t i = 0; i < 16; i++) o[at++] = dl * (float)((q[16 * run + i] >> shift) & 3) - ml;
+        }
+    }
+  }
+}
+
 // ferrum_gguf/src/codec/quant.rs:L111-L119 (Q8_0) and L120-L133 (Q4_0)
 void encode(int kind, const float* data, size_t n, uint8_t* out) {
+  if (kind == FC_Q2_K) return q2k_encode(data, n, out);
   for (size_t b = 0; b < n / QK; b++) {
     const float* blk = data + b * QK;
     uint8_t* o = out + b * block_bytes(kind);
@@ -252,6 +401,7 @@ void encode(int kind, const float* data, size_t n, uint8_t* out) {
 
 // ferrum_gguf/src/codec/quant.rs:L50-L88
 void decode(int kind, const uint8_t* bytes, size_t n, float* out) {
+  if (kind == FC_Q2_K) return q2k_decode(bytes, n, out);
   for (size_t b = 0; b < n / QK; b++) {
     const uint8_t* p = bytes + b * block_bytes(kind);
     float* o = out + b * QK;
@@ -733,26 +883,34 @@ OR_API uint8_t or_fp8_encode(int kind, float x) { return fp8_encode(kind, x); }
 
 OR_API size_t or_block_bytes(int kind, size_t n) {
   if (kind == FC_F32) return n * 4;
+  if (kind == FC_Q2_K) return n % QK_K ? 0 : n / QK_K * Q2K_BLOCK;
   if (n % QK) return 0;
   return n / QK * block_bytes(kind);
 }
 
+// `effective` (ferrum_wgpu/src/ops/quant.rs:L134-L144): Q2_K needs 256-wide blocks; a width that is whole
+// 32s only is stored as Q4_0 instead.
+OR_API int or_effective_kind(int kind, size_t k) {
+  return (kind == FC_Q2_K && k % QK_K != 0 && k > 0 && k % QK == 0) ? FC_Q4_0 : kind;
+}
+OR_API int32_t or_q2k_nearest_int(float x) { return q2k_nearest_int(x); }
+
 // ferrum_gguf::quant::encode / decode over whole-block data; returns FC_ERR_SHAPE for a length
 // that is not whole blocks (quant.rs:L19-L23)
 OR_API int or_encode(int kind, const float* data, size_t n, uint8_t* out) {
-  if (n % QK) return FC_ERR_SHAPE;
+  if (n % (kind == FC_Q2_K ? QK_K : QK)) return FC_ERR_SHAPE;
   encode(kind, data, n, out);
   return FC_OK;
 }
 OR_API int or_decode(int kind, const uint8_t* bytes, size_t n, float* out) {
-  if (n % QK) return FC_ERR_SHAPE;
+  if (n % (kind == FC_Q2_K ? QK_K : QK)) return FC_ERR_SHAPE;
   decode(kind, bytes, n, out);
   return FC_OK;
 }
 
 // ferrum_wgpu/src/ops/quant.rs:L238-L252: `[k, n]` f32 -> transpose -> encode rows
 OR_API int or_quantise_matrix(int kind, const float* w, size_t k, size_t n, uint8_t* out) {
-  if (k == 0 || k % QK) return FC_ERR_SHAPE;
+  if (k == 0 || k % (kind == FC_Q2_K ? QK_K : QK)) return FC_ERR_SHAPE;
   std::vector<float> rows(k * n);
   transpose(w, k, n, rows.data());
   encode(kind, rows.data(), k * n, out);
@@ -762,6 +920,7 @@ OR_API int or_quantise_matrix(int kind, const float* w, size_t k, size_t n, uint
 // The `snap` closure of ferrum_wgpu/src/models/llama/mod.rs:L188-L199: quantise, decode,
 // transpose back to `[k, n]`; an ineligible width is returned unchanged
 OR_API int or_snap_matrix(int kind, const float* w, size_t k, size_t n, float* out) {
+  kind = or_effective_kind(kind, k);
   if (kind == FC_F32 || k == 0 || k % QK) {
     std::copy(w, w + k * n, out);
     return FC_OK;
@@ -781,7 +940,7 @@ OR_API int or_snap_rows(int kind, const float* data, size_t n, float* out) {
     std::copy(data, data + n, out);
     return FC_OK;
   }
-  if (n % QK) return FC_ERR_SHAPE;
+  if (n % (kind == FC_Q2_K ? QK_K : QK)) return FC_ERR_SHAPE;
   std::vector<uint8_t> bytes(or_block_bytes(kind, n));
   encode(kind, data, n, bytes.data());
   decode(kind, bytes.data(), n, out);

@@ -42,6 +42,7 @@ def lib() -> C.CDLL:
         "or_f16_to_f32": (f, [C.c_uint16]), "or_f32_to_f16": (C.c_uint16, [f]),
         "or_fp8_decode": (f, [C.c_int, C.c_uint8]), "or_fp8_encode": (C.c_uint8, [C.c_int, f]),
         "or_mxfp4_half_scale": (f, [C.c_uint8]), "or_mxfp4_scale_byte": (C.c_uint8, [f]),
+        "or_effective_kind": (C.c_int, [C.c_int, sz]), "or_q2k_nearest_int": (i32, [f]),
         "or_block_bytes": (sz, [C.c_int, sz]),
         "or_encode": (C.c_int, [C.c_int, vp, sz, vp]), "or_decode": (C.c_int, [C.c_int, vp, sz, vp]),
         "or_quantise_matrix": (C.c_int, [C.c_int, vp, sz, sz, vp]),
@@ -120,14 +121,24 @@ def mxfp4_scale_byte(amax: float) -> int:
     return lib().or_mxfp4_scale_byte(C.c_float(amax))
 
 
+def effective_kind(kind: int, k: int) -> int:
+    """`effective` (ferrum_wgpu/src/ops/quant.rs:L134-L144): Q2_K on a width of whole 32s only is Q4_0."""
+    return lib().or_effective_kind(kind, k)
+
+
+def q2k_nearest_int(x: float) -> int:
+    """`nearest_int` (ferrum_gguf/src/codec/q2k.rs:L17-L20)."""
+    return lib().or_q2k_nearest_int(C.c_float(x))
+
+
 def block_bytes(kind: int, n: int) -> int:
     return lib().or_block_bytes(kind, n)
 
 
 def encode(kind: int, data) -> np.ndarray:
     d = _f32(data).reshape(-1)
-    if d.size % 32:
-        raise ValueError(f"{d.size} elements is not a multiple of the block size 32")
+    if d.size % (256 if kind == _ffi.FC_Q2_K else 32):
+        raise ValueError(f"{d.size} elements is not a multiple of the block size")
     out = np.empty(block_bytes(kind, d.size), dtype=np.uint8)
     assert lib().or_encode(kind, _p(d), d.size, _p(out)) == 0
     return out
@@ -135,7 +146,7 @@ def encode(kind: int, data) -> np.ndarray:
 
 def decode(kind: int, data: np.ndarray, n: int) -> np.ndarray:
     b = np.ascontiguousarray(data, dtype=np.uint8)
-    if b.size != block_bytes(kind, n) or n % 32:
+    if b.size != block_bytes(kind, n) or n % (256 if kind == _ffi.FC_Q2_K else 32):
         raise ValueError("tensor byte length does not match its type and element count")
     out = np.empty(n, dtype=np.float32)
     assert lib().or_decode(kind, _p(b), n, _p(out)) == 0
@@ -145,8 +156,8 @@ def decode(kind: int, data: np.ndarray, n: int) -> np.ndarray:
 def quantise_matrix(kind: int, w, k: int, n: int) -> np.ndarray:
     """`[k, n]` f32 -> GGUF block bytes of the transposed `[n, k]` rows (ops/quant.rs:L238-L252)."""
     w = _f32(w).reshape(-1)
-    if k % 32 or k == 0 or w.size != k * n:
-        raise ValueError(f"cannot quantise {w.size} elements as a {k} x {n} weight in whole 32-blocks")
+    if k % (256 if kind == _ffi.FC_Q2_K else 32) or k == 0 or w.size != k * n:
+        raise ValueError(f"cannot quantise {w.size} elements as a {k} x {n} weight in whole blocks")
     out = np.empty(block_bytes(kind, k * n), dtype=np.uint8)
     assert lib().or_quantise_matrix(kind, _p(w), k, n, _p(out)) == 0
     return out

@@ -687,3 +687,83 @@ def test_mxfp4_scale_byte_boundaries_agree_with_the_exponent_field():
             via_f64 = int(np.floor(np.float32(np.log2(np.float64(x))))) - 2 + 127
             assert orc.mxfp4_scale_byte(float(x)) == min(max(via_f64, 0), 254), (k, float(x))
         assert orc.mxfp4_scale_byte(float(p)) == min(max(k - 2 + 127, 0), 254)
+
+
+# ---- Q2_K (ferrum_gguf/src/codec/q2k.rs, decode blocks.rs:L199-L220; known answers of q2k/tests.rs) ----
+
+def _q2k_wave(n):
+    i = np.arange(n)
+    # q2k/tests.rs:L5-L9, in f32 like the reference
+    a = np.sin((i.astype(np.float32) * np.float32(0.37)).astype(np.float32), dtype=np.float32) * np.float32(0.8)
+    return (a + ((i * 7 % 13).astype(np.float32) - np.float32(6.0)) * np.float32(0.02)).astype(np.float32)
+
+
+def test_q2k_nearest_int_rounds_half_to_even():
+    for x, want in [(0.5, 0), (1.5, 2), (2.5, 2), (-0.5, 0), (-1.5, -2), (3.7, 4), (-3.7, -4), (0.0, 0)]:
+        assert orc.q2k_nearest_int(x) == want, x  # q2k/tests.rs:L16-L30
+
+
+def test_q2k_block_is_84_bytes_and_decodes_to_256_values():
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    raw = orc.encode(FC_Q2_K, _q2k_wave(512))
+    assert raw.size == 2 * 84 == orc.block_bytes(FC_Q2_K, 512)
+    assert orc.decode(FC_Q2_K, raw, 512).size == 512
+    assert orc.block_bytes(FC_Q2_K, 288) == 0  # whole super-blocks only
+
+
+def test_q2k_error_is_far_below_the_signal_and_every_sub_block_is_close():
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    data = _q2k_wave(1024)  # q2k/tests.rs:L41-L63
+    back = orc.decode(FC_Q2_K, orc.encode(FC_Q2_K, data), 1024)
+    signal = np.sqrt(np.mean(data.astype(np.float64) ** 2))
+    assert np.sqrt(np.mean((data - back).astype(np.float64) ** 2)) < 0.30 * signal
+    for j in range(64):
+        sub, got = data[16 * j:16 * j + 16], back[16 * j:16 * j + 16]
+        assert np.all(np.abs(sub - got) <= (sub.max() - sub.min()) / 3.0 + 0.02), j
+
+
+def test_q2k_constant_zero_and_all_negative_blocks_are_valid():
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    z = orc.encode(FC_Q2_K, np.zeros(256, np.float32))  # q2k/tests.rs:L66-L77
+    assert not z.any()
+    assert not orc.decode(FC_Q2_K, z, 256).any()
+    c = orc.decode(FC_Q2_K, orc.encode(FC_Q2_K, np.full(256, 0.5, np.float32)), 256)
+    assert np.all(np.abs(c - 0.5) < 0.2)
+    n = orc.decode(FC_Q2_K, orc.encode(FC_Q2_K, np.full(256, -0.5, np.float32)), 256)
+    assert np.all(np.abs(n + 0.5) < 0.05)
+
+
+def test_q2k_encoding_is_deterministic_and_each_block_is_independent():
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    data = _q2k_wave(512)  # q2k/tests.rs:L80-L86
+    a = orc.encode(FC_Q2_K, data)
+    assert np.array_equal(a, orc.encode(FC_Q2_K, data))
+    assert np.array_equal(a[:84], orc.encode(FC_Q2_K, data[:256]))
+    assert np.array_equal(a[84:], orc.encode(FC_Q2_K, data[256:]))
+
+
+def test_q2k_decode_agrees_with_an_independent_numpy_restatement():
+    """blocks.rs:L199-L220 by array indexing instead of the scan: element e of a super-block lives in byte
+    32 * (e // 128) + e % 32 at shift 2 * ((e % 128) // 32); sub-block e // 16 holds its scale and min."""
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    rng = np.random.default_rng(3)
+    raw = rng.integers(0, 256, size=3 * 84, dtype=np.uint8)
+    for b in range(3):  # finite f16 scales
+        raw[84 * b + 80:84 * b + 84] = np.array([0.013, 0.007], dtype=np.float16).view(np.uint8)
+    got = orc.decode(FC_Q2_K, raw, 768)
+    for b in range(3):
+        blk = raw[84 * b:84 * b + 84]
+        d, dmin = (np.float32(v) for v in blk[80:84].view(np.float16))
+        e = np.arange(256)
+        q = (blk[16 + 32 * (e // 128) + e % 32] >> (2 * ((e % 128) // 32))) & 3
+        sc = blk[e // 16]
+        want = (d * (sc & 15).astype(np.float32)) * q.astype(np.float32) - dmin * (sc >> 4).astype(np.float32)
+        assert np.array_equal(got[256 * b:256 * b + 256], want.astype(np.float32))
+
+
+def test_q2k_falls_back_to_q4_0_on_widths_of_whole_32s_only():
+    from ferrum_gpu_b200._ffi import FC_Q2_K
+    assert orc.effective_kind(FC_Q2_K, 512) == FC_Q2_K and orc.effective_kind(FC_Q2_K, 96) == FC_Q4_0
+    assert orc.effective_kind(FC_Q2_K, 24) == FC_Q2_K and orc.effective_kind(FC_Q8_0, 96) == FC_Q8_0
+    w = orc.rand_vec(96 * 5, 2)
+    assert np.array_equal(orc.snap_matrix(FC_Q2_K, w, 96, 5), orc.snap_matrix(FC_Q4_0, w, 96, 5))
