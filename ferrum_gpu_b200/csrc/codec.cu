@@ -296,10 +296,193 @@ __global__ void f16_to_f32_kernel(const __half* __restrict__ src, size_t total, 
   if (i < total) out[i] = __half2float(src[i]);
 }
 
+// ---- Q2_K (ferrum_gguf/src/codec/q2k.rs; decode ferrum_gguf/src/codec/blocks.rs:L199-L220) ----------
+// Every f32 operation is spelled with an explicit round-to-nearest intrinsic in the reference's order, so
+// the compiler can neither fuse nor reorder it: the encoder's answer depends on exact ties in `mad`.
+
+// q2k.rs:L17-L20
+__device__ __forceinline__ int q2k_nearest_int(float x) {
+  return (__float_as_int(__fadd_rn(x, 12582912.0f)) & 0x007fffff) - 0x00400000;
+}
+__device__ __forceinline__ int q2k_level(float iscale, float x, float mn) {
+  return min(max(q2k_nearest_int(__fmul_rn(iscale, __fsub_rn(x, mn))), 0), 3);
+}
+
+// q2k.rs:L25-L88: scale and min of 16 values on a 0..3 grid; the levels come back packed two bits each.
+__device__ void q2k_fit(const float (&x)[16], uint32_t& levels, float& scale_out, float& neg_min_out) {
+  float mn = x[0], mx = x[0];
+  float sum_w = fabsf(x[0]);
+  float sum_x = __fmul_rn(sum_w, x[0]);
+#pragma unroll
+  for (int i = 1; i < 16; i++) {
+    mn = fminf(mn, x[i]);
+    mx = fmaxf(mx, x[i]);
+    sum_w = __fadd_rn(sum_w, fabsf(x[i]));
+    sum_x = __fadd_rn(sum_x, __fmul_rn(fabsf(x[i]), x[i]));
+  }
+  if (mn > 0.0f) mn = 0.0f;
+  levels = 0;
+  if (mx == mn) {
+    scale_out = 0.0f;
+    neg_min_out = -mn;
+    return;
+  }
+  const float range = __fsub_rn(mx, mn);
+  float iscale = __fdiv_rn(3.0f, range);
+  float scale = __fdiv_rn(1.0f, iscale);
+  float best_mad = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; i++) {
+    const int q = q2k_level(iscale, x[i], mn);
+    levels |= (uint32_t)q << (2 * i);
+    const float diff = __fsub_rn(__fadd_rn(__fmul_rn(scale, (float)q), mn), x[i]);
+    best_mad = __fadd_rn(best_mad, __fmul_rn(fabsf(x[i]), fabsf(diff)));
+  }
+  float cur_mn = mn; // a winning candidate replaces the min, and later candidates are laid on the new one
+#pragma unroll 1
+  for (int step = 0; step <= 15; step++) {
+    iscale = __fdiv_rn(__fadd_rn(__fadd_rn(-0.5f, __fmul_rn(0.1f, (float)step)), 3.0f), __fsub_rn(mx, cur_mn));
+    float sum_l = 0.0f, sum_l2 = 0.0f, sum_xl = 0.0f;
+    uint32_t laux = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const int q = q2k_level(iscale, x[i], cur_mn);
+      laux |= (uint32_t)q << (2 * i);
+      const float wq = __fmul_rn(fabsf(x[i]), (float)q);
+      sum_l = __fadd_rn(sum_l, wq);
+      sum_l2 = __fadd_rn(sum_l2, __fmul_rn(wq, (float)q));
+      sum_xl = __fadd_rn(sum_xl, __fmul_rn(wq, x[i]));
+    }
+    const float d = __fsub_rn(__fmul_rn(sum_w, sum_l2), __fmul_rn(sum_l, sum_l));
+    if (d > 0.0f) {
+      float this_scale = __fdiv_rn(__fsub_rn(__fmul_rn(sum_w, sum_xl), __fmul_rn(sum_x, sum_l)), d);
+      float this_min = __fdiv_rn(__fsub_rn(__fmul_rn(sum_l2, sum_x), __fmul_rn(sum_l, sum_xl)), d);
+      if (this_min > 0.0f) {
+        this_min = 0.0f;
+        this_scale = __fdiv_rn(sum_xl, sum_l2);
+      }
+      float mad = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; i++) {
+        const float q = (float)((laux >> (2 * i)) & 3u);
+        const float diff = __fsub_rn(__fadd_rn(__fmul_rn(this_scale, q), this_min), x[i]);
+        mad = __fadd_rn(mad, __fmul_rn(fabsf(x[i]), fabsf(diff)));
+      }
+      if (mad < best_mad) {
+        levels = laux;
+        best_mad = mad;
+        scale = this_scale;
+        cur_mn = this_min;
+      }
+    }
+  }
+  scale_out = scale;
+  neg_min_out = -cur_mn;
+}
+
+// q2k.rs:L91-L150. One thread per 16-value sub-block, the 16 lanes of a super-block side by side: grid
+// (ceil(n / 8), k / 256), 128 threads = 8 output columns x 16 sub-blocks.
+__global__ void __launch_bounds__(128)
+    quantise_q2k_kernel(const float* __restrict__ w, uint32_t k, uint32_t n, uint8_t* __restrict__ qs, uint8_t* __restrict__ rec) {
+  const uint32_t j = threadIdx.x & 15, col_raw = blockIdx.x * 8 + (threadIdx.x >> 4), b = blockIdx.y;
+  const uint32_t col = min(col_raw, n - 1); // lanes past the end work on the last column and store nothing
+  float x[16];
+#pragma unroll
+  for (int i = 0; i < 16; i++) x[i] = w[(size_t)(b * QK_K + 16 * j + i) * n + col];
+  uint32_t levels;
+  float scale, neg_min;
+  q2k_fit(x, levels, scale, neg_min);
+  float max_scale = scale, max_min = neg_min;
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) { // over the super-block's 16 lanes
+    max_scale = fmaxf(max_scale, __shfl_xor_sync(0xffffffffu, max_scale, o, 16));
+    max_min = fmaxf(max_min, __shfl_xor_sync(0xffffffffu, max_min, o, 16));
+  }
+  max_scale = fmaxf(0.0f, max_scale);
+  max_min = fmaxf(0.0f, max_min);
+  uint32_t packed = 0;
+  __half d = __float2half_rn(0.0f), dmin = __float2half_rn(0.0f);
+  if (max_scale > 0.0f) {
+    packed = (uint32_t)q2k_nearest_int(__fmul_rn(__fdiv_rn(15.0f, max_scale), scale)) & 0xffu; // `as u8`
+    d = __float2half_rn(__fdiv_rn(max_scale, 15.0f));
+  }
+  if (max_min > 0.0f) {
+    packed |= (((uint32_t)q2k_nearest_int(__fmul_rn(__fdiv_rn(15.0f, max_min), neg_min)) & 0xffu) << 4) & 0xffu;
+    dmin = __float2half_rn(__fdiv_rn(max_min, 15.0f));
+  }
+  // the levels again, against the scales as stored
+  const float sc = __fmul_rn(__half2float(d), (float)(packed & 15u));
+  if (sc != 0.0f) {
+    const float dm = __fmul_rn(__half2float(dmin), (float)(packed >> 4));
+    levels = 0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const int q = min(max(q2k_nearest_int(__fdiv_rn(__fadd_rn(x[i], dm), sc)), 0), 3);
+      levels |= (uint32_t)q << (2 * i);
+    }
+  }
+  if (col_raw >= n) return;
+  const size_t sb = (size_t)col * (k / QK_K) + b;
+  reinterpret_cast<uint32_t*>(qs)[sb * 16 + j] = levels;
+  rec[sb * 20 + j] = (uint8_t)packed;
+  if (j == 0) {
+    *reinterpret_cast<__half*>(rec + sb * 20 + 16) = d;
+    *reinterpret_cast<__half*>(rec + sb * 20 + 18) = dmin;
+  }
+}
+
+// 84-byte file blocks <-> planes; one thread per super-block. File element e sits in byte
+// 16 + 32 * (e / 128) + e % 32 at shift 2 * ((e % 128) / 32) (blocks.rs:L199-L220).
+__global__ void repack_q2k_kernel(const uint8_t* __restrict__ blocks, size_t total, uint8_t* __restrict__ qs, uint8_t* __restrict__ rec) {
+  const size_t sb = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (sb >= total) return;
+  const uint8_t* p = blocks + sb * 84;
+  for (int j = 0; j < 16; j++) {
+    uint32_t word = 0;
+    for (int i = 0; i < 16; i++) {
+      const int e = 16 * j + i;
+      word |= (uint32_t)((p[16 + 32 * (e / 128) + e % 32] >> (2 * ((e % 128) / 32))) & 3) << (2 * i);
+    }
+    reinterpret_cast<uint32_t*>(qs)[sb * 16 + j] = word;
+    rec[sb * 20 + j] = p[j];
+  }
+  for (int i = 0; i < 4; i++) rec[sb * 20 + 16 + i] = p[80 + i];
+}
+__global__ void export_q2k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ rec, size_t total, uint8_t* __restrict__ blocks) {
+  const size_t sb = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (sb >= total) return;
+  uint8_t* p = blocks + sb * 84;
+  for (int j = 0; j < 16; j++) p[j] = rec[sb * 20 + j];
+  for (int i = 0; i < 64; i++) p[16 + i] = 0;
+  for (int e = 0; e < 256; e++) {
+    const uint32_t q = (reinterpret_cast<const uint32_t*>(qs)[sb * 16 + e / 16] >> (2 * (e % 16))) & 3;
+    p[16 + 32 * (e / 128) + e % 32] |= (uint8_t)(q << (2 * ((e % 128) / 32)));
+  }
+  for (int i = 0; i < 4; i++) p[80 + i] = rec[sb * 20 + 16 + i];
+}
+// Bit-exact decode, one thread per sub-block: (d * sc) * q - dmin * m, each product and the difference rounded once.
+__global__ void dequant_q2k_kernel(const uint8_t* __restrict__ qs, const uint8_t* __restrict__ rec, size_t total_sub, float* __restrict__ out) {
+  const size_t s = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= total_sub) return;
+  const size_t sb = s / 16;
+  const uint8_t sc = rec[sb * 20 + s % 16];
+  const float d = __half2float(*reinterpret_cast<const __half*>(rec + sb * 20 + 16));
+  const float dmin = __half2float(*reinterpret_cast<const __half*>(rec + sb * 20 + 18));
+  const float dl = __fmul_rn(d, (float)(sc & 15)), ml = __fmul_rn(dmin, (float)(sc >> 4));
+  const uint32_t word = reinterpret_cast<const uint32_t*>(qs)[s];
+  for (int i = 0; i < 16; i++) out[s * 16 + i] = __fsub_rn(__fmul_rn(dl, (float)((word >> (2 * i)) & 3)), ml);
+}
+
 } // namespace
 
 int k_quantise_kn(FcDevice* dev, int kind, const float* w, uint32_t k, uint32_t n, uint8_t* qs, __half* sc) {
-  if (k == 0 || k % QK || n == 0) return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole 32-element blocks", k, n);
+  if (k == 0 || k % kind_block_elems(kind) || n == 0)
+    return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole %u-element blocks", k, n, kind_block_elems(kind));
+  if (kind == FC_Q2_K) {
+    FC_LAUNCH(dev, "quantise_q2_k",
+              quantise_q2k_kernel<<<dim3((n + 7) / 8, k / QK_K), 128, 0, dev->stream>>>(w, k, n, qs, (uint8_t*)sc));
+    return FC_OK;
+  }
   if (kind == FC_F16) {
     dim3 g16((n + 31) / 32, (k + 31) / 32), b16(32, 8);
     FC_LAUNCH(dev, "quantise_f16", f16_from_kn_kernel<<<g16, b16, 0, dev->stream>>>(w, k, n, (__half*)qs));
@@ -332,6 +515,11 @@ int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, 
     FC_CUDA(dev, cudaMemcpyAsync(qs, blocks, (size_t)k * n * 2, cudaMemcpyDeviceToDevice, dev->stream));
     return FC_OK;
   }
+  if (kind == FC_Q2_K) {
+    const size_t sbs = (size_t)(k / QK_K) * n;
+    FC_LAUNCH(dev, "repack_q2_k", repack_q2k_kernel<<<(unsigned)((sbs + 127) / 128), 128, 0, dev->stream>>>(blocks, sbs, qs, (uint8_t*)sc));
+    return FC_OK;
+  }
   size_t total = (size_t)(k / QK) * n;
   unsigned grid = (unsigned)((total + 127) / 128);
   if (kind_byte_blocks(kind))
@@ -348,6 +536,12 @@ int k_repack_blocks(FcDevice* dev, int kind, const uint8_t* blocks, uint32_t k, 
 int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks) {
   if (m.kind == FC_F16) {
     FC_CUDA(dev, cudaMemcpyAsync(blocks, m.qs, (size_t)m.k * m.n * 2, cudaMemcpyDeviceToDevice, dev->stream));
+    return FC_OK;
+  }
+  if (m.kind == FC_Q2_K) {
+    const size_t sbs = (size_t)(m.k / QK_K) * m.n;
+    FC_LAUNCH(dev, "export_q2_k",
+              export_q2k_kernel<<<(unsigned)((sbs + 127) / 128), 128, 0, dev->stream>>>(m.qs, (const uint8_t*)m.sc, sbs, blocks));
     return FC_OK;
   }
   size_t total = (size_t)(m.k / QK) * m.n;
@@ -371,6 +565,12 @@ int k_dequant(FcDevice* dev, const QMat& m, float* out) {
   if (m.kind == FC_F16) {
     const size_t tot = (size_t)m.k * m.n;
     FC_LAUNCH(dev, "dequant_f16", f16_to_f32_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, dev->stream>>>((const __half*)m.qs, tot, out));
+    return FC_OK;
+  }
+  if (m.kind == FC_Q2_K) {
+    const size_t subs = (size_t)(m.k / 16) * m.n;
+    FC_LAUNCH(dev, "dequant_q2_k",
+              dequant_q2k_kernel<<<(unsigned)((subs + 127) / 128), 128, 0, dev->stream>>>(m.qs, (const uint8_t*)m.sc, subs, out));
     return FC_OK;
   }
   size_t total = (size_t)(m.k / QK) * m.n;

@@ -81,6 +81,9 @@ int fc_pinned(FcDevice* dev, size_t bytes, void** out);
 //  FC_F32:  qs = f32  [n][k];            sc = nullptr
 //  FC_F16:  qs = f16  [n][k];            sc = nullptr
 //  FC_FP8_E4M3 / FC_FP8_E5M2: Q8_0's planes, the bytes being FP8 codes instead of int8 quants
+//  FC_Q2_K: super-blocks of 256 (k a multiple of 256). qs = u8 [n][k/4], 2 bits per element in element
+//           order (64 bytes per super-block; 32-bit word j is sub-block j, 16 elements); sc = 20-byte
+//           records [n][k/256]: the 16 scale/min bytes of the sub-blocks in element order, then d and dmin (f16)
 //  FC_MXFP4: qs = u8 [n][k/2], 16 bytes per block in element order (byte i: element 2i in the low nibble,
 //           2i+1 in the high one), each nibble an E2M1 code; sc = u16 [n][k/32], the bf16 bit pattern
 //           of the block's power-of-two scale 2^(e-127) (all 255 scale bytes fit: the smallest is a
@@ -110,12 +113,24 @@ __host__ __device__ constexpr bool kind_byte_blocks(int kind) { return kind == F
 // half a byte per element, 16 bytes per block: Q4_0 and MXFP4 share addressing (not the nibble order)
 __host__ __device__ constexpr bool kind_nibble_blocks(int kind) { return kind == FC_Q4_0 || kind == FC_MXFP4; }
 __host__ __device__ constexpr bool kind_has_scales(int kind) { return kind_byte_blocks(kind) || kind_nibble_blocks(kind); }
-static inline bool kind_known(int kind) { return kind >= FC_F32 && kind <= FC_MXFP4; }
+static inline bool kind_known(int kind) { return kind >= FC_F32 && kind <= FC_Q2_K; }
+constexpr uint32_t QK_K = 256; // elements of a Q2_K super-block
+static inline uint32_t kind_block_elems(int kind) { return kind == FC_Q2_K ? QK_K : QK; }
+// ops/quant.rs:L134-L144 (`effective`): Q2_K on a width of whole 32s but not whole 256s is stored as Q4_0
+static inline int effective_kind(int kind, uint64_t k) {
+  return (kind == FC_Q2_K && k % QK_K != 0 && k > 0 && k % QK == 0) ? FC_Q4_0 : kind;
+}
 
 static inline size_t qmat_qs_bytes(int kind, size_t k, size_t n) {
-  return kind_byte_blocks(kind) ? k * n : kind_nibble_blocks(kind) ? k * n / 2 : kind == FC_F16 ? k * n * 2 : k * n * 4;
+  return kind_byte_blocks(kind)     ? k * n
+         : kind_nibble_blocks(kind) ? k * n / 2
+         : kind == FC_Q2_K          ? k * n / 4
+         : kind == FC_F16           ? k * n * 2
+                                    : k * n * 4;
 }
-static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) { return kind_has_scales(kind) ? (k / QK) * n * 2 : 0; }
+static inline size_t qmat_sc_bytes(int kind, size_t k, size_t n) {
+  return kind == FC_Q2_K ? (k / QK_K) * n * 20 : kind_has_scales(kind) ? (k / QK) * n * 2 : 0;
+}
 
 #ifdef __CUDACC__
 // Two FP8 codes (the low 16 bits of `two`) as two fp16 values, low byte in the low half. Exact: every

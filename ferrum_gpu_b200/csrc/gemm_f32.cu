@@ -54,6 +54,15 @@ __global__ void __launch_bounds__(256)
           const uint32_t qw[2] = {q.x, q.y};
 #pragma unroll
           for (int j = 0; j < 8; j++) v[j] = __fmul_rn(d, (float)(int8_t)((qw[j >> 2] >> (8 * (j & 3))) & 0xff));
+        } else if (KIND == FC_Q2_K) { // (d * sc) * q - dmin * m, as the decoder rounds it
+          const uint32_t kk = k0 + part * 8, sub = kk / 16;
+          const uint8_t* rec = reinterpret_cast<const uint8_t*>(w.sc) + ((size_t)row * (k / QK_K) + kk / QK_K) * 20;
+          const uint32_t word = reinterpret_cast<const uint32_t*>(w.qs)[(size_t)row * (k / 16) + sub] >> (2 * (kk % 16));
+          const uint8_t sc = rec[sub % 16];
+          const float dl = __fmul_rn(__half2float(*reinterpret_cast<const __half*>(rec + 16)), (float)(sc & 15));
+          const float ml = __fmul_rn(__half2float(*reinterpret_cast<const __half*>(rec + 18)), (float)(sc >> 4));
+#pragma unroll
+          for (int j = 0; j < 8; j++) v[j] = __fsub_rn(__fmul_rn(dl, (float)((word >> (2 * j)) & 3)), ml);
         } else if (KIND == FC_MXFP4) {
           const uint32_t q = *reinterpret_cast<const uint32_t*>(w.qs + (size_t)row * (k / 2) + (k0 / QK) * 16 + part * 4);
           const float d = block_scale_f32<KIND>(w.sc[(size_t)row * (k / QK) + k0 / QK]);
@@ -151,6 +160,8 @@ int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float*
     FC_LAUNCH(dev, "qgemm_f32_fp8", qgemm_f32_kernel<FC_FP8_E5M2><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else if (w.kind == FC_MXFP4)
     FC_LAUNCH(dev, "qgemm_f32_mxfp4", qgemm_f32_kernel<FC_MXFP4><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
+  else if (w.kind == FC_Q2_K)
+    FC_LAUNCH(dev, "qgemm_f32_q2_k", qgemm_f32_kernel<FC_Q2_K><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   else
     FC_LAUNCH(dev, "qgemm_f32_f32", qgemm_f32_kernel<FC_F32><<<grid, 256, 0, dev->stream>>>(w, x, m, y, ep));
   return FC_OK;

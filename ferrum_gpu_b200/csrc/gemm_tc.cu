@@ -149,6 +149,12 @@ struct RowRegs<FC_Q8_0> {
   uint32_t sc;
 };
 template <>
+struct RowRegs<FC_Q2_K> {
+  uint4 q[1];   // 64 two-bit levels: word j is sub-block j (an array so the other kinds' branches still parse)
+  uint32_t sc;  // the four sub-blocks' scale / min bytes
+  uint32_t dd;  // d | dmin << 16 (f16 bits) of the super-block
+};
+template <>
 struct RowRegs<FC_MXFP4> {
   uint4 q[2];
   uint32_t sc;
@@ -174,7 +180,14 @@ struct RowRegs<FC_F16> {
 
 template <int KIND>
 __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32_t row, uint32_t it, bool valid) {
-  if (kind_nibble_blocks(KIND)) { // (rows past the end decode to zero: nibble 8 of Q4_0, code 0 of MXFP4)
+  if (KIND == FC_Q2_K) { // a 64-k slice is a quarter of a super-block; rows past the end decode to zero
+    RowRegs<FC_Q2_K>& rr = (RowRegs<FC_Q2_K>&)r;
+    const uint32_t* rec =
+        reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(w.sc) + ((size_t)row * (w.k / QK_K) + (it >> 2)) * 20);
+    rr.q[0] = valid ? __ldg(reinterpret_cast<const uint4*>(w.qs + (size_t)row * (w.k / 4) + (size_t)it * 16)) : make_uint4(0, 0, 0, 0);
+    rr.sc = valid ? __ldg(rec + (it & 3)) : 0u;
+    rr.dd = valid ? __ldg(rec + 4) : 0u;
+  } else if (kind_nibble_blocks(KIND)) { // (rows past the end decode to zero: nibble 8 of Q4_0, code 0 of MXFP4)
     const uint32_t zero = KIND == FC_Q4_0 ? 0x88888888u : 0u;
     const uint4* p = reinterpret_cast<const uint4*>(w.qs + (size_t)row * (w.k / 2) + (size_t)it * 32);
     r.q[0] = valid ? __ldg(p) : make_uint4(zero, zero, zero, zero);
@@ -213,6 +226,26 @@ __device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_s
     dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
     dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
     dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+  } else if (KIND == FC_Q2_K) { // (d * sc) * q - dmin * m in f32, one rounding to fp16
+    const RowRegs<FC_Q2_K>& rr = (const RowRegs<FC_Q2_K>&)r;
+    const float d = __half2float(__ushort_as_half((unsigned short)(rr.dd & 0xffffu)));
+    const float dmin = __half2float(__ushort_as_half((unsigned short)(rr.dd >> 16)));
+    const uint32_t words[4] = {rr.q[0].x, rr.q[0].y, rr.q[0].z, rr.q[0].w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const uint32_t sc = (rr.sc >> (8 * j)) & 0xffu;
+      const float dl = d * (float)(sc & 15u), ml = dmin * (float)(sc >> 4);
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const uint32_t b = words[j] >> (16 * h);
+        uint32_t o[4];
+#pragma unroll
+        for (int p = 0; p < 4; p++)
+          o[p] = pack_f16(fmaf(dl, (float)((b >> (4 * p)) & 3u), -ml), fmaf(dl, (float)((b >> (4 * p + 2)) & 3u), -ml));
+        const uint32_t addr = row_smem + (((uint32_t)(2 * j + h) ^ sw) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+      }
+    }
   } else if (KIND == FC_MXFP4) {
     const RowRegs<FC_Q4_0>& rr = (const RowRegs<FC_Q4_0>&)r;
     dequant_mxfp4_block(rr.q[0], __uint_as_float(rr.sc << 16), row_smem, sw, 0);
@@ -536,6 +569,7 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   if (w.kind == FC_FP8_E4M3) return pick_epi<FC_FP8_E4M3>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_FP8_E5M2) return pick_epi<FC_FP8_E5M2>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_MXFP4) return pick_epi<FC_MXFP4>(dev, tmap, w, args, epi, grid);
+  if (w.kind == FC_Q2_K) return pick_epi<FC_Q2_K>(dev, tmap, w, args, epi, grid);
   return pick_epi<FC_F32>(dev, tmap, w, args, epi, grid);
 }
 

@@ -35,6 +35,10 @@ struct Chunk<FC_F16> {
   static constexpr int ELEMS = 8;
 };
 template <>
+struct Chunk<FC_Q2_K> {
+  static constexpr int ELEMS = 64; // four 16-element sub-blocks, each with its own scale and min
+};
+template <>
 struct Chunk<FC_MXFP4> {
   static constexpr int ELEMS = 32;
 };
@@ -139,6 +143,33 @@ __device__ __forceinline__ float chunk_dot(const uint4& wq, const float* __restr
   return acc;
 }
 
+// Q2_K: the contribution of one 64-element chunk, sum over its sub-blocks j of
+// (d * sc_j) * sum(x q) - (dmin * m_j) * sum(x). `sx` holds the four sums of x (shared by the rows).
+__device__ __forceinline__ float q2k_chunk(const uint4& wq, const float* __restrict__ xs, const float (&sx)[4], uint32_t scales,
+                                           uint32_t d_dmin) {
+  const float d = __half2float(__ushort_as_half((unsigned short)(d_dmin & 0xffffu)));
+  const float dmin = __half2float(__ushort_as_half((unsigned short)(d_dmin >> 16)));
+  const uint32_t words[4] = {wq.x, wq.y, wq.z, wq.w};
+  float acc = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i += 4) {
+      const float4 xv = *reinterpret_cast<const float4*>(xs + 16 * j + i);
+      const uint32_t b = words[j] >> (2 * i);
+      sq = fmaf(xv.x, (float)(b & 3u), sq);
+      sq = fmaf(xv.y, (float)((b >> 2) & 3u), sq);
+      sq = fmaf(xv.z, (float)((b >> 4) & 3u), sq);
+      sq = fmaf(xv.w, (float)((b >> 6) & 3u), sq);
+    }
+    const uint32_t sc = (scales >> (8 * j)) & 0xffu;
+    acc = fmaf(d * (float)(sc & 15u), sq, acc);
+    acc = fmaf(-(dmin * (float)(sc >> 4)), sx[j], acc);
+  }
+  return acc;
+}
+
 __device__ __forceinline__ float gelu_f(float x) {
   const float K = 0.7978846f; // ferrum_ref/src/kernels/nn.rs:L12-L15
   return 0.5f * x * (1.0f + tanhf(K * (x + 0.044715f * x * x * x)));
@@ -231,9 +262,35 @@ __global__ void __launch_bounds__(256)
         for (int r = 0; r < R; r++)
           d[r] = block_scale_f32<KIND>(w.sc[(size_t)rows[r] * nb + (kind_byte_blocks(KIND) ? (c >> 1) : c)]);
       }
+      uint32_t q2_sc[R], q2_d[R]; // Q2_K: the chunk's four scale/min bytes and the super-block's d, dmin
+      if (KIND == FC_Q2_K) {
+#pragma unroll
+        for (int r = 0; r < R; r++) {
+          const uint32_t* rec =
+              reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(w.sc) + ((size_t)rows[r] * (k / QK_K) + (c >> 2)) * 20);
+          q2_sc[r] = rec[c & 3];
+          q2_d[r] = rec[4];
+        }
+      }
 #pragma unroll
       for (int m = 0; m < M; m++) {
         const float* xp = xs + (size_t)m * k + (size_t)c * ELEMS;
+        if (KIND == FC_Q2_K) {
+          float sx[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float t = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+              const float4 xv = *reinterpret_cast<const float4*>(xp + 16 * j + i);
+              t += (xv.x + xv.y) + (xv.z + xv.w);
+            }
+            sx[j] = t;
+          }
+#pragma unroll
+          for (int r = 0; r < R; r++) acc[r][m] += q2k_chunk(wq[r], xp, sx, q2_sc[r], q2_d[r]);
+          continue;
+        }
 #pragma unroll
         for (int r = 0; r < R; r++) {
           float s = chunk_dot<KIND>(wq[r], xp);
@@ -324,6 +381,7 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
   if (w.kind == FC_FP8_E4M3) return pick_m<FC_FP8_E4M3>(dev, w, x, m, y, ep);
   if (w.kind == FC_FP8_E5M2) return pick_m<FC_FP8_E5M2>(dev, w, x, m, y, ep);
   if (w.kind == FC_MXFP4) return pick_m<FC_MXFP4>(dev, w, x, m, y, ep);
+  if (w.kind == FC_Q2_K) return pick_m<FC_Q2_K>(dev, w, x, m, y, ep);
   return pick_m<FC_F32>(dev, w, x, m, y, ep);
 }
 

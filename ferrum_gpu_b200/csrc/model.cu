@@ -74,7 +74,8 @@ void model_free(FcModel* m) {
 }
 
 uint64_t matrix_bytes(int qkind, uint64_t k, uint64_t n) {
-  if (qkind != FC_F32 && k % QK == 0) return qmat_qs_bytes(qkind, k, n) + qmat_sc_bytes(qkind, k, n);
+  qkind = effective_kind(qkind, k);
+  if (qkind != FC_F32 && k % kind_block_elems(qkind) == 0) return qmat_qs_bytes(qkind, k, n) + qmat_sc_bytes(qkind, k, n);
   return k * n * 4;
 }
 

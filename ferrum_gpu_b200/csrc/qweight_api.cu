@@ -7,6 +7,7 @@ int tc_check_errors(FcDevice* dev);                                             
 
 FC_API size_t fc_block_bytes(int kind, size_t n_elems) {
   if (kind == FC_F32) return n_elems * 4;
+  if (kind == FC_Q2_K) return n_elems % QK_K ? 0 : n_elems / QK_K * 84;
   if (n_elems % QK) return 0;
   if (kind_byte_blocks(kind)) return n_elems / QK * 34;
   if (kind == FC_Q4_0) return n_elems / QK * 18;
@@ -34,7 +35,8 @@ FC_API int fc_qweight_create_from_blocks(FcDevice* dev, int kind, const uint8_t*
   cudaSetDevice(dev->ordinal);
   if (!blocks) return fc_fail(dev, FC_ERR_ARG, "fc_qweight_create_from_blocks: NULL blocks");
   if (!kind_known(kind) || kind == FC_F32) return fc_fail(dev, FC_ERR_ARG, "block upload takes a block format or F16, not kind %d", kind);
-  if (k == 0 || n == 0 || k % QK) return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole 32-element blocks", k, n);
+  if (k == 0 || n == 0 || k % kind_block_elems(kind))
+    return fc_fail(dev, FC_ERR_SHAPE, "a %u x %u weight is not whole %u-element blocks", k, n, kind_block_elems(kind));
   const size_t want = fc_block_bytes(kind, (size_t)k * n);
   if (n_bytes != want)
     return fc_fail(dev, FC_ERR_SHAPE, "%zu bytes is not the %zu a %u x %u weight needs", n_bytes, want, k, n);

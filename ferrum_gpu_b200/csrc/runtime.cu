@@ -224,6 +224,7 @@ int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, c
     n_max = ns[i] > n_max ? ns[i] : n_max;
   }
   if (k == 0 || n_total == 0 || n_total > 0x7fffffffu) return fc_fail(dev, FC_ERR_SHAPE, "empty or oversized weight");
+  kind = effective_kind(kind, k);              // Q2_K on a width of whole 32s only: Q4_0 (ops/quant.rs:L134-L144)
   if (kind != FC_F32 && k % QK) kind = FC_F32; // ineligible width stays f32 (ops/quant.rs:L125-L134, lin.rs:L54-L61)
   if (!kind_known(kind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
   const uint32_t n = (uint32_t)n_total;
@@ -255,7 +256,7 @@ int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, c
       break;
     }
     uint8_t* qs = (uint8_t*)w->qs_alloc + qmat_qs_bytes(kind, k, row0);
-    __half* sc = w->sc_alloc ? (__half*)w->sc_alloc + (size_t)(k / QK) * row0 : nullptr;
+    __half* sc = w->sc_alloc ? (__half*)((uint8_t*)w->sc_alloc + qmat_sc_bytes(kind, k, row0)) : nullptr;
     rc = kind == FC_F32 ? k_transpose_kn(dev, stage, k, ns[i], (float*)qs) : k_quantise_kn(dev, kind, stage, k, ns[i], qs, sc);
     if (rc == FC_OK && cudaStreamSynchronize(dev->stream) != cudaSuccess) {
       dev->lost = true;

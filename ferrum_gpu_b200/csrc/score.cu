@@ -103,7 +103,7 @@ FC_API int fc_model_set_head_shard(FcModel* m, uint32_t shard, uint32_t n_shards
   QMat v = full;
   v.n = v1 - v0;
   v.qs = full.qs + qmat_qs_bytes(full.kind, full.k, v0);
-  v.sc = full.sc ? full.sc + (size_t)(full.k / QK) * v0 : nullptr;
+  v.sc = full.sc ? (const __half*)((const uint8_t*)full.sc + qmat_sc_bytes(full.kind, full.k, v0)) : nullptr;
   m->head_view = v;
   m->shard = shard, m->n_shards = n_shards, m->v0 = v0, m->v1 = v1;
   return FC_OK;

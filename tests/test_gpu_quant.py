@@ -131,3 +131,61 @@ def test_batched_decode_tensor_product_keeps_f32_accuracy(dev, kind, rows, k, n)
         cols = linear_q(dev, eye, qw, rows)
         assert np.array_equal(cols, want_w.reshape(k, n)[np.arange(rows) * 2])
     qw.close()
+
+
+# ---- Q2_K: super-blocks of 256 with 4-bit sub-block scales and mins (ops/quant.rs:L42-L43) -------------
+
+def _q2k_inputs(k, n):
+    i = np.arange(k * n)
+    wave = (np.sin(i.astype(np.float32) * np.float32(0.37), dtype=np.float32) * np.float32(0.8)
+            + ((i * 7 % 13).astype(np.float32) - np.float32(6.0)) * np.float32(0.02)).astype(np.float32)
+    return [helpers.nasty(k * n), orc.rand_vec(k * n, 4) * np.float32(0.02), wave,
+            np.abs(orc.rand_vec(k * n, 6)), -np.abs(orc.rand_vec(k * n, 7))]
+
+
+@pytest.mark.parametrize("k,n", [(256, 1), (256, 5), (512, 3), (768, 130), (1024, 64)])
+def test_q2k_device_encoder_and_decoder_are_bit_identical_to_the_cpu_codec(dev, k, n):
+    """The 16-candidate scale search of `fit` (ferrum_gguf/src/codec/q2k.rs:L25-L88) decides on exact ties of
+    an f32 error sum, so the device encoder repeats the reference's operations one rounding at a time."""
+    for w in _q2k_inputs(k, n):
+        raw = orc.quantise_matrix(int(QKind.Q2_K), w, k, n)
+        qw = upload_quantised(dev, QKind.Q2_K, w, k, n)
+        assert (qw.kind(), qw.k(), qw.n()) == (QKind.Q2_K, k, n)
+        assert qw.device_bytes() == k * n * 84 // 256
+        assert np.array_equal(qw.blocks(), raw), (k, n)
+        rows = orc.decode(int(QKind.Q2_K), raw, k * n).reshape(n, k)
+        assert np.array_equal(qw.dequantised().view(np.uint32), rows.view(np.uint32))
+        qw.close()
+        qb = upload_qweight(dev, QKind.Q2_K, raw, k, n)  # the file-block upload and its inverse
+        assert np.array_equal(qb.blocks(), raw)
+        assert np.array_equal(qb.dequantised().view(np.uint32), rows.view(np.uint32))
+        if k == 256:
+            got = linear_q(dev, np.eye(k, dtype=np.float32), qb, k)  # y[r, col] = W[col, r]
+            assert np.array_equal(got, rows.T)
+        qb.close()
+
+
+def test_q2k_on_a_width_of_whole_32s_only_is_stored_as_q4_0(dev):
+    """`effective` (ops/quant.rs:L134-L144)."""
+    k, n = 96, 7
+    w = orc.rand_vec(k * n, 4)
+    qw = upload_quantised(dev, QKind.Q2_K, w, k, n)
+    assert qw.kind() == QKind.Q4_0
+    assert np.array_equal(qw.blocks(), orc.quantise_matrix(int(QKind.Q4_0), w, k, n))
+    qw.close()
+    with pytest.raises(CudaError):
+        upload_qweight(dev, QKind.Q2_K, np.zeros(84, np.uint8), 96, 1)
+
+
+@pytest.mark.parametrize("rows,k,n", [(1, 256, 100), (7, 512, 13), (8, 2816, 70), (33, 1024, 200), (64, 768, 130),
+                                      (130, 768, 257)])
+def test_q2k_linear_matches_the_cpu_matmul_on_the_dequantised_weights(dev, rows, k, n):
+    w = orc.rand_vec(k * n, 4) * np.float32(1.0 / np.sqrt(k))
+    want_w = orc.snap_matrix(int(QKind.Q2_K), w, k, n)
+    x = orc.rand_vec(rows * k, 5)
+    want = orc.matmul(x, want_w, rows, k, n)
+    qw = upload_quantised(dev, QKind.Q2_K, w, k, n)
+    got = linear_q(dev, x, qw, rows)
+    assert orc.max_rel_err(got, want) < REDUCING, (rows, k, n)
+    assert np.array_equal(got, linear_q(dev, x, qw, rows))
+    qw.close()

@@ -182,3 +182,40 @@ def test_largest_sweep_shapes_on_sampled_output_columns(dev, kind):
             err = (np.abs(got - want) / np.maximum(np.abs(want), 1.0)).max()
             assert err < tol, (kind, n, m, mode, err)
         qw.close()
+
+
+@pytest.mark.parametrize("hidden", [512, 320])
+def test_q2k_llama_decode_scoring_and_tensor_forward_match_the_oracle(dev, hidden):
+    """Q2_K needs input widths of whole 256s: with hidden = 320 the down projection is stored as Q4_0 instead
+    (`effective`, ops/quant.rs:L134-L144), the rest stays Q2_K. The oracle computes with the same dequantised
+    weights; the exact path stays at 1e-5, the tensor path at the scoring tolerances."""
+    cfg = LlamaConfig(vocab=96, ctx=256, dim=256, heads=4, kv_heads=2, head_dim=64, layers=2, hidden=hidden, rope_dim=64,
+                      rope_base=10000.0, rope_type=_ffi.FC_ROPE_NORM, eps=1e-5)
+    m = random_llama(cfg, seed=5, std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_llama(m, int(QKind.Q2_K), snap_embedding=False)
+    oracle = orc.OracleLlama(ref, threads=8)
+    g = CudaLlama(dev, m, QKind.Q2_K, max_streams=12)
+    ids = random_tokens(9, 150, cfg.vocab)
+    want = oracle.forward_logits(ids)
+    assert orc.max_rel_err(g.forward_all(ids[:40]), want[:40]) < 1e-5
+    got = g.forward_all(ids, Mode.TENSOR_F16)
+    err, scale = orc.max_rel_err(got, want), np.abs(want).max()
+    assert err < LOGIT_TOL and np.abs(got - want).max() < 0.03 * scale, (hidden, err, scale)
+    seqs = np.stack([random_tokens(20 + i, 131, cfg.vocab) for i in range(2)])
+    lp, gr, nll = g.score_batch(seqs, Mode.TENSOR_F16)
+    for s in range(2):
+        wlp, wgr = oracle.score(seqs[s])
+        assert abs(float(np.mean(lp[s] - wlp))) < NLL_TOL and np.abs(lp[s] - wlp).max() < 2 * LOGIT_TOL
+    # token-by-token decode, one stream and twelve (the 9..64-row products fall back to the exact tiled kernel)
+    o1 = orc.OracleLlama(ref)
+    for t in ids[:6]:
+        assert orc.max_rel_err(g.feed(int(t)), o1.feed(int(t))) < 1e-5
+    g.reset()
+    toks = np.stack([random_tokens(50 + s, 3, cfg.vocab) for s in range(12)])
+    oracles = [orc.OracleLlama(ref) for _ in range(12)]
+    for i in range(3):
+        am, lg = g.feed_batch(toks[:, i], want_logits=True)
+        for s in range(12):
+            assert orc.max_rel_err(lg[s], oracles[s].feed(int(toks[s, i]))) < 2e-5
+            assert am[s] == orc.argmax(lg[s])
+    g.close()
