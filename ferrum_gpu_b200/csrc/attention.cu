@@ -202,13 +202,18 @@ __global__ void __launch_bounds__(256)
 
 } // namespace
 
+bool attn_decode_appends(uint32_t heads, uint32_t kv_heads, uint32_t hd, const float* scratch) {
+  return scratch && attn_decode_split_supports(heads, kv_heads, hd);
+}
+
 int k_attn_decode(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                   uint32_t hd, const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx,
-                  float* out, float* scratch, __half* xh, __half* xl, uint32_t mp) {
+                  float* out, float* scratch, __half* xh, __half* xl, uint32_t mp, bool append_kv) {
   if (!rows) return FC_OK;
   if (scratch && attn_decode_split_supports(heads, kv_heads, hd))
-    return k_attn_decode_split(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, scratch, out, xh, xl, mp);
-  if (xh) return fc_fail(dev, FC_ERR_ARG, "only the context-split decode attention writes fp16 terms");
+    return k_attn_decode_split(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, scratch, out, xh, xl, mp,
+                               append_kv);
+  if (xh || append_kv) return fc_fail(dev, FC_ERR_ARG, "only the context-split decode attention writes fp16 terms or the cache");
   if (hd % 4 || hd > 256 || 256 % hd)
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "decode attention needs head_dim in {4,8,...,256} dividing 256, not %u", hd);
   const uint32_t G = heads / kv_heads;

@@ -53,7 +53,7 @@ template <int G>
 __global__ void __launch_bounds__(128)
     attn_decode_split_kernel(const float* __restrict__ qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
                              const int32_t* __restrict__ positions, const int32_t* __restrict__ streams, KvLayer kv,
-                             uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst) {
+                             uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst, bool append) {
   __shared__ float sm_m[4][G], sm_l[4][G];
   __shared__ __align__(16) float sm_o[4][G][HD];
   const uint32_t split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
@@ -98,9 +98,20 @@ __global__ void __launch_bounds__(128)
       const uint32_t j = j0 + warp * 16 + i * 4 + grp;
       const bool ok = j < p1;
       const size_t off = (size_t)(ok ? j : p0) * HD;
-      const float4 k0 = *reinterpret_cast<const float4*>(kbase + off), k1 = *reinterpret_cast<const float4*>(kbase + off + 4);
-      vv[i][0] = *reinterpret_cast<const float4*>(vbase + off);
-      vv[i][1] = *reinterpret_cast<const float4*>(vbase + off + 4);
+      // `append`: the row's own k and v (models without RoPE) have not been stored yet - the lane group
+      // that meets the newest position takes them from the qkv row and stores them on the way
+      const bool fresh = append && j + 1 == len;
+      const float* kp = fresh ? qkv + (size_t)r * q_stride + (size_t)(heads + kvh) * HD + sub * 8 : kbase + off;
+      const float* vp = fresh ? qkv + (size_t)r * q_stride + (size_t)(heads + kv_heads + kvh) * HD + sub * 8 : vbase + off;
+      const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
+      vv[i][0] = *reinterpret_cast<const float4*>(vp);
+      vv[i][1] = *reinterpret_cast<const float4*>(vp + 4);
+      if (fresh) {
+        float* kc = kv.k + (((size_t)slot * kv_heads + kvh) * ctx + j) * HD + sub * 8;
+        float* vc = kv.v + (((size_t)slot * kv_heads + kvh) * ctx + j) * HD + sub * 8;
+        *reinterpret_cast<float4*>(kc) = k0, *reinterpret_cast<float4*>(kc + 4) = k1;
+        *reinterpret_cast<float4*>(vc) = vv[i][0], *reinterpret_cast<float4*>(vc + 4) = vv[i][1];
+      }
 #pragma unroll
       for (int g = 0; g < G; g++) {
         float d = q[g][0] * k0.x;
@@ -205,11 +216,11 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, uint
 template <int G>
 int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
            const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t n_splits,
-           float* scratch, const DecodeOut& dst) {
+           float* scratch, const DecodeOut& dst, bool append) {
   dim3 grid(n_splits, kv_heads, rows);
   FC_LAUNCH(dev, "attn_decode",
             attn_decode_split_kernel<G><<<grid, 128, 0, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
-                                                                       n_splits, scratch, dst));
+                                                                       n_splits, scratch, dst, append));
   if (n_splits > 1) {
     dim3 mg(kv_heads, rows);
     FC_LAUNCH(dev, "attn_decode_merge",
@@ -265,18 +276,18 @@ bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd) 
 
 int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                         const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
-                        float* out, __half* xh, __half* xl, uint32_t mp) {
+                        float* out, __half* xh, __half* xl, uint32_t mp, bool append) {
   if (!rows) return FC_OK;
   const uint32_t ns = attn_decode_splits(dev, rows, heads, kv_heads, ctx);
   DecodeOut dst;
   dst.out = out, dst.xh = xh, dst.xl = xl, dst.mp = mp;
   switch (heads / kv_heads) {
-    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
-    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
-    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
-    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
-    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
-    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst);
+    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
   }
   return fc_fail(dev, FC_ERR_UNSUPPORTED, "split decode attention: group size %u", heads / kv_heads);
 }

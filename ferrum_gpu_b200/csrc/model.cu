@@ -209,8 +209,14 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     FC_TRY(k_qlinear_f32(dev, l.qkv.w->m, b.x, rows, b.qkv, e_qkv));
     pend = DeferredReduce();
     const bool to_cache = mode != ATTN_STATELESS;
-    FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
-                     to_cache ? &l.kv : nullptr, m->ctx, &qkv_sum));
+    // Without RoPE the launch below would only copy k and v into the cache: the decode attention does that itself.
+    const bool attn_appends =
+        mode == ATTN_DECODE && !m->rope.cos && attn_decode_appends(m->heads, m->kv_heads, m->hd, m->attn_scratch);
+    if (attn_appends)
+      FC_TRY(k_flush_deferred(dev, qkv_sum));
+    else
+      FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
+                       to_cache ? &l.kv : nullptr, m->ctx, &qkv_sum));
     Epilogue e_wo;
     if (mode == ATTN_DECODE) {
       __half *xh = nullptr, *xl = nullptr;
@@ -221,7 +227,7 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
         e_wo.presplit = true;
       }
       FC_TRY(k_attn_decode(dev, b.qkv, m->qkv_w(), rows, m->heads, m->kv_heads, m->hd, positions, streams, l.kv, m->ctx,
-                           b.attn, m->attn_scratch, xh, xl, mp));
+                           b.attn, m->attn_scratch, xh, xl, mp, attn_appends));
     } else if (mode == ATTN_STATELESS)
       FC_TRY(k_attn_causal_f32(dev, b.qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, b.attn));
     else
