@@ -46,6 +46,8 @@ int k_norm_f16(FcDevice* dev, bool layernorm, const float* x, const float* g, co
                 float eps, __half* y);
 int k_rope_f16(FcDevice* dev, __half* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
                 const float* cos, const float* sin, uint32_t rope_dim, uint32_t type, const int32_t* positions);
+int k_kv_store_f16(FcDevice* dev, const __half* qkv, uint32_t t, uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t slot,
+                   uint32_t start, uint32_t ctx, float* k_cache, float* v_cache);
 int k_attn_causal_f16(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads,
                        uint32_t kv_heads, uint32_t hd, __half* out);
 int k_partial_merge(FcDevice* dev, const float* tiles, uint32_t n_tiles, uint32_t rows, float* out);

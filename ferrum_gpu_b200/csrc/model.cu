@@ -655,11 +655,38 @@ FC_API int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, 
   cudaSetDevice(dev->ordinal);
   if (stream_id >= m->max_streams) return fc_fail(dev, FC_ERR_RANGE, "stream %u of %u", stream_id, m->max_streams);
   if (n == 0) return FC_OK;
-  if (mode != FC_EXACT_F32) return fc_fail(dev, FC_ERR_UNSUPPORTED, "prefill runs in FC_EXACT_F32 only");
+  if (mode != FC_EXACT_F32 && mode != FC_TENSOR_F16) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "prefill needs the whole head on this device");
   const uint32_t start = m->pos[stream_id];
   if (start + n > m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
   FC_TRY(check_ids(m, ids, n));
+  if (mode == FC_TENSOR_F16) {
+    // The prompt goes through the scoring kernels (fp16 operands, f32 accumulation) and leaves its rotated
+    // k and v in the stream's f32 cache; the stream must be empty (the causal kernel sees the prompt only).
+    if (start != 0)
+      return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core prefill fills an empty stream: stream %u holds %u tokens", stream_id,
+                     start);
+    FC_TRY(arena_reserve(m, (size_t)n * 8 + 512 + (size_t)n * m->dim * 2 + 256 + model_tc_trunk_bytes(m, n) + 4096));
+    int32_t* t_ids = (int32_t*)arena_take(m, (size_t)n * 4);
+    int32_t* t_pos = (int32_t*)arena_take(m, (size_t)n * 4);
+    __half* hid = (__half*)arena_take(m, (size_t)n * m->dim * 2);
+    FC_TRY(upload_positions(m, 1, n, 0, t_pos));
+    FC_TRY(upload_ids(m, ids, n, t_ids));
+    FC_TRY(model_trunk_tc(m, t_ids, t_pos, 1, n, hid, (int32_t)stream_id));
+    if (logits_out || argmax_out) {
+      FC_TRY(model_logits_tc(m, hid + (size_t)(n - 1) * m->dim, 1, m->logits));
+      if (argmax_out) {
+        FC_TRY(k_argmax(dev, m->logits, 1, m->vocab, m->d_argmax, m->argmax_scratch));
+        FC_CUDA(dev, cudaMemcpyAsync(argmax_out, m->d_argmax, 4, cudaMemcpyDeviceToHost, dev->stream));
+      }
+      if (logits_out)
+        FC_CUDA(dev, cudaMemcpyAsync(logits_out, m->logits, (size_t)m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+    }
+    FC_TRY(tc_check_errors(dev));
+    FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    m->pos[stream_id] = n;
+    return FC_OK;
+  }
   PassBufs b;
   FC_TRY(carve_pass(m, n, &b, (size_t)n * 12 + 768));
   int32_t* d_ids = (int32_t*)arena_take(m, (size_t)n * 4);

@@ -78,8 +78,10 @@ int model_trunk_f32(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, 
                     float* hidden_out);
 
 // bf16 tensor-core passes (model_tc.cu)
+// `cache_stream` >= 0 (one sequence from position 0 only): every layer's rotated k and v also go into that
+// stream's cache, so decode can continue from a prompt that went through the tensor-core passes.
 int model_trunk_tc(FcModel* m, const int32_t* ids_dev, const int32_t* pos_dev, uint32_t n_seqs, uint32_t t,
-                   __half* hidden_out);
+                   __half* hidden_out, int32_t cache_stream = -1);
 int model_head_partial_tc(FcModel* m, const __half* hidden, const int32_t* targets_dev, uint32_t rows,
                           float* partial);
 int model_logits_tc(FcModel* m, const __half* hidden, uint32_t rows, float* logits);

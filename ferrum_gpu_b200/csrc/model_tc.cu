@@ -85,9 +85,10 @@ int k_qgemm_tc(FcDevice* dev, FcQWeight* w, const float* x_dev, uint32_t m, floa
 }
 
 int model_trunk_tc(FcModel* m, const int32_t* ids, const int32_t* positions, uint32_t n_seqs, uint32_t t,
-                   __half* hidden_out) {
+                   __half* hidden_out, int32_t cache_stream) {
   FcDevice* dev = m->dev;
   FC_TRY(check_tc_shapes(m));
+  if (cache_stream >= 0 && n_seqs != 1) return fc_fail(dev, FC_ERR_ARG, "one sequence fills one stream's cache");
   const uint32_t rows = n_seqs * t, d = m->dim;
   float* x = (float*)arena_take(m, (size_t)rows * d * 4);
   __half* h = (__half*)arena_take(m, (size_t)rows * d * 2);
@@ -113,6 +114,8 @@ int model_trunk_tc(FcModel* m, const int32_t* ids, const int32_t* positions, uin
       FC_TRY(k_rope_f16(dev, qkv, rows, m->heads, m->kv_heads, m->hd, m->rope.cos, m->rope.sin, m->rope.rope_dim,
                          m->rope.type, positions));
     }
+    if (cache_stream >= 0)
+      FC_TRY(k_kv_store_f16(dev, qkv, t, m->heads, m->kv_heads, m->hd, (uint32_t)cache_stream, 0, m->ctx, l.kv.k, l.kv.v));
     FC_TRY(k_attn_causal_f16(dev, qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, attn));
     TcArgs a_wo;
     a_wo.m = rows, a_wo.bias = l.wo.bias, a_wo.out_f32 = x, a_wo.ldo = d;

@@ -257,6 +257,29 @@ int k_norm_f16(FcDevice* dev, bool layernorm, const float* x, const float* g, co
   return FC_OK;
 }
 
+// The k and v columns of `t` fp16 qkv rows (one sequence, positions start..start + t - 1) into one stream's
+// f32 cache: what feed's two cache copies do (ferrum_wgpu/src/models/llama/mod.rs:L393-L399), for a prompt
+// that went through the tensor-core passes. One CTA per row.
+__global__ void kv_store_f16_kernel(const __half* __restrict__ qkv, uint32_t heads, uint32_t kv_heads, uint32_t hd,
+                                    uint32_t slot, uint32_t start, uint32_t ctx, float* __restrict__ kc, float* __restrict__ vc) {
+  const uint32_t r = blockIdx.x, qd = heads * hd, kvd = kv_heads * hd;
+  const __half* row = qkv + (size_t)r * (qd + 2 * kvd);
+  for (uint32_t i = threadIdx.x; i < kvd; i += blockDim.x) {
+    const uint32_t h = i / hd, e = i % hd;
+    const size_t dst = (((size_t)slot * kv_heads + h) * ctx + start + r) * hd + e;
+    kc[dst] = __half2float(row[qd + i]);
+    vc[dst] = __half2float(row[qd + kvd + i]);
+  }
+}
+
+int k_kv_store_f16(FcDevice* dev, const __half* qkv, uint32_t t, uint32_t heads, uint32_t kv_heads, uint32_t hd, uint32_t slot,
+                   uint32_t start, uint32_t ctx, float* k_cache, float* v_cache) {
+  if (!t) return FC_OK;
+  FC_LAUNCH(dev, "kv_store_f16",
+            kv_store_f16_kernel<<<t, 128, 0, dev->stream>>>(qkv, heads, kv_heads, hd, slot, start, ctx, k_cache, v_cache));
+  return FC_OK;
+}
+
 int k_rope_f16(FcDevice* dev, __half* qkv, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t hd,
                 const float* cos, const float* sin, uint32_t rope_dim, uint32_t type, const int32_t* positions) {
   if (!rows || !cos) return FC_OK;

@@ -257,8 +257,11 @@ int fc_model_topk(FcModel* m, uint32_t row, uint32_t k, float repetition_penalty
 int fc_topk_dev(FcDevice* dev, const float* logits_dev, uint32_t vocab, uint32_t k, float repetition_penalty,
                 const int32_t* recent, uint32_t n_recent, int32_t* idx_out, float* val_out, uint32_t* n_out);
 /* Feed `n` prompt tokens of one stream in one batched pass (new: the reference feeds a prompt
- * token by token, engine/mod.rs:L226-L229). Equivalent to n calls of fc_model_feed; returns
- * the last position's logits / argmax when asked. */
+ * token by token, engine/mod.rs:L226-L229). FC_EXACT_F32: equivalent to n calls of fc_model_feed, at any
+ * position of the stream. FC_TENSOR_F16: the prompt runs through the scoring kernels (fp16 operands, f32
+ * accumulation; logits within the scoring tolerance) and its k and v land in the stream's f32 cache, so
+ * decode continues with fc_model_feed; the stream must be empty. Returns the last position's logits /
+ * argmax when asked. */
 int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, uint32_t n,
                      float* logits_out, int32_t* argmax_out, int mode);
 /* Stateless full causal forward, every position's logits `[n, vocab]`. Replaces

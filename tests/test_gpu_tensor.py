@@ -219,3 +219,32 @@ def test_q2k_llama_decode_scoring_and_tensor_forward_match_the_oracle(dev, hidde
             assert orc.max_rel_err(lg[s], oracles[s].feed(int(toks[s, i]))) < 2e-5
             assert am[s] == orc.argmax(lg[s])
     g.close()
+
+
+@pytest.mark.parametrize("kind", [QKind.Q4_0, QKind.Q8_0])
+def test_tensor_core_prefill_fills_the_cache_and_decode_continues_from_it(dev, kind):
+    """A prompt through the scoring kernels (`prefill(..., Mode.TENSOR_F16)`) leaves its k and v in the f32
+    cache: the last position's logits and the logits of the exactly decoded tokens that follow stay within
+    the scoring tolerance of the f32 oracle, on a second stream while the first holds another context."""
+    cfg = llama_tc_cfg(rope_type=_ffi.FC_ROPE_NEOX, rope_base=1e6, vocab=104, kv_heads=1)
+    m = random_llama(cfg, seed=5, biases=True, std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_llama(m, int(kind), snap_embedding=False)
+    g = CudaLlama(dev, m, kind, max_streams=2)
+    g.prefill(random_tokens(3, 9, cfg.vocab), stream=0)  # an unrelated context in the other stream
+    ids = random_tokens(9, 140, cfg.vocab)
+    oracle = orc.OracleLlama(ref, threads=8)
+    want = [oracle.feed(int(t)) for t in ids]
+    got = g.prefill(ids[:131], stream=1, mode=Mode.TENSOR_F16)
+    assert g.pos(1) == 131 and g.pos(0) == 9
+    scale = max(1.0, float(np.abs(want[130]).max()))
+    assert np.abs(got - want[130]).max() < LOGIT_TOL * scale
+    for i in range(131, 140):
+        lg = g.feed(int(ids[i]), stream=1)
+        assert np.abs(lg - want[i]).max() < LOGIT_TOL * max(1.0, float(np.abs(want[i]).max())), i
+    with pytest.raises(Exception, match="empty stream"):
+        g.prefill(ids[:4], stream=1, mode=Mode.TENSOR_F16)
+    # the exact prefill of the same prompt agrees with the tensor one to the same tolerance
+    g.reset(1)
+    exact = g.prefill(ids[:131], stream=1)
+    assert np.abs(exact - got).max() < LOGIT_TOL * scale and orc.max_rel_err(exact, want[130]) < 1e-5
+    g.close()
