@@ -26,11 +26,14 @@ class SampleParams:
 @dataclass
 class GenOpts:
     """The fields of `GenOpts` this path uses (engine/mod.rs:L189-L202): how many tokens, how to pick them, the
-    seed of the draw and how many recent tokens the repetition penalty looks at."""
+    seed of the draw and how many recent tokens the repetition penalty looks at. `prefill` (new here) feeds the
+    prompt in one batched pass instead of token by token as `generate_with` does: Mode.EXACT_F32 (the same logits
+    to 1e-5) or Mode.TENSOR_F16 (the scoring kernels; logits to the scoring tolerance)."""
     max_new: int = 16
     sampling: SampleParams | None = None
     seed: int = 1
     penalty_window: int = 64
+    prefill: Mode | None = None
 
 
 class Rng:
@@ -159,8 +162,11 @@ class CudaBackend:
                 if not 1 <= sp.top_k <= 1024:
                     raise ValueError("sampled decoding on the device needs 1 <= top_k <= 1024")
                 rng = Rng(opts.seed)
-                for t in out:
-                    m.feed_greedy(t)
+                if opts.prefill is None:
+                    for t in out:
+                        m.feed_greedy(t)
+                else:
+                    m.prefill(out, mode=opts.prefill)
                 for i in range(opts.max_new):
                     recent = out[-opts.penalty_window:] if sp.repetition_penalty != 1.0 else ()
                     idx, val = m.topk(sp.top_k, 0, sp.repetition_penalty, recent)
@@ -170,8 +176,11 @@ class CudaBackend:
                         m.feed_greedy(nxt)
                 return out
             nxt = None
-            for t in out:
-                nxt = m.feed_greedy(t)
+            if opts.prefill is None:
+                for t in out:
+                    nxt = m.feed_greedy(t)
+            else:
+                nxt = argmax(m.prefill(out, mode=opts.prefill))
             for i in range(opts.max_new):
                 out.append(nxt)
                 if i + 1 < opts.max_new:

@@ -115,6 +115,8 @@ def test_greedy_decode_token_for_token(dev, kind):
     assert be.kind() == "cuda" and "B200" in be.name()
     assert be.generate(m, [3, 1, 4], GenOpts(max_new=7)) == want
     assert generate_with(be.llama_decoder(m), [3, 1, 4], GenOpts(max_new=7)) == want
+    # the prompt in one batched pass instead of token by token: the same tokens
+    assert be.generate(m, [3, 1, 4], GenOpts(max_new=7, prefill=Mode.EXACT_F32)) == want
     with pytest.raises(RuntimeError, match="not available"):
         be.train()
 

@@ -248,3 +248,17 @@ def test_tensor_core_prefill_fills_the_cache_and_decode_continues_from_it(dev, k
     exact = g.prefill(ids[:131], stream=1)
     assert np.abs(exact - got).max() < LOGIT_TOL * scale and orc.max_rel_err(exact, want[130]) < 1e-5
     g.close()
+
+
+def test_generate_with_a_tensor_core_prefill_continues_like_the_oracle(dev):
+    """`GenOpts.prefill = Mode.TENSOR_F16`: the prompt runs through the scoring kernels, the new tokens through
+    the exact decode path; on a model with well-separated logits the greedy continuation is the oracle's."""
+    from ferrum_gpu_b200 import CudaBackend, GenOpts, generate_with
+    cfg = llama_tc_cfg(vocab=64)
+    m = random_llama(cfg, seed=12, std=0.3, gain_jitter=0.1)  # large weights: logits far apart
+    oracle = orc.OracleLlama(orc.dequantised_llama(m, int(QKind.Q8_0), snap_embedding=False))
+    prompt = [int(t) for t in random_tokens(4, 70, cfg.vocab)]
+    want = generate_with(oracle.feed, prompt, GenOpts(max_new=6))
+    got = CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=6, prefill=Mode.TENSOR_F16))
+    assert got[:70] == prompt and len(got) == 76
+    assert got == want
