@@ -27,7 +27,17 @@ struct Error : std::runtime_error {
   Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
 };
 
-enum class QKind { F32 = FC_F32, Q8_0 = FC_Q8_0, Q4_0 = FC_Q4_0 };
+// ops::quant::QKind (ferrum_wgpu/src/ops/quant.rs:L27-L44), plus F32 for matrices kept unquantised
+enum class QKind {
+  F32 = FC_F32,
+  Q8_0 = FC_Q8_0,
+  Q4_0 = FC_Q4_0,
+  F16 = FC_F16,
+  Fp8E4M3 = FC_FP8_E4M3,
+  Fp8E5M2 = FC_FP8_E5M2,
+  Fp4 = FC_MXFP4,
+  Q2K = FC_Q2_K,
+};
 enum class Mode { ExactF32 = FC_EXACT_F32, TensorF16 = FC_TENSOR_F16 };
 
 class Gpu {
@@ -137,6 +147,13 @@ class ResidentModel {
     std::vector<std::pair<int32_t, float>> out(n);
     for (uint32_t i = 0; i < n; i++) out[i] = {idx[i], val[i]};
     return out;
+  }
+  // A whole prompt in one batched pass (the reference feeds it token by token, engine/mod.rs:L226-L229);
+  // returns the last position's logits. Mode::TensorF16 needs an empty stream.
+  std::vector<float> prefill(const std::vector<int32_t>& ids, uint32_t stream = 0, Mode mode = Mode::ExactF32) {
+    std::vector<float> logits(vocab_);
+    gpu_.check(fc_model_prefill(h_, stream, ids.data(), (uint32_t)ids.size(), logits.data(), nullptr, (int)mode));
+    return logits;
   }
   // forward_all (models/llama/forward.rs:L13-L17)
   std::vector<float> forward_all(const std::vector<int32_t>& ids, Mode mode = Mode::ExactF32) {
