@@ -146,12 +146,20 @@ __global__ void __launch_bounds__(256)
 // conversion so that the next block's loads are in flight while the current one is multiplied.
 template <int KIND>
 struct BlockRegs {
-  uint32_t q[kind_byte_blocks(KIND) ? 4 : 2];
+  uint32_t q[KIND == FC_F16 ? 8 : kind_byte_blocks(KIND) ? 4 : 2]; // F16: the lane's 8 values of each row as they are
   __half d[2];
 };
 template <int KIND>
 __device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, uint32_t row_g, uint32_t row_g8, uint32_t kb, int t) {
   const uint32_t nb = w.k / QK;
+  if (KIND == FC_F16) { // no scale: 16 bytes of each row
+    const uint4 qa = __ldg(reinterpret_cast<const uint4*>(w.qs + ((size_t)row_g * w.k + (size_t)kb * QK + 8 * t) * 2));
+    const uint4 qb = __ldg(reinterpret_cast<const uint4*>(w.qs + ((size_t)row_g8 * w.k + (size_t)kb * QK + 8 * t) * 2));
+    r.q[0] = qa.x, r.q[1] = qa.y, r.q[KIND == FC_F16 ? 2 : 0] = qa.z, r.q[KIND == FC_F16 ? 3 : 0] = qa.w;
+    r.q[KIND == FC_F16 ? 4 : 0] = qb.x, r.q[KIND == FC_F16 ? 5 : 0] = qb.y, r.q[KIND == FC_F16 ? 6 : 0] = qb.z,
+                             r.q[KIND == FC_F16 ? 7 : 0] = qb.w;
+    return;
+  }
   r.d[0] = w.sc[(size_t)row_g * nb + kb];
   r.d[1] = w.sc[(size_t)row_g8 * nb + kb];
   if (kind_byte_blocks(KIND)) {
@@ -165,7 +173,15 @@ __device__ __forceinline__ void load_block(BlockRegs<KIND>& r, const QMat& w, ui
 }
 template <int KIND>
 __device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a[2][4]) {
-  if (KIND == FC_MXFP4) { // element order: pairs (0,1) (2,3) | (4,5) (6,7) are the two k16 steps
+  if (KIND == FC_F16) { // the stored halves are the fragment
+#pragma unroll
+    for (int s = 0; s < 2; s++) {
+      a[s][0] = r.q[KIND == FC_F16 ? 2 * s : 0];
+      a[s][2] = r.q[KIND == FC_F16 ? 2 * s + 1 : 0];
+      a[s][1] = r.q[KIND == FC_F16 ? 4 + 2 * s : 0];
+      a[s][3] = r.q[KIND == FC_F16 ? 5 + 2 * s : 0];
+    }
+  } else if (KIND == FC_MXFP4) { // element order: pairs (0,1) (2,3) | (4,5) (6,7) are the two k16 steps
     uint32_t ha[4], hb[4];
     e2m1x8_to_f16x2(r.q[0], ha);
     e2m1x8_to_f16x2(r.q[1], hb);
@@ -263,7 +279,8 @@ __global__ void __launch_bounds__(128)
       if (kb0 + bi + 1 < kb_end) load_block<KIND>(nxt, w, row_g, row_g8, kb0 + bi + 1, t); // in flight under this block's MMAs
       uint32_t a[2][4];
       block_frags<KIND>(cur, a);
-      const float dg = block_scale_f32<KIND>(cur.d[0]), dg8 = block_scale_f32<KIND>(cur.d[1]);
+      const float dg = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(cur.d[0]);
+      const float dg8 = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(cur.d[1]);
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
         float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -314,8 +331,8 @@ __global__ void __launch_bounds__(128)
 template <int KIND>
 struct Mma8 {
   static constexpr int ST = 4;
-  static constexpr int WBYTES = kind_byte_blocks(KIND) ? 128 : 64;  // packed bytes of one row of a 128-k slice
-  static constexpr int WROW = kind_byte_blocks(KIND) ? 160 : 80;    // padded: lanes (g, t) read conflict-free
+  static constexpr int WBYTES = KIND == FC_F16 ? 256 : kind_byte_blocks(KIND) ? 128 : 64;  // bytes of one row of a 128-k slice
+  static constexpr int WROW = KIND == FC_F16 ? 320 : kind_byte_blocks(KIND) ? 160 : 80;    // padded: lanes (g, t) read conflict-free
   static constexpr int W_STAGE = 64 * WROW;
   static constexpr int SC_STAGE = 64 * 8;                    // 4 f16 scales per row
   static constexpr int XF_STAGE = 8 * XS * 4;                // f32 x slice
@@ -355,10 +372,11 @@ __global__ void __launch_bounds__(128)
     for (int j = 0; j < PER_ROW * 64 / 128; j++) {
       const uint32_t c = threadIdx.x + 128 * j, row = c / PER_ROW, ch = c % PER_ROW;
       const uint32_t grow = min(cta_row0 + row, n - 1); // rows past the end are computed and dropped
-      const uint8_t* src = w.qs + (size_t)grow * (kind_byte_blocks(KIND) ? k : k / 2) + (size_t)kb0 * (C::WBYTES / 4) + ch * 16;
+      const uint8_t* src =
+          w.qs + (size_t)grow * (KIND == FC_F16 ? 2 * k : kind_byte_blocks(KIND) ? k : k / 2) + (size_t)kb0 * (C::WBYTES / 4) + ch * 16;
       cp_async16(smem_u32(wq + st * C::W_STAGE + row * C::WROW + ch * 16), src);
     }
-    if (threadIdx.x < 64) {
+    if (KIND != FC_F16 && threadIdx.x < 64) {
       const uint32_t grow = min(cta_row0 + threadIdx.x, n - 1);
       cp_async8(smem_u32(scs + st * C::SC_STAGE + threadIdx.x * 8), w.sc + (size_t)grow * nblocks + kb0);
     }
@@ -410,7 +428,12 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
     for (int bi = 0; bi < 4; bi++) {
       uint32_t a[2][4];
-      if (KIND == FC_MXFP4) {
+      if (KIND == FC_F16) {
+        const uint4 qa = *reinterpret_cast<const uint4*>(wst + r0 * C::WROW + bi * 64 + 16 * t);
+        const uint4 qb = *reinterpret_cast<const uint4*>(wst + r1 * C::WROW + bi * 64 + 16 * t);
+        a[0][0] = qa.x, a[0][2] = qa.y, a[1][0] = qa.z, a[1][2] = qa.w;
+        a[0][1] = qb.x, a[0][3] = qb.y, a[1][1] = qb.z, a[1][3] = qb.w;
+      } else if (KIND == FC_MXFP4) {
         uint32_t ha[4], hb[4];
         e2m1x8_to_f16x2(*reinterpret_cast<const uint32_t*>(wst + r0 * C::WROW + bi * 16 + 4 * t), ha);
         e2m1x8_to_f16x2(*reinterpret_cast<const uint32_t*>(wst + r1 * C::WROW + bi * 16 + 4 * t), hb);
@@ -454,7 +477,8 @@ __global__ void __launch_bounds__(128)
           a[s][3] = h2sub(((wb >> (8 * s + 4)) & 0x000f000fu) | 0x64006400u, 0x64086408u);
         }
       }
-      const float dg = block_scale_f32<KIND>(sst[r0 * 4 + bi]), dg8 = block_scale_f32<KIND>(sst[r1 * 4 + bi]);
+      const float dg = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(sst[r0 * 4 + bi]);
+      const float dg8 = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(sst[r1 * 4 + bi]);
       float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       const uint32_t off = g * XSTRIDE + bi * QK + 8 * t;
 #pragma unroll
@@ -527,7 +551,7 @@ int pick_nb(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, ui
 } // namespace
 
 bool qmatvec_mma_supports(const QMat& w, uint32_t m) {
-  return kind_has_scales(w.kind) && m >= 1 && m <= 64 && w.k % XS == 0;
+  return (kind_has_scales(w.kind) || w.kind == FC_F16) && m >= 1 && m <= 64 && w.k % XS == 0;
 }
 
 // Device scratch the product needs: the two fp16 terms of x and the split-K partial sums.
@@ -562,6 +586,7 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_FP8_E5M2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       Mma8<FC_FP8_E5M2>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_MXFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_MXFP4>::SMEM));
+    FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_F16>::SMEM));
     attr = true;
   }
   if (w.kind == FC_Q8_0)
@@ -576,6 +601,9 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   else if (w.kind == FC_MXFP4)
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_MXFP4><<<grid, 128, Mma8<FC_MXFP4>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
+  else if (w.kind == FC_F16)
+    FC_LAUNCH(dev, "qmatvec_mma8",
+              qmatvec_mma8_kernel<FC_F16><<<grid, 128, Mma8<FC_F16>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
   else
     FC_LAUNCH(dev, "qmatvec_mma8",
               qmatvec_mma8_kernel<FC_Q4_0><<<grid, 128, Mma8<FC_Q4_0>::SMEM, dev->stream>>>(w, x, m, y, part, bps, ep));
@@ -649,6 +677,8 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
     FC_TRY(pick_nb<FC_FP8_E5M2>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else if (w.kind == FC_MXFP4)
     FC_TRY(pick_nb<FC_MXFP4>(dev, w, xh, xl, m, y, part, splits, bps, ep));
+  else if (w.kind == FC_F16)
+    FC_TRY(pick_nb<FC_F16>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   else
     FC_TRY(pick_nb<FC_Q4_0>(dev, w, xh, xl, m, y, part, splits, bps, ep));
   if (splits > 1 && ep.defer_out && ep.act == ACT_NONE) { // the consumer's norm + split launch finishes the sum

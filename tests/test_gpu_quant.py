@@ -112,7 +112,7 @@ def test_sweep_shapes_of_the_isolated_matmul_config(dev, kind):
         qw.close()
 
 
-@pytest.mark.parametrize("kind", KINDS + FP8 + MX)
+@pytest.mark.parametrize("kind", KINDS + FP8 + MX + [QKind.F16])
 @pytest.mark.parametrize("rows,k,n", [(9, 128, 8), (16, 256, 70), (33, 1024, 200), (64, 2816, 130), (40, 384, 1536)])
 def test_batched_decode_tensor_product_keeps_f32_accuracy(dev, kind, rows, k, n):
     """9..64 rows (concurrent decode streams) run on mma.sync with x split into two fp16 terms and the
