@@ -222,10 +222,9 @@ int k_attn_decode(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t r
   while (gc > 1 && fixed + (size_t)gc * ctx * 4 > 200 * 1024) gc--;
   const size_t smem = fixed + (size_t)gc * ctx * 4;
   if (smem > 220 * 1024) return fc_fail(dev, FC_ERR_UNSUPPORTED, "decode attention: context %u exceeds shared memory", ctx);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static OncePerDevice attr_set;
+  if (attr_set.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
   }
   dim3 grid(kv_heads, rows);
   FC_LAUNCH(dev, "attn_decode",
@@ -242,11 +241,10 @@ static int attn_causal(FcDevice* dev, bool from_cache, const float* qkv, uint32_
   const uint32_t t_cap = start + t;
   const size_t smem = (size_t)8 * t_cap * 4;
   if (smem > 220 * 1024) return fc_fail(dev, FC_ERR_UNSUPPORTED, "attention: %u positions exceed shared memory", t_cap);
-  static bool attr_set = false;
-  if (!attr_set) {
+  static OncePerDevice attr_set;
+  if (attr_set.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(attn_causal_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
     FC_CUDA(dev, cudaFuncSetAttribute(attn_causal_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-    attr_set = true;
   }
   dim3 grid((t + 7) / 8, heads, n_seqs);
   if (from_cache)

@@ -450,15 +450,16 @@ int k_attn_causal_tmem(FcDevice* dev, const __half* qkv, uint32_t n_seqs, uint32
   CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)qkv, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);
-  static bool attr = false;
-  if (!attr) {
+  static OncePerDevice attr;
+  if (attr.first(dev->ordinal)) {
+    attr.again(dev->ordinal); // (until the checks below have passed)
     cudaFuncAttributes fa;
     FC_CUDA(dev, cudaFuncGetAttributes(&fa, attn_tmem_kernel));
     if (fa.numRegs * THREADS < REGS_NEEDED)
       return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-memory attention was compiled with %d registers per thread; its "
                      "register rebalancing needs %d", fa.numRegs, (REGS_NEEDED + THREADS - 1) / THREADS);
     FC_CUDA(dev, cudaFuncSetAttribute(attn_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    attr = true;
+    attr.first(dev->ordinal);
   }
   // persistent: one CTA per SM walks the (query block, sequence, head) items, heaviest blocks first
   const uint64_t items = (uint64_t)((t + 255) / 256) * heads * n_seqs;

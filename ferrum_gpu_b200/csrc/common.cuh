@@ -70,6 +70,21 @@ int fc_post_launch(FcDevice* dev, const char* what);
     FC_TRY(fc_post_launch((dev), (what))); \
   } while (0)
 
+// A kernel's attributes (dynamic shared memory limit) are set per device: a once-flag per device ordinal, one
+// static instance per kernel instantiation.
+struct OncePerDevice {
+  bool done[64] = {};
+  bool first(int ordinal) {
+    if (ordinal < 0 || ordinal >= 64) return true; // (out of the table: set the attribute every time)
+    if (done[ordinal]) return false;
+    done[ordinal] = true;
+    return true;
+  }
+  void again(int ordinal) { // the set-up did not complete: the next call repeats it
+    if (ordinal >= 0 && ordinal < 64) done[ordinal] = false;
+  }
+};
+
 // Pinned staging buffer of at least `bytes` (grown on demand).
 int fc_pinned(FcDevice* dev, size_t bytes, void** out);
 

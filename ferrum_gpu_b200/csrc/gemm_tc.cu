@@ -504,15 +504,16 @@ EncodeTiledFn encode_fn() {
 template <int KIND, int EPI>
 int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, dim3 grid) {
   auto kern = qgemm_tc_kernel<KIND, EPI>;
-  static bool attr = false; // one per instantiation
-  if (!attr) {
+  static OncePerDevice attr; // one per instantiation
+  if (attr.first(dev->ordinal)) {
+    attr.again(dev->ordinal); // (until the checks below have passed)
     cudaFuncAttributes fa;
     FC_CUDA(dev, cudaFuncGetAttributes(&fa, kern));
     if (fa.numRegs * THREADS < REGS_NEEDED)
       return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product was compiled with %d registers per thread; its register "
                      "rebalancing needs %d", fa.numRegs, (REGS_NEEDED + THREADS - 1) / THREADS);
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
-    attr = true;
+    attr.first(dev->ordinal);
   }
   static const char* const names[] = {"qgemm_tc_f32", "qgemm_tc_f16", "qgemm_tc_resid", "qgemm_tc_swiglu", "qgemm_tc_lse",
                                       "qgemm_tc_qkv"};

@@ -331,10 +331,9 @@ int launch(FcDevice* dev, const QMat& w, const float* x, float* y, const Epilogu
   constexpr int R = M <= 2 ? 4 : 2;
   const size_t smem = (size_t)M * w.k * sizeof(float);
   auto kern = qmatvec_kernel<KIND, M, LPR, R>;
-  static bool attr = false; // once per instantiation: the largest staging buffer the host entry admits
-  if (!attr) {
+  static OncePerDevice attr; // once per instantiation: the largest staging buffer the host entry admits
+  if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
   }
   const uint32_t groups_per_block = 8 * (32 / LPR);
   const uint32_t n_groups = (w.n + R - 1) / R;

@@ -530,10 +530,9 @@ int launch(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, uin
            uint32_t splits, uint32_t bps, const Epilogue& ep) {
   auto kern = qmatvec_mma_kernel<KIND, NB>;
   const size_t smem = (size_t)2 * 2 * NB * 8 * XSTRIDE * sizeof(__half);
-  static bool attr = false;
-  if (!attr) {
+  static OncePerDevice attr;
+  if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr = true;
   }
   dim3 grid((w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, splits);
   FC_LAUNCH(dev, "qmatvec_mma", kern<<<grid, 128, smem, dev->stream>>>(w, xh, xl, m, y, partial, bps, ep));
@@ -577,8 +576,8 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
   float* partial = (float*)(((uintptr_t)scratch + (size_t)2 * 64 * w.k * 2 + 255) & ~(uintptr_t)255);
   float* part = splits > 1 ? partial : nullptr;
   dim3 grid(row_ctas, splits);
-  static bool attr = false;
-  if (!attr) {
+  static OncePerDevice attr;
+  if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q8_0>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_Q4_0>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_FP8_E4M3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -587,7 +586,6 @@ static int k_qmatvec_mma8(FcDevice* dev, const QMat& w, const float* x, uint32_t
                                       Mma8<FC_FP8_E5M2>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_MXFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_MXFP4>::SMEM));
     FC_CUDA(dev, cudaFuncSetAttribute(qmatvec_mma8_kernel<FC_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Mma8<FC_F16>::SMEM));
-    attr = true;
   }
   if (w.kind == FC_Q8_0)
     FC_LAUNCH(dev, "qmatvec_mma8",
