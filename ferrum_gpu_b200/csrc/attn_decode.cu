@@ -23,6 +23,7 @@ namespace {
 
 constexpr int HD = 64;
 constexpr int POS_PER_ITER = 64; // positions a CTA consumes per loop iteration (4 warps x 4 groups x 4)
+constexpr size_t TILE_BYTES = (size_t)2 * 2 * POS_PER_ITER * HD * 4; // two stages of a K and a V tile
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -67,8 +68,6 @@ __global__ void __launch_bounds__(128)
       dst.xh[at] = dst.xl[at] = __float2half_rn(0.0f);
     }
   const uint32_t slot = streams ? (uint32_t)streams[r] : 0;
-  const float* kbase = kv.k + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
-  const float* vbase = kv.v + ((size_t)slot * kv_heads + kvh) * ctx * HD + sub * 8;
 
   // this lane's 8 channels of each query head, pre-scaled by log2(e) / sqrt(64): scores live in the
   // log2 domain so the exponentials are single ex2 instructions
@@ -89,29 +88,66 @@ __global__ void __launch_bounds__(128)
     for (int i = 0; i < 8; i++) acc[g][i] = 0.0f;
   }
 
-  for (uint32_t j0 = p0; j0 < p1; j0 += POS_PER_ITER) {
+  // K and V tiles of 64 positions travel through two shared-memory stages by cp.async: the loads of the next
+  // tile are in flight while this one is multiplied (with two 242-register CTAs per SM, loads held in
+  // registers left the kernel waiting on memory latency). A position's row is 16 chunks of 16 bytes; a lane
+  // reads chunks 2 * sub and 2 * sub + 1, the upper four lanes of a group in the opposite order, which keeps
+  // the eight lanes of one position on 32 different banks.
+  extern __shared__ __align__(16) float tiles[]; // [2 stages][K, V][64 positions][64]
+  constexpr uint32_t TILE = POS_PER_ITER * HD;
+  const float* krow_new = qkv + (size_t)r * q_stride + (size_t)(heads + kvh) * HD;
+  const float* vrow_new = qkv + (size_t)r * q_stride + (size_t)(heads + kv_heads + kvh) * HD;
+  const float* kcache = kv.k + ((size_t)slot * kv_heads + kvh) * ctx * HD;
+  const float* vcache = kv.v + ((size_t)slot * kv_heads + kvh) * ctx * HD;
+  if (append && p0 < len && p1 == len) {
+    // the row's own k and v (models without RoPE) are not in the cache yet: this CTA's range ends with them,
+    // so it stores them; the tiles below take that position from the qkv row
+    float* kc = kv.k + (((size_t)slot * kv_heads + kvh) * ctx + (len - 1)) * HD;
+    float* vc = kv.v + (((size_t)slot * kv_heads + kvh) * ctx + (len - 1)) * HD;
+    if (threadIdx.x < HD) kc[threadIdx.x] = krow_new[threadIdx.x];
+    else vc[threadIdx.x - HD] = vrow_new[threadIdx.x - HD];
+  }
+  auto stage = [&](uint32_t j0, uint32_t buf) {
+#pragma unroll
+    for (int c = 0; c < 16; c++) { // 2 tensors x 64 positions x 16 chunks over 128 threads
+      const uint32_t id = threadIdx.x + 128 * c, tensor = id >> 10, pos = (id >> 4) & 63, ch = id & 15;
+      const uint32_t j = j0 + pos;
+      const uint32_t jj = j < p1 ? j : p0; // past the range: any valid row (its scores are masked)
+      const bool fresh = append && jj + 1 == len;
+      const float* src = tensor ? (fresh ? vrow_new : vcache + (size_t)jj * HD) : (fresh ? krow_new : kcache + (size_t)jj * HD);
+      const uint32_t dst_addr = (uint32_t)__cvta_generic_to_shared(tiles + (buf * 2 + tensor) * TILE + pos * HD + ch * 4);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_addr), "l"(src + ch * 4) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int c_first = 2 * sub + (sub >> 2), c_second = 2 * sub + 1 - (sub >> 2);
+  if (p0 < p1) stage(p0, 0);
+  uint32_t buf = 0;
+  for (uint32_t j0 = p0; j0 < p1; j0 += POS_PER_ITER, buf ^= 1) {
+    if (j0 + POS_PER_ITER < p1) {
+      stage(j0 + POS_PER_ITER, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float* kt = tiles + (buf * 2) * TILE;
+    const float* vt = kt + TILE;
     // this lane group's 4 positions of the iteration
     float s[4][G];
     float4 vv[4][2];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      const uint32_t j = j0 + warp * 16 + i * 4 + grp;
-      const bool ok = j < p1;
-      const size_t off = (size_t)(ok ? j : p0) * HD;
-      // `append`: the row's own k and v (models without RoPE) have not been stored yet - the lane group
-      // that meets the newest position takes them from the qkv row and stores them on the way
-      const bool fresh = append && j + 1 == len;
-      const float* kp = fresh ? qkv + (size_t)r * q_stride + (size_t)(heads + kvh) * HD + sub * 8 : kbase + off;
-      const float* vp = fresh ? qkv + (size_t)r * q_stride + (size_t)(heads + kv_heads + kvh) * HD + sub * 8 : vbase + off;
-      const float4 k0 = *reinterpret_cast<const float4*>(kp), k1 = *reinterpret_cast<const float4*>(kp + 4);
-      vv[i][0] = *reinterpret_cast<const float4*>(vp);
-      vv[i][1] = *reinterpret_cast<const float4*>(vp + 4);
-      if (fresh) {
-        float* kc = kv.k + (((size_t)slot * kv_heads + kvh) * ctx + j) * HD + sub * 8;
-        float* vc = kv.v + (((size_t)slot * kv_heads + kvh) * ctx + j) * HD + sub * 8;
-        *reinterpret_cast<float4*>(kc) = k0, *reinterpret_cast<float4*>(kc + 4) = k1;
-        *reinterpret_cast<float4*>(vc) = vv[i][0], *reinterpret_cast<float4*>(vc + 4) = vv[i][1];
-      }
+      const uint32_t pl = warp * 16 + i * 4 + grp;
+      const bool ok = j0 + pl < p1;
+      const float4 ka = *reinterpret_cast<const float4*>(kt + pl * HD + c_first * 4);
+      const float4 kb = *reinterpret_cast<const float4*>(kt + pl * HD + c_second * 4);
+      const float4 va = *reinterpret_cast<const float4*>(vt + pl * HD + c_first * 4);
+      const float4 vb = *reinterpret_cast<const float4*>(vt + pl * HD + c_second * 4);
+      const bool swap = sub >= 4; // the upper lanes fetched their second chunk first
+      const float4 k0 = swap ? kb : ka, k1 = swap ? ka : kb;
+      vv[i][0] = swap ? vb : va;
+      vv[i][1] = swap ? va : vb;
 #pragma unroll
       for (int g = 0; g < G; g++) {
         float d = q[g][0] * k0.x;
@@ -123,6 +159,7 @@ __global__ void __launch_bounds__(128)
         s[i][g] = ok ? d : -INFINITY;
       }
     }
+    __syncthreads(); // (registers hold what this iteration needs: the stage may be refilled)
 #pragma unroll
     for (int g = 0; g < G; g++) {
       const float bm = fmaxf(fmaxf(s[0][g], s[1][g]), fmaxf(s[2][g], s[3][g]));
@@ -218,8 +255,11 @@ int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, ui
            const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t n_splits,
            float* scratch, const DecodeOut& dst, bool append) {
   dim3 grid(n_splits, kv_heads, rows);
+  static OncePerDevice attr;
+  if (attr.first(dev->ordinal))
+    FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILE_BYTES));
   FC_LAUNCH(dev, "attn_decode",
-            attn_decode_split_kernel<G><<<grid, 128, 0, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
+            attn_decode_split_kernel<G><<<grid, 128, TILE_BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
                                                                        n_splits, scratch, dst, append));
   if (n_splits > 1) {
     dim3 mg(kv_heads, rows);
@@ -235,7 +275,9 @@ int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, ui
 template <int G>
 static int resident_ctas() {
   static int n = 0;
-  if (!n && cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_split_kernel<G>, 128, 0) != cudaSuccess) {
+  if (!n && (cudaFuncSetAttribute(attn_decode_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILE_BYTES) !=
+                 cudaSuccess ||
+             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_split_kernel<G>, 128, TILE_BYTES) != cudaSuccess)) {
     cudaGetLastError();
     n = 2;
   }
