@@ -4,9 +4,8 @@
 // Grid (split, kv-head, row). A CTA of 4 warps owns a contiguous range of cached positions of one
 // (stream, kv-head) and serves all G query heads that share the kv-head from one pass over K and V,
 // so the cache - the dominant HBM traffic of batched decode - is read exactly once per step.
-// A warp works on 4 positions at a time: 8 lanes per position, each lane holding 8 of the 64
-// channels (two 16-byte loads of K, two of V; a position's 256-byte row is one coalesced segment).
-// Scores are reduced over the 8 lanes with shuffles; the softmax is online with one rescale per
+// A warp works on 4 positions at a time: 8 lanes per position, which divide the position's 64 channels and
+// the G query heads among them and read the K and V rows from a tile staged in shared memory. The softmax is online with one rescale per
 // block of 4 positions per lane group. Lane groups, warps and finally splits are merged with the
 // usual (max, sum, weighted output) rule; with one split the CTA writes the result directly.
 //
@@ -69,30 +68,39 @@ __global__ void __launch_bounds__(128)
     }
   const uint32_t slot = streams ? (uint32_t)streams[r] : 0;
 
-  // this lane's 8 channels of each query head, pre-scaled by log2(e) / sqrt(64): scores live in the
-  // log2 domain so the exponentials are single ex2 instructions
-  float q[G][8];
+  // The 8 lanes of a lane group share one cached position and divide it two ways: CP lanes split the 64
+  // channels (CH each), 8 / CP groups of lanes split the G query heads (HL each). More head groups mean fewer
+  // shuffles per score and fewer softmax updates per lane, more channel parts mean fewer shared-memory reads
+  // (every lane of a head group reads its CH channels of the K and V row): 8 heads run as 2 head groups x 4
+  // channel parts (one lane per head, each reading whole rows, was bound by those reads; one head group, each
+  // lane holding 8 channels for all 8 heads, by shuffles and eight softmax updates per lane). q is pre-scaled
+  // by log2(e) / sqrt(64): scores live in the log2 domain so the exponentials are single ex2 instructions.
+  constexpr int CP = (G == 1 || G == 3) ? 8 : 4;
+  constexpr int HGROUPS = 8 / CP, HL = G / HGROUPS, CH = HD / CP;
+  static_assert(HL * HGROUPS == G, "the head groups divide the heads");
+  const int part = sub % CP, h0 = (sub / CP) * HL;
+  float q[HL][CH];
   const float qs = 0.125f * 1.4426950408889634f;
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    const float* qp = qkv + (size_t)r * q_stride + (size_t)(kvh * G + g) * HD + sub * 8;
-    const float4 a = *reinterpret_cast<const float4*>(qp), b = *reinterpret_cast<const float4*>(qp + 4);
-    q[g][0] = a.x * qs, q[g][1] = a.y * qs, q[g][2] = a.z * qs, q[g][3] = a.w * qs;
-    q[g][4] = b.x * qs, q[g][5] = b.y * qs, q[g][6] = b.z * qs, q[g][7] = b.w * qs;
+  for (int h = 0; h < HL; h++) {
+    const float* qp = qkv + (size_t)r * q_stride + (size_t)(kvh * G + h0 + h) * HD + part * CH;
+#pragma unroll
+    for (int c = 0; c < CH; c += 4) {
+      const float4 a = *reinterpret_cast<const float4*>(qp + c);
+      q[h][c] = a.x * qs, q[h][c + 1] = a.y * qs, q[h][c + 2] = a.z * qs, q[h][c + 3] = a.w * qs;
+    }
   }
-  float m[G], l[G], acc[G][8];
+  float m[HL], l[HL], acc[HL][CH];
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    m[g] = -INFINITY, l[g] = 0.0f;
+  for (int h = 0; h < HL; h++) {
+    m[h] = -INFINITY, l[h] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) acc[g][i] = 0.0f;
+    for (int c = 0; c < CH; c++) acc[h][c] = 0.0f;
   }
 
   // K and V tiles of 64 positions travel through two shared-memory stages by cp.async: the loads of the next
-  // tile are in flight while this one is multiplied (with two 242-register CTAs per SM, loads held in
-  // registers left the kernel waiting on memory latency). A position's row is 16 chunks of 16 bytes; a lane
-  // reads chunks 2 * sub and 2 * sub + 1, the upper four lanes of a group in the opposite order, which keeps
-  // the eight lanes of one position on 32 different banks.
+  // tile are in flight while this one is multiplied, and the lanes of a group can all read the same row
+  // (a shared-memory broadcast) instead of each holding a slice of it in registers.
   extern __shared__ __align__(16) float tiles[]; // [2 stages][K, V][64 positions][64]
   constexpr uint32_t TILE = POS_PER_ITER * HD;
   const float* krow_new = qkv + (size_t)r * q_stride + (size_t)(heads + kvh) * HD;
@@ -120,7 +128,6 @@ __global__ void __launch_bounds__(128)
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const int c_first = 2 * sub + (sub >> 2), c_second = 2 * sub + 1 - (sub >> 2);
   if (p0 < p1) stage(p0, 0);
   uint32_t buf = 0;
   for (uint32_t j0 = p0; j0 < p1; j0 += POS_PER_ITER, buf ^= 1) {
@@ -131,80 +138,89 @@ __global__ void __launch_bounds__(128)
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
-    const float* kt = tiles + (buf * 2) * TILE;
+    const float* kt = tiles + (buf * 2) * TILE + part * CH;
     const float* vt = kt + TILE;
     // this lane group's 4 positions of the iteration
-    float s[4][G];
-    float4 vv[4][2];
+    float s[4][HL];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       const uint32_t pl = warp * 16 + i * 4 + grp;
+      float k[CH];
+#pragma unroll
+      for (int c = 0; c < CH; c += 4) {
+        const float4 kk = *reinterpret_cast<const float4*>(kt + pl * HD + c);
+        k[c] = kk.x, k[c + 1] = kk.y, k[c + 2] = kk.z, k[c + 3] = kk.w;
+      }
       const bool ok = j0 + pl < p1;
-      const float4 ka = *reinterpret_cast<const float4*>(kt + pl * HD + c_first * 4);
-      const float4 kb = *reinterpret_cast<const float4*>(kt + pl * HD + c_second * 4);
-      const float4 va = *reinterpret_cast<const float4*>(vt + pl * HD + c_first * 4);
-      const float4 vb = *reinterpret_cast<const float4*>(vt + pl * HD + c_second * 4);
-      const bool swap = sub >= 4; // the upper lanes fetched their second chunk first
-      const float4 k0 = swap ? kb : ka, k1 = swap ? ka : kb;
-      vv[i][0] = swap ? vb : va;
-      vv[i][1] = swap ? va : vb;
 #pragma unroll
-      for (int g = 0; g < G; g++) {
-        float d = q[g][0] * k0.x;
-        d = fmaf(q[g][1], k0.y, d), d = fmaf(q[g][2], k0.z, d), d = fmaf(q[g][3], k0.w, d);
-        d = fmaf(q[g][4], k1.x, d), d = fmaf(q[g][5], k1.y, d), d = fmaf(q[g][6], k1.z, d), d = fmaf(q[g][7], k1.w, d);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        s[i][g] = ok ? d : -INFINITY;
+      for (int h = 0; h < HL; h++) {
+        float d = q[h][0] * k[0];
+#pragma unroll
+        for (int c = 1; c < CH; c++) d = fmaf(q[h][c], k[c], d);
+#pragma unroll
+        for (int o = 1; o < CP; o <<= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        s[i][h] = ok ? d : -INFINITY;
       }
     }
-    __syncthreads(); // (registers hold what this iteration needs: the stage may be refilled)
+    float p[4][HL], corr[HL];
 #pragma unroll
-    for (int g = 0; g < G; g++) {
-      const float bm = fmaxf(fmaxf(s[0][g], s[1][g]), fmaxf(s[2][g], s[3][g]));
-      const float mn = fmaxf(m[g], bm);
-      if (mn == -INFINITY) continue; // nothing valid yet for this group
-      const float corr = ex2(m[g] - mn);
-      m[g] = mn;
-      float p[4];
+    for (int h = 0; h < HL; h++) {
+      const float bm = fmaxf(fmaxf(s[0][h], s[1][h]), fmaxf(s[2][h], s[3][h]));
+      const float mn = fmaxf(m[h], bm);
+      if (mn == -INFINITY) { // nothing valid yet for this group: leave the state as it is
+        corr[h] = 1.0f;
 #pragma unroll
-      for (int i = 0; i < 4; i++) p[i] = ex2(s[i][g] - mn);
-      l[g] = fmaf(l[g], corr, (p[0] + p[1]) + (p[2] + p[3]));
+        for (int i = 0; i < 4; i++) p[i][h] = 0.0f;
+        continue;
+      }
+      corr[h] = ex2(m[h] - mn);
+      m[h] = mn;
 #pragma unroll
-      for (int c = 0; c < 8; c++) {
-        float a = acc[g][c] * corr;
+      for (int i = 0; i < 4; i++) p[i][h] = ex2(s[i][h] - mn);
+      l[h] = fmaf(l[h], corr[h], (p[0][h] + p[1][h]) + (p[2][h] + p[3][h]));
+    }
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const float v = c < 4 ? (&vv[i][0].x)[c] : (&vv[i][1].x)[c - 4];
-          a = fmaf(p[i], v, a);
+    for (int h = 0; h < HL; h++)
+#pragma unroll
+      for (int c = 0; c < CH; c++) acc[h][c] *= corr[h];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const float* vr = vt + (warp * 16 + i * 4 + grp) * HD;
+#pragma unroll
+      for (int c = 0; c < CH; c += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(vr + c);
+#pragma unroll
+        for (int h = 0; h < HL; h++) {
+          acc[h][c] = fmaf(p[i][h], v.x, acc[h][c]);
+          acc[h][c + 1] = fmaf(p[i][h], v.y, acc[h][c + 1]);
+          acc[h][c + 2] = fmaf(p[i][h], v.z, acc[h][c + 2]);
+          acc[h][c + 3] = fmaf(p[i][h], v.w, acc[h][c + 3]);
         }
-        acc[g][c] = a;
       }
     }
+    __syncthreads(); // the stage may be refilled
   }
 
   // merge the 4 lane groups of the warp (lanes with equal `sub`)
 #pragma unroll
-  for (int g = 0; g < G; g++) {
-    float mm = fmaxf(m[g], __shfl_xor_sync(0xffffffffu, m[g], 8));
+  for (int h = 0; h < HL; h++) {
+    float mm = fmaxf(m[h], __shfl_xor_sync(0xffffffffu, m[h], 8));
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
-    const float sc = m[g] == -INFINITY ? 0.0f : ex2(m[g] - mm);
-    float ll = l[g] * sc;
+    const float sc = m[h] == -INFINITY ? 0.0f : ex2(m[h] - mm);
+    float ll = l[h] * sc;
     ll += __shfl_xor_sync(0xffffffffu, ll, 8);
     ll += __shfl_xor_sync(0xffffffffu, ll, 16);
 #pragma unroll
-    for (int c = 0; c < 8; c++) {
-      float a = acc[g][c] * sc;
+    for (int c = 0; c < CH; c++) {
+      float a = acc[h][c] * sc;
       a += __shfl_xor_sync(0xffffffffu, a, 8);
       a += __shfl_xor_sync(0xffffffffu, a, 16);
-      acc[g][c] = a;
+      acc[h][c] = a;
     }
-    m[g] = mm, l[g] = ll;
     if (grp == 0) {
-      if (sub == 0) sm_m[warp][g] = mm, sm_l[warp][g] = ll;
+      if (part == 0) sm_m[warp][h0 + h] = mm, sm_l[warp][h0 + h] = ll;
 #pragma unroll
-      for (int c = 0; c < 8; c++) sm_o[warp][g][sub * 8 + c] = acc[g][c];
+      for (int c = 0; c < CH; c++) sm_o[warp][h0 + h][part * CH + c] = acc[h][c];
     }
   }
   __syncthreads();
