@@ -79,6 +79,12 @@ __global__ void __launch_bounds__(128)
   constexpr int HGROUPS = 8 / CP, HL = G / HGROUPS, CH = HD / CP;
   static_assert(HL * HGROUPS == G, "the head groups divide the heads");
   const int part = sub % CP, h0 = (sub / CP) * HL;
+  // The CP lanes of a head group read their 16-byte chunks of a row at the same time, CH * 4 bytes apart: that
+  // is 2 lanes per bank. The upper half of the lanes therefore walks its chunks rotated by one (register slot
+  // c4 holds chunk (c4 + rot) % NCH, for q, K, V and the output alike), which spreads the 8 lanes of a
+  // position over all 32 banks.
+  constexpr int NCH = CH / 4;
+  const int rot = part >= CP / 2 ? 1 : 0;
   float q[HL][CH];
   const float qs = 0.125f * 1.4426950408889634f;
 #pragma unroll
@@ -86,7 +92,7 @@ __global__ void __launch_bounds__(128)
     const float* qp = qkv + (size_t)r * q_stride + (size_t)(kvh * G + h0 + h) * HD + part * CH;
 #pragma unroll
     for (int c = 0; c < CH; c += 4) {
-      const float4 a = *reinterpret_cast<const float4*>(qp + c);
+      const float4 a = *reinterpret_cast<const float4*>(qp + ((c / 4 + rot) & (NCH - 1)) * 4);
       q[h][c] = a.x * qs, q[h][c + 1] = a.y * qs, q[h][c + 2] = a.z * qs, q[h][c + 3] = a.w * qs;
     }
   }
@@ -148,7 +154,7 @@ __global__ void __launch_bounds__(128)
       float k[CH];
 #pragma unroll
       for (int c = 0; c < CH; c += 4) {
-        const float4 kk = *reinterpret_cast<const float4*>(kt + pl * HD + c);
+        const float4 kk = *reinterpret_cast<const float4*>(kt + pl * HD + ((c / 4 + rot) & (NCH - 1)) * 4);
         k[c] = kk.x, k[c + 1] = kk.y, k[c + 2] = kk.z, k[c + 3] = kk.w;
       }
       const bool ok = j0 + pl < p1;
@@ -188,7 +194,7 @@ __global__ void __launch_bounds__(128)
       const float* vr = vt + (warp * 16 + i * 4 + grp) * HD;
 #pragma unroll
       for (int c = 0; c < CH; c += 4) {
-        const float4 v = *reinterpret_cast<const float4*>(vr + c);
+        const float4 v = *reinterpret_cast<const float4*>(vr + ((c / 4 + rot) & (NCH - 1)) * 4);
 #pragma unroll
         for (int h = 0; h < HL; h++) {
           acc[h][c] = fmaf(p[i][h], v.x, acc[h][c]);
@@ -220,7 +226,7 @@ __global__ void __launch_bounds__(128)
     if (grp == 0) {
       if (part == 0) sm_m[warp][h0 + h] = mm, sm_l[warp][h0 + h] = ll;
 #pragma unroll
-      for (int c = 0; c < CH; c++) sm_o[warp][h0 + h][part * CH + c] = acc[h][c];
+      for (int c = 0; c < CH; c++) sm_o[warp][h0 + h][part * CH + ((c / 4 + rot) & (NCH - 1)) * 4 + (c & 3)] = acc[h][c];
     }
   }
   __syncthreads();
