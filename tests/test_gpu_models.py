@@ -269,6 +269,12 @@ def test_config1_greedy_decode_reproduces_the_oracle_tokens(dev):
         tok_g, tok_o = orc.argmax(lg), orc.argmax(lo)
     assert worst < FORWARD, worst
     assert out_g == out_o
+    # embed; per layer qkv (norm fused), attention (stores the row's k and v itself: no RoPE), wo, fc (norm
+    # fused, GELU), proj; head (final norm fused), argmax
+    g.reset()
+    before = dev.launch_count()
+    g.feed(prompt[0])
+    assert dev.launch_count() - before == 1 + 5 * cfg.layers + 2
     # the device-side greedy path produces the same continuation
     assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128))[16:] == out_o
     g.close()
