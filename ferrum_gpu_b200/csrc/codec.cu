@@ -288,7 +288,12 @@ __global__ void f16_from_kn_kernel(const float* __restrict__ w, uint32_t k, uint
   __syncthreads();
   for (uint32_t j = threadIdx.y; j < 32; j += 8) {
     const uint32_t c = c0 + j, r = r0 + threadIdx.x; // out row = column of w
-    if (c < n && r < k) out[(size_t)c * k + r] = __float2half_rn(tile[threadIdx.x][j]);
+    if (c < n && r < k) {
+      const float v = tile[threadIdx.x][j];
+      // a NaN becomes the reference's quiet NaN with the input's sign (f16.rs:L25-L53), not the hardware's 0x7fff
+      out[(size_t)c * k + r] =
+          v != v ? __ushort_as_half((unsigned short)(((__float_as_uint(v) >> 16) & 0x8000u) | 0x7e00u)) : __float2half_rn(v);
+    }
   }
 }
 __global__ void f16_to_f32_kernel(const __half* __restrict__ src, size_t total, float* __restrict__ out) {

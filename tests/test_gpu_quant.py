@@ -189,3 +189,34 @@ def test_q2k_linear_matches_the_cpu_matmul_on_the_dequantised_weights(dev, rows,
     assert orc.max_rel_err(got, want) < REDUCING, (rows, k, n)
     assert np.array_equal(got, linear_q(dev, x, qw, rows))
     qw.close()
+
+
+@pytest.mark.parametrize("kind", STORED + [QKind.Q2_K])
+def test_device_encoder_matches_the_cpu_encoder_on_special_values(dev, kind):
+    """NaN, infinities, signed zeros, subnormals and values past the f16 range inside otherwise ordinary
+    blocks: the device encoder takes the same branches as the CPU one (`f32::max` ignores NaN, `as i8` sends
+    NaN to 0, an infinite scale makes every code NaN, ...)."""
+    k, n = 512, 6
+    w = (orc.rand_vec(k * n, 12) * np.float32(0.5)).reshape(k, n)
+    if kind != QKind.Q2_K:
+        # (Q2_K's `nearest_int` reads the low bits of `x + 12582912.0`: for a NaN that is the payload, which an x86
+        # host and the GPU choose differently - the reference's own answer depends on the machine there)
+        w[3, 0] = np.nan
+        w[40, 1] = np.inf
+        w[77, 2] = -np.inf
+        w[288:320, 0] = np.nan          # an all-NaN block
+        w[300, 5] = np.float32(3.0e38)  # (Q2_K: a super-block scale past the f16 range is infinite, and inf * 0 a NaN)
+    w[100, 3] = -0.0
+    w[130:140, 4] = np.float32(1e-41)   # subnormal f32
+    w[301, 5] = np.float32(-7.0e4)      # past the f16 range
+    w[256:288, 0] = 0.0                 # an all-zero block
+    w = w.reshape(-1)
+    raw = orc.quantise_matrix(int(kind), w, k, n)
+    qw = upload_quantised(dev, kind, w, k, n)
+    assert np.array_equal(qw.blocks(), raw), kind
+    want = orc.decode(int(kind), raw, k * n)
+    got = qw.dequantised().reshape(-1)
+    assert np.array_equal(np.isnan(got), np.isnan(want))
+    ok = ~np.isnan(want)
+    assert np.array_equal(got[ok].view(np.uint32), want[ok].view(np.uint32)), kind
+    qw.close()
