@@ -89,7 +89,7 @@ EXPORTS = (
     "fc_qmatmul_dev_noalloc",
     "fc_llama_plan_bytes", "fc_gpt2_plan_bytes", "fc_llama_create", "fc_gpt2_create",
     "fc_model_destroy", "fc_model_pos", "fc_model_reset", "fc_model_info", "fc_model_feed",
-    "fc_model_feed_batch", "fc_model_topk", "fc_topk_dev", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
+    "fc_model_feed_batch", "fc_model_decode_greedy", "fc_model_topk", "fc_topk_dev", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
     "fc_model_score_dev", "fc_model_set_head_shard", "fc_model_trunk_dev",
     "fc_model_head_partial_dev", "fc_score_combine_dev",
 )
@@ -152,6 +152,7 @@ def load() -> C.CDLL:
         "fc_model_info": (C.c_int, [vp, P(u32), P(u32), P(u32), P(C.c_int), P(u64)]),
         "fc_model_feed": (C.c_int, [vp, u32, i32, vp, P(i32)]),
         "fc_model_feed_batch": (C.c_int, [vp, u32, vp, vp, vp, vp]),
+        "fc_model_decode_greedy": (C.c_int, [vp, u32, vp, vp, u32, vp]),
         "fc_model_prefill": (C.c_int, [vp, u32, vp, u32, vp, P(i32), C.c_int]),
         "fc_model_forward_all": (C.c_int, [vp, vp, u32, vp, C.c_int]),
         "fc_model_score": (C.c_int, [vp, vp, u32, u32, C.c_int, vp, vp, vp]),

@@ -58,6 +58,8 @@ void model_free(FcModel* m) {
   cudaSetDevice(m->dev->ordinal);
   cudaStreamSynchronize(m->dev->stream);
   model_tc_free(m);
+  for (cudaGraphExec_t g : m->chain_graphs)
+    if (g) cudaGraphExecDestroy(g);
   for (cudaGraphExec_t g : m->graphs)
     if (g) cudaGraphExecDestroy(g);
   if (m->pin_dec) cudaFreeHost(m->pin_dec);
@@ -133,6 +135,8 @@ int alloc_common(FcModel* m) {
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_pos));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
+  FC_TRY(dev_alloc(m, (size_t)m->ctx * s * 4, (void**)&m->d_chain_log));
+  FC_TRY(dev_alloc(m, 16, (void**)&m->d_chain_cnt));
   FC_TRY(dev_alloc(m, argmax_scratch_bytes(s), &m->argmax_scratch));
   FC_CUDA(m->dev, cudaMemsetAsync(m->argmax_scratch, 0, argmax_scratch_bytes(s), m->dev->stream));
   // partial results of the context-split decode attention: the largest need over every batch width
@@ -635,6 +639,98 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
   FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
   if (argmax_out) memcpy(argmax_out, p + 3 * n, n * 4);
   for (uint32_t i = 0; i < n; i++) m->pos[stream_ids[i]]++; // only a step that fully succeeded advances
+  return FC_OK;
+}
+
+// The link of a chained greedy step: the previous step's picks become this step's tokens (and are logged),
+// every row moves one position on.
+__global__ void chain_advance_kernel(const int32_t* __restrict__ argmax, int32_t* __restrict__ ids, int32_t* __restrict__ pos,
+                                     int32_t* __restrict__ log, uint32_t* __restrict__ cnt, uint32_t n) {
+  const uint32_t r = threadIdx.x, step = *cnt;
+  __syncthreads(); // everyone has read the counter before it moves
+  if (r < n) {
+    const int32_t tok = argmax[r];
+    ids[r] = tok;
+    pos[r] += 1;
+    log[(size_t)step * n + r] = tok;
+  }
+  if (r == 0) *cnt = step + 1;
+}
+
+FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* first_tokens, uint32_t steps,
+                                  int32_t* tokens_out) {
+  if (!m || !stream_ids || !first_tokens || !tokens_out) return FC_ERR_ARG;
+  FcDevice* dev = m->dev;
+  cudaSetDevice(dev->ordinal);
+  if (n == 0 || steps == 0) return FC_OK;
+  if (n > m->max_streams || n > 1024) return fc_fail(dev, FC_ERR_SHAPE, "%u rows for a model of %u streams", n, m->max_streams);
+  for (uint32_t i = 0; i < n; i++) {
+    if (stream_ids[i] >= m->max_streams) return fc_fail(dev, FC_ERR_RANGE, "stream %u of %u", stream_ids[i], m->max_streams);
+    if (m->pos[stream_ids[i]] + steps > m->ctx)
+      return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
+  }
+  // the first step takes its tokens from the host like any other (and checks streams and ids)
+  FC_TRY(fc_model_feed_batch(m, n, stream_ids, first_tokens, nullptr, tokens_out));
+  if (steps == 1) return FC_OK;
+  const bool graph_mode = m->graph_ok && dev->fail_after < 0 && !dev->profiling;
+  if (!graph_mode) { // fault injection and per-kernel profiling step on the host
+    for (uint32_t s = 1; s < steps; s++)
+      FC_TRY(fc_model_feed_batch(m, n, stream_ids, tokens_out + (size_t)(s - 1) * n, nullptr, tokens_out + (size_t)s * n));
+    return FC_OK;
+  }
+  // Steps 1 .. steps-1 run back to back on the device: d_ids / d_pos / d_streams still hold step 0's rows and
+  // d_argmax its picks; each further step starts with the link kernel instead of host copies, and the host
+  // waits once at the end.
+  auto enqueue_link = [&]() -> int {
+    FC_LAUNCH(dev, "chain_advance",
+              chain_advance_kernel<<<1, 1024, 0, dev->stream>>>(m->d_argmax, m->d_ids, m->d_pos, m->d_chain_log, m->d_chain_cnt, n));
+    PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
+    DeferredReduce tail;
+    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false, &tail));
+    Epilogue e_head;
+    e_head.scratch = m->mma_scratch;
+    e_head.pending = &tail;
+    norm_before(m, e_head, m->normf_g, m->normf_b, m->h);
+    FC_TRY(k_qlinear_f32(dev, m->head_view, m->x, n, m->logits, e_head));
+    FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax, m->argmax_scratch));
+    return FC_OK;
+  };
+  if (m->chain_graphs.size() <= n) {
+    m->chain_graphs.resize(n + 1, nullptr);
+    m->chain_launches.resize(n + 1, 0);
+  }
+  FC_CUDA(dev, cudaMemsetAsync(m->d_chain_cnt, 0, 4, dev->stream));
+  uint32_t done = 1;
+  if (!m->chain_graphs[n]) {
+    const uint64_t l0 = dev->launches;
+    cudaGraph_t graph = nullptr;
+    bool ok = cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+    int rc = ok ? enqueue_link() : FC_OK;
+    if (ok) ok = cudaStreamEndCapture(dev->stream, &graph) == cudaSuccess && rc == FC_OK && graph;
+    if (ok) ok = cudaGraphInstantiate(&m->chain_graphs[n], graph, 0) == cudaSuccess;
+    if (graph) cudaGraphDestroy(graph);
+    if (ok) {
+      m->chain_launches[n] = dev->launches - l0;
+      dev->launches = l0;
+    } else { // without the graph the steps go through the host one by one
+      cudaGetLastError();
+      m->chain_graphs[n] = nullptr;
+      dev->launches = l0;
+      for (uint32_t s = 1; s < steps; s++)
+        FC_TRY(fc_model_feed_batch(m, n, stream_ids, tokens_out + (size_t)(s - 1) * n, nullptr, tokens_out + (size_t)s * n));
+      return FC_OK;
+    }
+  }
+  for (; done < steps; done++) {
+    FC_CUDA(dev, cudaGraphLaunch(m->chain_graphs[n], dev->stream));
+    dev->launches += m->chain_launches[n];
+  }
+  // the log holds the tokens the links consumed: the picks of steps 0 .. steps-2; the last picks are in d_argmax
+  if (steps > 2)
+    FC_CUDA(dev, cudaMemcpyAsync(tokens_out + n, m->d_chain_log + n, (size_t)(steps - 2) * n * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaMemcpyAsync(tokens_out + (size_t)(steps - 1) * n, m->d_argmax, (size_t)n * 4, cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  for (uint32_t i = 0; i < n; i++) m->pos[stream_ids[i]] += steps - 1; // (step 0 advanced them once already)
   return FC_OK;
 }
 

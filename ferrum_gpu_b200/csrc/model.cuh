@@ -58,6 +58,12 @@ struct FcModel {
   std::vector<uint64_t> graph_launches;
   std::vector<uint8_t> graph_warm;
   bool graph_ok = true;
+  // chained greedy decode (fc_model_decode_greedy): the step that takes its tokens from the previous step's
+  // argmax on the device, one graph per batch width; the tokens it consumed, in order; how many steps so far
+  std::vector<cudaGraphExec_t> chain_graphs;
+  std::vector<uint64_t> chain_launches;
+  int32_t* d_chain_log = nullptr; // [ctx][max_streams]
+  uint32_t* d_chain_cnt = nullptr;
   Arena arena;
   void* tc = nullptr; // state of the bf16 tensor-core path (built on first use)
 

@@ -181,10 +181,10 @@ class CudaBackend:
                     nxt = m.feed_greedy(t)
             else:
                 nxt = argmax(m.prefill(out, mode=opts.prefill))
-            for i in range(opts.max_new):
+            if opts.max_new > 0:
                 out.append(nxt)
-                if i + 1 < opts.max_new:
-                    nxt = m.feed_greedy(nxt)
+            if opts.max_new > 1:  # the remaining picks in one call, chained on the device
+                out.extend(int(t) for t in m.decode_greedy([nxt], opts.max_new - 1)[:, 0])
             return out
         finally:
             m.close()

@@ -75,6 +75,18 @@ class ResidentModel:
                                                      lg.ctypes.data if want_logits else None, am.ctypes.data))
         return am, lg
 
+    def decode_greedy(self, tokens, steps: int, streams=None) -> np.ndarray:
+        """`steps` greedy steps of several streams in one call, chained on the device: step 0 feeds `tokens`,
+        every further step the previous picks. Returns the picks `[steps, n]` - what `steps` calls of
+        `feed_batch` would return."""
+        tokens = _i32(tokens)
+        n = tokens.size
+        streams = np.arange(n, dtype=np.uint32) if streams is None else np.ascontiguousarray(streams, dtype=np.uint32)
+        out = np.empty((steps, n), dtype=np.int32)
+        self.dev.check(self._lib.fc_model_decode_greedy(self._h, n, streams.ctypes.data, tokens.ctypes.data, steps,
+                                                        out.ctypes.data))
+        return out
+
     def prefill(self, ids, stream: int = 0, mode: Mode = Mode.EXACT_F32) -> np.ndarray:
         """Feed a whole prompt in one batched pass; returns the last position's logits."""
         ids = _i32(ids)

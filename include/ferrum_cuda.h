@@ -242,6 +242,13 @@ int fc_model_feed(FcModel* m, uint32_t stream_id, int32_t token, float* logits_o
  * NULL. */
 int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* tokens,
                         float* logits_out, int32_t* argmax_out);
+/* `steps` greedy decode steps of `n` streams in one call (new: the reference's generate loop reads every
+ * token back before it feeds it, engine/mod.rs:L230-L240): step 0 feeds `first_tokens`, every further step
+ * feeds the previous step's first-maximum picks, chained on the device without a host round trip.
+ * `tokens_out` is `[steps][n]`: the picks of every step, exactly what `steps` calls of fc_model_feed_batch
+ * with `argmax_out` would return. Every stream needs room for `steps` more positions. */
+int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* first_tokens,
+                           uint32_t steps, int32_t* tokens_out);
 /* Candidates for sampled decoding, selected on the device (new: the reference reads the whole logits
  * row back for every sampled token, engine/mod.rs:L230-L240). Applies the repetition penalty of
  * `sampling::sample` over `recent` (in order, a repeated token is penalised again,

@@ -135,6 +135,13 @@ class ResidentModel {
     gpu_.check(fc_model_feed(h_, stream, token, nullptr, &a));
     return a;
   }
+  // `steps` greedy steps chained on the device: step 0 feeds `token`, every further step the previous pick
+  // (the greedy branch of generate_with, engine/mod.rs:L230-L240, without a host round trip per token).
+  std::vector<int32_t> decode_greedy(int32_t token, uint32_t steps, uint32_t stream = 0) {
+    std::vector<int32_t> out(steps);
+    gpu_.check(fc_model_decode_greedy(h_, 1, &stream, &token, steps, out.data()));
+    return out;
+  }
   // The candidates sampling::sample keeps for top_k = k (ferrum_model/src/sampling.rs:L44-L66) from the
   // logits row of the last decode step, selected on the device: (token, penalised logit) pairs in its order.
   std::vector<std::pair<int32_t, float>> topk(uint32_t k, uint32_t row = 0, float repetition_penalty = 1.0f,

@@ -325,3 +325,39 @@ def test_greedy_pick_over_a_long_row_keeps_the_first_maximum(dev):
                 assert am[s] == orc.argmax(lg[s]) and am[s] < 10000, (streams, step, s)
                 assert np.array_equal(lg[s][:10000], lg[s][10000:])
         g.close()
+
+
+@pytest.mark.parametrize("streams", [1, 3, 12])
+def test_chained_greedy_decode_returns_the_picks_of_step_by_step_decode(dev, streams):
+    """`decode_greedy` chains the steps on the device (the picks of one step are the tokens of the next, no host
+    round trip): the same tokens, positions and cache as feeding step by step, and decode can continue either
+    way afterwards."""
+    from ferrum_gpu_b200.hostmodel import LlamaConfig
+    cfg = LlamaConfig(vocab=200, ctx=40, dim=128, heads=2, kv_heads=1, head_dim=64, layers=2, hidden=256, rope_dim=64,
+                      rope_base=1e6, rope_type=_ffi.FC_ROPE_NEOX, eps=1e-6)
+    m = random_llama(cfg, seed=4, biases=True, std=0.3, gain_jitter=0.1)
+    a = CudaLlama(dev, m, QKind.Q8_0, max_streams=streams)
+    b = CudaLlama(dev, m, QKind.Q8_0, max_streams=streams)
+    first = random_tokens(3, streams, cfg.vocab)
+    for s in range(streams):  # different context lengths per stream
+        pre = random_tokens(10 + s, 2 + s % 3, cfg.vocab)
+        a.prefill(pre, stream=s)
+        b.prefill(pre, stream=s)
+    want, tok = [], first
+    for _ in range(9):
+        tok, _ = a.feed_batch(tok)
+        want.append(tok.copy())
+    got = b.decode_greedy(first, 9)
+    assert np.array_equal(got, np.stack(want))
+    assert all(a.pos(s) == b.pos(s) for s in range(streams))
+    # continue: one more chained call of two steps against two single steps
+    t1, _ = a.feed_batch(want[-1])
+    t2, _ = a.feed_batch(t1)
+    assert np.array_equal(b.decode_greedy(got[-1], 2), np.stack([t1, t2]))
+    one = b.decode_greedy(t2, 1)
+    t3, _ = a.feed_batch(t2)
+    assert np.array_equal(one[0], t3)
+    with pytest.raises(CudaError, match="context"):
+        b.decode_greedy(t3, cfg.ctx)
+    a.close()
+    b.close()
