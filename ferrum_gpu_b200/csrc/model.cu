@@ -63,6 +63,7 @@ void model_free(FcModel* m) {
   for (cudaGraphExec_t g : m->graphs)
     if (g) cudaGraphExecDestroy(g);
   if (m->pin_dec) cudaFreeHost(m->pin_dec);
+  if (m->score_stage) cudaFree(m->score_stage);
   for (auto& l : m->layers) {
     qweight_free(l.qkv.w);
     qweight_free(l.wo.w);
@@ -136,7 +137,7 @@ int alloc_common(FcModel* m) {
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_streams));
   FC_TRY(dev_alloc(m, (size_t)s * 4, (void**)&m->d_argmax));
   FC_TRY(dev_alloc(m, (size_t)m->ctx * s * 4, (void**)&m->d_chain_log));
-  FC_TRY(dev_alloc(m, 16, (void**)&m->d_chain_cnt));
+  FC_TRY(dev_alloc(m, (size_t)s * 4 + 16, (void**)&m->d_chain_cnt));
   FC_TRY(dev_alloc(m, argmax_scratch_bytes(s), &m->argmax_scratch));
   FC_CUDA(m->dev, cudaMemsetAsync(m->argmax_scratch, 0, argmax_scratch_bytes(s), m->dev->stream));
   // partial results of the context-split decode attention: the largest need over every batch width
@@ -194,10 +195,10 @@ static void norm_before(const FcModel* m, Epilogue& e, const float* g, const flo
 
 int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32_t* positions, const int32_t* streams,
                   uint32_t rows, AttnMode mode, uint32_t n_seqs, uint32_t t, uint32_t start, int32_t stream,
-                  bool final_norm, DeferredReduce* tail = nullptr) {
+                  bool final_norm, DeferredReduce* tail = nullptr, bool embedded = false) {
   FcDevice* dev = m->dev;
   const uint32_t d = m->dim;
-  FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, b.x));
+  if (!embedded) FC_TRY(k_embed(dev, m->tok, m->pos_table, ids, positions, rows, d, b.x)); // (else b.x holds the rows)
   // The two products that write the residual stream (wo, ff2) may leave their split-K sum to the norm
   // launch of the product that reads it next: `pend` is that unfinished sum, consumed (or finished on
   // its own) by the very next k_qlinear_f32.
@@ -657,6 +658,53 @@ __global__ void chain_advance_kernel(const int32_t* __restrict__ argmax, int32_t
   if (r == 0) *cnt = step + 1;
 }
 
+// The link for vocabularies one CTA scans quickly: it also takes the pick itself (first maximum, NaN never
+// wins - the rule of argmax_kernel) from the previous step's logits and writes the embedding row, which
+// saves the argmax and the embedding launch of every chained step. One CTA per row, one counter per row.
+__global__ void __launch_bounds__(256)
+    chain_link_kernel(const float* __restrict__ logits, uint32_t vocab, const float* __restrict__ tok_table,
+                      const float* __restrict__ pos_table, uint32_t d, int32_t* __restrict__ argmax, int32_t* __restrict__ ids,
+                      int32_t* __restrict__ pos, int32_t* __restrict__ log, uint32_t* __restrict__ cnt, uint32_t n,
+                      float* __restrict__ x) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  __shared__ int s_tok, s_pos;
+  const uint32_t r = blockIdx.x;
+  const float* row = logits + (size_t)r * vocab;
+  float best = -INFINITY;
+  int idx = 0x7fffffff;
+  for (uint32_t i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best) best = v, idx = (int)i;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > best || (ov == best && oi < idx)) best = ov, idx = oi;
+  }
+  if (lane == 0) bv[warp] = best, bi[warp] = idx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; w++)
+      if (bv[w] > best || (bv[w] == best && bi[w] < idx)) best = bv[w], idx = bi[w];
+    const int tok = idx == 0x7fffffff ? 0 : idx;
+    const uint32_t step = cnt[r];
+    cnt[r] = step + 1;
+    argmax[r] = tok;
+    ids[r] = tok;
+    s_pos = pos[r] + 1;
+    pos[r] = s_pos;
+    log[(size_t)step * n + r] = tok;
+    s_tok = tok;
+  }
+  __syncthreads();
+  const float* src = tok_table + (size_t)s_tok * d;
+  const float* ps = pos_table ? pos_table + (size_t)s_pos * d : nullptr;
+  for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) x[(size_t)r * d + i] = ps ? src[i] + ps[i] : src[i];
+}
+
 FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream_ids, const int32_t* first_tokens, uint32_t steps,
                                   int32_t* tokens_out) {
   if (!m || !stream_ids || !first_tokens || !tokens_out) return FC_ERR_ARG;
@@ -681,25 +729,31 @@ FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream
   // Steps 1 .. steps-1 run back to back on the device: d_ids / d_pos / d_streams still hold step 0's rows and
   // d_argmax its picks; each further step starts with the link kernel instead of host copies, and the host
   // waits once at the end.
+  const bool fused_link = m->vocab <= 8192; // the link scans the logits row itself
   auto enqueue_link = [&]() -> int {
-    FC_LAUNCH(dev, "chain_advance",
-              chain_advance_kernel<<<1, 1024, 0, dev->stream>>>(m->d_argmax, m->d_ids, m->d_pos, m->d_chain_log, m->d_chain_cnt, n));
+    if (fused_link)
+      FC_LAUNCH(dev, "chain_link",
+                chain_link_kernel<<<n, 256, 0, dev->stream>>>(m->logits, m->vocab, m->tok, m->pos_table, m->dim, m->d_argmax, m->d_ids,
+                                                              m->d_pos, m->d_chain_log, m->d_chain_cnt, n, m->x));
+    else
+      FC_LAUNCH(dev, "chain_advance",
+                chain_advance_kernel<<<1, 1024, 0, dev->stream>>>(m->d_argmax, m->d_ids, m->d_pos, m->d_chain_log, m->d_chain_cnt, n));
     PassBufs b{m->x, m->h, m->qkv, m->attn, m->ff, m->act};
     DeferredReduce tail;
-    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false, &tail));
+    FC_TRY(run_stack_f32(m, b, m->d_ids, m->d_pos, m->d_streams, n, ATTN_DECODE, 0, 0, 0, 0, false, &tail, fused_link));
     Epilogue e_head;
     e_head.scratch = m->mma_scratch;
     e_head.pending = &tail;
     norm_before(m, e_head, m->normf_g, m->normf_b, m->h);
     FC_TRY(k_qlinear_f32(dev, m->head_view, m->x, n, m->logits, e_head));
-    FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax, m->argmax_scratch));
+    if (!fused_link) FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax, m->argmax_scratch));
     return FC_OK;
   };
   if (m->chain_graphs.size() <= n) {
     m->chain_graphs.resize(n + 1, nullptr);
     m->chain_launches.resize(n + 1, 0);
   }
-  FC_CUDA(dev, cudaMemsetAsync(m->d_chain_cnt, 0, 4, dev->stream));
+  FC_CUDA(dev, cudaMemsetAsync(m->d_chain_cnt, 0, (size_t)m->max_streams * 4, dev->stream));
   uint32_t done = 1;
   if (!m->chain_graphs[n]) {
     const uint64_t l0 = dev->launches;
@@ -726,6 +780,7 @@ FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream
     dev->launches += m->chain_launches[n];
   }
   // the log holds the tokens the links consumed: the picks of steps 0 .. steps-2; the last picks are in d_argmax
+  if (fused_link) FC_TRY(k_argmax(dev, m->logits, n, m->vocab, m->d_argmax, m->argmax_scratch)); // (of the last step)
   if (steps > 2)
     FC_CUDA(dev, cudaMemcpyAsync(tokens_out + n, m->d_chain_log + n, (size_t)(steps - 2) * n * 4, cudaMemcpyDeviceToHost, dev->stream));
   FC_CUDA(dev, cudaMemcpyAsync(tokens_out + (size_t)(steps - 1) * n, m->d_argmax, (size_t)n * 4, cudaMemcpyDeviceToHost, dev->stream));
@@ -857,25 +912,26 @@ FC_API int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint3
   if (n_seqs == 0) return FC_OK;
   FC_TRY(check_ids(m, ids, (size_t)n_seqs * seq_len));
   const size_t rows = (size_t)n_seqs * (seq_len - 1);
-  int32_t* d_ids = nullptr;
-  float* d_lp = nullptr;
-  uint8_t* d_gr = nullptr;
-  double* d_nll = nullptr;
-  auto cleanup = [&]() {
-    if (d_ids) cudaFree(d_ids);
-    if (d_lp) cudaFree(d_lp);
-    if (d_gr) cudaFree(d_gr);
-    if (d_nll) cudaFree(d_nll);
-  };
-  cudaError_t e = cudaMalloc((void**)&d_ids, (size_t)n_seqs * seq_len * 4);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&d_lp, rows * 4);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&d_gr, rows);
-  if (e == cudaSuccess) e = cudaMalloc((void**)&d_nll, (size_t)n_seqs * 8);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    cleanup();
-    return fc_fail(dev, FC_ERR_OOM, "cannot allocate scoring buffers: %s", cudaGetErrorString(e));
+  auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t b_ids = al((size_t)n_seqs * seq_len * 4), b_lp = al(rows * 4), b_gr = al(rows), b_nll = al((size_t)n_seqs * 8);
+  const size_t need = b_ids + b_lp + b_gr + b_nll;
+  if (need > m->score_stage_bytes) {
+    FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    if (m->score_stage) cudaFree(m->score_stage);
+    m->score_stage = nullptr;
+    m->score_stage_bytes = 0;
+    const cudaError_t e = cudaMalloc(&m->score_stage, need);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fc_fail(dev, FC_ERR_OOM, "cannot allocate scoring buffers: %s", cudaGetErrorString(e));
+    }
+    m->score_stage_bytes = need;
   }
+  uint8_t* base = (uint8_t*)m->score_stage;
+  int32_t* d_ids = (int32_t*)base;
+  float* d_lp = (float*)(base + b_ids);
+  uint8_t* d_gr = base + b_ids + b_lp;
+  double* d_nll = (double*)(base + b_ids + b_lp + b_gr);
   int rc = FC_OK;
   if (cudaMemcpyAsync(d_ids, ids, (size_t)n_seqs * seq_len * 4, cudaMemcpyHostToDevice, dev->stream) != cudaSuccess)
     rc = fc_fail(dev, FC_ERR_DEVICE, "upload of ids failed");
@@ -890,6 +946,5 @@ FC_API int fc_model_score(FcModel* m, const int32_t* ids, uint32_t n_seqs, uint3
       rc = fc_fail(dev, FC_ERR_DEVICE, "scoring failed: %s", cudaGetErrorString(cudaGetLastError()));
     }
   }
-  cleanup();
   return rc;
 }

@@ -58,6 +58,10 @@ struct FcModel {
   std::vector<uint64_t> graph_launches;
   std::vector<uint8_t> graph_warm;
   bool graph_ok = true;
+  // device staging of fc_model_score's host buffers (ids up; log-probs, flags, sums down): kept between
+  // calls and grown on demand - an allocation and a free per call cost more than the copies on some hosts
+  void* score_stage = nullptr;
+  size_t score_stage_bytes = 0;
   // chained greedy decode (fc_model_decode_greedy): the step that takes its tokens from the previous step's
   // argmax on the device, one graph per batch width; the tokens it consumed, in order; how many steps so far
   std::vector<cudaGraphExec_t> chain_graphs;

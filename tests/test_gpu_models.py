@@ -327,13 +327,14 @@ def test_greedy_pick_over_a_long_row_keeps_the_first_maximum(dev):
         g.close()
 
 
+@pytest.mark.parametrize("vocab", [200, 9000])  # (the link takes the pick itself up to 8192 entries)
 @pytest.mark.parametrize("streams", [1, 3, 12])
-def test_chained_greedy_decode_returns_the_picks_of_step_by_step_decode(dev, streams):
+def test_chained_greedy_decode_returns_the_picks_of_step_by_step_decode(dev, streams, vocab):
     """`decode_greedy` chains the steps on the device (the picks of one step are the tokens of the next, no host
     round trip): the same tokens, positions and cache as feeding step by step, and decode can continue either
     way afterwards."""
     from ferrum_gpu_b200.hostmodel import LlamaConfig
-    cfg = LlamaConfig(vocab=200, ctx=40, dim=128, heads=2, kv_heads=1, head_dim=64, layers=2, hidden=256, rope_dim=64,
+    cfg = LlamaConfig(vocab=vocab, ctx=40, dim=128, heads=2, kv_heads=1, head_dim=64, layers=2, hidden=256, rope_dim=64,
                       rope_base=1e6, rope_type=_ffi.FC_ROPE_NEOX, eps=1e-6)
     m = random_llama(cfg, seed=4, biases=True, std=0.3, gain_jitter=0.1)
     a = CudaLlama(dev, m, QKind.Q8_0, max_streams=streams)
