@@ -222,14 +222,18 @@ __device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a
   }
 }
 
-// smem: [2 buffers][hi, lo][MP rows][XSTRIDE halves]
+// smem: [2 buffers][hi, lo][MP rows][128 halves]. A lane reads the 16 bytes of x it multiplies with one block
+// in one load; the 16-byte chunk index of odd rows is XORed with 4, so that the two rows a quarter-warp reads
+// lie in different halves of the banks (unpadded rows 256 bytes apart would all start on bank 0; with 8-byte
+// loads and rows padded by 32 bytes half of all shared-memory wavefronts of the kernel were bank conflicts).
 template <int KIND, int NB>
 __global__ void __launch_bounds__(128)
     qmatvec_mma_kernel(QMat w, const __half* __restrict__ xh, const __half* __restrict__ xl, uint32_t m, float* __restrict__ y,
                        float* __restrict__ partial, uint32_t blocks_per_split, Epilogue ep) {
   extern __shared__ __align__(16) __half xs[];
   constexpr int MP = NB * 8;
-  constexpr int PART = MP * XSTRIDE;  // halves of one part of one buffer
+  constexpr int XROW = XS;            // halves per staged row
+  constexpr int PART = MP * XROW;     // halves of one part of one buffer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const uint32_t n = w.n, k = w.k, nblocks = k / QK;
   const uint32_t row0 = blockIdx.x * ROWS_PER_CTA + warp * 16;
@@ -246,7 +250,7 @@ __global__ void __launch_bounds__(128)
       const uint32_t kk = k0 + ch * 8;
       if (kk < kb_end * QK) {
         const __half* src = (part ? xl : xh) + (size_t)r * k + kk;
-        cp_async16(smem_u32(xs + (size_t)buf * 2 * PART + part * PART + r * XSTRIDE + ch * 8), src);
+        cp_async16(smem_u32(xs + (size_t)buf * 2 * PART + part * PART + r * XROW + ((ch ^ ((r & 1) << 2)) * 8)), src);
       }
     }
   };
@@ -284,14 +288,13 @@ __global__ void __launch_bounds__(128)
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
         float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const uint32_t off = (nb * 8 + g) * XSTRIDE + bi * QK + 8 * t;
-#pragma unroll
-        for (int s = 0; s < 2; s++) {
-          const uint2 bh = *reinterpret_cast<const uint2*>(xhb + off + 4 * s);
-          const uint2 bl = *reinterpret_cast<const uint2*>(xlb + off + 4 * s);
-          mma_16816(c, a[s], bh.x, bh.y);
-          mma_16816(c, a[s], bl.x, bl.y);
-        }
+        const uint32_t off = (nb * 8 + g) * XROW + (((bi * 4 + t) ^ ((g & 1) << 2)) * 8);
+        const uint4 bh = *reinterpret_cast<const uint4*>(xhb + off);
+        const uint4 bl = *reinterpret_cast<const uint4*>(xlb + off);
+        mma_16816(c, a[0], bh.x, bh.y);
+        mma_16816(c, a[0], bl.x, bl.y);
+        mma_16816(c, a[1], bh.z, bh.w);
+        mma_16816(c, a[1], bl.z, bl.w);
         acc[nb][0] = fmaf(dg, c[0], acc[nb][0]);
         acc[nb][1] = fmaf(dg, c[1], acc[nb][1]);
         acc[nb][2] = fmaf(dg8, c[2], acc[nb][2]);
@@ -529,7 +532,7 @@ template <int KIND, int NB>
 int launch(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, uint32_t m, float* y, float* partial,
            uint32_t splits, uint32_t bps, const Epilogue& ep) {
   auto kern = qmatvec_mma_kernel<KIND, NB>;
-  const size_t smem = (size_t)2 * 2 * NB * 8 * XSTRIDE * sizeof(__half);
+  const size_t smem = (size_t)2 * 2 * NB * 8 * XS * sizeof(__half);
   static OncePerDevice attr;
   if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

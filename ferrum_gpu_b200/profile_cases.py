@@ -104,6 +104,17 @@ def decode(dev):
     g.close()
 
 
+def head64(dev):
+    """The vocabulary-head product of the 64-stream decode configuration: 64 rows of x against
+    151 936 x 1024 Q8_0 weights on the mma.sync decode kernel."""
+    k, n, m = 1024, 151936, 64
+    qw = upload_quantised(dev, QKind.Q8_0, _weights(k, n), k, n)
+    x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
+    for _ in range(3):
+        linear_q(dev, x, qw, m)
+    qw.close()
+
+
 def decode64(dev):
     """Four layers and the 151936-row head of the 64-stream decode configuration at 1500 cached positions:
     the per-launch times of one step (the full model repeats the layer launches 24 times)."""
@@ -118,7 +129,7 @@ def decode64(dev):
     g.close()
 
 
-CASES = {"gemm": gemm, "head": head, "matvec": matvec, "matvec8": matvec8, "decode": decode, "decode64": decode64, "score": score, "chunk": chunk,
+CASES = {"gemm": gemm, "head": head, "matvec": matvec, "matvec8": matvec8, "decode": decode, "decode64": decode64, "head64": head64, "score": score, "chunk": chunk,
          "attention": attention}
 
 if __name__ == "__main__":
