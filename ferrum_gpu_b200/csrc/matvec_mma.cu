@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(128)
         const float2 back = __half22float2(hi[i]);
         lo[i] = __floats2half2_rn(c0 - back.x, c1 - back.y);
       }
-      __half* dst = xs + (size_t)(sl & 1) * 2 * PART + xr * XSTRIDE + xk;
+      // (rows of 128 halves, the 16-byte chunk index of odd rows XORed with 4: see qmatvec_mma_kernel)
+      __half* dst = xs + (size_t)(sl & 1) * 2 * PART + xr * XS + (((xk >> 3) ^ ((xr & 1) << 2)) << 3);
       *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(hi);
       *reinterpret_cast<uint4*>(dst + PART) = *reinterpret_cast<const uint4*>(lo);
     }
@@ -483,14 +484,13 @@ __global__ void __launch_bounds__(128)
       const float dg = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(sst[r0 * 4 + bi]);
       const float dg8 = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(sst[r1 * 4 + bi]);
       float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      const uint32_t off = g * XSTRIDE + bi * QK + 8 * t;
-#pragma unroll
-      for (int s = 0; s < 2; s++) {
-        const uint2 bh = *reinterpret_cast<const uint2*>(xhb + off + 4 * s);
-        const uint2 bl = *reinterpret_cast<const uint2*>(xlb + off + 4 * s);
-        mma_16816(c, a[s], bh.x, bh.y);
-        mma_16816(c, a[s], bl.x, bl.y);
-      }
+      const uint32_t off = g * XS + (((bi * 4 + t) ^ ((g & 1) << 2)) * 8);
+      const uint4 bh = *reinterpret_cast<const uint4*>(xhb + off);
+      const uint4 bl = *reinterpret_cast<const uint4*>(xlb + off);
+      mma_16816(c, a[0], bh.x, bh.y);
+      mma_16816(c, a[0], bl.x, bl.y);
+      mma_16816(c, a[1], bh.z, bh.w);
+      mma_16816(c, a[1], bl.z, bl.w);
       acc[0] = fmaf(dg, c[0], acc[0]);
       acc[1] = fmaf(dg, c[1], acc[1]);
       acc[2] = fmaf(dg8, c[2], acc[2]);
