@@ -29,6 +29,7 @@ struct FcDevice {
   void* pinned = nullptr;  // pinned host staging for results and small inputs
   size_t pinned_bytes = 0;
   int* d_flag = nullptr;   // device int for kernels that report a status
+  int matvec_choice = 0;   // fc_debug_matvec_kernel: which kernel multiplies 1..8 rows (0: the library's rule)
   // per-kernel timing (off by default): one event pair per launch, summed by name on report
   bool profiling = false;
   struct ProfSpan {
@@ -244,6 +245,9 @@ int k_export_blocks(FcDevice* dev, const QMat& m, uint8_t* blocks_dev);
 int k_dequant(FcDevice* dev, const QMat& m, float* out_nk_dev);
 // matvec.cu: m <= 8 rows
 int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
+// matvec1.cu: one row of a block format, streamed through shared memory onto mma.sync
+bool qmatvec1_supports(const FcDevice* dev, const QMat& w);
+int k_qmatvec1(FcDevice* dev, const QMat& w, const float* x, float* y, const Epilogue& ep);
 // gemm_f32.cu: any m
 int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
 // The exact-f32 product of any m: picks matvec or tiled GEMM.

@@ -8,9 +8,6 @@
 // memory) is read once and reused for the R rows. Integer quants are turned into floats with
 // bit tricks (no I2F), the per-block f16 scale multiplies the block's partial sum, accumulation
 // is f32, and the LPR partial sums are combined with warp shuffles.
-#include <cstdlib>
-#include <cstring>
-
 #include "common.cuh"
 #include "ops.cuh"
 
@@ -390,18 +387,23 @@ int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y
 //     grow with the rows, the FMA kernel's does (8 rows of K = 4096, N = 32000 Q4_0: 74 us against 540);
 //   - one row: the f32 FMA matvec (49 us against 71 on that matrix); 1..8 rows without scratch or of
 //     another kind likewise; everything else: the tiled f32 product.
-// FERRUM_CUDA_MATVEC=fma|mma overrides the choice for 1..8 rows (measurement aid).
+//   - one row of a block format whose width the streamed kernel takes (matvec1.cu): that kernel.
+// fc_debug_matvec_kernel overrides the choice for 1..8 rows (measurement aid).
 bool qlinear_takes_wide_mma(const QMat& w, uint32_t m, const void* scratch) {
   return scratch && m > 8 && qmatvec_mma_supports(w, m); // (x lives in the library's own aligned buffers there)
 }
 
 int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep_in) {
   if (m == 0) return FC_OK;
-  static const int forced = [] {
-    const char* e = getenv("FERRUM_CUDA_MATVEC");
-    return !e ? 0 : !strcmp(e, "fma") ? 1 : !strcmp(e, "mma") ? 2 : 0;
-  }();
+  const int forced = dev->matvec_choice; // 0: the rule above; 1: FMA kernel; 2: small-batch mma.sync kernel
   Epilogue ep = ep_in;
+  if (m == 1 && forced == 0 && qmatvec1_supports(dev, w)) {
+    if (ep.pending && ep.pending->splits) FC_TRY(k_flush_deferred(dev, *ep.pending));
+    ep.pending = nullptr;
+    ep.defer_out = nullptr;
+    if (ep.presplit) return fc_fail(dev, FC_ERR_ARG, "a pre-split x needs the 9..64-row tensor-core product");
+    return k_qmatvec1(dev, w, x, y, ep);
+  }
   const bool fma_ok = m <= 8 && (size_t)m * w.k * 4 <= 200 * 1024 && w.k % 4 == 0;
   // (the tensor-core kernels stage x with 16-byte asynchronous copies)
   const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0 || ep.presplit);

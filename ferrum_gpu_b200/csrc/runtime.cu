@@ -155,6 +155,12 @@ FC_API int fc_debug_fail_after(FcDevice* dev, int64_t n_launches) {
   return FC_OK;
 }
 
+FC_API int fc_debug_matvec_kernel(FcDevice* dev, int choice) {
+  if (!dev || choice < 0 || choice > 2) return FC_ERR_ARG;
+  dev->matvec_choice = choice;
+  return FC_OK;
+}
+
 FC_API int fc_debug_profile(FcDevice* dev, int enable) {
   if (!dev) return FC_ERR_ARG;
   cudaSetDevice(dev->ordinal);

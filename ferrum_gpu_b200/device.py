@@ -83,6 +83,10 @@ class Device:
         """Bracket every launch with CUDA events (per-kernel timing); off by default."""
         self.check(self._lib.fc_debug_profile(self._h, 1 if enable else 0))
 
+    def matvec_kernel(self, choice: int):
+        """Measurement hook: 0 = the library's rule, 1 = f32 FMA kernel, 2 = small-batch mma.sync kernel (1..8 rows)."""
+        self.check(self._lib.fc_debug_matvec_kernel(self._h, int(choice)))
+
     def profile_report(self) -> dict:
         """{kernel: {"launches": n, "ms": total}} since the last report; synchronises."""
         buf = C.create_string_buffer(1 << 16)

@@ -93,6 +93,11 @@ uint64_t fc_device_launch_count(FcDevice* dev);
  * further launch is refused with FC_ERR_INJECTED *before it reaches the device*; a negative
  * value disarms the hook. No GPU fault is ever produced. */
 int fc_debug_fail_after(FcDevice* dev, int64_t n_launches);
+/* Which kernel multiplies 1..8 rows of x by a packed matrix in exact-f32 mode: 0 = the library's own rule
+ * (one row of a block format: the streamed tensor-core kernel; 2..8 rows: the small-batch mma.sync kernel),
+ * 1 = the f32 FMA kernel, 2 = the small-batch mma.sync kernel. Measurement hook; results stay within the
+ * exact path's tolerance whichever runs. */
+int fc_debug_matvec_kernel(FcDevice* dev, int choice);
 /* Per-kernel device timing, the counterpart of the reference's one-kernel-at-a-time profiler
  * (ferrum_wgpu/benches/profile_train.rs:L15-L25): while enabled every launch is bracketed by a pair
  * of CUDA events on the device's stream. The report is a JSON object
