@@ -92,6 +92,9 @@ EXPORTS = (
     "fc_model_feed_batch", "fc_model_decode_greedy", "fc_model_topk", "fc_topk_dev", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
     "fc_model_score_dev", "fc_model_set_head_shard", "fc_model_trunk_dev",
     "fc_model_head_partial_dev", "fc_score_combine_dev",
+    "fc_model_score_ragged", "fc_score_windows", "fc_model_token_logprobs",
+    "fc_group_sequences", "fc_group_unique_id", "fc_group_create", "fc_group_destroy", "fc_group_score",
+    "fc_group_last_exchange_ms",
 )
 
 LIB_NAME = "libferrum_cuda.so"
@@ -162,6 +165,15 @@ def load() -> C.CDLL:
         "fc_model_trunk_dev": (C.c_int, [vp, vp, u32, u32, C.c_int, vp]),
         "fc_model_head_partial_dev": (C.c_int, [vp, vp, vp, u32, C.c_int, vp]),
         "fc_score_combine_dev": (C.c_int, [vp, vp, u32, vp, u32, u32, vp, vp, vp]),
+        "fc_model_score_ragged": (C.c_int, [vp, vp, vp, u32, C.c_int, vp, vp, vp]),
+        "fc_score_windows": (u32, [u32, u32, u32, vp, vp, vp, u32]),
+        "fc_model_token_logprobs": (C.c_int, [vp, vp, vp, vp, u32, C.c_int, vp, vp, vp]),
+        "fc_group_sequences": (u32, [u32, u32, u32, vp, u32]),
+        "fc_group_unique_id": (C.c_int, [vp, sz]),
+        "fc_group_create": (C.c_int, [vp, vp, u32, u32, u32, vp, sz, P(vp)]),
+        "fc_group_destroy": (C.c_int, [vp]),
+        "fc_group_score": (C.c_int, [vp, vp, u32, u32, C.c_int, vp]),
+        "fc_group_last_exchange_ms": (C.c_int, [vp, vp]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

@@ -55,7 +55,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 if verbose and out:
                     print(out)
     if force or jobs or _stale(OUT, objs):
-        run([NVCC] + ARCH + ["-shared", "-o", OUT] + objs + ["-lcudart"])
+        run([NVCC] + ARCH + ["-shared", "-o", OUT] + objs + ["-lcudart", "-ldl"])
     return OUT
 
 

@@ -123,6 +123,40 @@ class ResidentModel:
                                                 gr.ctypes.data, nll.ctypes.data))
         return lp, gr.astype(bool), nll
 
+    def score_ragged(self, seqs, mode: Mode = Mode.EXACT_F32):
+        """Scores sequences of different lengths in batched passes (the server's concurrent requests,
+        serving/routes.rs:L301-L309): per sequence (logprob[len-1], greedy[len-1]) as `score` gives them, and the
+        f64 NLL sums `[n]`."""
+        seqs = [_i32(s).reshape(-1) for s in seqs]
+        offsets = np.zeros(len(seqs) + 1, dtype=np.uint32)
+        offsets[1:] = np.cumsum([s.size for s in seqs])
+        flat = np.concatenate(seqs) if seqs else np.zeros(0, dtype=np.int32)
+        n_out = max(int(offsets[-1]) - len(seqs), 0)
+        lp = np.empty(n_out, dtype=np.float32)
+        gr = np.empty(n_out, dtype=np.uint8)
+        nll = np.empty(len(seqs), dtype=np.float64)
+        self.dev.check(self._lib.fc_model_score_ragged(self._h, flat.ctypes.data, offsets.ctypes.data, len(seqs), int(mode),
+                                                       lp.ctypes.data, gr.ctypes.data, nll.ctypes.data))
+        cut = (offsets - np.arange(len(seqs) + 1, dtype=np.uint32)).astype(np.int64)
+        return ([lp[cut[i]:cut[i + 1]] for i in range(len(seqs))],
+                [gr[cut[i]:cut[i + 1]].astype(bool) for i in range(len(seqs))], nll)
+
+    def token_logprobs(self, streams, from_=None, mode: Mode = Mode.EXACT_F32):
+        """`serving::score::token_logprobs` (serving/score.rs:L27-L49) for several id streams at once, every
+        window of every stream in one ragged batch: [(logprob f64, n_tokens, greedy)] per stream."""
+        streams = [_i32(s).reshape(-1) for s in streams]
+        offsets = np.zeros(len(streams) + 1, dtype=np.uint32)
+        offsets[1:] = np.cumsum([s.size for s in streams])
+        flat = np.concatenate(streams) if streams else np.zeros(0, dtype=np.int32)
+        frm = None if from_ is None else np.ascontiguousarray(from_, dtype=np.uint32)
+        lp = np.empty(len(streams), dtype=np.float64)
+        nt = np.empty(len(streams), dtype=np.uint64)
+        gr = np.empty(len(streams), dtype=np.uint8)
+        self.dev.check(self._lib.fc_model_token_logprobs(self._h, flat.ctypes.data, offsets.ctypes.data,
+                                                         None if frm is None else frm.ctypes.data, len(streams),
+                                                         int(mode), lp.ctypes.data, nt.ctypes.data, gr.ctypes.data))
+        return [(float(lp[i]), int(nt[i]), bool(gr[i])) for i in range(len(streams))]
+
     # -- device-pointer variants (benchmark, multi-GPU) -----------------------------------------
     def score_dev(self, ids_ptr: int, n_seqs: int, seq_len: int, mode: Mode, logprob_ptr: int, greedy_ptr: int,
                   nll_ptr: int):

@@ -67,6 +67,7 @@ enum { FC_EXACT_F32 = 0, FC_TENSOR_F16 = 1 };
 typedef struct FcDevice FcDevice;
 typedef struct FcQWeight FcQWeight;
 typedef struct FcModel FcModel;
+typedef struct FcGroup FcGroup;
 
 /* ---- device ------------------------------------------------------------------------------ */
 /* Replaces ferrum_wgpu::device::Gpu::open / GpuBackend::open (device/mod.rs:L98-L176,
@@ -315,6 +316,55 @@ int fc_model_head_partial_dev(FcModel* m, const void* hidden_dev, const int32_t*
 int fc_score_combine_dev(FcDevice* dev, const float* partials_dev, uint32_t n_shards,
                          const int32_t* targets_dev, uint32_t n_seqs, uint32_t rows_per_seq,
                          float* logprob_dev, uint8_t* greedy_dev, double* nll_sum_dev);
+
+/* ---- scoring callers: unequal lengths and sliding windows ------------------------------------ */
+/* Score `n_seqs` sequences of different lengths in batched passes (new: the server scores its concurrent
+ * requests one after another, ferrum_gpu_core/src/serving/routes.rs:L301-L309, limits.rs:L32). Sequence s is
+ * ids[offsets[s] .. offsets[s + 1]) (2 .. ctx + 1 ids; `offsets` has n_seqs + 1 entries). Per sequence the
+ * results are those of fc_model_score on it alone; they are packed: sequence s owns entries
+ * offsets[s] - s .. offsets[s + 1] - (s + 1) of `logprob_out` / `greedy_out` (nullable), and
+ * `nll_sum_out[s]` (nullable) is its -sum of log-probabilities in f64, ascending position. */
+int fc_model_score_ragged(FcModel* m, const int32_t* ids, const uint32_t* offsets, uint32_t n_seqs, int mode,
+                          float* logprob_out, uint8_t* greedy_out, double* nll_sum_out);
+/* The window partition of serving::score::token_logprobs (ferrum_gpu_core/src/serving/score.rs:L27-L49) for a
+ * stream of `n_ids` ids scored from target index `from` (clamped to 1) with a context of `ctx` positions:
+ * window w is ids[start[w] .. end[w]) (at most ctx + 1 ids) and contributes targets first[w] .. end[w]; every
+ * target is scored exactly once with at least half a context of history. Returns the number of windows and
+ * fills at most `cap` entries of each (nullable) array. Pure host arithmetic. */
+uint32_t fc_score_windows(uint32_t n_ids, uint32_t from, uint32_t ctx, uint32_t* start_out, uint32_t* end_out,
+                          uint32_t* first_out, uint32_t cap);
+/* token_logprobs for `n_streams` id streams at once: stream j is ids[offsets[j] .. offsets[j + 1]), scored
+ * from target index from[j] (`from` NULL = 1 everywhere). All windows of all streams go through one
+ * fc_model_score_ragged batch; `logprob_out[j]` is the f64 sum of log p over the stream's targets in ascending
+ * order, `n_tokens_out[j]` their count, `greedy_out[j]` 1 when every one was the first argmax
+ * (Score { logprob, n_tokens, greedy }, score.rs:L9-L17; a stream with nothing to score gives (0, 0, 1)). */
+int fc_model_token_logprobs(FcModel* m, const int32_t* ids, const uint32_t* offsets, const uint32_t* from,
+                            uint32_t n_streams, int mode, double* logprob_out, uint64_t* n_tokens_out,
+                            uint8_t* greedy_out);
+
+/* ---- groups of GPUs (multi-GPU scoring behind the ABI) ----------------------------------------
+ * A group is `world` ranks, each with its own open device and resident model, in one or several processes
+ * (one thread per rank inside a process). It owns its NCCL communicators; NCCL is loaded at run time
+ * (libnccl.so.2), so everything else in this header works without it. With `vocab_shards` == 1 every rank
+ * holds the whole head and scores sequences rank, rank + world, ...; with more, consecutive ranks form groups
+ * that split the head by vocabulary rows (Lin::Sharded's column blocks on different GPUs,
+ * ferrum_wgpu/src/models/llama/lin.rs:L41-L53,L76-L90) and exchange final hidden states and per-row
+ * (max, sum-exp, target logit, first argmax) partials through local HBM. */
+/* Sequences part, part + parts, ... below n_seqs (the rule both partitions use). Returns their count. */
+uint32_t fc_group_sequences(uint32_t n_seqs, uint32_t part, uint32_t parts, uint32_t* out, uint32_t cap);
+/* The rendezvous token (128 bytes): made by one rank, carried to the others by the caller. */
+int fc_group_unique_id(uint8_t* id_out, size_t id_bytes);
+/* Join the group as `rank` of `world`. Collective: every rank calls it with the same token. With
+ * vocab_shards > 1 the model's head is restricted to this rank's shard (fc_model_set_head_shard). */
+int fc_group_create(FcDevice* dev, FcModel* model, uint32_t rank, uint32_t world, uint32_t vocab_shards,
+                    const uint8_t* id, size_t id_bytes, FcGroup** out);
+int fc_group_destroy(FcGroup* g);
+/* Total NLL of each of `n_seqs` sequences of `seq_len` ids (host, the same array on every rank);
+ * `nll_sum_out[n_seqs]` is filled on every rank. Collective. */
+int fc_group_score(FcGroup* g, const int32_t* ids, uint32_t n_seqs, uint32_t seq_len, int mode, double* nll_sum_out);
+/* Device milliseconds of the last fc_group_score call's exchanges: [0] all-gather of hidden states, [1] of the
+ * partials (0 without a split head), [2] the all-reduce of the NLL sums. */
+int fc_group_last_exchange_ms(FcGroup* g, float* ms_out);
 
 #ifdef __cplusplus
 }

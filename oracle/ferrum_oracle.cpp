@@ -451,9 +451,76 @@ void matmul_rows(const float* a, const float* b, size_t rows, size_t k, size_t n
   }
 }
 
+// ferrum_ref/src/kernels/tuned.rs:L10-L134 (`matmul_tuned`): the reference's speed baseline. Output columns in
+// panels of NC, the contraction in panels of KC, a 4 x 8 register tile inside, plain loops on the edges; every
+// output element still sums k in ascending order, so the result is bit-identical to the simple kernel.
+constexpr size_t T_KC = 256, T_NC = 256, T_MR = 4, T_NR = 8;
+
+// tuned.rs:L75-L97 (`edge`): rows ia..ib, columns ja..jb, p in pp..p1
+void tuned_edge(const float* a, const float* b, size_t k, size_t n, size_t ia, size_t ib, size_t r0, size_t ja, size_t jb,
+                size_t pp, size_t p1, float* out) {
+  for (size_t i = ia; i < ib; i++)
+    for (size_t p = pp; p < p1; p++) {
+      const float av = a[i * k + p];
+      float* o = out + (i - r0) * n;
+      const float* brow = b + p * n;
+      for (size_t j = ja; j < jb; j++) o[j] += av * brow[j];
+    }
+}
+
+// tuned.rs:L44-L72 (`micro`): the register tile, loaded from and stored back to `out`
+void tuned_micro(const float* a, const float* b, size_t k, size_t n, size_t i, size_t r0, size_t j, size_t pp, size_t p1,
+                 float* out) {
+  float acc[T_MR][T_NR];
+  for (size_t r = 0; r < T_MR; r++) std::memcpy(acc[r], out + (i + r - r0) * n + j, sizeof acc[r]);
+  for (size_t p = pp; p < p1; p++) {
+    const float* bs = b + p * n + j;
+    for (size_t r = 0; r < T_MR; r++) {
+      const float av = a[(i + r) * k + p];
+      for (size_t c = 0; c < T_NR; c++) acc[r][c] += av * bs[c];
+    }
+  }
+  for (size_t r = 0; r < T_MR; r++) std::memcpy(out + (i + r - r0) * n + j, acc[r], sizeof acc[r]);
+}
+
+// tuned.rs:L16-L42 (`block`): rows r0..r1 into `out` (those rows, indexed locally, pre-zeroed)
+void tuned_block(const float* a, const float* b, size_t k, size_t n, size_t r0, size_t r1, float* out) {
+  for (size_t jj = 0; jj < n; jj += T_NC) {
+    const size_t j1 = std::min(jj + T_NC, n);
+    for (size_t pp = 0; pp < k; pp += T_KC) {
+      const size_t p1 = std::min(pp + T_KC, k);
+      size_t i = r0;
+      for (; i + T_MR <= r1; i += T_MR) {
+        size_t j = jj;
+        for (; j + T_NR <= j1; j += T_NR) tuned_micro(a, b, k, n, i, r0, j, pp, p1, out);
+        if (j < j1) tuned_edge(a, b, k, n, i, i + T_MR, r0, j, j1, pp, p1, out);
+      }
+      if (i < r1) tuned_edge(a, b, k, n, i, r1, r0, jj, j1, pp, p1, out);
+    }
+  }
+}
+
+// tuned.rs:L99-L134: rows split over scoped threads
+void matmul_tuned(const float* a, const float* b, size_t m, size_t k, size_t n, float* out, int threads) {
+  std::fill(out, out + m * n, 0.0f);
+  if (m == 0 || n == 0) return;
+  const size_t per = (m + (size_t)std::max(threads, 1) - 1) / (size_t)std::max(threads, 1);
+  std::vector<std::thread> pool;
+  for (size_t r0 = 0; r0 < m; r0 += per) {
+    const size_t r1 = std::min(r0 + per, m);
+    pool.emplace_back(tuned_block, a, b, k, n, r0, r1, out + r0 * n);
+  }
+  for (auto& t : pool) t.join();
+}
+
+// Which kernel the model passes multiply with: the simple one (what `--device cpu` runs,
+// ferrum_ref/src/models/llama/mod.rs:L177-L184) unless the all-cores baseline asks for the tuned one.
+bool g_use_tuned = false;
+
 // ferrum_ref/src/kernels/matmul.rs:L62-L69 (threads == 1) and L73-L94 (rows split over scoped
 // threads; bit-identical for any thread count because rows are independent)
 void matmul(const float* a, const float* b, size_t m, size_t k, size_t n, float* out, int threads) {
+  if (g_use_tuned) return matmul_tuned(a, b, m, k, n, out, threads);
   std::fill(out, out + m * n, 0.0f);
   if (m == 0 || n == 0) return;
   if (threads <= 1 || m == 1) {
@@ -717,7 +784,8 @@ std::vector<float> linear(const std::vector<float>& x, const std::vector<float>&
 
 // ferrum_ref/src/models/llama/mod.rs:L209-L259 (`run`): ids through the stack starting at the
 // cache length, appending keys and values; logits for every new row
-int llama_run(OrLlama& m, const int32_t* ids, size_t n, float* logits_out) {
+// (`last_only`: the head product for the last new row alone - rows are independent, so its logits are the same)
+int llama_run(OrLlama& m, const int32_t* ids, size_t n, float* logits_out, bool last_only = false) {
   const FcLlamaConfig& c = m.cfg;
   size_t d = c.dim, kvd = (size_t)c.kv_heads * c.head_dim, qd = (size_t)c.heads * c.head_dim;
   for (size_t i = 0; i < n; i++)
@@ -764,7 +832,10 @@ int llama_run(OrLlama& m, const int32_t* ids, size_t n, float* logits_out) {
     for (size_t i = 0; i < n * d; i++) x[i] = x[i] + f[i];
   }
   rmsnorm(x.data(), m.out_norm.data(), n, d, c.eps, h.data());
-  matmul(h.data(), m.head.data(), n, d, c.vocab, logits_out, m.threads);
+  if (last_only)
+    matmul(h.data() + (n - 1) * d, m.head.data(), 1, d, c.vocab, logits_out, 1);
+  else
+    matmul(h.data(), m.head.data(), n, d, c.vocab, logits_out, m.threads);
   return FC_OK;
 }
 
@@ -970,6 +1041,11 @@ OR_API void or_transpose(const float* data, size_t rows, size_t cols, float* out
 OR_API void or_matmul(const float* a, const float* b, size_t m, size_t k, size_t n, float* out, int threads) {
   matmul(a, b, m, k, n, out, threads);
 }
+OR_API void or_matmul_tuned(const float* a, const float* b, size_t m, size_t k, size_t n, float* out, int threads) {
+  matmul_tuned(a, b, m, k, n, out, threads);
+}
+// Every later product of the model passes on the tuned kernel (1) or the simple one (0); results are bit-identical.
+OR_API void or_set_tuned(int on) { g_use_tuned = on != 0; }
 OR_API void or_rand_vec(size_t len, uint64_t seed, float* out) { rand_vec(len, seed, out); }
 OR_API float or_gelu(float x) { return gelu(x); }
 OR_API float or_silu(float x) { return silu(x); }
@@ -1151,6 +1227,14 @@ OR_API int or_llama_extend(void* h, const int32_t* ids, uint32_t n, float* logit
   auto* m = (OrLlama*)h;
   if (or_llama_pos(h) + n > m->cfg.ctx) return FC_ERR_CONTEXT_FULL;
   return llama_run(*m, ids, n, logits_out);
+}
+
+// The same, returning the logits of the last new position only (a long prompt of a large-vocabulary model)
+OR_API int or_llama_extend_last(void* h, const int32_t* ids, uint32_t n, float* logits_last) {
+  auto* m = (OrLlama*)h;
+  if (n == 0) return FC_ERR_SHAPE;
+  if (or_llama_pos(h) + n > m->cfg.ctx) return FC_ERR_CONTEXT_FULL;
+  return llama_run(*m, ids, n, logits_last, true);
 }
 
 OR_API void* or_gpt2_create(const FcGpt2Config* cfg, const FcGpt2Weights* w, int threads) {

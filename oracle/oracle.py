@@ -51,6 +51,9 @@ def lib() -> C.CDLL:
         "or_pack_reference_layout": (C.c_int, [C.c_int, vp, sz, sz, vp]),
         "or_transpose": (None, [vp, sz, sz, vp]),
         "or_matmul": (None, [vp, vp, sz, sz, sz, vp, C.c_int]),
+        "or_matmul_tuned": (None, [vp, vp, sz, sz, sz, vp, C.c_int]),
+        "or_set_tuned": (None, [C.c_int]),
+        "or_llama_extend_last": (C.c_int, [vp, vp, u32, vp]),
         "or_rand_vec": (None, [sz, u64, vp]),
         "or_gelu": (f, [f]), "or_silu": (f, [f]),
         "or_layernorm": (None, [vp, vp, vp, sz, sz, vp]),
@@ -204,6 +207,19 @@ def matmul(a, b, m: int, k: int, n: int, threads: int = 1) -> np.ndarray:
     out = np.empty(m * n, dtype=np.float32)
     lib().or_matmul(_p(a), _p(b), m, k, n, _p(out), threads)
     return out
+
+
+def matmul_tuned(a, b, m: int, k: int, n: int, threads: int = 1) -> np.ndarray:
+    """`matmul_tuned` (ferrum_ref/src/kernels/tuned.rs:L99-L134): cache panels and a 4 x 8 register tile."""
+    a, b = _f32(a), _f32(b)
+    out = np.empty(m * n, dtype=np.float32)
+    lib().or_matmul_tuned(_p(a), _p(b), m, k, n, _p(out), threads)
+    return out
+
+
+def set_tuned(on: bool):
+    """Model passes multiply with the tuned kernel (the all-cores speed baseline) or the simple one."""
+    lib().or_set_tuned(1 if on else 0)
 
 
 def rand_vec(n: int, seed: int) -> np.ndarray:
@@ -385,6 +401,14 @@ class OracleLlama:
         rc = lib().or_llama_extend(self.h, _p(ids), ids.size, _p(out))
         _raise(rc, self.model.cfg, None)
         return out.reshape(ids.size, self.vocab)
+
+    def extend_last(self, ids) -> np.ndarray:
+        """`extend`, returning the logits of the last new position only."""
+        ids = np.ascontiguousarray(ids, dtype=np.int32)
+        out = np.empty(self.vocab, dtype=np.float32)
+        rc = lib().or_llama_extend_last(self.h, _p(ids), ids.size, _p(out))
+        _raise(rc, self.model.cfg, None)
+        return out
 
     def forward_logits(self, ids) -> np.ndarray:
         ids = np.ascontiguousarray(ids, dtype=np.int32)

@@ -31,7 +31,7 @@ def _worker(rank, world, port, vocab_shards, mode_value, q):
     from ferrum_gpu_b200 import Mode, QKind
     from ferrum_gpu_b200.group import GroupScorer
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)  # carries the rendezvous token only: the group owns its NCCL
     try:
         cfg, model = _model()
         gs = GroupScorer(model, QKind.Q4_0, vocab_shards=vocab_shards, mode=Mode(mode_value))
