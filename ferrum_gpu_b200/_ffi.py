@@ -83,7 +83,7 @@ class FcGpt2Weights(C.Structure):
 EXPORTS = (
     "fc_device_open", "fc_device_close", "fc_device_name", "fc_device_props", "fc_last_error",
     "fc_device_stream", "fc_device_sync", "fc_device_launch_count", "fc_debug_fail_after",
-    "fc_debug_profile", "fc_debug_profile_report", "fc_debug_matvec_kernel", "fc_debug_attention_f16",
+    "fc_debug_profile", "fc_debug_profile_report", "fc_debug_matvec_kernel", "fc_debug_raise_status", "fc_debug_attention_f16",
     "fc_block_bytes", "fc_qweight_create", "fc_qweight_create_from_blocks", "fc_qweight_destroy",
     "fc_qweight_info", "fc_qweight_blocks", "fc_dequant", "fc_qmatmul", "fc_qmatmul_dev",
     "fc_qmatmul_dev_noalloc",
@@ -132,6 +132,7 @@ def load() -> C.CDLL:
         "fc_debug_fail_after": (C.c_int, [vp, i64]),
         "fc_debug_profile": (C.c_int, [vp, C.c_int]),
         "fc_debug_matvec_kernel": (C.c_int, [vp, C.c_int]),
+        "fc_debug_raise_status": (C.c_int, [vp, C.c_int]),
         "fc_debug_profile_report": (C.c_int, [vp, C.c_char_p, sz]),
         "fc_model_topk": (C.c_int, [vp, u32, u32, C.c_float, vp, u32, vp, vp, P(u32)]),
         "fc_topk_dev": (C.c_int, [vp, vp, u32, u32, C.c_float, vp, u32, vp, vp, P(u32)]),

@@ -714,7 +714,7 @@ FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream
   if (n > m->max_streams || n > 1024) return fc_fail(dev, FC_ERR_SHAPE, "%u rows for a model of %u streams", n, m->max_streams);
   for (uint32_t i = 0; i < n; i++) {
     if (stream_ids[i] >= m->max_streams) return fc_fail(dev, FC_ERR_RANGE, "stream %u of %u", stream_ids[i], m->max_streams);
-    if (m->pos[stream_ids[i]] + steps > m->ctx)
+    if ((uint64_t)m->pos[stream_ids[i]] + steps > m->ctx) // (64 bits: a step count near 2^32 must not wrap)
       return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
   }
   // the first step takes its tokens from the host like any other (and checks streams and ids)
@@ -809,7 +809,7 @@ FC_API int fc_model_prefill(FcModel* m, uint32_t stream_id, const int32_t* ids, 
   if (mode != FC_EXACT_F32 && mode != FC_TENSOR_F16) return fc_fail(dev, FC_ERR_ARG, "unknown arithmetic mode %d", mode);
   if (m->n_shards != 1) return fc_fail(dev, FC_ERR_UNSUPPORTED, "prefill needs the whole head on this device");
   const uint32_t start = m->pos[stream_id];
-  if (start + n > m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
+  if ((uint64_t)start + n > m->ctx) return fc_fail(dev, FC_ERR_CONTEXT_FULL, "context of %u tokens is full", m->ctx);
   FC_TRY(check_ids(m, ids, n));
   if (mode == FC_TENSOR_F16) {
     // The prompt goes through the scoring kernels (fp16 operands, f32 accumulation) and leaves its rotated

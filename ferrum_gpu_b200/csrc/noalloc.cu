@@ -23,6 +23,8 @@ __half* g_scratch_ptr[MAX_DEVICES] = {}; // device address of g_x_scratch on eac
 FC_API int fc_qmatmul_dev_noalloc(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev) {
   if (!w || !x_dev || !y_dev) return FC_ERR_ARG;
   FcDevice* dev = w->dev;
+  if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev)) & 15)
+    return fc_fail(dev, FC_ERR_ARG, "x_dev and y_dev must be 16-byte aligned"); // (the kernels move 16-byte pieces)
   cudaSetDevice(dev->ordinal);
   if (m == 0) return FC_OK;
   if ((size_t)m * w->m.k > NOALLOC_MAX_ELEMS)

@@ -129,6 +129,10 @@ FC_API int fc_dequant(FcQWeight* w, float* out, size_t out_elems) {
 FC_API int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, int mode) {
   if (!w || !x_dev || !y_dev) return FC_ERR_ARG;
   FcDevice* dev = w->dev;
+  // the kernels read x and write y in 16-byte pieces: a pointer into the middle of a buffer is refused here,
+  // before any launch
+  if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev)) & 15)
+    return fc_fail(dev, FC_ERR_ARG, "x_dev and y_dev must be 16-byte aligned");
   cudaSetDevice(dev->ordinal);
   if (mode == FC_EXACT_F32) {
     Epilogue ep;

@@ -140,9 +140,26 @@ FC_API const char* fc_last_error(FcDevice* dev) {
 
 FC_API void* fc_device_stream(FcDevice* dev) { return dev ? (void*)dev->stream : nullptr; }
 
+// Also the place where a caller of the device-pointer entry points learns that a kernel gave up a bounded wait:
+// the status word the kernels raise is read with the synchronisation and cleared.
 FC_API int fc_device_sync(FcDevice* dev) {
   if (!dev) return FC_ERR_ARG;
   cudaSetDevice(dev->ordinal);
+  int flag = 0;
+  if (dev->d_flag) FC_CUDA(dev, cudaMemcpyAsync(&flag, dev->d_flag, sizeof(int), cudaMemcpyDeviceToHost, dev->stream));
+  FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+  if (flag != 0) {
+    cudaMemsetAsync(dev->d_flag, 0, sizeof(int), dev->stream);
+    return fc_fail(dev, FC_ERR_TIMEOUT, "a kernel gave up a bounded wait (status %d): results since the last synchronisation are incomplete", flag);
+  }
+  return FC_OK;
+}
+
+// Test hook: raise the status word the way a kernel that gave up a wait does (no kernel has to time out).
+FC_API int fc_debug_raise_status(FcDevice* dev, int value) {
+  if (!dev || !dev->d_flag) return FC_ERR_ARG;
+  cudaSetDevice(dev->ordinal);
+  FC_CUDA(dev, cudaMemcpyAsync(dev->d_flag, &value, sizeof(int), cudaMemcpyHostToDevice, dev->stream));
   FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
   return FC_OK;
 }

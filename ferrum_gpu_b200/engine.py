@@ -26,13 +26,14 @@ class SampleParams:
 @dataclass
 class GenOpts:
     """The fields of `GenOpts` this path uses (engine/mod.rs:L189-L202): how many tokens, how to pick them, the
-    seed of the draw and how many recent tokens the repetition penalty looks at. `prefill` (new here) feeds the
+    seed of the draw and how many recent tokens the repetition penalty looks at (0: the whole history, as
+    `generate_with` passes it to `sample`). `prefill` (new here) feeds the
     prompt in one batched pass instead of token by token as `generate_with` does: Mode.EXACT_F32 (the same logits
     to 1e-5) or Mode.TENSOR_F16 (the scoring kernels; logits to the scoring tolerance)."""
     max_new: int = 16
     sampling: SampleParams | None = None
     seed: int = 1
-    penalty_window: int = 64
+    penalty_window: int = 0
     prefill: Mode | None = None
 
 
@@ -98,19 +99,49 @@ def argmax(logits) -> int:
     return best
 
 
-def generate_with(feed, prompt, opts: GenOpts):
-    """`generate_with` (engine/mod.rs:L204-L242): feed each prompt token, then sample greedily; the
-    last sampled token is not fed."""
+def sample(logits, p: SampleParams, recent, rng: Rng) -> int:
+    """`sampling::sample` (ferrum_model/src/sampling.rs:L44-L100) on a host logits row: repetition penalty over
+    `recent` (in order, a repeated token is penalised again), argmax at temperature 0, else the candidates by
+    descending logit (ties: lower index first, NaN dropped), top_k, softmax, nucleus cut, one draw."""
+    f = np.float32
+    l = np.array(logits, dtype=np.float32)
+    if p.repetition_penalty != 1.0:
+        for t in recent:
+            if 0 <= t < l.size:
+                l[t] = f(l[t] / f(p.repetition_penalty)) if l[t] > 0.0 else f(l[t] * f(p.repetition_penalty))
+    if p.temperature <= 0.0:
+        return argmax(l)
+    idx = [i for i in range(l.size) if not np.isnan(l[i])]
+    if not idx:
+        return 0
+    # f32::total_cmp descending with a stable sort: -0.0 sorts below +0.0, ties keep the lower index first
+    key = l.view(np.int32).astype(np.int64)
+    key = np.where(key < 0, -(key & 0x7FFFFFFF) - 1, key)
+    idx.sort(key=lambda i: -int(key[i]))
+    if p.top_k > 0:
+        idx = idx[:p.top_k]
+    return sample_candidates(idx, [l[i] for i in idx], p, rng)
+
+
+def generate_with(feed, ctx: int, prompt, opts: GenOpts):
+    """`generate_with` (engine/mod.rs:L204-L242): feed each prompt token, then sample `opts.max_new` tokens,
+    stopping when the context is full; the last sampled token is not fed. Returns only the new tokens."""
     if len(prompt) == 0:
         raise ValueError("the prompt is empty")
-    out = list(int(t) for t in prompt)
+    if len(prompt) >= ctx:
+        raise ValueError(f"the prompt has {len(prompt)} tokens but the context is {ctx}")
+    params = opts.sampling or SampleParams()
+    rng = Rng(opts.seed)
     logits = None
-    for t in out:
-        logits = feed(t)
-    for i in range(opts.max_new):
-        nxt = argmax(logits)
+    for t in prompt:
+        logits = feed(int(t))
+    history = [int(t) for t in prompt]
+    out = []
+    while len(out) < opts.max_new and len(history) < ctx:
+        nxt = sample(logits, params, history[-opts.penalty_window:] if opts.penalty_window else history, rng)
         out.append(nxt)
-        if i + 1 < opts.max_new:
+        history.append(nxt)
+        if len(history) < ctx and len(out) < opts.max_new:
             logits = feed(nxt)
     return out
 
@@ -149,42 +180,59 @@ class CudaBackend:
         return lambda token: m.feed(token)
 
     def generate(self, model, prompt, opts: GenOpts):
-        """`Backend::generate`: the argmax, or the top-k candidates of a sampled draw, are taken on the device;
-        a logits row is read back only for sampling without a top_k (1..1024)."""
+        """`Backend::generate` with `generate_with`'s contract (engine/mod.rs:L204-L242): only the new tokens come
+        back, a prompt that does not leave room is an error, and generation stops when the context is full. The
+        argmax, or the top-k candidates of a sampled draw, are taken on the device; a logits row is read back only
+        for sampling without a top_k in 1..1024."""
         if len(prompt) == 0:
             raise ValueError("the prompt is empty")
+        ctx = model.cfg.ctx
+        if len(prompt) >= ctx:
+            raise ValueError(f"the prompt has {len(prompt)} tokens but the context is {ctx}")
+        max_new = min(opts.max_new, ctx - len(prompt))  # history reaches ctx: stop there
         cls = CudaLlama if isinstance(model, Llama) else CudaGpt2
         m = cls(self.dev, model, self.weights)
         try:
-            out = [int(t) for t in prompt]
+            history = [int(t) for t in prompt]
+            out = []
             sp = opts.sampling
             if sp is not None and sp.temperature > 0.0:
-                if not 1 <= sp.top_k <= 1024:
-                    raise ValueError("sampled decoding on the device needs 1 <= top_k <= 1024")
                 rng = Rng(opts.seed)
+                on_device = 1 <= sp.top_k <= 1024
+                logits = None
                 if opts.prefill is None:
-                    for t in out:
-                        m.feed_greedy(t)
+                    for t in history:
+                        logits = m.feed_greedy(t) if on_device else m.feed(t)
                 else:
-                    m.prefill(out, mode=opts.prefill)
-                for i in range(opts.max_new):
-                    recent = out[-opts.penalty_window:] if sp.repetition_penalty != 1.0 else ()
-                    idx, val = m.topk(sp.top_k, 0, sp.repetition_penalty, recent)
-                    nxt = sample_candidates(idx, val, sp, rng)
+                    logits = m.prefill(history, mode=opts.prefill)
+                while len(out) < max_new:
+                    recent = history[-opts.penalty_window:] if opts.penalty_window else history
+                    if on_device:
+                        idx, val = m.topk(sp.top_k, 0, sp.repetition_penalty,
+                                          recent if sp.repetition_penalty != 1.0 else ())
+                        nxt = sample_candidates(idx, val, sp, rng)
+                    else:
+                        nxt = sample(logits, sp, recent, rng)
                     out.append(nxt)
-                    if i + 1 < opts.max_new:
-                        m.feed_greedy(nxt)
+                    history.append(nxt)
+                    if len(history) < ctx and len(out) < max_new:
+                        logits = m.feed_greedy(nxt) if on_device else m.feed(nxt)
                 return out
+            if max_new == 0:
+                return out
+            if sp is not None and sp.repetition_penalty != 1.0:  # greedy with a penalty: the host loop
+                return generate_with(lambda t: m.feed(t), ctx, history, opts)
             nxt = None
             if opts.prefill is None:
-                for t in out:
+                for t in history:
                     nxt = m.feed_greedy(t)
             else:
-                nxt = argmax(m.prefill(out, mode=opts.prefill))
-            if opts.max_new > 0:
-                out.append(nxt)
-            if opts.max_new > 1:  # the remaining picks in one call, chained on the device
-                out.extend(int(t) for t in m.decode_greedy([nxt], opts.max_new - 1)[:, 0])
+                nxt = argmax(m.prefill(history, mode=opts.prefill))
+            out.append(nxt)
+            # the remaining picks in one call, chained on the device; the last pick is not fed, so the chain
+            # consumes max_new - 1 positions and history ends at len(prompt) + max_new <= ctx
+            if max_new > 1:
+                out.extend(int(t) for t in m.decode_greedy([nxt], max_new - 1)[:, 0])
             return out
         finally:
             m.close()

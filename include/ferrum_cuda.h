@@ -86,7 +86,14 @@ const char* fc_last_error(FcDevice* dev);
 /* The CUDA stream (a cudaStream_t) all work of this handle is enqueued on, and a full
  * synchronise of it. */
 void* fc_device_stream(FcDevice* dev);
+/* Waits for the stream and reports what the enqueued work could not report when it was launched: FC_ERR_TIMEOUT
+ * when a kernel since the last synchronisation gave up one of its bounded waits (its results are incomplete;
+ * the status is cleared), FC_ERR_DEVICE for a CUDA failure. Callers of the *_dev entry points, which return
+ * before the work runs, learn of such a failure here. */
 int fc_device_sync(FcDevice* dev);
+/* Test hook: sets the status word a kernel raises when it gives up a wait, so that the reporting path can be
+ * tested without a kernel that times out. */
+int fc_debug_raise_status(FcDevice* dev, int value);
 /* Kernels launched by this library on this device since it was opened. */
 uint64_t fc_device_launch_count(FcDevice* dev);
 /* Host-side fault injection, replaces Gpu::fail_after / sweep_faults
@@ -149,7 +156,9 @@ int fc_dequant(FcQWeight* w, float* out_n_k, size_t out_elems);
 /* `y[m, n] = x[m, k] * W` with host buffers (copies inside). Replaces ops::quant::linear_q
  * (ferrum_wgpu/src/ops/quant.rs:L326-L381). `mode` is FC_EXACT_F32 or FC_TENSOR_F16. */
 int fc_qmatmul(FcQWeight* w, const float* x, uint32_t m, float* y, int mode);
-/* The same on device buffers, enqueued on the device's stream, no synchronisation. */
+/* The same on device buffers, enqueued on the device's stream, no synchronisation. `x_dev` and `y_dev` must be
+ * 16-byte aligned (the kernels move 16-byte pieces; a misaligned pointer is refused with FC_ERR_ARG before any
+ * launch). A kernel that gives up a bounded wait is reported by the next fc_device_sync, not here. */
 int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, int mode);
 
 /* The tensor-core product of fc_qmatmul_dev (mode FC_TENSOR_F16) for callers that must not trigger a
@@ -162,7 +171,10 @@ int fc_qmatmul_dev(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev, i
  * refused with FC_ERR_SHAPE. `x_dev` and `y_dev` are the caller's. The first call on a device looks
  * up the array's device address; make that call before starting any stream capture. All calls share
  * the one array: two of them overlapping on the GPU (different streams or devices' handles on the
- * same GPU) race, and the array keeps the previous call's contents between calls. */
+ * same GPU) race, and the array keeps the previous call's contents between calls. `x_dev` and `y_dev` must be
+ * 16-byte aligned. While per-kernel timing (fc_debug_profile) is on, the library creates CUDA events around the
+ * launches, which is an allocation of the driver's: leave it off where none is allowed. A kernel that gives up a
+ * bounded wait is reported by the next fc_device_sync. */
 int fc_qmatmul_dev_noalloc(FcQWeight* w, const float* x_dev, uint32_t m, float* y_dev);
 
 /* ---- resident models ---------------------------------------------------------------------- */

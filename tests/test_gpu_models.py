@@ -110,15 +110,26 @@ def test_greedy_decode_token_for_token(dev, kind):
     m = helpers.ref_random_llama(cfg, 11, biases, tied)
     ref = m if kind is None else orc.dequantised_llama(m, int(kind), snap_embedding=False)
     oracle = orc.OracleLlama(ref)
-    want = generate_with(oracle.feed, [3, 1, 4], GenOpts(max_new=7))
+    want = generate_with(oracle.feed, cfg.ctx, [3, 1, 4], GenOpts(max_new=7))
+    assert len(want) == 7, "only the new tokens come back (engine/mod.rs:L204-L242)"
     be = CudaBackend(dev, kind)
     assert be.kind() == "cuda" and "B200" in be.name()
     assert be.generate(m, [3, 1, 4], GenOpts(max_new=7)) == want
-    assert generate_with(be.llama_decoder(m), [3, 1, 4], GenOpts(max_new=7)) == want
+    assert generate_with(be.llama_decoder(m), cfg.ctx, [3, 1, 4], GenOpts(max_new=7)) == want
     # the prompt in one batched pass instead of token by token: the same tokens
     assert be.generate(m, [3, 1, 4], GenOpts(max_new=7, prefill=Mode.EXACT_F32)) == want
+    # generation stops when the context is full, and a prompt that leaves no room is an error
+    room = cfg.ctx - 3
+    assert be.generate(m, [3, 1, 4], GenOpts(max_new=room + 5)) == generate_with(oracle_fresh(ref).feed, cfg.ctx, [3, 1, 4], GenOpts(max_new=room + 5))
+    assert len(be.generate(m, [3, 1, 4], GenOpts(max_new=room + 5))) == room
+    with pytest.raises(ValueError, match=f"the prompt has {cfg.ctx} tokens but the context is {cfg.ctx}"):
+        be.generate(m, IDS[:cfg.ctx], GenOpts(max_new=1))
     with pytest.raises(RuntimeError, match="not available"):
         be.train()
+
+
+def oracle_fresh(model):
+    return orc.OracleLlama(model)
 
 
 def test_reset_rewinds_and_stale_cache_entries_do_not_leak(dev):
@@ -276,7 +287,7 @@ def test_config1_greedy_decode_reproduces_the_oracle_tokens(dev):
     g.feed(prompt[0])
     assert dev.launch_count() - before == 1 + 5 * cfg.layers + 2
     # the device-side greedy path produces the same continuation
-    assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128))[16:] == out_o
+    assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128)) == out_o
     g.close()
 
 
@@ -360,5 +371,12 @@ def test_chained_greedy_decode_returns_the_picks_of_step_by_step_decode(dev, str
     assert np.array_equal(one[0], t3)
     with pytest.raises(CudaError, match="context"):
         b.decode_greedy(t3, cfg.ctx)
+    # a step count near 2^32 must not wrap past the check: refused before any launch
+    before = dev.launch_count()
+    ids = np.arange(streams, dtype=np.uint32)
+    tok = np.ascontiguousarray(t3, dtype=np.int32)
+    sink = np.zeros(streams, dtype=np.int32)  # (never written: the call is refused)
+    rc = _ffi.load().fc_model_decode_greedy(b._h, streams, ids.ctypes.data, tok.ctypes.data, 0xFFFFFFFF, sink.ctypes.data)
+    assert rc == _ffi.FC_ERR_CONTEXT_FULL and dev.launch_count() == before
     a.close()
     b.close()

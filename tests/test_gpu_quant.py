@@ -220,3 +220,15 @@ def test_device_encoder_matches_the_cpu_encoder_on_special_values(dev, kind):
     ok = ~np.isnan(want)
     assert np.array_equal(got[ok].view(np.uint32), want[ok].view(np.uint32)), kind
     qw.close()
+
+
+def test_a_given_up_wait_is_reported_by_the_next_synchronisation(dev):
+    """The device-pointer products return before their kernels run; a kernel that gives up a bounded wait raises
+    a status word, and fc_device_sync is where the caller learns of it. The word is raised from the host here: no
+    kernel has to time out."""
+    lib = _ffi.load()
+    assert lib.fc_device_sync(dev.handle) == _ffi.FC_OK
+    dev.check(lib.fc_debug_raise_status(dev.handle, 3))
+    assert lib.fc_device_sync(dev.handle) == _ffi.FC_ERR_TIMEOUT
+    assert b"bounded wait" in lib.fc_last_error(dev.handle)
+    assert lib.fc_device_sync(dev.handle) == _ffi.FC_OK, "the status is cleared once reported"

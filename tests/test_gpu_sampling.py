@@ -87,7 +87,7 @@ def test_sampled_generation_matches_the_oracle_loop(dev):
     cfg = tiny_llama_cfg()
     m = random_llama(cfg, seed=21, std=0.3)
     sp = SampleParams(temperature=0.9, top_k=8, top_p=0.95, repetition_penalty=1.1)
-    opts = GenOpts(max_new=7, sampling=sp, seed=5, penalty_window=64)
+    opts = GenOpts(max_new=7, sampling=sp, seed=5)
     prompt = [1, 4, 2]
     got = CudaBackend(dev, None).generate(m, prompt, opts)
     oracle = orc.OracleLlama(m)
@@ -96,7 +96,7 @@ def test_sampled_generation_matches_the_oracle_loop(dev):
     for t in out:
         logits = oracle.feed(t)
     for i in range(opts.max_new):
-        nxt = orc.sample(logits, sp.temperature, sp.top_k, sp.top_p, sp.repetition_penalty, out[-64:], rng)
+        nxt = orc.sample(logits, sp.temperature, sp.top_k, sp.top_p, sp.repetition_penalty, out, rng)
         out.append(nxt)
         if i + 1 < opts.max_new:
             logits = oracle.feed(nxt)
