@@ -58,6 +58,7 @@ void model_free(FcModel* m) {
   cudaSetDevice(m->dev->ordinal);
   cudaStreamSynchronize(m->dev->stream);
   model_tc_free(m);
+  decode_cluster_free(m);
   for (cudaGraphExec_t g : m->chain_graphs)
     if (g) cudaGraphExecDestroy(g);
   for (cudaGraphExec_t g : m->graphs)
@@ -588,6 +589,19 @@ FC_API int fc_model_feed_batch(FcModel* m, uint32_t n, const uint32_t* stream_id
     p[n + i] = (int32_t)m->pos[stream_ids[i]];
     p[2 * n + i] = (int32_t)stream_ids[i];
   }
+  // One stream of a small GPT-2-style model: the whole step is one cluster kernel (decode_cluster.cu).
+  if (n == 1 && m->n_shards == 1 && decode_cluster_ready(m)) {
+    FC_CUDA(dev, cudaMemcpyAsync(m->d_ids, p, 4, cudaMemcpyHostToDevice, dev->stream));
+    FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + 1, 4, cudaMemcpyHostToDevice, dev->stream));
+    FC_TRY(k_decode_cluster(m, stream_ids[0], 1, false));
+    FC_CUDA(dev, cudaMemcpyAsync(p + 3, m->d_argmax, 4, cudaMemcpyDeviceToHost, dev->stream));
+    if (logits_out)
+      FC_CUDA(dev, cudaMemcpyAsync(logits_out, m->logits, (size_t)m->vocab * 4, cudaMemcpyDeviceToHost, dev->stream));
+    FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    if (argmax_out) argmax_out[0] = p[3];
+    m->pos[stream_ids[0]]++;
+    return FC_OK;
+  }
   auto enqueue_step = [&]() -> int {
     FC_CUDA(dev, cudaMemcpyAsync(m->d_ids, p, n * 4, cudaMemcpyHostToDevice, dev->stream));
     FC_CUDA(dev, cudaMemcpyAsync(m->d_pos, p + n, n * 4, cudaMemcpyHostToDevice, dev->stream));
@@ -720,6 +734,17 @@ FC_API int fc_model_decode_greedy(FcModel* m, uint32_t n, const uint32_t* stream
   // the first step takes its tokens from the host like any other (and checks streams and ids)
   FC_TRY(fc_model_feed_batch(m, n, stream_ids, first_tokens, nullptr, tokens_out));
   if (steps == 1) return FC_OK;
+  if (n == 1 && m->n_shards == 1 && decode_cluster_ready(m)) {
+    // the remaining steps in one launch: the kernel takes each pick as the next token itself
+    FC_CUDA(dev, cudaMemsetAsync(m->d_chain_cnt, 0, 4, dev->stream));
+    FC_TRY(k_decode_cluster(m, stream_ids[0], steps - 1, true));
+    if (steps > 2)
+      FC_CUDA(dev, cudaMemcpyAsync(tokens_out + 1, m->d_chain_log + 1, (size_t)(steps - 2) * 4, cudaMemcpyDeviceToHost, dev->stream));
+    FC_CUDA(dev, cudaMemcpyAsync(tokens_out + (steps - 1), m->d_argmax, 4, cudaMemcpyDeviceToHost, dev->stream));
+    FC_CUDA(dev, cudaStreamSynchronize(dev->stream));
+    m->pos[stream_ids[0]] += steps - 1;
+    return FC_OK;
+  }
   const bool graph_mode = m->graph_ok && dev->fail_after < 0 && !dev->profiling;
   if (!graph_mode) { // fault injection and per-kernel profiling step on the host
     for (uint32_t s = 1; s < steps; s++)

@@ -70,6 +70,7 @@ struct FcModel {
   uint32_t* d_chain_cnt = nullptr;
   Arena arena;
   void* tc = nullptr; // state of the bf16 tensor-core path (built on first use)
+  void* dc = nullptr; // state of the one-launch single-stream decode (decode_cluster.cu; probed on first use)
 
   uint32_t qd() const { return heads * hd; }
   uint32_t kvd() const { return kv_heads * hd; }
@@ -100,3 +101,7 @@ size_t model_tc_trunk_bytes(const FcModel* m, size_t rows); // workspace model_t
 size_t model_tc_head_bytes(const FcModel* m, size_t rows);  // workspace model_head_partial_tc takes
 int model_interleave_gate_up(FcDevice* dev, FcQWeight* w, uint32_t hidden, uint32_t group);
 int tc_check_errors(FcDevice* dev);
+// decode_cluster.cu: a small GPT-2-style model decodes one stream as one kernel per run of tokens
+bool decode_cluster_ready(FcModel* m);
+int k_decode_cluster(FcModel* m, uint32_t stream, uint32_t steps, bool chained);
+void decode_cluster_free(FcModel* m);

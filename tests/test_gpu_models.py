@@ -280,14 +280,57 @@ def test_config1_greedy_decode_reproduces_the_oracle_tokens(dev):
         tok_g, tok_o = orc.argmax(lg), orc.argmax(lo)
     assert worst < FORWARD, worst
     assert out_g == out_o
-    # embed; per layer qkv (norm fused), attention (stores the row's k and v itself: no RoPE), wo, fc (norm
-    # fused, GELU), proj; head (final norm fused), argmax
+    # the whole token is one launch: the stages of a token are separated by the barriers of a thread-block
+    # cluster, not by launches (as separate launches: embed; per layer qkv, attention, wo, fc, proj; head, argmax)
     g.reset()
     before = dev.launch_count()
     g.feed(prompt[0])
-    assert dev.launch_count() - before == 1 + 5 * cfg.layers + 2
+    assert dev.launch_count() - before == 1
+    # and a chain of greedy steps is two: the first step, then all the others
+    before = dev.launch_count()
+    assert g.decode_greedy([prompt[1]], 9)[:, 0].tolist() == generate_with(orc.OracleGpt2(ref).feed, cfg.ctx, prompt[:2], GenOpts(max_new=9))
+    assert dev.launch_count() - before == 2
     # the device-side greedy path produces the same continuation
     assert CudaBackend(dev, QKind.Q8_0).generate(m, prompt, GenOpts(max_new=128)) == out_o
+    g.close()
+
+
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
+def test_one_launch_decode_of_a_small_gpt2_matches_the_oracle_on_any_stream(dev, kind):
+    """The cluster kernel behind `feed` / `decode_greedy` for GPT-2-style models with 64-wide heads: every logits
+    row within 1e-5 of the CPU oracle over the dequantised weights, on a stream other than 0, with a chained run
+    that equals step-by-step decoding and leaves the same cache behind."""
+    cfg = Gpt2Config(vocab=300, ctx=40, dim=128, heads=2, layers=3, hidden=256)
+    m = random_gpt2(cfg, seed=9, std=0.08, bias_std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_gpt2(m, int(kind), snap_embedding=False)
+    oracle = orc.OracleGpt2(ref)
+    g = CudaGpt2(dev, m, kind, max_streams=3)
+    toks = random_tokens(12, 14, cfg.vocab).tolist()
+    before = dev.launch_count()
+    for i, t in enumerate(toks):
+        lo = oracle.feed(t)
+        lg = g.feed(t, stream=2)
+        assert orc.max_rel_err(lg, lo) < FORWARD, (kind, i)
+        g.feed_greedy(t, stream=1)  # (stream 1 runs the same tokens, interleaved)
+    assert dev.launch_count() - before == 2 * len(toks), "one launch per token"
+    assert g.pos(2) == len(toks) and g.pos(1) == len(toks) and g.pos(0) == 0
+    # chained greedy on stream 2 against step-by-step on stream 1 (same history)
+    first = int(orc.argmax(lg))
+    chain = g.decode_greedy([first], 11, streams=[2])[:, 0].tolist()
+    t, want = first, []
+    for _ in range(11):
+        t = g.feed_greedy(t, stream=1)
+        want.append(t)
+    assert chain == want
+    lo = None
+    t = first
+    for i in range(11):  # and both equal the oracle's greedy continuation
+        lo = oracle.feed(t)
+        t = orc.argmax(lo)
+        assert t == want[i], i
+    assert g.pos(2) == g.pos(1) == len(toks) + 11
+    # decode continues from the chained state
+    assert orc.max_rel_err(g.feed(want[-1], stream=2), oracle.feed(want[-1])) < FORWARD
     g.close()
 
 
