@@ -1,12 +1,18 @@
 """Benchmark of the quantised scoring hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --case NAME      # one small, self-terminating workload of a hot kernel, for an ncu capture
 
 Workload (N = 1): the Llama-style scoring configuration - 12 layers, d_model 768, 12 query / 4 KV
 heads, SwiGLU 2048, vocab 32000, Q4_0 weights drawn from N(0, 0.02) - scoring 256 sequences of 1024
 uniform-random token ids for their total log-probability (fp16 tensor-core path, f32 accumulation). One step = one pass
 over the 256 sequences of a rank. With N > 1 every rank holds a replica and scores its own 256
-sequences (no data-path collective); the per-sequence NLL sums are all-gathered at the end of each step.
+sequences (no data-path collective); the per-sequence NLL sums are all-gathered at the end of each step
+(`value`, weak scaling). The same line then carries `strong` (the 256 sequences of the configuration shared
+out over the N ranks) and `c5` (the GPT-2-124M configuration, 512 x 1024, through the multi-GPU group of the
+C ABI with the head split over 2 and 4 vocabulary shards, beside the replicated head on the same sequences).
+At N = 1 it also carries `decode` (batch-1 greedy decode of the GPT-2-style configuration), `decode64` (the
+64-stream Qwen2-style decode) and `sweep` (the isolated quantised product over the whole shape grid).
 Everything is synthetic: there is no dataset and no checkpoint.
 
 Prints ONE JSON line (rank 0).
@@ -95,8 +101,10 @@ def c3_flops_per_token(cfg) -> float:
 
 
 def run_reference(args, rank: int):
-    """The reference's own CPU path for this workload, restated (no Rust toolchain exists here): the
-    f32 oracle over the dequantised weights, all host threads, on a bounded sample per step."""
+    """The reference's own CPU path for this workload, restated (no Rust toolchain exists here): the f32 oracle
+    over the dequantised weights on the reference's tuned kernel (`matmul_tuned`, ferrum_ref/src/kernels/tuned.rs:
+    cache panels, a 4 x 8 register tile, rows split over all host threads - "the speed baseline for GPU gates",
+    bit-identical to the simple kernel), on a bounded sample per step."""
     if rank != 0:
         return
     from ferrum_gpu_b200 import _ffi
@@ -106,8 +114,9 @@ def run_reference(args, rank: int):
     cfg = config_c3()
     model = random_llama(cfg, seed=1)
     ref = orc.dequantised_llama(model, _ffi.FC_Q4_0, snap_embedding=False)
+    orc.set_tuned(True)
     oracle = orc.OracleLlama(ref, threads=cores)
-    sample_len = 129
+    sample_len = 257
     ids = random_tokens(100, sample_len, cfg.vocab)
     for _ in range(min(args.warmup, 1)):
         oracle.score(ids)
@@ -116,7 +125,7 @@ def run_reference(args, rank: int):
         oracle.score(ids)
     dt = (time.perf_counter() - t0) / args.steps
     value = (sample_len - 1) / dt
-    sample = f"1 sequence x {sample_len} tokens per step (of 256 x 1024), f32 oracle, {cores} threads"
+    sample = f"1 sequence x {sample_len} tokens per step (of 256 x 1024), f32 oracle on the tuned kernel, {cores} threads"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -135,6 +144,9 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--seqs", type=int, default=N_SEQS, help="sequences per rank (256 = the benchmark workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the isolated-product shape grid (about a minute)")
+    ap.add_argument("--no-c5", action="store_true", help="skip the split-head GPT-2-124M leg of a multi-GPU run")
+    ap.add_argument("--case", default=None, help="run one profiling case and exit: " + ", ".join(sorted(CASES)))
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--decode64", action="store_true", help="(default now; kept so that older command lines still parse)")
     ap.add_argument("--no-decode64", action="store_true",
@@ -145,6 +157,9 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.case:
+        run_case(args.case)
         return
 
     import torch
@@ -232,6 +247,12 @@ def main():
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te.item())
 
+    strong = c5 = None
+    if world > 1:
+        strong = bench_strong(dev, g, stream, ids_host, world, rank, local, args)
+        if not args.no_c5:
+            c5 = bench_c5(world, rank, args)
+
     out = None
     if rank == 0:
         # per-kernel device time of one step (event pairs around every launch), for the roofline
@@ -276,6 +297,10 @@ def main():
             "mfu_of_sustained": (lin_flops + attn_flops) * rows / (ms_step * 1e-3) / 1e12 / tf_sust,
             "nll_checksum": nll_total,
         }
+        if strong:
+            out["strong"] = strong
+        if c5:
+            out["c5"] = c5
         if not args.no_decode and world == 1:
             time.sleep(3.0)  # a separate, latency-bound workload: let the clocks recover from the power-capped scoring steps
             dsamp = ClockSampler(local)
@@ -284,6 +309,8 @@ def main():
             out["decode"]["clocks"] = dsamp.stop()
             if not args.no_decode64:
                 out["decode64"] = bench_decode64(dev, hbm)
+        if not args.no_sweep and world == 1:
+            out["sweep"] = bench_sweep(dev, hbm, tf_burst)
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(cfg, model)
     g.close()
@@ -322,27 +349,45 @@ def bench_decode(dev, hbm_gbs):
             "note": "weights (11 MB) live in L2; the limiter is launch/dependency latency, not HBM"}
 
 
-def bench_decode64(dev, hbm_gbs, streams=64, prefill=1536, steps=32):
+def bench_decode64(dev, hbm_gbs, streams=64, prefill=1536, steps=512):
     """Batched KV-cached decode: the Qwen2-style configuration (24 layers, d_model 1024, 16 q / 2 kv heads,
     SwiGLU 2816, vocab 151936, tied head, q/k/v biases, Q8_0, f32 KV cache), 64 streams each with a
-    1536-token prefill, then `steps` greedy steps of all streams together (of the configuration's 512;
-    the cache length grows from 1536, the step cost with it)."""
+    1536-token prefill, then the configuration's 512 greedy steps of all streams together, chained on the
+    device in one call (the cache grows from 1536 to 2048 positions, the step cost with it; the first and
+    the last 32 steps are also timed on their own)."""
     from ferrum_gpu_b200 import CudaLlama, QKind
     from ferrum_gpu_b200.hostmodel import config_c4, random_llama, random_tokens
     cfg = config_c4()
     model = random_llama(cfg, seed=2, biases=True, tied=True)
     g = CudaLlama(dev, model, QKind.Q8_0, max_streams=streams)
+    toks = random_tokens(7, streams, cfg.vocab)
+    for _ in range(3):  # eager step, graph capture, first replay - on throw-away positions
+        g.feed_batch(toks)
+    for s in range(streams):
+        g.reset(s)
     t0 = time.perf_counter()
     for s in range(streams):
         g.prefill(random_tokens(500 + s, prefill, cfg.vocab), stream=s)
     prefill_s = time.perf_counter() - t0
-    toks = random_tokens(7, streams, cfg.vocab)
-    for _ in range(3):  # eager step, graph capture, first replay
-        toks, _ = g.feed_batch(toks)
     dev.sync()
+    head_n = min(32, steps // 2)
     t0 = time.perf_counter()
-    toks = g.decode_greedy(toks, steps)[-1]  # the steps chained on the device, one call
-    dt = (time.perf_counter() - t0) / steps
+    toks = g.decode_greedy(toks, head_n)[-1]
+    first_ms = (time.perf_counter() - t0) / head_n * 1e3
+    mid = steps - 2 * head_n
+    t1 = time.perf_counter()
+    if mid > 0:
+        toks = g.decode_greedy(toks, mid)[-1]
+    t2 = time.perf_counter()
+    toks = g.decode_greedy(toks, head_n)[-1]
+    t3 = time.perf_counter()
+    last_ms = (t3 - t2) / head_n * 1e3
+    dt = (t3 - t0) / steps
+    for s in range(streams):
+        g.reset(s)
+    g.prefill(random_tokens(500, prefill, cfg.vocab), stream=0)  # (a step at the initial cache length, per kernel)
+    for s in range(1, streams):
+        g.prefill(random_tokens(500 + s, 8, cfg.vocab), stream=s)
     dev.profile(True)
     g.feed_batch(toks)
     prof = dev.profile_report()
@@ -356,17 +401,152 @@ def bench_decode64(dev, hbm_gbs, streams=64, prefill=1536, steps=32):
         g.prefill(random_tokens(500, prefill, cfg.vocab), stream=0, mode=Mode.TENSOR_F16)
         tc_s = time.perf_counter() - t0
     wbytes = g.weight_bytes()
-    mean_len = prefill + 3 + steps / 2
+    mean_len = prefill + steps / 2
     kv_bytes = 2 * cfg.kv_dim * 4 * mean_len * cfg.layers * streams
     g.close()
     total = sum(v["ms"] for v in prof.values()) or 1.0
     return {"workload": f"c4-qwen2-24L-d1024-q8_0-{streams}streams-{prefill}+{steps}", "tok_s": streams / dt,
-            "ms_per_step": dt * 1e3, "prefill_s": prefill_s,
+            "ms_per_step": dt * 1e3, "ms_per_step_first32": first_ms, "ms_per_step_last32": last_ms, "prefill_s": prefill_s,
             "prefill_tok_s": {"exact_f32": streams * prefill / prefill_s, "tensor_f16": prefill / tc_s},
             "bytes_per_step": wbytes + kv_bytes,
             "hbm_frac": (wbytes + kv_bytes) / dt / 1e9 / hbm_gbs,
-            "kernel_shares": {k: round(v["ms"] / total, 3) for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])[:6]},
-            "profiled_step_ms": total}
+            "launches_of_a_step": {k: v["launches"] for k, v in sorted(prof.items(), key=lambda kv: -kv[1]["ms"])[:8]}}
+
+
+def bench_sweep(dev, hbm_gbs, tf_burst):
+    """The isolated quantised product Y[M,N] = X[M,K] W[N,K]^T over the configuration's grid: K in {768, 2048,
+    4096} x N in {768, 2816, 11008, 32000} x M in {1, 8, 64, 512, 4096}, Q4_0 and Q8_0; X ~ N(0, 1) f32 and
+    W ~ N(0, 0.02) on the device. M <= 64 runs the exact decode kernels and is reported as packed weight bytes
+    per second against the measured copy bandwidth; M >= 512 runs the tcgen05 product and is reported as
+    2 M N K flop per second against the measured burst bf16 peak. Timing: CUDA events around batches of
+    back-to-back launches that rotate over several copies of the weight (together above 256 MB where a copy is
+    small enough to make eight of them, else the entry says `l2`), best of three batches."""
+    import ctypes as C
+    import torch
+    from ferrum_gpu_b200 import Mode, QKind, upload_quantised, _ffi
+    lib = _ffi.load()
+    st = torch.cuda.ExternalStream(dev.stream())
+    rng = np.random.default_rng(11)
+    rows = []
+    for k in (768, 2048, 4096):
+        for n in (768, 2816, 11008, 32000):
+            wt = (rng.standard_normal(k * n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+            for kind in (QKind.Q4_0, QKind.Q8_0):
+                wbytes = k * n * (18 if kind == QKind.Q4_0 else 34) / 32
+                copies = int(min(8, max(1, -(-256e6 // wbytes))))
+                qws = [upload_quantised(dev, kind, wt, k, n) for _ in range(copies)]
+                cold = copies * wbytes >= 256e6
+                for m in (1, 8, 64, 512, 4096):
+                    x = torch.randn(m, k, device="cuda")
+                    y = torch.empty(m, n, device="cuda")
+                    mode = int(Mode.EXACT_F32 if m <= 64 else Mode.TENSOR_F16)
+                    reps = 3 if m >= 512 else 4
+                    for q in qws:
+                        dev.check(lib.fc_qmatmul_dev(q.handle, x.data_ptr(), m, y.data_ptr(), mode))
+                    dev.sync()
+                    best = None
+                    for _ in range(3):
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(st)
+                        for _ in range(reps):
+                            for q in qws:
+                                dev.check(lib.fc_qmatmul_dev(q.handle, x.data_ptr(), m, y.data_ptr(), mode))
+                        e1.record(st)
+                        e1.synchronize()
+                        us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
+                        best = us if best is None else min(best, us)
+                    dev.sync()
+                    if m <= 64:
+                        rate = wbytes / best / 1e3  # GB/s
+                        rows.append([k, n, m, kind.label(), round(best, 1), round(rate), round(rate / hbm_gbs, 3),
+                                     "hbm" if cold else "l2"])
+                    else:
+                        rate = 2.0 * m * n * k / best / 1e6  # TFLOP/s
+                        rows.append([k, n, m, kind.label(), round(best, 1), round(rate, 1), round(rate / tf_burst, 3), "tensor"])
+                    del x, y
+                for q in qws:
+                    q.close()
+    return {"columns": ["K", "N", "M", "kind", "us", "GB/s | TFLOP/s", "frac of measured peak", "bound"], "rows": rows}
+
+
+def bench_strong(dev, g, stream, ids_host, world, rank, local, args):
+    """Strong scaling of the scoring configuration: its 256 sequences shared out over the ranks (256 / N each),
+    the per-sequence NLL sums all-gathered at the end of every step; same timing protocol as the weak number."""
+    import torch
+    import torch.distributed as dist
+    from ferrum_gpu_b200 import Mode
+    per = N_SEQS // world
+    ids = np.ascontiguousarray(ids_host[:per])
+    with torch.cuda.stream(stream):
+        ids_dev = torch.from_numpy(ids).to(f"cuda:{local}")
+        nll = torch.zeros(per, dtype=torch.float64, device=f"cuda:{local}")
+        gathered = torch.zeros(world * per, dtype=torch.float64, device=f"cuda:{local}")
+
+        def step():
+            g.score_dev(ids_dev.data_ptr(), per, SEQ_LEN, Mode.TENSOR_F16, 0, 0, nll.data_ptr())
+            dist.all_gather_into_tensor(gathered, nll)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            step()
+        e1.record(stream)
+        stream.synchronize()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / args.steps
+    return {"scaling": "strong", "seqs_total": per * world, "seqs_per_gpu": per, "ms_per_step": ms,
+            "value": per * world * (SEQ_LEN - 1) / (ms * 1e-3), "unit": UNIT}
+
+
+def bench_c5(world, rank, args):
+    """The GPT-2-124M configuration (12 layers, d_model 768, vocab 50257 tied, Q4_0), 512 sequences x 1024, through
+    the multi-GPU group of the C ABI (fc_group_score: host ids in, NLL sums out on every rank, NCCL inside the
+    library): the replicated head, then the head split over 2 and 4 vocabulary shards. Per layout: tokens/s from
+    the slowest rank's wall time per call, the device time of the exchanges, and the largest difference of a
+    sequence's NLL from the replicated head's on the same sequences."""
+    import torch
+    import torch.distributed as dist
+    from ferrum_gpu_b200 import Mode, QKind
+    from ferrum_gpu_b200.group import GroupScorer
+    from ferrum_gpu_b200.hostmodel import config_c5, random_gpt2, random_tokens
+    cfg = config_c5()
+    model = random_gpt2(cfg, seed=3, tied=True)
+    n_seqs = 512
+    ids = np.stack([random_tokens(7000 + i, SEQ_LEN, cfg.vocab) for i in range(n_seqs)])
+    res, base = {}, None
+    for shards in (1, 2, 4):
+        if world % shards:
+            continue
+        gs = GroupScorer(model, QKind.Q4_0, vocab_shards=shards, mode=Mode.TENSOR_F16)
+        nll = None
+        for _ in range(2):
+            nll = gs.score(ids)
+        dist.barrier()
+        times = []
+        for _ in range(max(2, min(args.steps, 3))):
+            t0 = time.perf_counter()
+            nll = gs.score(ids)
+            times.append(time.perf_counter() - t0)
+        ex = gs.exchange_ms()
+        gs.close()
+        t = torch.tensor([min(times)], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        if shards == 1:
+            base = nll
+        res[f"vocab_shards_{shards}"] = {
+            "tok_s": n_seqs * (SEQ_LEN - 1) / float(t.item()), "ms_per_call": float(t.item()) * 1e3,
+            "exchange_ms": {"hidden_all_gather": ex[0], "partials_all_gather": ex[1], "nll_all_reduce": ex[2]},
+            "max_abs_nll_diff_vs_replicated": float(np.abs(nll - base).max()), "nll_checksum": float(nll.sum())}
+    return {"workload": "c5-gpt2-124M-q4_0-scoring-512x1024", "entry": "fc_group_score (host ids, NCCL inside the library)",
+            "layouts": res} if rank == 0 else None
 
 
 def cpu_baseline(cfg, model):
@@ -383,6 +563,148 @@ def cpu_baseline(cfg, model):
     dt = time.perf_counter() - t0
     return {"value": (n - 1) / dt, "unit": UNIT, "cores": 1, "kind": "port",
             "sample": f"1 sequence x {n} tokens (of 256 x 1024), single thread as `--device cpu` runs scoring"}
+
+
+# ---- small, self-terminating workloads of the hot kernels, sized for an `ncu` capture (inputs above the 126 MB
+# L2 where DRAM figures matter, a few launches, well under a GB on the device): python bench.py --case NAME
+
+def _weights(k, n, seed=1):
+    return (np.random.default_rng(seed).standard_normal(k * n, dtype=np.float32) * np.float32(0.02)).astype(np.float32)
+
+
+def case_gemm(dev):
+    """tensor-core product, Q4_0, M=16384 K=768 N=1280"""
+    from ferrum_gpu_b200 import Mode, QKind, linear_q, upload_quantised
+    k, n, m = 768, 1280, 16384
+    qw = upload_quantised(dev, QKind.Q4_0, _weights(k, n), k, n)
+    x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
+    for _ in range(3):
+        linear_q(dev, x, qw, m, Mode.TENSOR_F16)
+    qw.close()
+
+
+def _case_matvec(dev, m):
+    from ferrum_gpu_b200 import QKind, linear_q, upload_quantised
+    k, n = 4096, 32000
+    x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
+    for kind in (QKind.Q4_0, QKind.Q8_0):
+        qw = upload_quantised(dev, kind, _weights(k, n), k, n)
+        for _ in range(3):
+            linear_q(dev, x, qw, m)
+        qw.close()
+
+
+def case_matvec(dev):
+    """decode product of one row, Q4_0 and Q8_0, K=4096 N=32000"""
+    _case_matvec(dev, 1)
+
+
+def case_matvec8(dev):
+    """tensor-core decode product, 8 rows, K=4096 N=32000"""
+    _case_matvec(dev, 8)
+
+
+def _c3_model(dev, layers=None, max_streams=1):
+    from ferrum_gpu_b200 import CudaLlama, QKind
+    from ferrum_gpu_b200.hostmodel import config_c3, random_llama
+    cfg = config_c3()
+    if layers:
+        cfg.layers = layers
+    return cfg, CudaLlama(dev, random_llama(cfg, seed=1), QKind.Q4_0, max_streams=max_streams)
+
+
+def case_score(dev):
+    """8 sequences x 1024 of the Llama scoring configuration, 2 layers"""
+    from ferrum_gpu_b200 import Mode
+    from ferrum_gpu_b200.hostmodel import random_tokens
+    cfg, g = _c3_model(dev, layers=2)
+    ids = np.stack([random_tokens(10 + i, 1024, cfg.vocab) for i in range(8)])
+    for _ in range(2):
+        g.score_batch(ids, Mode.TENSOR_F16)
+    g.close()
+
+
+def case_chunk(dev):
+    """32 sequences x 1024, one layer (a quarter of one bench chunk: per-launch DRAM traffic scales with the rows)"""
+    from ferrum_gpu_b200 import Mode
+    from ferrum_gpu_b200.hostmodel import random_tokens
+    cfg, g = _c3_model(dev, layers=1)
+    ids = np.stack([random_tokens(10 + i, 1024, cfg.vocab) for i in range(32)])
+    for _ in range(2):
+        g.score_batch(ids, Mode.TENSOR_F16)
+    g.close()
+
+
+def case_attention(dev):
+    """the causal attention kernels alone, 16 x 1024 x 12 heads"""
+    n_seqs, t, heads, kv = 16, 1024, 12, 4
+    qkv = np.random.default_rng(0).standard_normal((n_seqs * t, (heads + 2 * kv) * 64)).astype(np.float16)
+    for variant in (1, 3):
+        dev.attention_f16(qkv, n_seqs, t, heads, kv, variant=variant, iters=1)
+
+
+def _case_decode(dev, streams, layers, vocab, tied):
+    from ferrum_gpu_b200 import CudaLlama, QKind
+    from ferrum_gpu_b200.hostmodel import LlamaConfig, random_llama, random_tokens
+    cfg = LlamaConfig(vocab=vocab, ctx=2048, dim=1024, heads=16, kv_heads=2, head_dim=64, layers=layers, hidden=2816,
+                      rope_dim=64, rope_base=1e6, rope_type=1, eps=1e-6)
+    g = CudaLlama(dev, random_llama(cfg, seed=1, biases=True, tied=tied), QKind.Q8_0, max_streams=streams)
+    for s in range(streams):
+        g.prefill(random_tokens(s, 1500, cfg.vocab), stream=s)
+    toks = random_tokens(99, streams, cfg.vocab)
+    for _ in range(3):
+        g.feed_batch(toks)
+    g.close()
+
+
+def case_decode(dev):
+    """batched decode step: 16 streams at cache length ~1500, 2 layers"""
+    _case_decode(dev, 16, 2, 32000, False)
+
+
+def case_decode64(dev):
+    """four layers and the 151936-row head of the 64-stream decode configuration at 1500 cached positions"""
+    _case_decode(dev, 64, 4, 151936, True)
+
+
+def case_head64(dev):
+    """the vocabulary-head product of the 64-stream decode configuration: 64 rows against 151936 x 1024 Q8_0"""
+    from ferrum_gpu_b200 import QKind, linear_q, upload_quantised
+    k, n, m = 1024, 151936, 64
+    qw = upload_quantised(dev, QKind.Q8_0, _weights(k, n), k, n)
+    x = np.random.default_rng(2).standard_normal(m * k, dtype=np.float32)
+    for _ in range(3):
+        linear_q(dev, x, qw, m)
+    qw.close()
+
+
+def case_decode1(dev):
+    """batch-1 greedy decode of the GPT-2-style configuration: 16 prompt tokens, then 64 chained steps"""
+    from ferrum_gpu_b200 import CudaGpt2, QKind
+    from ferrum_gpu_b200.hostmodel import config_c1, random_gpt2, random_tokens
+    cfg = config_c1()
+    m = CudaGpt2(dev, random_gpt2(cfg, seed=1), QKind.Q8_0)
+    tok = 0
+    for t in random_tokens(2, 16, cfg.vocab):
+        tok = m.feed_greedy(int(t))
+    m.decode_greedy([tok], 64)
+    m.close()
+
+
+CASES = {"gemm": case_gemm, "matvec": case_matvec, "matvec8": case_matvec8, "decode": case_decode, "decode64": case_decode64,
+         "head64": case_head64, "score": case_score, "head": case_score, "chunk": case_chunk, "attention": case_attention,
+         "decode1": case_decode1}
+
+
+def run_case(name):
+    from ferrum_gpu_b200 import Device
+    d = Device.open(0)
+    try:
+        CASES[name](d)
+        d.sync()
+        print("case", name, "done;", d.launch_count(), "launches")
+    finally:
+        d.close()
 
 
 if __name__ == "__main__":
