@@ -119,7 +119,7 @@ def test_config5_width_scores_the_odd_vocabulary_whole_and_in_two_shards(dev):
 def test_rope_scaling_on_the_device_matches_the_oracle(dev, scaling):
     """ferrum_ref/src/models/llama/ops.rs:L80-L101: theta = p * freq / ff * (1 / linear). The tables are built on
     the host by the library; decode, forward_all and the tensor path must all see the scaled angles."""
-    cfg = helpers.tiny_llama_cfg(vocab=29, ctx=24, dim=64, heads=2, kv_heads=1, head_dim=32, hidden=96, rope_dim=32)
+    cfg = helpers.tiny_llama_cfg(vocab=29, ctx=24, dim=128, heads=2, kv_heads=1, head_dim=64, hidden=128, rope_dim=64)
     if scaling in ("linear", "both"):
         cfg.rope_linear_factor = 2.0
     if scaling in ("freq_factors", "both"):
@@ -128,7 +128,7 @@ def test_rope_scaling_on_the_device_matches_the_oracle(dev, scaling):
     oracle = orc.OracleLlama(m)
     ids = [i % cfg.vocab for i in helpers_ids()]
     want = oracle.forward_logits(ids)
-    plain = helpers.tiny_llama_cfg(vocab=29, ctx=24, dim=64, heads=2, kv_heads=1, head_dim=32, hidden=96, rope_dim=32)
+    plain = helpers.tiny_llama_cfg(vocab=29, ctx=24, dim=128, heads=2, kv_heads=1, head_dim=64, hidden=128, rope_dim=64)
     unscaled = orc.OracleLlama(helpers.ref_random_llama(plain, 17, False, False)).forward_logits(ids)
     assert np.abs(want - unscaled).max() > 1e-3, "the scaling must matter for this test to mean anything"
     g = CudaLlama(dev, m)
