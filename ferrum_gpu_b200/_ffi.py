@@ -79,6 +79,32 @@ class FcGpt2Weights(C.Structure):
                 ("lnf_b", f32p), ("head", f32p)]
 
 
+class FcTensor(C.Structure):
+    """One weight tensor: f32 `[in, out]` (kind FC_F32) or the tensor's GGUF block bytes (a block kind)."""
+    _fields_ = [("data", C.c_void_p), ("kind", C.c_int)]
+
+
+LLAMA_MATS = ("wq", "wk", "wv", "wo", "gate", "up", "down")
+GPT2_MATS = ("wq", "wk", "wv", "wo", "w1", "w2")
+
+
+class FcLlamaBlockT(C.Structure):
+    _fields_ = [(n, FcTensor if n in LLAMA_MATS else f32p) for n in LLAMA_BLOCK_FIELDS]
+
+
+class FcLlamaTensors(C.Structure):
+    _fields_ = [("tok", FcTensor), ("blocks", C.POINTER(FcLlamaBlockT)), ("out_norm", f32p), ("head", FcTensor)]
+
+
+class FcGpt2BlockT(C.Structure):
+    _fields_ = [(n, FcTensor if n in GPT2_MATS else f32p) for n in GPT2_BLOCK_FIELDS]
+
+
+class FcGpt2Tensors(C.Structure):
+    _fields_ = [("tok", FcTensor), ("pos", f32p), ("blocks", C.POINTER(FcGpt2BlockT)), ("lnf_g", f32p), ("lnf_b", f32p),
+                ("head", FcTensor)]
+
+
 # Every symbol include/ferrum_cuda.h declares; tests check that the built library exports them.
 EXPORTS = (
     "fc_device_open", "fc_device_close", "fc_device_name", "fc_device_props", "fc_last_error",
@@ -88,6 +114,7 @@ EXPORTS = (
     "fc_qweight_info", "fc_qweight_blocks", "fc_dequant", "fc_qmatmul", "fc_qmatmul_dev",
     "fc_qmatmul_dev_noalloc",
     "fc_llama_plan_bytes", "fc_gpt2_plan_bytes", "fc_llama_create", "fc_gpt2_create",
+    "fc_llama_create_from_tensors", "fc_gpt2_create_from_tensors",
     "fc_model_destroy", "fc_model_pos", "fc_model_reset", "fc_model_info", "fc_model_feed",
     "fc_model_feed_batch", "fc_model_decode_greedy", "fc_model_topk", "fc_topk_dev", "fc_model_prefill", "fc_model_forward_all", "fc_model_score",
     "fc_model_score_dev", "fc_model_set_head_shard", "fc_model_trunk_dev",
@@ -151,6 +178,8 @@ def load() -> C.CDLL:
         "fc_gpt2_plan_bytes": (u64, [P(FcGpt2Config), C.c_int, u32]),
         "fc_llama_create": (C.c_int, [vp, P(FcLlamaConfig), P(FcLlamaWeights), C.c_int, u32, u64, P(vp)]),
         "fc_gpt2_create": (C.c_int, [vp, P(FcGpt2Config), P(FcGpt2Weights), C.c_int, u32, u64, P(vp)]),
+        "fc_llama_create_from_tensors": (C.c_int, [vp, P(FcLlamaConfig), P(FcLlamaTensors), C.c_int, u32, u64, P(vp)]),
+        "fc_gpt2_create_from_tensors": (C.c_int, [vp, P(FcGpt2Config), P(FcGpt2Tensors), C.c_int, u32, u64, P(vp)]),
         "fc_model_destroy": (C.c_int, [vp]),
         "fc_model_pos": (C.c_int, [vp, u32, P(u32)]),
         "fc_model_reset": (C.c_int, [vp, u32]),

@@ -253,7 +253,15 @@ int k_qgemm_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float*
 // The exact-f32 product of any m: picks matvec or tiled GEMM.
 int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
 
-// Upload helpers (weights.cu)
+// Upload helpers (runtime.cu)
+// One host tensor of a weight: kind FC_F32 = an f32 `[in, out]` matrix (the reference's host layout), a block kind =
+// the GGUF bytes of the `[out, in]` tensor.
+struct WeightSrc {
+  const void* p;
+  int kind;
+};
+int qweight_from_parts(FcDevice* dev, int kind, const WeightSrc* parts, const uint32_t* ns, int count, uint32_t k,
+                       FcQWeight** out);
 int qweight_from_f32(FcDevice* dev, int kind, const float* w_in_out_host, uint32_t k, uint32_t n, FcQWeight** out);
 int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats_host, const uint32_t* ns, int count,
                             uint32_t k, FcQWeight** out);

@@ -403,13 +403,44 @@ FC_API uint64_t fc_gpt2_plan_bytes(const FcGpt2Config* c, int qkind, uint32_t ma
   return plan_bytes(s, qkind, max_streams);
 }
 
+// The token table stays f32 on the device (models/llama/mod.rs:L133,L303): an f32 table is copied, a table that
+// arrives as GGUF blocks is repacked and decoded there (bit-identical to quant::decode).
+static int upload_table(FcModel* m, const FcTensor& t, uint32_t rows, uint32_t d, float** out) {
+  if (t.kind == FC_F32) return upload_f32(m, (const float*)t.data, (size_t)rows * d, out);
+  FcQWeight* q = nullptr;
+  const WeightSrc src{t.data, t.kind};
+  FC_TRY(qweight_from_parts(m->dev, t.kind, &src, &rows, 1, d, &q));
+  int rc = dev_alloc(m, (size_t)rows * d * 4, (void**)out);
+  if (rc == FC_OK) rc = k_dequant(m->dev, q->m, *out);
+  if (rc == FC_OK && cudaStreamSynchronize(m->dev->stream) != cudaSuccess) rc = fc_fail(m->dev, FC_ERR_DEVICE, "decoding the token table failed");
+  qweight_free(q);
+  return rc;
+}
+static WeightSrc src_of(const FcTensor& t) { return WeightSrc{t.data, t.kind}; }
+
 FC_API int fc_llama_create(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaWeights* w, int qkind,
                            uint32_t max_streams, uint64_t budget_bytes, FcModel** out) {
   if (!dev || !out) return FC_ERR_ARG;
   *out = nullptr;
-  cudaSetDevice(dev->ordinal);
   if (!valid_llama(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid Llama configuration");
   if (!w || !w->tok || !w->blocks || !w->out_norm || !w->head) return fc_fail(dev, FC_ERR_ARG, "missing weights");
+  std::vector<FcLlamaBlockT> blocks(c->layers);
+  for (uint32_t i = 0; i < c->layers; i++) {
+    const FcLlamaBlock& b = w->blocks[i];
+    blocks[i] = FcLlamaBlockT{b.attn_norm, {b.wq, FC_F32}, b.bq, {b.wk, FC_F32}, b.bk, {b.wv, FC_F32}, b.bv, {b.wo, FC_F32},
+                              b.ffn_norm,  {b.gate, FC_F32}, {b.up, FC_F32}, {b.down, FC_F32}};
+  }
+  const FcLlamaTensors t{{w->tok, FC_F32}, blocks.data(), w->out_norm, {w->head, FC_F32}};
+  return fc_llama_create_from_tensors(dev, c, &t, qkind, max_streams, budget_bytes, out);
+}
+
+FC_API int fc_llama_create_from_tensors(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaTensors* w, int qkind,
+                                        uint32_t max_streams, uint64_t budget_bytes, FcModel** out) {
+  if (!dev || !out) return FC_ERR_ARG;
+  *out = nullptr;
+  cudaSetDevice(dev->ordinal);
+  if (!valid_llama(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid Llama configuration");
+  if (!w || !w->tok.data || !w->blocks || !w->out_norm || !w->head.data) return fc_fail(dev, FC_ERR_ARG, "missing weights");
   if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
   if (!kind_known(qkind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
   FC_TRY(check_budget(dev, fc_llama_plan_bytes(c, qkind, max_streams), budget_bytes)); // before any allocation
@@ -442,32 +473,38 @@ FC_API int fc_llama_create(FcDevice* dev, const FcLlamaConfig* c, const FcLlamaW
     if ((rc = upload_f32(m, hs.data(), hs.size(), &m->sin)) != FC_OK) return fail(rc);
     m->rope.cos = m->cos, m->rope.sin = m->sin, m->rope.rope_dim = c->rope_dim, m->rope.type = c->rope_type;
   }
-  if ((rc = upload_f32(m, w->tok, (size_t)c->vocab * d, &m->tok)) != FC_OK) return fail(rc);
+  if ((rc = upload_table(m, w->tok, c->vocab, d, &m->tok)) != FC_OK) return fail(rc);
   if ((rc = upload_f32(m, w->out_norm, d, &m->normf_g)) != FC_OK) return fail(rc);
   m->layers.resize(c->layers);
   for (uint32_t li = 0; li < c->layers; li++) {
-    const FcLlamaBlock& b = w->blocks[li];
+    const FcLlamaBlockT& b = w->blocks[li];
     Layer& l = m->layers[li];
-    if (!b.attn_norm || !b.wq || !b.wk || !b.wv || !b.wo || !b.ffn_norm || !b.gate || !b.up || !b.down)
+    if (!b.attn_norm || !b.wq.data || !b.wk.data || !b.wv.data || !b.wo.data || !b.ffn_norm || !b.gate.data || !b.up.data ||
+        !b.down.data)
       return fail(fc_fail(dev, FC_ERR_ARG, "block %u is missing a tensor", li));
     if ((rc = upload_f32(m, b.attn_norm, d, &l.norm1_g)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.ffn_norm, d, &l.norm2_g)) != FC_OK) return fail(rc);
-    const float* qkv_m[3] = {b.wq, b.wk, b.wv};
+    const WeightSrc qkv_m[3] = {src_of(b.wq), src_of(b.wk), src_of(b.wv)};
     const uint32_t qkv_n[3] = {qd, kvd, kvd};
-    if ((rc = qweight_from_f32_concat(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
     const float* qkv_b[3] = {b.bq, b.bk, b.bv};
     if ((rc = upload_bias_concat(m, qkv_b, qkv_n, 3, &l.qkv.bias)) != FC_OK) return fail(rc);
-    if ((rc = qweight_from_f32(dev, qkind, b.wo, qd, d, &l.wo.w)) != FC_OK) return fail(rc);
-    const float* gu_m[2] = {b.gate, b.up};
+    const WeightSrc wo_m = src_of(b.wo), down_m = src_of(b.down);
+    if ((rc = qweight_from_parts(dev, qkind, &wo_m, &d, 1, qd, &l.wo.w)) != FC_OK) return fail(rc);
+    const WeightSrc gu_m[2] = {src_of(b.gate), src_of(b.up)};
     const uint32_t gu_n[2] = {hid, hid};
-    if ((rc = qweight_from_f32_concat(dev, qkind, gu_m, gu_n, 2, d, &l.ff1.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, gu_m, gu_n, 2, d, &l.ff1.w)) != FC_OK) return fail(rc);
     if (hid % 64 == 0) { // 64 gate rows then their 64 up rows: what the SwiGLU epilogue of the tensor path reads
       if ((rc = model_interleave_gate_up(dev, l.ff1.w, hid, 64)) != FC_OK) return fail(rc);
       m->gu_group = 64;
     }
-    if ((rc = qweight_from_f32(dev, qkind, b.down, hid, d, &l.ff2.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, &down_m, &d, 1, hid, &l.ff2.w)) != FC_OK) return fail(rc);
   }
-  if ((rc = qweight_from_f32(dev, qkind, w->head, d, c->vocab, &m->head.w)) != FC_OK) return fail(rc);
+  {
+    const WeightSrc head_m = src_of(w->head);
+    const uint32_t vocab = c->vocab;
+    if ((rc = qweight_from_parts(dev, qkind, &head_m, &vocab, 1, d, &m->head.w)) != FC_OK) return fail(rc);
+  }
   if ((rc = alloc_common(m)) != FC_OK) return fail(rc);
   *out = m;
   return FC_OK;
@@ -477,9 +514,26 @@ FC_API int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* c, const FcGpt2Weig
                           uint64_t budget_bytes, FcModel** out) {
   if (!dev || !out) return FC_ERR_ARG;
   *out = nullptr;
-  cudaSetDevice(dev->ordinal);
   if (!valid_gpt2(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid GPT-2 configuration");
   if (!w || !w->tok || !w->pos || !w->blocks || !w->lnf_g || !w->lnf_b || !w->head)
+    return fc_fail(dev, FC_ERR_ARG, "missing weights");
+  std::vector<FcGpt2BlockT> blocks(c->layers);
+  for (uint32_t i = 0; i < c->layers; i++) {
+    const FcGpt2Block& b = w->blocks[i];
+    blocks[i] = FcGpt2BlockT{b.ln1_g, b.ln1_b, {b.wq, FC_F32}, b.bq, {b.wk, FC_F32}, b.bk, {b.wv, FC_F32}, b.bv, {b.wo, FC_F32}, b.bo,
+                             b.ln2_g, b.ln2_b, {b.w1, FC_F32}, b.b1, {b.w2, FC_F32}, b.b2};
+  }
+  const FcGpt2Tensors t{{w->tok, FC_F32}, w->pos, blocks.data(), w->lnf_g, w->lnf_b, {w->head, FC_F32}};
+  return fc_gpt2_create_from_tensors(dev, c, &t, qkind, max_streams, budget_bytes, out);
+}
+
+FC_API int fc_gpt2_create_from_tensors(FcDevice* dev, const FcGpt2Config* c, const FcGpt2Tensors* w, int qkind,
+                                       uint32_t max_streams, uint64_t budget_bytes, FcModel** out) {
+  if (!dev || !out) return FC_ERR_ARG;
+  *out = nullptr;
+  cudaSetDevice(dev->ordinal);
+  if (!valid_gpt2(c)) return fc_fail(dev, FC_ERR_SHAPE, "invalid GPT-2 configuration");
+  if (!w || !w->tok.data || !w->pos || !w->blocks || !w->lnf_g || !w->lnf_b || !w->head.data)
     return fc_fail(dev, FC_ERR_ARG, "missing weights");
   if (max_streams == 0) return fc_fail(dev, FC_ERR_ARG, "max_streams must be positive");
   if (!kind_known(qkind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", qkind);
@@ -497,34 +551,40 @@ FC_API int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* c, const FcGpt2Weig
     model_free(m);
     return code;
   };
-  if ((rc = upload_f32(m, w->tok, (size_t)c->vocab * d, &m->tok)) != FC_OK) return fail(rc);
+  if ((rc = upload_table(m, w->tok, c->vocab, d, &m->tok)) != FC_OK) return fail(rc);
   if ((rc = upload_f32(m, w->pos, (size_t)c->ctx * d, &m->pos_table)) != FC_OK) return fail(rc);
   if ((rc = upload_f32(m, w->lnf_g, d, &m->normf_g)) != FC_OK) return fail(rc);
   if ((rc = upload_f32(m, w->lnf_b, d, &m->normf_b)) != FC_OK) return fail(rc);
   m->layers.resize(c->layers);
   for (uint32_t li = 0; li < c->layers; li++) {
-    const FcGpt2Block& b = w->blocks[li];
+    const FcGpt2BlockT& b = w->blocks[li];
     Layer& l = m->layers[li];
-    const float* need[] = {b.ln1_g, b.ln1_b, b.wq, b.bq, b.wk, b.bk, b.wv, b.bv, b.wo, b.bo, b.ln2_g, b.ln2_b, b.w1, b.b1, b.w2, b.b2};
-    for (const float* p : need)
+    const void* need[] = {b.ln1_g, b.ln1_b, b.wq.data, b.bq, b.wk.data, b.bk, b.wv.data, b.bv, b.wo.data, b.bo, b.ln2_g, b.ln2_b,
+                          b.w1.data, b.b1, b.w2.data, b.b2};
+    for (const void* p : need)
       if (!p) return fail(fc_fail(dev, FC_ERR_ARG, "block %u is missing a tensor", li));
     if ((rc = upload_f32(m, b.ln1_g, d, &l.norm1_g)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.ln1_b, d, &l.norm1_b)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.ln2_g, d, &l.norm2_g)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.ln2_b, d, &l.norm2_b)) != FC_OK) return fail(rc);
-    const float* qkv_m[3] = {b.wq, b.wk, b.wv};
+    const WeightSrc qkv_m[3] = {src_of(b.wq), src_of(b.wk), src_of(b.wv)};
     const uint32_t qkv_n[3] = {d, d, d};
-    if ((rc = qweight_from_f32_concat(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, qkv_m, qkv_n, 3, d, &l.qkv.w)) != FC_OK) return fail(rc);
     const float* qkv_b[3] = {b.bq, b.bk, b.bv};
     if ((rc = upload_bias_concat(m, qkv_b, qkv_n, 3, &l.qkv.bias)) != FC_OK) return fail(rc);
-    if ((rc = qweight_from_f32(dev, qkind, b.wo, d, d, &l.wo.w)) != FC_OK) return fail(rc);
+    const WeightSrc wo_m = src_of(b.wo), w1_m = src_of(b.w1), w2_m = src_of(b.w2);
+    if ((rc = qweight_from_parts(dev, qkind, &wo_m, &d, 1, d, &l.wo.w)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.bo, d, &l.wo.bias)) != FC_OK) return fail(rc);
-    if ((rc = qweight_from_f32(dev, qkind, b.w1, d, hid, &l.ff1.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, &w1_m, &hid, 1, d, &l.ff1.w)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.b1, hid, &l.ff1.bias)) != FC_OK) return fail(rc);
-    if ((rc = qweight_from_f32(dev, qkind, b.w2, hid, d, &l.ff2.w)) != FC_OK) return fail(rc);
+    if ((rc = qweight_from_parts(dev, qkind, &w2_m, &d, 1, hid, &l.ff2.w)) != FC_OK) return fail(rc);
     if ((rc = upload_f32(m, b.b2, d, &l.ff2.bias)) != FC_OK) return fail(rc);
   }
-  if ((rc = qweight_from_f32(dev, qkind, w->head, d, c->vocab, &m->head.w)) != FC_OK) return fail(rc);
+  {
+    const WeightSrc head_m = src_of(w->head);
+    const uint32_t vocab = c->vocab;
+    if ((rc = qweight_from_parts(dev, qkind, &head_m, &vocab, 1, d, &m->head.w)) != FC_OK) return fail(rc);
+  }
   if ((rc = alloc_common(m)) != FC_OK) return fail(rc);
   *out = m;
   return FC_OK;

@@ -235,29 +235,43 @@ void qweight_free(FcQWeight* w) {
   delete w;
 }
 
-// Quantise `count` host matrices `[k, ns[i]]` that share the input width and stack their output
-// rows into one device weight of n = sum(ns) rows (q, k and v, or gate and up, become one launch).
-int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, const uint32_t* ns, int count,
-                            uint32_t k, FcQWeight** out) {
+// Build one device weight of n = sum(ns) output rows from `count` host tensors that share the input width k (q, k
+// and v, or gate and up, become one weight). A part of kind FC_F32 is an f32 `[k, ns[i]]` matrix and is quantised
+// to `kind` on the device; a part of a block kind is the GGUF bytes of the tensor (ns[i] rows of k / 32 blocks)
+// and is repacked as it is (ferrum_gguf/src/io/reader.rs:L298 hands exactly these bytes) - no dequantise /
+// transpose / requantise round trip, and bit-identical to it by the reference's identity test
+// (ferrum_wgpu/src/ops/quant/tests.rs:L89-L104). All parts must come out as the same stored format.
+int qweight_from_parts(FcDevice* dev, int kind, const WeightSrc* parts, const uint32_t* ns, int count, uint32_t k,
+                       FcQWeight** out) {
   *out = nullptr;
   uint64_t n_total = 0;
-  uint32_t n_max = 0;
-  for (int i = 0; i < count; i++) {
-    n_total += ns[i];
-    n_max = ns[i] > n_max ? ns[i] : n_max;
-  }
-  if (k == 0 || n_total == 0 || n_total > 0x7fffffffu) return fc_fail(dev, FC_ERR_SHAPE, "empty or oversized weight");
+  size_t stage_bytes = 0;
   kind = effective_kind(kind, k);              // Q2_K on a width of whole 32s only: Q4_0 (ops/quant.rs:L134-L144)
   if (kind != FC_F32 && k % QK) kind = FC_F32; // ineligible width stays f32 (ops/quant.rs:L125-L134, lin.rs:L54-L61)
-  if (!kind_known(kind)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", kind);
+  int stored = -1;
+  for (int i = 0; i < count; i++) {
+    n_total += ns[i];
+    if (!parts[i].p) return fc_fail(dev, FC_ERR_ARG, "a weight tensor is missing");
+    const int pk = parts[i].kind == FC_F32 ? kind : parts[i].kind;
+    if (!kind_known(pk)) return fc_fail(dev, FC_ERR_ARG, "unknown weight kind %d", pk);
+    if (parts[i].kind != FC_F32 && k % kind_block_elems(pk))
+      return fc_fail(dev, FC_ERR_SHAPE, "a width of %u is not whole %u-element blocks", k, kind_block_elems(pk));
+    if (stored >= 0 && pk != stored)
+      return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensors of one stacked weight are stored in different formats (%d and %d)", stored, pk);
+    stored = pk;
+    const size_t b = parts[i].kind == FC_F32 ? (size_t)k * ns[i] * 4 : fc_block_bytes(pk, (size_t)k * ns[i]);
+    stage_bytes = b > stage_bytes ? b : stage_bytes;
+  }
+  if (k == 0 || n_total == 0 || n_total > 0x7fffffffu) return fc_fail(dev, FC_ERR_SHAPE, "empty or oversized weight");
+  kind = stored;
   const uint32_t n = (uint32_t)n_total;
   FcQWeight* w = new FcQWeight();
   w->dev = dev;
   const size_t qs_bytes = qmat_qs_bytes(kind, k, n), sc_bytes = qmat_sc_bytes(kind, k, n);
-  float* stage = nullptr;
+  uint8_t* stage = nullptr;
   cudaError_t e = cudaMalloc(&w->qs_alloc, qs_bytes);
   if (e == cudaSuccess && sc_bytes) e = cudaMalloc(&w->sc_alloc, sc_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&stage, (size_t)k * n_max * 4);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&stage, stage_bytes);
   if (e != cudaSuccess) {
     cudaGetLastError();
     qweight_free(w);
@@ -273,14 +287,20 @@ int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, c
   int rc = FC_OK;
   size_t row0 = 0;
   for (int i = 0; i < count && rc == FC_OK; i++) {
-    e = cudaMemcpyAsync(stage, mats[i], (size_t)k * ns[i] * 4, cudaMemcpyHostToDevice, dev->stream);
+    const bool f32 = parts[i].kind == FC_F32;
+    const size_t bytes = f32 ? (size_t)k * ns[i] * 4 : fc_block_bytes(kind, (size_t)k * ns[i]);
+    e = cudaMemcpyAsync(stage, parts[i].p, bytes, cudaMemcpyHostToDevice, dev->stream);
     if (e != cudaSuccess) {
       rc = fc_fail(dev, FC_ERR_DEVICE, "weight upload failed: %s", cudaGetErrorString(e));
       break;
     }
     uint8_t* qs = (uint8_t*)w->qs_alloc + qmat_qs_bytes(kind, k, row0);
     __half* sc = w->sc_alloc ? (__half*)((uint8_t*)w->sc_alloc + qmat_sc_bytes(kind, k, row0)) : nullptr;
-    rc = kind == FC_F32 ? k_transpose_kn(dev, stage, k, ns[i], (float*)qs) : k_quantise_kn(dev, kind, stage, k, ns[i], qs, sc);
+    if (!f32)
+      rc = k_repack_blocks(dev, kind, stage, k, ns[i], qs, sc);
+    else
+      rc = kind == FC_F32 ? k_transpose_kn(dev, (const float*)stage, k, ns[i], (float*)qs)
+                          : k_quantise_kn(dev, kind, (const float*)stage, k, ns[i], qs, sc);
     if (rc == FC_OK && cudaStreamSynchronize(dev->stream) != cudaSuccess) {
       dev->lost = true;
       rc = fc_fail(dev, FC_ERR_DEVICE, "weight upload failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -294,6 +314,14 @@ int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, c
   }
   *out = w;
   return FC_OK;
+}
+
+// The same from f32 `[k, ns[i]]` matrices only.
+int qweight_from_f32_concat(FcDevice* dev, int kind, const float* const* mats, const uint32_t* ns, int count,
+                            uint32_t k, FcQWeight** out) {
+  std::vector<WeightSrc> parts(count);
+  for (int i = 0; i < count; i++) parts[i] = WeightSrc{mats[i], FC_F32};
+  return qweight_from_parts(dev, kind, parts.data(), ns, count, k, out);
 }
 
 int qweight_from_f32(FcDevice* dev, int kind, const float* w_host, uint32_t k, uint32_t n, FcQWeight** out) {

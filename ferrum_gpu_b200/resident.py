@@ -195,26 +195,108 @@ def _kind(quant) -> int:
 
 
 class CudaLlama(ResidentModel):
-    """`GpuLlama::new(gpu, model, quant, budget)` (models/llama/mod.rs:L219-L314)."""
+    """`GpuLlama::new(gpu, model, quant, budget)` (models/llama/mod.rs:L219-L314). `packed` (from `pack_model`, or
+    the tensors of a quantised file): matrices that arrive as GGUF blocks of `packed_kind` (default `quant`) and are
+    repacked as they are."""
 
     def __init__(self, dev: Device, model: Llama, quant: QKind | None = None, budget: int | None = None,
-                 max_streams: int = 1):
-        cfg, w = model.c_structs()
+                 max_streams: int = 1, packed: dict | None = None, packed_kind: QKind | None = None):
         h = C.c_void_p()
-        dev.check(_ffi.load().fc_llama_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
-                                              budget or 0, C.byref(h)))
+        if packed is None:
+            cfg, w = model.c_structs()
+            dev.check(_ffi.load().fc_llama_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
+                                                  budget or 0, C.byref(h)))
+        else:
+            cfg, w, keep = _tensor_structs(model, packed_kind or quant, packed)
+            dev.check(_ffi.load().fc_llama_create_from_tensors(dev.handle, C.byref(cfg), C.byref(w), _kind(quant),
+                                                               max_streams, budget or 0, C.byref(h)))
+            del keep
         super().__init__(dev, h, model.cfg, quant, max_streams)
+
+
+def pack_model(dev: Device, model, kind: QKind) -> dict:
+    """The model's matrices as GGUF block bytes, the way a quantised file holds them (token table, block matrices
+    and head; ferrum_model/src/gguf/llama/mod.rs:L297-L316): {name or (layer, name): uint8 array}. Encoded by the
+    device encoder, which is bit-identical to `ferrum_gguf::quant::encode`."""
+    from .quant import upload_quantised
+    c = model.cfg
+    out = {}
+
+    def blocks_of(w, k, n):
+        q = upload_quantised(dev, kind, w, k, n)
+        b = q.blocks()
+        q.close()
+        return b
+
+    # the table is quantised along its rows of `dim`: as an [in, out] matrix that is its transpose
+    tok_t = np.ascontiguousarray(np.asarray(model.tok, dtype=np.float32).reshape(c.vocab, c.dim).T)
+    out["tok"] = blocks_of(tok_t, c.dim, c.vocab)
+    out["head"] = blocks_of(model.head, c.dim, c.vocab)
+    names = _ffi.LLAMA_MATS if isinstance(model, Llama) else _ffi.GPT2_MATS
+    for i, b in enumerate(model.blocks):
+        for name in names:
+            k, n = model.mat_shape(name)
+            out[(i, name)] = blocks_of(getattr(b, name), k, n)
+    return out
+
+
+def _tensor_structs(model, kind: QKind, packed: dict):
+    """(config, FcLlamaTensors | FcGpt2Tensors, keep-alive list) with every matrix found in `packed` handed over as
+    blocks of `kind` and the rest as f32."""
+    c = model.cfg
+    keep = []
+
+    def tensor(key, f32_array):
+        if key in packed:
+            a = np.ascontiguousarray(packed[key], dtype=np.uint8)
+            keep.append(a)
+            return _ffi.FcTensor(a.ctypes.data, int(kind))
+        a = np.ascontiguousarray(f32_array, dtype=np.float32)
+        keep.append(a)
+        return _ffi.FcTensor(a.ctypes.data, _ffi.FC_F32)
+
+    def f32p(a):
+        if a is None:
+            return None
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        keep.append(a)
+        return a.ctypes.data_as(_ffi.f32p)
+
+    llama = isinstance(model, Llama)
+    cfg, _ = model.c_structs()
+    mats = _ffi.LLAMA_MATS if llama else _ffi.GPT2_MATS
+    fields = _ffi.LLAMA_BLOCK_FIELDS if llama else _ffi.GPT2_BLOCK_FIELDS
+    arr = ((_ffi.FcLlamaBlockT if llama else _ffi.FcGpt2BlockT) * c.layers)()
+    keep.append(arr)
+    for i, b in enumerate(model.blocks):
+        for name in fields:
+            if name in mats:
+                setattr(arr[i], name, tensor((i, name), getattr(b, name)))
+            else:
+                setattr(arr[i], name, f32p(getattr(b, name)))
+    if llama:
+        w = _ffi.FcLlamaTensors(tensor("tok", model.tok), arr, f32p(model.out_norm), tensor("head", model.head))
+    else:
+        w = _ffi.FcGpt2Tensors(tensor("tok", model.tok), f32p(model.pos), arr, f32p(model.lnf_g), f32p(model.lnf_b),
+                               tensor("head", model.head))
+    return cfg, w, keep
 
 
 class CudaGpt2(ResidentModel):
     """`GpuGpt2::new` (models/gpt2.rs:L134-L190), with quantised weights added."""
 
     def __init__(self, dev: Device, model: Gpt2, quant: QKind | None = None, budget: int | None = None,
-                 max_streams: int = 1):
-        cfg, w = model.c_structs()
+                 max_streams: int = 1, packed: dict | None = None, packed_kind: QKind | None = None):
         h = C.c_void_p()
-        dev.check(_ffi.load().fc_gpt2_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
-                                             budget or 0, C.byref(h)))
+        if packed is None:
+            cfg, w = model.c_structs()
+            dev.check(_ffi.load().fc_gpt2_create(dev.handle, C.byref(cfg), C.byref(w), _kind(quant), max_streams,
+                                                 budget or 0, C.byref(h)))
+        else:
+            cfg, w, keep = _tensor_structs(model, packed_kind or quant, packed)
+            dev.check(_ffi.load().fc_gpt2_create_from_tensors(dev.handle, C.byref(cfg), C.byref(w), _kind(quant),
+                                                              max_streams, budget or 0, C.byref(h)))
+            del keep
         super().__init__(dev, h, model.cfg, quant, max_streams)
 
 

@@ -223,6 +223,56 @@ typedef struct {
   const float* head; /* [dim, vocab] */
 } FcGpt2Weights;
 
+/* One weight tensor as the host hands it over. kind FC_F32: `data` is an f32 `[in, out]` row-major matrix (the layout
+ * of ferrum_ref::llama::Llama, models/llama/mod.rs:L100-L147; a token table: `[vocab, dim]`). A block kind (FC_Q8_0,
+ * FC_Q4_0, FC_F16, ...): `data` is the tensor's GGUF bytes exactly as ferrum_gguf::Gguf::tensor_bytes returns them
+ * (ferrum_gguf/src/io/reader.rs:L298): `out` rows of `in / 32` blocks (a token table: `vocab` rows of `dim / 32`). */
+typedef struct {
+  const void* data;
+  int kind;
+} FcTensor;
+typedef struct {
+  const float* attn_norm;
+  FcTensor wq;
+  const float* bq;
+  FcTensor wk;
+  const float* bk;
+  FcTensor wv;
+  const float* bv;
+  FcTensor wo;
+  const float* ffn_norm;
+  FcTensor gate, up, down;
+} FcLlamaBlockT;
+typedef struct {
+  FcTensor tok;
+  const FcLlamaBlockT* blocks;
+  const float* out_norm;
+  FcTensor head;
+} FcLlamaTensors;
+typedef struct {
+  const float *ln1_g, *ln1_b;
+  FcTensor wq;
+  const float* bq;
+  FcTensor wk;
+  const float* bk;
+  FcTensor wv;
+  const float* bv;
+  FcTensor wo;
+  const float* bo;
+  const float *ln2_g, *ln2_b;
+  FcTensor w1;
+  const float* b1;
+  FcTensor w2;
+  const float* b2;
+} FcGpt2BlockT;
+typedef struct {
+  FcTensor tok;
+  const float* pos;
+  const FcGpt2BlockT* blocks;
+  const float *lnf_g, *lnf_b;
+  FcTensor head;
+} FcGpt2Tensors;
+
 /* Device bytes a resident model of this shape needs (weights, RoPE tables, KV caches for
  * `max_streams` streams, decode scratch). Replaces models::llama::plan
  * (ferrum_wgpu/src/models/llama/mod.rs:L108-L182). 0 for an invalid config. */
@@ -239,6 +289,16 @@ int fc_llama_create(FcDevice* dev, const FcLlamaConfig* cfg, const FcLlamaWeight
  * is new: the reference's resident GPT-2 is f32 only. */
 int fc_gpt2_create(FcDevice* dev, const FcGpt2Config* cfg, const FcGpt2Weights* w, int qkind,
                    uint32_t max_streams, uint64_t budget_bytes, FcModel** out);
+/* The same from tensors that may each be f32 or packed blocks: a block tensor is repacked on the device as it is -
+ * what Lin::upload wants to do with a file's quantised tensors instead of dequantise -> transpose -> requantise
+ * (ferrum_wgpu/src/models/llama/lin.rs:L30-L62) - and the result is bit-identical to the f32 route by the
+ * reference's identity test (ferrum_wgpu/src/ops/quant/tests.rs:L89-L104); an f32 tensor is quantised to `qkind` as
+ * in fc_llama_create. The tensors stacked into one weight (q, k, v; gate, up) must end up in the same format. A
+ * token table given as blocks is decoded on the device (the table stays f32 there). */
+int fc_llama_create_from_tensors(FcDevice* dev, const FcLlamaConfig* cfg, const FcLlamaTensors* w, int qkind,
+                                 uint32_t max_streams, uint64_t budget_bytes, FcModel** out);
+int fc_gpt2_create_from_tensors(FcDevice* dev, const FcGpt2Config* cfg, const FcGpt2Tensors* w, int qkind,
+                                uint32_t max_streams, uint64_t budget_bytes, FcModel** out);
 int fc_model_destroy(FcModel* m);
 
 /* GpuLlama::{pos, reset} (models/llama/mod.rs:L331-L340) per stream. reset only rewinds the

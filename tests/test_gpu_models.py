@@ -132,6 +132,49 @@ def oracle_fresh(model):
     return orc.OracleLlama(model)
 
 
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
+def test_a_model_uploaded_from_file_blocks_equals_the_f32_upload_bit_for_bit(dev, kind):
+    """Raw-block upload at the model level (ferrum_gguf/src/io/reader.rs:L298 hands packed bytes): every matrix and
+    the token table arrive as GGUF blocks and are repacked as they are. By the reference's identity test
+    (ferrum_wgpu/src/ops/quant/tests.rs:L89-L104: requantising decoded blocks returns the same blocks) the resident
+    model must be the one the f32 route builds from the decoded weights, so every logit is equal bit for bit."""
+    from ferrum_gpu_b200.resident import pack_model
+    name, cfg, biases, tied = variants()[1]  # NEOX, q/k/v biases, tied head
+    m = helpers.ref_random_llama(cfg, 23, biases, tied)
+    ref = orc.dequantised_llama(m, int(kind), snap_embedding=True)  # what loading the quantised file gives
+    packed = pack_model(dev, ref, kind)
+    oracle_blocks = orc.quantise_matrix(int(kind), ref.blocks[0].wq, cfg.dim, cfg.q_dim)
+    assert np.array_equal(packed[(0, "wq")], oracle_blocks), "the device encoder writes the file's bytes"
+    a = CudaLlama(dev, ref, kind)                    # f32 -> quantise on the device
+    b = CudaLlama(dev, ref, kind, packed=packed)     # blocks -> repack
+    for i, t in enumerate(IDS[:cfg.ctx]):
+        la, lb = a.feed(t), b.feed(t)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32)), (kind, i)
+    assert a.weight_bytes() == b.weight_bytes()
+    # a mixed hand-over: some tensors as blocks, the rest f32
+    some = {k: v for k, v in packed.items() if k in ("head", (0, "down"), (1, "wo"))}
+    c = CudaLlama(dev, ref, kind, packed=some)
+    c.prefill(IDS[:cfg.ctx - 1])
+    a.reset()
+    a.prefill(IDS[:cfg.ctx - 1])
+    assert np.array_equal(a.feed(IDS[cfg.ctx - 1]), c.feed(IDS[cfg.ctx - 1]))
+    # tensors stacked into one weight must share a format
+    bad = {(0, "wq"): packed[(0, "wq")]}
+    other = QKind.Q4_0 if kind == QKind.Q8_0 else QKind.Q8_0
+    with pytest.raises(CudaError, match="different formats"):
+        CudaLlama(dev, ref, other, packed=bad, packed_kind=kind)
+    for g in (a, b, c):
+        g.close()
+    # GPT-2: the same through fc_gpt2_create_from_tensors
+    gcfg = gpt2_cfg()
+    gm = orc.dequantised_gpt2(helpers.ref_random_gpt2(gcfg, 5), int(kind), snap_embedding=True)
+    ga, gb = CudaGpt2(dev, gm, kind), CudaGpt2(dev, gm, kind, packed=pack_model(dev, gm, kind))
+    for t in (3, 1, 4, 1, 5):
+        assert np.array_equal(ga.feed(t), gb.feed(t))
+    ga.close()
+    gb.close()
+
+
 def test_reset_rewinds_and_stale_cache_entries_do_not_leak(dev):
     """models/llama/tests.rs:L215-L229: reset only rewinds pos; attention reads 0..len only."""
     name, cfg, biases, tied = variants()[0]
