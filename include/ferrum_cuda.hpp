@@ -230,17 +230,26 @@ class CudaBackend {
     auto m = std::make_shared<CudaGpt2>(gpu_, cfg, w, weights_);
     return [m](int32_t t) { return m->feed(t); };
   }
-  // generate (engine/mod.rs:L204-L242): feed each prompt token, then greedy; the last sampled token is not fed
+  // generate_with (engine/mod.rs:L204-L242), greedy: feed each prompt token, then pick until `max_new` tokens are
+  // out or the context is full; the last pick is not fed. Returns only the new tokens. The picks after the first
+  // are chained on the device in one call.
   std::vector<int32_t> generate(const FcLlamaConfig& cfg, const FcLlamaWeights& w, const std::vector<int32_t>& prompt,
                                 uint32_t max_new) {
     if (prompt.empty()) throw Error(FC_ERR_ARG, "the prompt is empty");
+    if (prompt.size() >= cfg.ctx)
+      throw Error(FC_ERR_CONTEXT_FULL, "the prompt has " + std::to_string(prompt.size()) + " tokens but the context is " +
+                                           std::to_string(cfg.ctx));
+    const uint32_t room = cfg.ctx - (uint32_t)prompt.size();
+    if (max_new > room) max_new = room; // history reaches ctx: stop there
     CudaLlama m(gpu_, cfg, w, weights_);
-    std::vector<int32_t> out = prompt;
+    std::vector<int32_t> out;
     int32_t next = 0;
     for (int32_t t : prompt) next = m.feed_greedy(t);
-    for (uint32_t i = 0; i < max_new; i++) {
-      out.push_back(next);
-      if (i + 1 < max_new) next = m.feed_greedy(next);
+    if (max_new == 0) return out;
+    out.push_back(next);
+    if (max_new > 1) {
+      const auto rest = m.decode_greedy(next, max_new - 1);
+      out.insert(out.end(), rest.begin(), rest.end());
     }
     return out;
   }
