@@ -8,13 +8,14 @@
 // the HBM rate. Here the multiply-adds run on the tensor cores and the only per-weight work left is
 // the unpack to fp16 (about 1.2 slots per weight):
 //
-//   * one persistent CTA per SM owns a contiguous range of 16-row tiles. Work items are (tile, K slice)
-//     pairs dealt round-robin to the warps, slices of one tile to neighbouring warps, so at any time the
-//     CTA streams one contiguous region of the plane. Each warp is a pipeline of its own: lane 0 keeps a
-//     ring of TMA box loads in flight (16 rows x 256 bytes of packed quants, 128B-swizzled, plus the
-//     rows' f16 scales of the same K range; completion on the stage's mbarrier), so the bytes in flight
-//     per SM are set by the rings (about 130 KB), not by registers, and no warp waits for another. The
-//     K slices of a tile are added up by whichever warp finishes last, in slice order (no atomics on
+//   * one persistent CTA per SM owns a contiguous range of 16-row tiles. Its work is counted in units
+//     (one tile x one stage of K) laid out tile after tile, and every warp takes an equal, contiguous
+//     share of the units, whatever the number of tiles: a share may end in the middle of a tile and the
+//     next warp carries on from there. Each warp is a pipeline of its own: lane 0 keeps a ring of TMA
+//     box loads in flight (16 rows x 256 bytes of packed quants, 128B-swizzled, plus the rows' f16
+//     scales of the same K range; completion on the stage's mbarrier), so the bytes in flight per SM are
+//     set by the rings (about 130 KB), not by registers, and no warp waits for another. The pieces of a
+//     tile that was cut are added up by whichever warp brings the last one, in K order (no atomics on
 //     the values: repeated runs are bit-identical);
 //   * lane (g, t) reads 16 bytes of two rows and unpacks them into A fragments of
 //     mma.sync.m16n8k16 (fp16 in, f32 accumulate). The quants are small integers, exact in fp16;
@@ -37,18 +38,17 @@ namespace {
 
 constexpr int MAX_STAGES = 8;
 constexpr int TILE_ROWS = 16;
-constexpr int TBUF = 4;                          // tiles whose K slices may be pending at once
-constexpr int MAX_SLICES = 32;
 constexpr int XR = 32;                           // elements of x one thread stages, at most
 constexpr uint32_t HDR_BYTES = 2304;             // norm scratch, zero region, slice counters, barriers
-constexpr uint32_t CNT_OFF = 640;                // uint32 count[TBUF], gen[TBUF]
+constexpr uint32_t CNT_OFF = 640;                // uint32 [MAX_WARPS]: pieces of a cut tile that have arrived
+constexpr int MAX_WARPS = 16;
 constexpr uint32_t NORM_RED_OFF = 128;           // float [32]
 constexpr uint32_t ZERO_OFF = 512;               // 128 zero bytes (the B operand of lanes whose column belongs to another block)
 constexpr uint32_t BAR_OFF = 1024;               // uint64 [MAX_WARPS][MAX_STAGES]
 constexpr uint32_t SMEM_LIMIT = 227 * 1024;
 
 struct Plan {
-  uint32_t grid, tile_base, tile_rem, n_stage_iters, ipi, ks, n_stages, kpad, x_off_lo, xs_off, part_off, ring_off, sc_off, sc_stage;
+  uint32_t grid, tile_base, tile_rem, n_stage_iters, n_stages, kpad, x_off_lo, xs_off, part_off, ring_off, sc_off, sc_stage;
   size_t smem;
 };
 
@@ -143,6 +143,7 @@ __global__ void __launch_bounds__(NW * 32, 1)
   uint8_t* smem = smem_raw + (base - tc::smem_u32(smem_raw));
   constexpr bool BYTES = kind_byte_blocks(KIND);      // one byte per weight (else half a byte)
   constexpr int WARPS = NW, THREADS = NW * 32;
+  static_assert(NW <= MAX_WARPS, "the piece counters are one per warp");
   constexpr uint32_t W_STAGE = TILE_ROWS * LINES * 128;
   constexpr uint32_t SC_PER_STAGE = (BYTES ? 4u : 8u) * LINES; // blocks of one row in a stage
   constexpr uint32_t SC_STAGE = TILE_ROWS * SC_PER_STAGE * 2;
@@ -158,16 +159,19 @@ __global__ void __launch_bounds__(NW * 32, 1)
   // this CTA's tiles: tile_base each, one more for the first tile_rem CTAs
   const uint32_t t0 = blockIdx.x * pl.tile_base + min(blockIdx.x, pl.tile_rem);
   const uint32_t n_tiles = pl.tile_base + (blockIdx.x < pl.tile_rem ? 1u : 0u);
-  // work items: K slices of `ipi` stage iterations; item id -> (tile t0 + id / KS, slice id % KS)
-  const uint32_t KS = pl.ks, ipi = pl.ipi, n_items = n_tiles * KS;
-  volatile uint32_t* cnt = reinterpret_cast<volatile uint32_t*>(smem + CNT_OFF);
-  volatile uint32_t* gen = cnt + TBUF;
-  float* part = reinterpret_cast<float*>(smem + pl.part_off); // [TBUF][KS][16]
+  // work units: unit u is stage iteration u % iters of tile t0 + u / iters. Warp w of the `weff` warps that work
+  // takes units [U w / weff, U (w + 1) / weff): never empty, since weff <= U
+  const uint32_t iters = pl.n_stage_iters;
+  const uint32_t U = n_tiles * iters, weff = min((uint32_t)NW, U);
+  auto begin_of = [&](uint32_t w) { return (uint32_t)((uint64_t)U * w / weff); };
+  auto warp_of = [&](uint32_t u) { return (uint32_t)((((uint64_t)u + 1) * weff - 1) / U); }; // whose share holds unit u
+  uint32_t* cnt = reinterpret_cast<uint32_t*>(smem + CNT_OFF);
+  float* part = reinterpret_cast<float*>(smem + pl.part_off); // [2 * warps][16]: a warp's first and last piece
 
   if (threadIdx.x == 0) {
     tc::prefetch_tmap(&tmap_w);
     tc::prefetch_tmap(&tmap_s);
-    for (int i = 0; i < 2 * TBUF; i++) cnt[i] = 0u;
+    for (int i = 0; i < MAX_WARPS; i++) cnt[i] = 0u;
   }
   if (lane == 0) {
     for (uint32_t s = 0; s < S; s++) tc::mbar_init(&full[s], 1);
@@ -177,7 +181,6 @@ __global__ void __launch_bounds__(NW * 32, 1)
   __syncwarp();
 
   // Loads of (tile, stage iteration) pairs, in the order this warp will consume them.
-  const uint32_t iters = pl.n_stage_iters;
   const uint32_t ring_u32 = tc::smem_u32(ring), sc_u32 = tc::smem_u32(sc_ring), full_u32 = tc::smem_u32(full);
   auto issue = [&](uint32_t tile, uint32_t si, uint32_t it) { // lane 0 only
     const uint32_t s = it % S;
@@ -196,22 +199,26 @@ __global__ void __launch_bounds__(NW * 32, 1)
                  : "memory");
   };
 
-  // Warp w takes items w, w + WARPS, ... The prologue of its ring goes out before x is staged: the weight stream
-  // starts at once. (ahead_id, ahead_si) is the next load to issue, ahead_it its running number.
+  // The prologue of the warp's ring goes out before x is staged: the weight stream starts at once.
+  // (ahead_tl, ahead_si) is the next load to issue, ahead_it its running number, ahead_left the loads still to issue.
   const bool dead = *err_flag != 0; // an earlier launch gave up: do not wait again
-  uint32_t ahead_id = warp, ahead_si = (warp % KS) * ipi, ahead_it = 0;
+  const bool works = (uint32_t)warp < weff;
+  const uint32_t u_begin = works ? begin_of(warp) : 0u, u_end = works ? begin_of(warp + 1) : 0u;
+  const uint32_t tl_first = u_begin / iters;
+  uint32_t ahead_tl = tl_first, ahead_si = u_begin - tl_first * iters, ahead_it = 0, ahead_left = u_end - u_begin;
   auto run_ahead = [&](uint32_t it) { // lane 0: fill every slot whose previous use (iteration < it) is over
-    while (ahead_it < it + S && ahead_id < n_items) {
-      const uint32_t slice = ahead_id % KS;
-      issue(t0 + ahead_id / KS, ahead_si, ahead_it);
-      ahead_it++;
-      if (++ahead_si == min(iters, (slice + 1) * ipi)) {
-        ahead_id += WARPS;
-        ahead_si = (ahead_id % KS) * ipi;
-      }
+    while (ahead_it < it + S && ahead_left) {
+      issue(t0 + ahead_tl, ahead_si, ahead_it);
+      ahead_it++, ahead_left--;
+      if (++ahead_si == iters) ahead_si = 0, ahead_tl++;
     }
   };
   if (lane == 0 && !dead) run_ahead(0);
+  // The launch may overlap the end of the kernel before it in the stream (programmatic dependent launch): the
+  // weights are never written by a kernel, so their stream could start above; x, y and the residual may be that
+  // kernel's results and are touched only below this wait. The kernel after this one may begin its own prologue.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // x -> hi / lo fp16 terms in shared memory: the RMSNorm / LayerNorm of x first when the product is fed the raw
   // residual stream, then a power-of-two scale that brings max |x| into [1024, 2048) (both terms keep their
@@ -314,15 +321,18 @@ __global__ void __launch_bounds__(NW * 32, 1)
   const bool act1 = BYTES ? (g >= 4 && ((g - 4) >> 1) == (t >> 1)) : act0;
   constexpr uint32_t XSTEP = BYTES ? 128u : 256u; // bytes of one x term per step
   const uint8_t* x_lane = x_term + (BYTES ? t * 32u : t * 64u);
-  const uint8_t* bx_base[2] = {act0 ? x_lane : zero, act1 ? x_lane : zero};
+  // (lanes that read zeros read them from banks the x values of their quarter-warp do not use)
+  const uint8_t* zero_lane = zero + (BYTES ? ((g & 2) ? 0u : 64u) : 32u);
+  const uint8_t* bx_base[2] = {act0 ? x_lane : zero_lane, act1 ? x_lane : zero_lane};
   const uint32_t bx_mul[2] = {act0 ? 1u : 0u, act1 ? 1u : 0u};
 
   uint32_t it = 0;
-  for (uint32_t id = warp; id < n_items; id += WARPS) {
-    const uint32_t tl = id / KS, slice = id % KS, tile = t0 + tl;
-    const uint32_t si_end = min(iters, (slice + 1) * ipi);
+  for (uint32_t u = u_begin; u < u_end;) { // one piece per pass: the units of this share that belong to one tile
+    const uint32_t tl = u / iters, si_begin = u - tl * iters, tile = t0 + tl;
+    const uint32_t si_end = min(iters, si_begin + (u_end - u));
+    u += si_end - si_begin;
     float acc_g = 0.0f, acc_g8 = 0.0f;
-    for (uint32_t si = slice * ipi; si < si_end; si++, it++) {
+    for (uint32_t si = si_begin; si < si_end; si++, it++) {
       if (lane == 0) run_ahead(it); // the slot of iteration it - 1 is free: every lane passed the __syncwarp below
       const uint32_t s = it % S;
       if (!tc::mbar_wait(&full[s], (it / S) & 1)) {
@@ -448,49 +458,34 @@ __global__ void __launch_bounds__(NW * 32, 1)
       if (ep.resid) v = ep.resid[row] + v;
       y[row] = v;
     };
-    if (KS == 1) {
+    if (si_begin == 0 && si_end == iters) { // the whole tile was this warp's
       if (t < 2) finish(tile * TILE_ROWS + rho + (t ? 8u : 0u), t ? acc_g8 : acc_g);
       continue;
     }
-    // K slices: leave the partial sums in the tile's buffer; the warp that brings the last slice adds them up in
-    // slice order. A buffer is reused every TBUF tiles: wait (bounded) until its previous tile has been finished.
-    const uint32_t buf = tl % TBUF, use = tl / TBUF;
-    uint32_t ready = 1;
-    if (lane == 0) {
-      ready = 0;
-      for (uint32_t spin = 0; spin < tc::WAIT_LIMIT; spin++)
-        if (gen[buf] >= use) {
-          ready = 1;
-          break;
-        }
-    }
-    if (!__shfl_sync(0xffffffffu, ready, 0)) {
-      if (lane == 0) *err_flag = 1;
-      return;
-    }
-    float* pb = part + (buf * KS) * TILE_ROWS;
+    // A cut tile: its pieces belong to the consecutive warps wa..wb. Each leaves its partial sums in a slot of its
+    // own (a warp has at most two pieces of cut tiles: its first and its last) and counts itself in at wa's counter,
+    // which no other tile uses; the warp that arrives last adds the pieces up in K order.
+    const uint32_t wa = warp_of(tl * iters), wb = warp_of(tl * iters + iters - 1);
+    float* mine = part + (2 * warp + (tl != tl_first ? 1 : 0)) * TILE_ROWS;
     if (t == 0) {
-      pb[slice * TILE_ROWS + rho] = acc_g;
-      pb[slice * TILE_ROWS + rho + 8] = acc_g8;
+      mine[rho] = acc_g;
+      mine[rho + 8] = acc_g8;
     }
     __syncwarp();
     uint32_t last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(const_cast<uint32_t*>(&cnt[buf]), 1u) == KS - 1 ? 1u : 0u;
+      last = atomicAdd(&cnt[wa], 1u) == wb - wa ? 1u : 0u;
     }
     if (__shfl_sync(0xffffffffu, last, 0)) {
       __threadfence_block();
       if (lane < TILE_ROWS) {
         float v = 0.0f;
-        for (uint32_t sl = 0; sl < KS; sl++) v += pb[sl * TILE_ROWS + lane];
+        for (uint32_t w2 = wa; w2 <= wb; w2++) {
+          const uint32_t slot = 2 * w2 + (tl != begin_of(w2) / iters ? 1u : 0u);
+          v += const_cast<const volatile float*>(part)[slot * TILE_ROWS + lane];
+        }
         finish(tile * TILE_ROWS + lane, v);
-      }
-      __syncwarp();
-      if (lane == 0) {
-        cnt[buf] = 0u;
-        __threadfence_block();
-        gen[buf] = use + 1;
       }
     }
   }
@@ -521,19 +516,13 @@ bool make_plan(const FcDevice* dev, const QMat& w, Plan& p) {
   const uint32_t w_stage = TILE_ROWS * lines * 128;
   p.sc_stage = TILE_ROWS * (bytes ? 4u : 8u) * lines * 2;
   p.n_stage_iters = (row_bytes + lines * 128 - 1) / (lines * 128);
-  // K slices only while a CTA has fewer tiles than warps: about one item per warp, each many stages long, so that
-  // the hand-over of partial sums is rare
-  const uint32_t t_max = p.tile_base + (p.tile_rem ? 1u : 0u);
-  uint32_t ks = nw / t_max;
-  ks = ks < 1 ? 1 : ks > MAX_SLICES ? MAX_SLICES : ks;
-  ks = ks > p.n_stage_iters ? p.n_stage_iters : ks;
-  p.ipi = (p.n_stage_iters + ks - 1) / ks;
-  p.ks = (p.n_stage_iters + p.ipi - 1) / p.ipi;
+  // (the kernel counts a CTA's work units, tiles x stage iterations, in 32 bits)
+  if ((uint64_t)(p.tile_base + 1) * p.n_stage_iters >= (1ull << 31)) return false;
   p.kpad = p.n_stage_iters * lines * (bytes ? 128u : 256u); // x is zero past k where a stage reaches past the row
   p.x_off_lo = HDR_BYTES + 2 * p.kpad + 16;          // the lo term 16 bytes off the hi term's banks
   p.xs_off = align_up(p.x_off_lo + 2 * p.kpad, 16);  // per-block sums of x (those past k are never read)
   p.part_off = align_up(p.xs_off + p.kpad / 32 * 4, 16);
-  p.ring_off = align_up(p.part_off + TBUF * p.ks * TILE_ROWS * 4, 1024);
+  p.ring_off = align_up(p.part_off + 2 * nw * TILE_ROWS * 4, 1024);
   const uint32_t per_stage = nw * (w_stage + p.sc_stage);
   if (p.ring_off + 2 * per_stage + 1024 > SMEM_LIMIT) return false;
   p.n_stages = (SMEM_LIMIT - 1024 - p.ring_off) / per_stage;
@@ -589,7 +578,13 @@ int launch_cfg(FcDevice* dev, const QMat& w, const float* x, float* y, const Epi
   auto kern = qmatvec1_kernel<KIND, NW, LINES>;
   static OncePerDevice attr;
   if (attr.first(dev->ordinal)) FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
-  FC_LAUNCH(dev, "qmatvec1", kern<<<p.grid, NW * 32, p.smem, dev->stream>>>(tw, ts, w.k, w.n, x, y, ep, p, dev->d_flag));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.grid), cfg.blockDim = dim3(NW * 32), cfg.dynamicSmemBytes = p.smem, cfg.stream = dev->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; // see the kernel's griddepcontrol.wait
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at, cfg.numAttrs = 1;
+  FC_LAUNCH(dev, "qmatvec1", cudaLaunchKernelEx(&cfg, kern, tw, ts, w.k, w.n, x, y, ep, p, dev->d_flag));
   return FC_OK;
 }
 
