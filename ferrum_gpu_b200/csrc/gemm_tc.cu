@@ -32,6 +32,23 @@ constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 column
 constexpr int REGS_CTRL = 40, REGS_PROD = 64, REGS_EPI = 152;
 constexpr int REGS_NEEDED = 32 * (4 * REGS_CTRL + 8 * REGS_PROD + 8 * REGS_EPI);
 
+// The kernel with the weights on the tensor-memory lanes (gemm_ts_main.cuh)
+constexpr uint32_t TS_BX = 192;                   // activation rows per tile: the MMA's N
+constexpr int X_STAGES = 6, W_STAGES = 4;
+constexpr uint32_t X_BYTES = TS_BX * TC_BK * 2;   // 24 KB: one TMA box
+constexpr uint32_t W_COLS = TC_BK / 2;            // tensor-memory columns of one weight stage (two f16 per column)
+constexpr uint32_t W_COL0 = 2 * TS_BX;            // after the two accumulator buffers
+static_assert(W_COL0 + W_STAGES * W_COLS <= 512, "tensor memory has 512 columns");
+constexpr uint32_t STG_OFF = X_STAGES * X_BYTES + 512; // after the rings and the barriers
+constexpr uint32_t STG_TILE = 32 * 32 * 4;        // one staged chunk of an epilogue warp (two per warp)
+constexpr uint32_t TS_SMEM_BYTES = STG_OFF + 8 * 2 * STG_TILE + 1024 /*alignment slack*/;
+constexpr int PSETS = 3;                          // producer sets of four warps
+constexpr int TS_THREADS = (4 + 4 * PSETS + 8) * 32;
+// setmaxnreg targets: 4 control warps, 4 * PSETS producer warps, 8 epilogue warps; the sum must fit the registers
+// the CTA is launched with (checked before the first launch)
+constexpr int TS_REGS_PROD = 64, TS_REGS_EPI = 120;
+constexpr int TS_REGS_NEEDED = 32 * (4 * REGS_CTRL + 4 * PSETS * TS_REGS_PROD + 8 * TS_REGS_EPI);
+
 enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
 
 // Both operands are fp16 (f32 accumulation). The block scale is an f16 and a quant has at most 8
@@ -54,35 +71,62 @@ __device__ __forceinline__ uint32_t f16x2_mul(uint32_t a, uint32_t b) {
   return r;
 }
 
-// One 32-element Q4_0 block (4 words, device nibble order) -> 4 chunks of 8 fp16 at `row_smem`,
-// chunk index c0..c0+3 of the 128-byte row, XOR-swizzled with the row number.
-__device__ __forceinline__ void dequant_q4_block(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+// Where a dequantised weight row goes, 16 bytes (eight f16 along K) at a time; chunk c covers k = 8c .. 8c + 7
+// of the 64-k slice and the chunks of a row come in ascending order.
+//
+// Into tensor memory: the row is one lane, the slice 32 columns of two f16 each; the sink gathers the four chunks
+// of a 32-k block and writes them with one 16-column store.
+// Into the shared-memory ring of the kernel that reads both operands from there: the K-major layout TMA produces,
+// 128-byte rows whose 16-byte chunks are XORed with the row number (128B swizzle).
+struct SmemSink {
+  uint32_t row_smem, sw;
+  template <int C>
+  __device__ __forceinline__ void put(uint32_t o0, uint32_t o1, uint32_t o2, uint32_t o3) {
+    const uint32_t addr = row_smem + ((((uint32_t)C) ^ sw) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
+  }
+};
+struct TmemSink {
+  uint32_t taddr; // lane base of this warp | first column of the stage
+  uint32_t v[16];
+  template <int C>
+  __device__ __forceinline__ void put(uint32_t o0, uint32_t o1, uint32_t o2, uint32_t o3) {
+    v[(C & 3) * 4 + 0] = o0, v[(C & 3) * 4 + 1] = o1, v[(C & 3) * 4 + 2] = o2, v[(C & 3) * 4 + 3] = o3;
+    if ((C & 3) == 3) tc::tmem_st_32x16(taddr + (C >> 2) * 16, v);
+  }
+};
+
+// One 32-element Q4_0 block (4 words, device nibble order) -> chunks C0 .. C0 + 3
+template <int C0, class Sink>
+__device__ __forceinline__ void dequant_q4_block(const uint4& q, __half d, Sink& sink) {
   const uint32_t dd = (uint32_t)__half_as_ushort(d) * 0x00010001u; // the f16 scale in both halves
   const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int w = 0; w < 4; w++) {
-    uint32_t o[4];
-#pragma unroll
-    for (int p = 0; p < 4; p++) {
-      // nibbles p and p+4 of the word are elements 2p and 2p+1: 0x6400 | nib is the fp16 1024 + nib
-      uint32_t t = ((words[w] >> (4 * p)) & 0x000f000fu) | 0x64006400u;
-      t = f16x2_sub(t, 0x64086408u); // - 1032: exact, (nib - 8)
-      o[p] = f16x2_mul(t, dd);        // one rounding
-    }
-    const uint32_t addr = row_smem + (((c0 + w) ^ sw) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-  }
+  auto one = [&](uint32_t w, uint32_t (&o)[4]) {
+    // nibbles p and p+4 of the word are elements 2p and 2p+1. In the low four mantissa bits of 0x6400 a nibble
+    // makes the fp16 1024 + nib, four bits higher under 0x5400 it makes 64 + nib: no shift for the odd places
+    const uint32_t w8 = w >> 8;
+    const uint32_t t0 = (w & 0x000f000fu) | 0x64006400u, t1 = (w & 0x00f000f0u) | 0x54005400u;
+    const uint32_t t2 = (w8 & 0x000f000fu) | 0x64006400u, t3 = (w8 & 0x00f000f0u) | 0x54005400u;
+    o[0] = f16x2_mul(f16x2_sub(t0, 0x64086408u), dd); // - 1032: exact, (nib - 8); then one rounding
+    o[1] = f16x2_mul(f16x2_sub(t1, 0x54805480u), dd); // - 72
+    o[2] = f16x2_mul(f16x2_sub(t2, 0x64086408u), dd);
+    o[3] = f16x2_mul(f16x2_sub(t3, 0x54805480u), dd);
+  };
+  uint32_t o[4];
+  one(words[0], o), sink.template put<C0>(o[0], o[1], o[2], o[3]);
+  one(words[1], o), sink.template put<C0 + 1>(o[0], o[1], o[2], o[3]);
+  one(words[2], o), sink.template put<C0 + 2>(o[0], o[1], o[2], o[3]);
+  one(words[3], o), sink.template put<C0 + 3>(o[0], o[1], o[2], o[3]);
 }
 
-// 16 int8 quants (one uint4 = half a Q8_0 block) -> 2 chunks
-__device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
-  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int h = 0; h < 2; h++) {
-    uint32_t o[4];
+// 16 int8 quants (one uint4 = half a Q8_0 block) -> chunks C0, C0 + 1
+template <int C0, class Sink>
+__device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, Sink& sink) {
+  auto one = [&](uint32_t wa, uint32_t wb, uint32_t (&o)[4]) {
+    const uint32_t w2[2] = {wa, wb};
 #pragma unroll
     for (int w = 0; w < 2; w++) {
-      const uint32_t u = words[2 * h + w] ^ 0x80808080u;
+      const uint32_t u = w2[w] ^ 0x80808080u;
       const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
       const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
       const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
@@ -90,45 +134,45 @@ __device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, uint32_
       o[2 * w] = pack_f16(f0 * d, f1 * d);
       o[2 * w + 1] = pack_f16(f2 * d, f3 * d);
     }
-    const uint32_t addr = row_smem + (((c0 + h) ^ sw) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-  }
+  };
+  uint32_t o[4];
+  one(q.x, q.y, o), sink.template put<C0>(o[0], o[1], o[2], o[3]);
+  one(q.z, q.w, o), sink.template put<C0 + 1>(o[0], o[1], o[2], o[3]);
 }
 
-// One 32-element MXFP4 block (4 words, element order) -> 4 chunks: E2M1 value times the power-of-two
+// One 32-element MXFP4 block (4 words, element order) -> chunks C0 .. C0 + 3: E2M1 value times the power-of-two
 // scale in f32 (the scale itself need not be an fp16 value), saturated to fp16
-__device__ __forceinline__ void dequant_mxfp4_block(const uint4& q, float d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
-  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int w = 0; w < 4; w++) {
-    uint32_t h[4], o[4];
-    e2m1x8_to_f16x2(words[w], h);
+template <int C0, class Sink>
+__device__ __forceinline__ void dequant_mxfp4_block(const uint4& q, float d, Sink& sink) {
+  auto one = [&](uint32_t w, uint32_t (&o)[4]) {
+    uint32_t h[4];
+    e2m1x8_to_f16x2(w, h);
 #pragma unroll
     for (int p = 0; p < 4; p++) {
       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[p]));
       o[p] = pack_f16(f.x * d, f.y * d);
     }
-    const uint32_t addr = row_smem + (((c0 + w) ^ sw) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-  }
+  };
+  uint32_t o[4];
+  one(q.x, o), sink.template put<C0>(o[0], o[1], o[2], o[3]);
+  one(q.y, o), sink.template put<C0 + 1>(o[0], o[1], o[2], o[3]);
+  one(q.z, o), sink.template put<C0 + 2>(o[0], o[1], o[2], o[3]);
+  one(q.w, o), sink.template put<C0 + 3>(o[0], o[1], o[2], o[3]);
 }
 
-// 16 FP8 codes (half a block) -> 2 chunks: code -> fp16 exactly, times the f16 scale, one rounding
-template <int KIND>
-__device__ __forceinline__ void dequant_fp8_half(const uint4& q, __half d, uint32_t row_smem, uint32_t sw, uint32_t c0) {
+// 16 FP8 codes (half a block) -> chunks C0, C0 + 1: code -> fp16 exactly, times the f16 scale, one rounding
+template <int KIND, int C0, class Sink>
+__device__ __forceinline__ void dequant_fp8_half(const uint4& q, __half d, Sink& sink) {
   const uint32_t dd = (uint32_t)__half_as_ushort(d) * 0x00010001u;
-  const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-  for (int h = 0; h < 2; h++) {
-    uint32_t o[4];
-#pragma unroll
-    for (int w = 0; w < 2; w++) {
-      o[2 * w] = f16x2_mul(fp8x2_to_f16x2<KIND>(words[2 * h + w]), dd);
-      o[2 * w + 1] = f16x2_mul(fp8x2_to_f16x2<KIND>(words[2 * h + w] >> 16), dd);
-    }
-    const uint32_t addr = row_smem + (((c0 + h) ^ sw) << 4);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-  }
+  auto one = [&](uint32_t wa, uint32_t wb, uint32_t (&o)[4]) {
+    o[0] = f16x2_mul(fp8x2_to_f16x2<KIND>(wa), dd);
+    o[1] = f16x2_mul(fp8x2_to_f16x2<KIND>(wa >> 16), dd);
+    o[2] = f16x2_mul(fp8x2_to_f16x2<KIND>(wb), dd);
+    o[3] = f16x2_mul(fp8x2_to_f16x2<KIND>(wb >> 16), dd);
+  };
+  uint32_t o[4];
+  one(q.x, q.y, o), sink.template put<C0>(o[0], o[1], o[2], o[3]);
+  one(q.z, q.w, o), sink.template put<C0 + 1>(o[0], o[1], o[2], o[3]);
 }
 
 __device__ __forceinline__ float gelu_f(float x) {
@@ -211,73 +255,79 @@ __device__ __forceinline__ void load_row(RowRegs<KIND>& r, const QMat& w, uint32
   }
 }
 
-template <int KIND>
-__device__ __forceinline__ void store_row(const RowRegs<KIND>& r, uint32_t row_smem, uint32_t sw) {
+template <int KIND, class Sink>
+__device__ __forceinline__ void emit_row(const RowRegs<KIND>& r, Sink& sink) {
   if (KIND == FC_Q4_0) {
     const RowRegs<FC_Q4_0>& rr = (const RowRegs<FC_Q4_0>&)r;
     const __half d0 = __ushort_as_half((unsigned short)(rr.sc & 0xffff)), d1 = __ushort_as_half((unsigned short)(rr.sc >> 16));
-    dequant_q4_block(rr.q[0], d0, row_smem, sw, 0);
-    dequant_q4_block(rr.q[1], d1, row_smem, sw, 4);
+    dequant_q4_block<0>(rr.q[0], d0, sink);
+    dequant_q4_block<4>(rr.q[1], d1, sink);
   } else if (KIND == FC_Q8_0) {
     const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
     const float d0 = __half2float(__ushort_as_half((unsigned short)(rr.sc & 0xffff)));
     const float d1 = __half2float(__ushort_as_half((unsigned short)(rr.sc >> 16)));
-    dequant_q8_half(rr.q[0], d0, row_smem, sw, 0);
-    dequant_q8_half(rr.q[1], d0, row_smem, sw, 2);
-    dequant_q8_half(rr.q[2], d1, row_smem, sw, 4);
-    dequant_q8_half(rr.q[3], d1, row_smem, sw, 6);
+    dequant_q8_half<0>(rr.q[0], d0, sink);
+    dequant_q8_half<2>(rr.q[1], d0, sink);
+    dequant_q8_half<4>(rr.q[2], d1, sink);
+    dequant_q8_half<6>(rr.q[3], d1, sink);
   } else if (KIND == FC_Q2_K) { // (d * sc) * q - dmin * m in f32, one rounding to fp16
     const RowRegs<FC_Q2_K>& rr = (const RowRegs<FC_Q2_K>&)r;
     const float d = __half2float(__ushort_as_half((unsigned short)(rr.dd & 0xffffu)));
     const float dmin = __half2float(__ushort_as_half((unsigned short)(rr.dd >> 16)));
-    const uint32_t words[4] = {rr.q[0].x, rr.q[0].y, rr.q[0].z, rr.q[0].w};
+    auto one = [&](uint32_t word, uint32_t scb, int h, uint32_t (&o)[4]) {
+      const float dl = d * (float)(scb & 15u), ml = dmin * (float)(scb >> 4);
+      const uint32_t b = word >> (16 * h);
 #pragma unroll
-    for (int j = 0; j < 4; j++) {
-      const uint32_t sc = (rr.sc >> (8 * j)) & 0xffu;
-      const float dl = d * (float)(sc & 15u), ml = dmin * (float)(sc >> 4);
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        const uint32_t b = words[j] >> (16 * h);
-        uint32_t o[4];
-#pragma unroll
-        for (int p = 0; p < 4; p++)
-          o[p] = pack_f16(fmaf(dl, (float)((b >> (4 * p)) & 3u), -ml), fmaf(dl, (float)((b >> (4 * p + 2)) & 3u), -ml));
-        const uint32_t addr = row_smem + (((uint32_t)(2 * j + h) ^ sw) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-      }
-    }
+      for (int p = 0; p < 4; p++)
+        o[p] = pack_f16(fmaf(dl, (float)((b >> (4 * p)) & 3u), -ml), fmaf(dl, (float)((b >> (4 * p + 2)) & 3u), -ml));
+    };
+    uint32_t o[4];
+    one(rr.q[0].x, rr.sc & 0xffu, 0, o), sink.template put<0>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].x, rr.sc & 0xffu, 1, o), sink.template put<1>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].y, (rr.sc >> 8) & 0xffu, 0, o), sink.template put<2>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].y, (rr.sc >> 8) & 0xffu, 1, o), sink.template put<3>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].z, (rr.sc >> 16) & 0xffu, 0, o), sink.template put<4>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].z, (rr.sc >> 16) & 0xffu, 1, o), sink.template put<5>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].w, rr.sc >> 24, 0, o), sink.template put<6>(o[0], o[1], o[2], o[3]);
+    one(rr.q[0].w, rr.sc >> 24, 1, o), sink.template put<7>(o[0], o[1], o[2], o[3]);
   } else if (KIND == FC_MXFP4) {
     const RowRegs<FC_Q4_0>& rr = (const RowRegs<FC_Q4_0>&)r;
-    dequant_mxfp4_block(rr.q[0], __uint_as_float(rr.sc << 16), row_smem, sw, 0);
-    dequant_mxfp4_block(rr.q[1], __uint_as_float(rr.sc & 0xffff0000u), row_smem, sw, 4);
+    dequant_mxfp4_block<0>(rr.q[0], __uint_as_float(rr.sc << 16), sink);
+    dequant_mxfp4_block<4>(rr.q[1], __uint_as_float(rr.sc & 0xffff0000u), sink);
   } else if (kind_is_fp8(KIND)) {
     const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
     const __half d0 = __ushort_as_half((unsigned short)(rr.sc & 0xffff)), d1 = __ushort_as_half((unsigned short)(rr.sc >> 16));
-    dequant_fp8_half<KIND>(rr.q[0], d0, row_smem, sw, 0);
-    dequant_fp8_half<KIND>(rr.q[1], d0, row_smem, sw, 2);
-    dequant_fp8_half<KIND>(rr.q[2], d1, row_smem, sw, 4);
-    dequant_fp8_half<KIND>(rr.q[3], d1, row_smem, sw, 6);
-  } else if (KIND == FC_F16) { // stored values are the operand: eight 16-byte pieces into their swizzled places
+    dequant_fp8_half<KIND, 0>(rr.q[0], d0, sink);
+    dequant_fp8_half<KIND, 2>(rr.q[1], d0, sink);
+    dequant_fp8_half<KIND, 4>(rr.q[2], d1, sink);
+    dequant_fp8_half<KIND, 6>(rr.q[3], d1, sink);
+  } else if (KIND == FC_F16) { // stored values are the operand
     const RowRegs<FC_F16>& rr = (const RowRegs<FC_F16>&)r;
-#pragma unroll
-    for (int c = 0; c < 8; c++) {
-      const uint32_t addr = row_smem + (((uint32_t)c ^ sw) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(rr.q[c].x), "r"(rr.q[c].y), "r"(rr.q[c].z),
-                   "r"(rr.q[c].w)
-                   : "memory");
-    }
+    sink.template put<0>(rr.q[0].x, rr.q[0].y, rr.q[0].z, rr.q[0].w);
+    sink.template put<1>(rr.q[1].x, rr.q[1].y, rr.q[1].z, rr.q[1].w);
+    sink.template put<2>(rr.q[2].x, rr.q[2].y, rr.q[2].z, rr.q[2].w);
+    sink.template put<3>(rr.q[3].x, rr.q[3].y, rr.q[3].z, rr.q[3].w);
+    sink.template put<4>(rr.q[4].x, rr.q[4].y, rr.q[4].z, rr.q[4].w);
+    sink.template put<5>(rr.q[5].x, rr.q[5].y, rr.q[5].z, rr.q[5].w);
+    sink.template put<6>(rr.q[6].x, rr.q[6].y, rr.q[6].z, rr.q[6].w);
+    sink.template put<7>(rr.q[7].x, rr.q[7].y, rr.q[7].z, rr.q[7].w);
   } else {
     const RowRegs<FC_F32>& rr = (const RowRegs<FC_F32>&)r;
-#pragma unroll
-    for (int c = 0; c < 8; c++) {
-      const uint4 a = rr.q[2 * c], b = rr.q[2 * c + 1];
-      const uint32_t o0 = pack_f16(__uint_as_float(a.x), __uint_as_float(a.y));
-      const uint32_t o1 = pack_f16(__uint_as_float(a.z), __uint_as_float(a.w));
-      const uint32_t o2 = pack_f16(__uint_as_float(b.x), __uint_as_float(b.y));
-      const uint32_t o3 = pack_f16(__uint_as_float(b.z), __uint_as_float(b.w));
-      const uint32_t addr = row_smem + (((uint32_t)c ^ sw) << 4);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o0), "r"(o1), "r"(o2), "r"(o3) : "memory");
-    }
+    auto one = [&](const uint4& a, const uint4& b, uint32_t (&o)[4]) {
+      o[0] = pack_f16(__uint_as_float(a.x), __uint_as_float(a.y));
+      o[1] = pack_f16(__uint_as_float(a.z), __uint_as_float(a.w));
+      o[2] = pack_f16(__uint_as_float(b.x), __uint_as_float(b.y));
+      o[3] = pack_f16(__uint_as_float(b.z), __uint_as_float(b.w));
+    };
+    uint32_t o[4];
+    one(rr.q[0], rr.q[1], o), sink.template put<0>(o[0], o[1], o[2], o[3]);
+    one(rr.q[2], rr.q[3], o), sink.template put<1>(o[0], o[1], o[2], o[3]);
+    one(rr.q[4], rr.q[5], o), sink.template put<2>(o[0], o[1], o[2], o[3]);
+    one(rr.q[6], rr.q[7], o), sink.template put<3>(o[0], o[1], o[2], o[3]);
+    one(rr.q[8], rr.q[9], o), sink.template put<4>(o[0], o[1], o[2], o[3]);
+    one(rr.q[10], rr.q[11], o), sink.template put<5>(o[0], o[1], o[2], o[3]);
+    one(rr.q[12], rr.q[13], o), sink.template put<6>(o[0], o[1], o[2], o[3]);
+    one(rr.q[14], rr.q[15], o), sink.template put<7>(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -482,6 +532,7 @@ __device__ __forceinline__ void epilogue_lse(const TcArgs& a, LseState& s, uint3
 }
 
 #include "gemm_tc_main.cuh"
+#include "gemm_ts_main.cuh"
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point: the library carries no link
 // dependency on libcuda, so it still loads (and exports its symbols) on a machine without a GPU.
@@ -521,6 +572,56 @@ int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArg
   return FC_OK;
 }
 
+template <int KIND, int EPI>
+int launch_ts(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, TcArgs a, dim3 grid) {
+  // The output as a TMA tensor of 32 x 32 boxes (16 columns wide for SwiGLU's halved output), when its base and
+  // row pitch are whole 16 bytes; otherwise the epilogue stores from registers.
+  CUtensorMap tmap_o = tmap;
+  {
+    const bool f32 = EPI == EPI_F32 || EPI == EPI_RESID;
+    void* out = f32 ? (void*)a.out_f32 : (void*)a.out_f16;
+    const uint64_t pitch = (uint64_t)a.ldo * (f32 ? 4 : 2);
+    const uint64_t cols = EPI == EPI_SWIGLU ? w.n / 2 : w.n;
+    if (out && pitch % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && cols > 0) {
+      const cuuint64_t dims[2] = {cols, a.m};
+      const cuuint64_t strides[1] = {pitch};
+      const cuuint32_t box[2] = {EPI == EPI_SWIGLU ? 16u : 32u, 32u};
+      const cuuint32_t estr[2] = {1, 1};
+      CUresult cr = encode_fn()(&tmap_o, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, out, dims, strides,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+      if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled (output) failed with %d", (int)cr);
+      a.out_tma = 1;
+    }
+  }
+  auto kern = qgemm_ts_kernel<KIND, EPI>;
+  static OncePerDevice attr; // one per instantiation
+  if (attr.first(dev->ordinal)) {
+    attr.again(dev->ordinal); // (until the checks below have passed)
+    cudaFuncAttributes fa;
+    FC_CUDA(dev, cudaFuncGetAttributes(&fa, kern));
+    if (fa.numRegs * TS_THREADS < TS_REGS_NEEDED)
+      return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product was compiled with %d registers per thread; its register "
+                     "rebalancing needs %d", fa.numRegs, (TS_REGS_NEEDED + TS_THREADS - 1) / TS_THREADS);
+    FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TS_SMEM_BYTES));
+    attr.first(dev->ordinal);
+  }
+  static const char* const names[] = {"qgemm_tc_f32", "qgemm_tc_f16", "qgemm_tc_resid", "qgemm_tc_swiglu"};
+  FC_LAUNCH(dev, names[EPI], kern<<<grid, TS_THREADS, TS_SMEM_BYTES, dev->stream>>>(tmap, tmap_o, w, a));
+  return FC_OK;
+}
+
+template <int KIND>
+int pick_epi_ts(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, int epi, dim3 grid) {
+  switch (epi) {
+    case EPI_F32: return launch_ts<KIND, EPI_F32>(dev, tmap, w, a, grid);
+    case EPI_F16: return launch_ts<KIND, EPI_F16>(dev, tmap, w, a, grid);
+    case EPI_RESID: return launch_ts<KIND, EPI_RESID>(dev, tmap, w, a, grid);
+    case EPI_SWIGLU: return launch_ts<KIND, EPI_SWIGLU>(dev, tmap, w, a, grid);
+  }
+  return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
+}
+
 template <int KIND>
 int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, int epi, dim3 grid) {
   switch (epi) {
@@ -547,23 +648,36 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "the fused qkv epilogue needs heads of 64 columns and, for NEOX, rope_dim 64");
   if ((epi == EPI_F16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "a f16 result needs n %% 8 == 0, not %u", w.n);
-  if (epi == EPI_SWIGLU && w.n % 128) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the SwiGLU epilogue needs n %% 128 == 0");
   if ((reinterpret_cast<uintptr_t>(a_dev) & 15) != 0) return fc_fail(dev, FC_ERR_ARG, "the A operand must be 16-byte aligned");
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  // The log-sum-exp head keeps the activation rows on the tensor-memory lanes (a thread folds one row's logits in
+  // registers); every other epilogue runs the kernel with the weight rows there.
+  const bool on_lanes = epi != EPI_LSE && epi != EPI_QKV;
+  const uint32_t box_rows = on_lanes ? TS_BX : TC_BM;
   CUtensorMap tmap;
   const cuuint64_t dims[2] = {w.k, args.m};
   const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
-  const cuuint32_t box[2] = {TC_BK, TC_BM};
+  const cuuint32_t box[2] = {TC_BK, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult cr = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)a_dev, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled failed with %d", (int)cr);
-  const uint64_t tiles = (uint64_t)((w.n + TC_BN - 1) / TC_BN) * ((args.m + TC_BM - 1) / TC_BM);
+  const uint64_t tiles = (uint64_t)((w.n + TC_BN - 1) / TC_BN) * ((args.m + box_rows - 1) / box_rows);
   if (tiles > 0x7fffffffull) return fc_fail(dev, FC_ERR_UNSUPPORTED, "%u rows exceed one launch of the tensor-core product", args.m);
   const uint32_t sms = (uint32_t)dev->prop.multiProcessorCount;
   dim3 grid((unsigned)(tiles < sms ? tiles : sms)); // persistent: one CTA per SM walks the tiles
+  if (on_lanes) {
+    if (w.kind == FC_Q4_0) return pick_epi_ts<FC_Q4_0>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_Q8_0) return pick_epi_ts<FC_Q8_0>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_F16) return pick_epi_ts<FC_F16>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_FP8_E4M3) return pick_epi_ts<FC_FP8_E4M3>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_FP8_E5M2) return pick_epi_ts<FC_FP8_E5M2>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_MXFP4) return pick_epi_ts<FC_MXFP4>(dev, tmap, w, args, epi, grid);
+    if (w.kind == FC_Q2_K) return pick_epi_ts<FC_Q2_K>(dev, tmap, w, args, epi, grid);
+    return pick_epi_ts<FC_F32>(dev, tmap, w, args, epi, grid);
+  }
   if (w.kind == FC_Q4_0) return pick_epi<FC_Q4_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_Q8_0) return pick_epi<FC_Q8_0>(dev, tmap, w, args, epi, grid);
   if (w.kind == FC_F16) return pick_epi<FC_F16>(dev, tmap, w, args, epi, grid);

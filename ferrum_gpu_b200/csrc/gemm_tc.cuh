@@ -25,6 +25,7 @@ struct TcArgs {
   uint32_t v0 = 0;
   float* partial = nullptr;
   int* err_flag = nullptr;
+  uint32_t out_tma = 0; // (set by the launch code) results leave through shared memory and TMA
   // EPI_QKV: host-built RoPE tables [ctx][rope_dim / 2], the row's position, pairing, and how many
   // leading columns (the q and k heads) are rotated; heads are 64 columns wide
   const float* rope_cos = nullptr;

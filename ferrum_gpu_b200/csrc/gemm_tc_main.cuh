@@ -172,7 +172,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         atomicExch(a.err_flag, ERR_WAIT_EMPTY);
         break;
       }
-      store_row<KIND>(cur, base + s * STAGE_BYTES + A_BYTES + r * 128, sw);
+      SmemSink sink{base + s * STAGE_BYTES + A_BYTES + r * 128, sw};
+      emit_row<KIND>(cur, sink);
       tc::fence_async_smem();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&full[s]);

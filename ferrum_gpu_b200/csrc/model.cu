@@ -494,9 +494,9 @@ FC_API int fc_llama_create_from_tensors(FcDevice* dev, const FcLlamaConfig* c, c
     const WeightSrc gu_m[2] = {src_of(b.gate), src_of(b.up)};
     const uint32_t gu_n[2] = {hid, hid};
     if ((rc = qweight_from_parts(dev, qkind, gu_m, gu_n, 2, d, &l.ff1.w)) != FC_OK) return fail(rc);
-    if (hid % 64 == 0) { // 64 gate rows then their 64 up rows: what the SwiGLU epilogue of the tensor path reads
-      if ((rc = model_interleave_gate_up(dev, l.ff1.w, hid, 64)) != FC_OK) return fail(rc);
-      m->gu_group = 64;
+    if (hid % 64 == 0) { // row 2i = gate i, row 2i + 1 = up i: the pair meets on neighbouring lanes of the tensor path's SwiGLU epilogue
+      if ((rc = model_interleave_gate_up(dev, l.ff1.w, hid, 1)) != FC_OK) return fail(rc);
+      m->gu_group = 1;
     }
     if ((rc = qweight_from_parts(dev, qkind, &down_m, &d, 1, hid, &l.ff2.w)) != FC_OK) return fail(rc);
   }

@@ -19,8 +19,8 @@ int check_tc_shapes(FcModel* m) {
                    "the tensor-core path needs dim, heads*head_dim and hidden to be multiples of 64 and head_dim 64 "
                    "(dim %u, q width %u, hidden %u, head_dim %u)",
                    m->dim, m->qd(), m->hidden, m->hd);
-  if (m->arch == ARCH_LLAMA && m->gu_group != 64)
-    return fc_fail(m->dev, FC_ERR_UNSUPPORTED, "the tensor-core path needs the gate/up rows interleaved by 64");
+  if (m->arch == ARCH_LLAMA && m->gu_group != 1)
+    return fc_fail(m->dev, FC_ERR_UNSUPPORTED, "the tensor-core path needs the gate and up rows of ff1 interleaved");
   return FC_OK;
 }
 } // namespace
@@ -34,8 +34,8 @@ size_t model_tc_head_bytes(const FcModel* m, size_t rows) {
   return al(rows * tiles * 16) + 1024;
 }
 
-// Re-order the fused gate/up weight so every 128 output rows hold 64 gate rows then the matching 64
-// up rows. Both planes are permuted by whole rows.
+// Re-order the fused gate/up weight into groups of `group` gate rows followed by their `group` up rows
+// (group 1: rows alternate gate, up). Both planes are permuted by whole rows.
 int model_interleave_gate_up(FcDevice* dev, FcQWeight* w, uint32_t hidden, uint32_t group) {
   const QMat& q = w->m;
   const size_t qs_row = qmat_qs_bytes(q.kind, q.k, 1), sc_row = qmat_sc_bytes(q.kind, q.k, 1);
