@@ -39,8 +39,8 @@ METRIC, UNIT = "scoring tok/s", "scored tokens/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the largest product (gate/up with the
 # SwiGLU epilogue, M = 131072 rows, K = 768, N = 4096) from an ncu capture of a quarter-size launch
-# (32 x 1024 rows: 52.1 MB read + 76.5 MB written), scaled by 4; see profiles/.
-NCU_TRAFFIC_BYTES = 4 * (52.11e6 + 76.48e6)
+# (32 x 1024 rows: 52.2 MB read + 80.3 MB written), scaled by 4; see profiles/.
+NCU_TRAFFIC_BYTES = 4 * (52.16e6 + 80.28e6)
 NCU_TRAFFIC_NOTE = ("gate/up product, per launch; algorithmic bytes are 740 MB (201 MB f16 rows in, 537 MB f16 out, "
                     "1.8 MB weights) - part of the output is still in L2 when the launch ends")
 
@@ -287,7 +287,7 @@ def main():
                     "d2h_bytes_per_step": int(lp.nbytes + rows + nll.nbytes)},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "qgemm_tc_kernel", "achieved": achieved, "peak": tf_sust,
+            "roofline": {"bound": "tensor", "kernel": "qgemm_ts_kernel + qgemm_tc_kernel (the products of one step)", "achieved": achieved, "peak": tf_sust,
                          "unit": "TFLOP/s", "frac": achieved / tf_sust, "peak_source": f"{peak_src} (sustained bf16)",
                          "frac_of_burst": achieved / tf_burst, "traffic": NCU_TRAFFIC_BYTES,
                          "traffic_note": NCU_TRAFFIC_NOTE,

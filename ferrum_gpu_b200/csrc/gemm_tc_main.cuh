@@ -28,6 +28,16 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
+// Bounded wait with suspended tries of up to 20 us each (about 1.3 s in all); polls the CTA's abort word.
+__device__ __forceinline__ bool wait_suspended(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+  for (uint32_t i = 0; i < (1u << 16); i++) {
+    if (tc::mbar_try_wait_for(bar, parity, 20000u)) return true;
+    if (*abort_word) return false;
+  }
+  *abort_word = 1;
+  return false;
+}
+
 template <int KIND, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
     qgemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const QMat w, const TcArgs a) {
@@ -168,7 +178,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         const uint32_t nrow = (ntile % tiles_n) * TC_BN + r;
         load_row<KIND>(nxt, w, nrow < w.n ? nrow : 0, nkk, nrow < w.n);
       }
-      if (!wait_or_abort(&empty[s], ph ^ 1, abort_word)) {
+      if (!wait_suspended(&empty[s], ph ^ 1, abort_word)) {
         atomicExch(a.err_flag, ERR_WAIT_EMPTY);
         break;
       }
@@ -205,7 +215,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
       };
       if (staged && EPI == EPI_RESID) load_resid(n0, rnext); // in flight while the tile's MMAs finish
-      if (!wait_or_abort(&acc_full[buf], aph, abort_word)) {
+      if (!wait_suspended(&acc_full[buf], aph, abort_word)) {
         atomicExch(a.err_flag, ERR_WAIT_ACC);
         break;
       }

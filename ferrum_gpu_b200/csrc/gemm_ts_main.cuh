@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     while (tile < total_tiles && !*abort_word) {
       const uint32_t t = it % W_STAGES, ph = (it / W_STAGES) & 1;
       if (DEEP) fetch(far, t2, k2);
-      if (!wait_or_abort(&w_empty[t], ph ^ 1, abort_word)) {
+      if (!wait_suspended(&w_empty[t], ph ^ 1, abort_word)) { // (suspended tries: twelve spinning warps cost the others issue slots)
         atomicExch(a.err_flag, ERR_WAIT_EMPTY);
         break;
       }
@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         }
         load_resid(x_first);
       }
-      bool ok = wait_or_abort(&acc_full[buf], aph, abort_word);
+      bool ok = wait_suspended(&acc_full[buf], aph, abort_word); // (the one long wait that is not on the tensor pipe's path)
       if (!ok) atomicExch(a.err_flag, ERR_WAIT_ACC);
       if (!__all_sync(0xffffffffu, ok)) break; // (the lanes leave together: the shuffles below take the whole warp)
       tc::tc_fence_after();

@@ -32,6 +32,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same, letting the hardware keep the thread suspended for up to `ns` nanoseconds per try (it is woken as
+// soon as the phase completes): a waiting warp then issues a handful of instructions per wait instead of spinning.
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait. Returns false when it gave up.
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
