@@ -2,16 +2,14 @@
 //   Y[m, n] = A[m, k] (f16) . dequant(W)[n, k]^T (fp16), f32 accumulators in tensor memory.
 // Replaces qlinear_tiled.wgsl for M >= 128 (ferrum_wgpu/src/shaders/quant/qlinear_tiled.wgsl:L93-L128).
 //
-// A persistent CTA per SM walks 256 x 128 output tiles, K in slices of 64 through a 3-deep
-// shared-memory ring (see gemm_tc_main.cuh for the warp roles and barriers):
-//   - the A slice (256 rows x 64 f16) arrives by TMA as one 128B-swizzled box;
-//   - the weight slice (128 rows x 64) is produced in the kernel: each producer thread owns one weight
-//     row, reads its packed blocks (Q4_0: 32 bytes + 2 scales per slice), dequantises them to f16 in
-//     registers and stores the 128-byte row into the same swizzled K-major layout TMA produces;
-//   - one thread issues tcgen05.mma into two 128 x 128 f32 accumulators in tensor memory that share
-//     the weight slice; tensor memory holds two tiles so the epilogue of one overlaps the next;
-//   - eight epilogue warps tcgen05.ld their lane quadrants and apply bias / activation / residual /
-//     SwiGLU / online log-sum-exp before storing.
+// Two kernel bodies share the packed-weight readers and dequantisers of this file:
+//   - gemm_ts_main.cuh: the weight rows on the tensor-memory lanes. A producer thread owns one weight row = one
+//     lane, dequantises its packed blocks of a 64-k slice and writes them into tensor memory, from where they are
+//     the MMA's A operand; the activations (192 rows x 64 f16 per TMA box) are the B operand. f32 / fp16 /
+//     residual / SwiGLU results leave through shared memory and bulk tensor stores. Every product but the head.
+//   - gemm_tc_main.cuh: the activation rows on the lanes, 256 x 128 tiles, both operands in shared memory (the
+//     weight slice dequantised into the swizzled K-major layout TMA produces). The vocabulary head: its epilogue
+//     folds a row of logits into (max, sum-exp, target logit, first argmax) in one thread's registers.
 #include "gemm_tc.cuh"
 #include "tc_ptx.cuh"
 
@@ -21,8 +19,7 @@ constexpr int STAGES = 3;
 constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2; // 32 KB: two 128-row halves
 constexpr uint32_t B_BYTES = TC_BN * TC_BK * 2; // 16 KB
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr uint32_t STG_WORDS = 32 * 36;          // per epilogue warp: a 32 x 32 f32 chunk, rows padded to 36
-constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + 8 * STG_WORDS * 4;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int THREADS = 640; // 20 warps: TMA, MMA, 2 idle, 8 producers, 8 epilogue
 constexpr uint32_t TMEM_COLS = 512; // two tiles x two accumulators x 128 columns
 // setmaxnreg targets of the three warp classes (4 control, 8 producer, 8 epilogue warps). The pool
@@ -339,148 +336,6 @@ __device__ __forceinline__ float ex2f_approx(float x) {
   return y;
 }
 
-// One thread's 32 consecutive accumulator columns [c, c + 32) of output row `row`.
-template <int EPI>
-__device__ __forceinline__ void epilogue_chunk(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* acc) {
-  if (row >= a.m) return;
-  if (EPI == EPI_F32 || EPI == EPI_RESID) {
-    float* dst = a.out_f32 + (size_t)row * a.ldo + col0;
-    if (((a.ldo | a.n) & 3) != 0) { // rows are not 16-byte aligned (odd vocabularies): scalar stores
-#pragma unroll
-      for (int j = 0; j < 32; j++) {
-        if (col0 + j < a.n) {
-          float v = __uint_as_float(acc[j]);
-          if (a.bias) v += a.bias[col0 + j];
-          if (EPI == EPI_RESID) v += dst[j];
-          dst[j] = v;
-        }
-      }
-      return;
-    }
-#pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      if (col0 + j >= a.n) break;
-      float4 v = make_float4(__uint_as_float(acc[j]), __uint_as_float(acc[j + 1]), __uint_as_float(acc[j + 2]),
-                             __uint_as_float(acc[j + 3]));
-      if (a.bias) {
-        const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + j);
-        v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
-      }
-      if (EPI == EPI_RESID) {
-        const float4 r = *reinterpret_cast<const float4*>(dst + j);
-        v.x += r.x, v.y += r.y, v.z += r.z, v.w += r.w;
-      }
-      *reinterpret_cast<float4*>(dst + j) = v;
-    }
-  } else if (EPI == EPI_F16) {
-    __half* dst = a.out_f16 + (size_t)row * a.ldo + col0;
-#pragma unroll
-    for (int j = 0; j < 32; j += 8) {
-      if (col0 + j >= a.n) break; // n is a multiple of 8 on this path
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        v[i] = __uint_as_float(acc[j + i]);
-        if (a.bias) v[i] += a.bias[col0 + j + i];
-        if (a.act == ACT_GELU) v[i] = gelu_f(v[i]);
-      }
-      *reinterpret_cast<uint4*>(dst + j) =
-          make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
-    }
-  }
-}
-
-// Residual epilogue in two halves so the loads of the residual stream are in flight while the MMAs of
-// the tile finish and while the previous chunk is being stored: 32 f32 of row `row` at column col0.
-__device__ __forceinline__ void resid_load(const TcArgs& a, uint32_t row, uint32_t col0, float4* r) {
-  const bool ok = row < a.m;
-  const float* src = a.out_f32 + (size_t)row * a.ldo + col0;
-#pragma unroll
-  for (int j = 0; j < 8; j++)
-    r[j] = ok && col0 + 4 * j < a.n ? *reinterpret_cast<const float4*>(src + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-}
-__device__ __forceinline__ void resid_store(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* acc, const float4* r) {
-  if (row >= a.m) return;
-  float* dst = a.out_f32 + (size_t)row * a.ldo + col0;
-#pragma unroll
-  for (int j = 0; j < 8; j++) {
-    if (col0 + 4 * j >= a.n) break;
-    float4 v = make_float4(__uint_as_float(acc[4 * j]) + r[j].x, __uint_as_float(acc[4 * j + 1]) + r[j].y,
-                           __uint_as_float(acc[4 * j + 2]) + r[j].z, __uint_as_float(acc[4 * j + 3]) + r[j].w);
-    if (a.bias) {
-      const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + 4 * j);
-      v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
-    }
-    *reinterpret_cast<float4*>(dst + 4 * j) = v;
-  }
-}
-
-// gate chunk g[32] and up chunk u[32] -> 32 activations
-__device__ __forceinline__ void epilogue_swiglu(const TcArgs& a, uint32_t row, uint32_t out_col0, const uint32_t* g,
-                                                const uint32_t* u) {
-  if (row >= a.m) return;
-  __half* dst = a.out_f16 + (size_t)row * a.ldo + out_col0;
-#pragma unroll
-  for (int j = 0; j < 32; j += 8) {
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float gv = __uint_as_float(g[j + i]), uv = __uint_as_float(u[j + i]);
-      v[i] = __fdividef(gv, 1.0f + ex2f_approx(gv * -1.4426950408889634f)) * uv;
-    }
-    *reinterpret_cast<uint4*>(dst + j) =
-        make_uint4(pack_f16(v[0], v[1]), pack_f16(v[2], v[3]), pack_f16(v[4], v[5]), pack_f16(v[6], v[7]));
-  }
-}
-
-// One 64-column head of a fused qkv row: lo = columns [0, 32), hi = [32, 64). Adds the bias, rotates
-// the head when it is a q or k head (rope.wgsl: NORM pairs (2i, 2i+1), NEOX pairs (i, i + 32); NEOX is
-// fused only for a full rotary of 64), rounds to f16 and stores 128 bytes.
-__device__ __forceinline__ void epilogue_qkv(const TcArgs& a, uint32_t row, uint32_t col0, const uint32_t* lo,
-                                             const uint32_t* hi) {
-  if (row >= a.m || col0 >= a.n) return;
-  float v[64];
-#pragma unroll
-  for (int i = 0; i < 32; i++) {
-    v[i] = __uint_as_float(lo[i]);
-    v[32 + i] = __uint_as_float(hi[i]);
-  }
-  if (a.bias) {
-#pragma unroll
-    for (int i = 0; i < 64; i += 4) {
-      const float4 b = *reinterpret_cast<const float4*>(a.bias + col0 + i);
-      v[i] += b.x, v[i + 1] += b.y, v[i + 2] += b.z, v[i + 3] += b.w;
-    }
-  }
-  if (a.rope_cos && col0 < a.rope_cols) {
-    const uint32_t half = a.rope_dim / 2;
-    const float* cs = a.rope_cos + (size_t)a.positions[row] * half;
-    const float* sn = a.rope_sin + (size_t)a.positions[row] * half;
-    if (a.rope_type == FC_ROPE_NORM) {
-#pragma unroll
-      for (int p = 0; p < 32; p++) {
-        if ((uint32_t)p < half) {
-          const float c = cs[p], s = sn[p], x = v[2 * p], y = v[2 * p + 1];
-          v[2 * p] = x * c - y * s;
-          v[2 * p + 1] = x * s + y * c;
-        }
-      }
-    } else { // NEOX with rope_dim == 64 (checked on the host)
-#pragma unroll
-      for (int p = 0; p < 32; p++) {
-        const float c = cs[p], s = sn[p], x = v[p], y = v[p + 32];
-        v[p] = x * c - y * s;
-        v[p + 32] = x * s + y * c;
-      }
-    }
-  }
-  __half* dst = a.out_f16 + (size_t)row * a.ldo + col0;
-#pragma unroll
-  for (int j = 0; j < 64; j += 8)
-    *reinterpret_cast<uint4*>(dst + j) = make_uint4(pack_f16(v[j], v[j + 1]), pack_f16(v[j + 2], v[j + 3]),
-                                                    pack_f16(v[j + 4], v[j + 5]), pack_f16(v[j + 6], v[j + 7]));
-}
-
 struct LseState {
   float mx = -INFINITY, se = 0.0f, tl = -INFINITY;
   int first = 0;
@@ -566,9 +421,7 @@ int launch_tc(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArg
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES));
     attr.first(dev->ordinal);
   }
-  static const char* const names[] = {"qgemm_tc_f32", "qgemm_tc_f16", "qgemm_tc_resid", "qgemm_tc_swiglu", "qgemm_tc_lse",
-                                      "qgemm_tc_qkv"};
-  FC_LAUNCH(dev, names[EPI], kern<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmap, w, a));
+  FC_LAUNCH(dev, "qgemm_tc_lse", kern<<<grid, THREADS, SMEM_BYTES, dev->stream>>>(tmap, w, a));
   return FC_OK;
 }
 
@@ -624,14 +477,7 @@ int pick_epi_ts(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcA
 
 template <int KIND>
 int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs& a, int epi, dim3 grid) {
-  switch (epi) {
-    case EPI_F32: return launch_tc<KIND, EPI_F32>(dev, tmap, w, a, grid);
-    case EPI_F16: return launch_tc<KIND, EPI_F16>(dev, tmap, w, a, grid);
-    case EPI_RESID: return launch_tc<KIND, EPI_RESID>(dev, tmap, w, a, grid);
-    case EPI_SWIGLU: return launch_tc<KIND, EPI_SWIGLU>(dev, tmap, w, a, grid);
-    case EPI_LSE: return launch_tc<KIND, EPI_LSE>(dev, tmap, w, a, grid);
-    case EPI_QKV: return launch_tc<KIND, EPI_QKV>(dev, tmap, w, a, grid);
-  }
+  if (epi == EPI_LSE) return launch_tc<KIND, EPI_LSE>(dev, tmap, w, a, grid);
   return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
 }
 
@@ -643,17 +489,15 @@ int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, T
   args.k = w.k;
   args.err_flag = dev->d_flag;
   if (w.k % TC_BK) return fc_fail(dev, FC_ERR_UNSUPPORTED, "the tensor-core product needs k %% 64 == 0, not %u", w.k);
-  if (epi == EPI_QKV && (w.n % 64 || args.ldo % 8 || args.rope_cols % 64 ||
-                         (args.rope_cos && args.rope_type != FC_ROPE_NORM && args.rope_dim != 64) || args.rope_dim > 64))
-    return fc_fail(dev, FC_ERR_UNSUPPORTED, "the fused qkv epilogue needs heads of 64 columns and, for NEOX, rope_dim 64");
   if ((epi == EPI_F16 || epi == EPI_SWIGLU) && (w.n % 8 || args.ldo % 8))
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "a f16 result needs n %% 8 == 0, not %u", w.n);
+  if (epi < EPI_F32 || epi > EPI_LSE) return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
   if ((reinterpret_cast<uintptr_t>(a_dev) & 15) != 0) return fc_fail(dev, FC_ERR_ARG, "the A operand must be 16-byte aligned");
   EncodeTiledFn enc = encode_fn();
   if (!enc) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
   // The log-sum-exp head keeps the activation rows on the tensor-memory lanes (a thread folds one row's logits in
   // registers); every other epilogue runs the kernel with the weight rows there.
-  const bool on_lanes = epi != EPI_LSE && epi != EPI_QKV;
+  const bool on_lanes = epi != EPI_LSE;
   const uint32_t box_rows = on_lanes ? TS_BX : TC_BM;
   CUtensorMap tmap;
   const cuuint64_t dims[2] = {w.k, args.m};

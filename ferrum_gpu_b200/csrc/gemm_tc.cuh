@@ -4,14 +4,13 @@
 
 #include "common.cuh"
 
-// What the epilogue does with the 128 x 128 f32 accumulator tile.
+// What the epilogue does with the f32 accumulator tile.
 enum {
   EPI_F32 = 0,    // out_f32[m][ldo]  = acc + bias
   EPI_F16 = 1,   // out_f16[m][ldo] = f16(act(acc + bias))
   EPI_RESID = 2,  // out_f32[m][ldo] += acc + bias          (residual stream, in place)
-  EPI_SWIGLU = 3, // out_f16[m][n/2] = f16(silu(gate) * up); weight rows interleaved 64 gate / 64 up
-  EPI_LSE = 4,    // partial[tile][m][4] = (max, sum exp, target logit | -inf, first argmax)
-  EPI_QKV = 5     // out_f16 = f16(rope(acc + bias)): heads of 64 columns, the first rope_cols rotated
+  EPI_SWIGLU = 3, // out_f16[m][n/2] = f16(silu(gate) * up); weight rows alternate gate, up
+  EPI_LSE = 4     // partial[tile][m][4] = (max, sum exp, target logit | -inf, first argmax)
 };
 
 struct TcArgs {
@@ -26,15 +25,9 @@ struct TcArgs {
   float* partial = nullptr;
   int* err_flag = nullptr;
   uint32_t out_tma = 0; // (set by the launch code) results leave through shared memory and TMA
-  // EPI_QKV: host-built RoPE tables [ctx][rope_dim / 2], the row's position, pairing, and how many
-  // leading columns (the q and k heads) are rotated; heads are 64 columns wide
-  const float* rope_cos = nullptr;
-  const float* rope_sin = nullptr;
-  const int32_t* positions = nullptr;
-  uint32_t rope_dim = 0, rope_type = FC_ROPE_NORM, rope_cols = 0;
 };
 
-constexpr uint32_t TC_BM = 256, TC_BN = 128, TC_BK = 64; // output tile of one CTA step, K slice
+constexpr uint32_t TC_BM = 256, TC_BN = 128, TC_BK = 64; // weight rows per tile (TC_BN), K slice; TC_BM: activation rows of the head's tile
 
 // y = a[m][k] (f16, row-major, device) . W^T with the epilogue `epi`. k % 64 == 0.
 int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a, int epi, TcArgs args);

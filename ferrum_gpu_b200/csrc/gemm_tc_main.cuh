@@ -1,4 +1,6 @@
-// The kernel body of gemm_tc.cu (included there, inside its anonymous namespace).
+// The first kernel body of gemm_tc.cu (included there, inside its anonymous namespace): the product with the
+// ACTIVATION rows on the tensor-memory lanes, kept for the vocabulary head's log-sum-exp epilogue, where a thread
+// folds one row's logits (max, sum of exponentials, target logit, first argmax) in its registers.
 //
 // Persistent: one CTA per SM walks output tiles of 256 x 128 (two 128-row accumulators that share
 // one dequantised weight slice, which halves the dequantisation work per MMA). Tensor memory holds
@@ -7,8 +9,8 @@
 //   warp 0        TMA producer: A slice, 256 rows x 64 f16 = one 32 KB swizzled box per K step
 //   warp 1        TMEM owner and MMA issuer: 2 accumulators x 4 MMAs (K = 16) per K step
 //   warps 4-7     weight producers of the even K steps: one weight row per thread, packed blocks ->
-//   warps 8-11    f16 swizzled slice; the same for the odd K steps. A producer's step is a chain of
-//                 latencies (wait for the stage, dequantise, proxy fence, arrive) longer than the MMAs
+//   warps 8-11    f16 swizzled slice in shared memory; the same for the odd K steps. A producer's step is a
+//                 chain of latencies (wait for the stage, dequantise, proxy fence, arrive) longer than the MMAs
 //                 of a step, so two sets leapfrog.
 //   warps 12-19   epilogue: warp w reads TMEM lane quadrant w % 4 of accumulator (w - 12) / 4
 //   (warps 2-3 idle: roles are aligned to groups of four warps so that setmaxnreg can move registers
@@ -196,95 +198,18 @@ __global__ void __launch_bounds__(THREADS, 1)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_EPI));
     // ---- epilogue ----
     const uint32_t e = warp - 12, half = e >> 2, quad = warp & 3;
-    float* stg = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256) + e * STG_WORDS; // this warp's 32 x 36 tile
     uint32_t tcnt = 0;
     for (uint32_t tile = blockIdx.x; tile < total_tiles && !*abort_word; tile += gridDim.x, tcnt++) {
       const uint32_t buf = tcnt & 1, aph = (tcnt >> 1) & 1;
       const uint32_t n0 = (tile % tiles_n) * TC_BN;
       const uint32_t out_row = (tile / tiles_n) * TC_BM + half * 128 + quad * 32 + lane;
-      const bool staged = (EPI == EPI_RESID || EPI == EPI_F32 || EPI == EPI_F16) && ((a.ldo | a.n) & 7) == 0;
-      const uint32_t wrow0 = (tile / tiles_n) * TC_BM + half * 128 + quad * 32; // first of this warp's 32 rows
-      const uint32_t tr = lane >> 3, tc4 = (lane & 7) * 4; // store mapping: rows tr + 4i, columns tc4..tc4+3
-      float4 rcur[8], rnext[8];
-      auto load_resid = [&](uint32_t col0, float4* r) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const uint32_t row = wrow0 + tr + 4 * i;
-          r[i] = (row < a.m && col0 + tc4 < a.n) ? *reinterpret_cast<const float4*>(a.out_f32 + (size_t)row * a.ldo + col0 + tc4)
-                                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-      };
-      if (staged && EPI == EPI_RESID) load_resid(n0, rnext); // in flight while the tile's MMAs finish
       if (!wait_suspended(&acc_full[buf], aph, abort_word)) {
         atomicExch(a.err_flag, ERR_WAIT_ACC);
         break;
       }
       tc::tc_fence_after();
       const uint32_t taddr = tmem_base + ((quad * 32) << 16) + buf * (2 * TC_BN) + half * TC_BN;
-      if (staged) {
-        // tcgen05.ld hands each lane one output row; storing that way touches 32 rows per instruction.
-        // The 32 x 32 chunk goes through a padded shared-memory tile instead and leaves with 8 lanes on
-        // each row: every global access of the warp is then 4 rows x 128 contiguous bytes.
-#pragma unroll 1
-        for (uint32_t c = 0; c < TC_BN / 32; c++) {
-          uint32_t acc[32];
-          tc::tmem_ld_32x32(taddr + c * 32, acc);
-          if (EPI == EPI_RESID) {
-#pragma unroll
-            for (int j = 0; j < 8; j++) rcur[j] = rnext[j];
-            if (c + 1 < TC_BN / 32) load_resid(n0 + (c + 1) * 32, rnext);
-          }
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 8; j++)
-            *reinterpret_cast<float4*>(stg + lane * 36 + 4 * j) =
-                make_float4(__uint_as_float(acc[4 * j]), __uint_as_float(acc[4 * j + 1]), __uint_as_float(acc[4 * j + 2]),
-                            __uint_as_float(acc[4 * j + 3]));
-          __syncwarp();
-          const uint32_t col = n0 + c * 32 + tc4;
-          if (col < a.n) {
-            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (a.bias) b4 = *reinterpret_cast<const float4*>(a.bias + col);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-              const uint32_t row = wrow0 + tr + 4 * i;
-              float4 v = *reinterpret_cast<const float4*>(stg + (tr + 4 * i) * 36 + tc4);
-              v.x += b4.x, v.y += b4.y, v.z += b4.z, v.w += b4.w;
-              if (EPI == EPI_RESID) v.x += rcur[i].x, v.y += rcur[i].y, v.z += rcur[i].z, v.w += rcur[i].w;
-              if (row < a.m) {
-                if (EPI == EPI_F16) {
-                  if (a.act == ACT_GELU) v.x = gelu_f(v.x), v.y = gelu_f(v.y), v.z = gelu_f(v.z), v.w = gelu_f(v.w);
-                  *reinterpret_cast<uint2*>(a.out_f16 + (size_t)row * a.ldo + col) =
-                      make_uint2(pack_f16(v.x, v.y), pack_f16(v.z, v.w));
-                } else {
-                  *reinterpret_cast<float4*>(a.out_f32 + (size_t)row * a.ldo + col) = v;
-                }
-              }
-            }
-          }
-          __syncwarp();
-        }
-      } else if (EPI == EPI_SWIGLU) {
-        // columns [0, 64) of the tile are gate rows, [64, 128) the matching up rows
-#pragma unroll 1
-        for (uint32_t c = 0; c < 2; c++) {
-          uint32_t g[32], u[32];
-          tc::tmem_ld_32x32(taddr + c * 32, g);
-          tc::tmem_ld_32x32(taddr + 64 + c * 32, u);
-          tc::tmem_ld_wait();
-          epilogue_swiglu(a, out_row, (n0 / 2) + c * 32, g, u);
-        }
-      } else if (EPI == EPI_QKV) {
-        // two heads of 64 columns per tile
-#pragma unroll 1
-        for (uint32_t c = 0; c < 2; c++) {
-          uint32_t lo[32], hi[32];
-          tc::tmem_ld_32x32(taddr + c * 64, lo);
-          tc::tmem_ld_32x32(taddr + c * 64 + 32, hi);
-          tc::tmem_ld_wait();
-          epilogue_qkv(a, out_row, n0 + c * 64, lo, hi);
-        }
-      } else if (EPI == EPI_LSE) {
+      { // the head's online log-sum-exp: this thread folds its row's 128 logits of the tile in registers
         LseState st;
         const int target = out_row < a.m ? a.targets[out_row] : -1;
 #pragma unroll 1
@@ -297,14 +222,6 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (out_row < a.m)
           *reinterpret_cast<float4*>(a.partial + ((size_t)(tile % tiles_n) * a.m + out_row) * 4) =
               make_float4(st.mx, st.se, st.tl, (float)st.first);
-      } else {
-#pragma unroll 1
-        for (uint32_t c = 0; c < TC_BN / 32; c++) {
-          uint32_t acc[32];
-          tc::tmem_ld_32x32(taddr + c * 32, acc);
-          tc::tmem_ld_wait();
-          epilogue_chunk<EPI>(a, out_row, n0 + c * 32, acc);
-        }
       }
       // this warp's reads of the buffer are complete: hand it back to the MMA issuer
       tc::tc_fence_before();

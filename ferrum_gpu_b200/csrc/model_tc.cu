@@ -101,19 +101,11 @@ int model_trunk_tc(FcModel* m, const int32_t* ids, const int32_t* positions, uin
     FC_TRY(k_norm_f16(dev, ln, x, l.norm1_g, l.norm1_b, rows, d, m->eps, h));
     TcArgs a_qkv;
     a_qkv.m = rows, a_qkv.bias = l.qkv.bias, a_qkv.out_f16 = qkv, a_qkv.ldo = m->qkv_w();
-    // RoPE in the product's epilogue (EPI_QKV) is exact on the f32 accumulators but makes that
-    // epilogue the kernel's bottleneck (295 TFLOP/s measured against 860 for the plain fp16 store),
-    // so the rotation runs as its own 16-byte-vectorised pass over the q and k columns instead.
-    const bool fuse_rope = false;
-    if (fuse_rope) {
-      a_qkv.rope_cos = m->rope.cos, a_qkv.rope_sin = m->rope.sin, a_qkv.positions = positions;
-      a_qkv.rope_dim = m->rope.rope_dim, a_qkv.rope_type = m->rope.type, a_qkv.rope_cols = m->qd() + m->kvd();
-      FC_TRY(k_qgemm_tc_f16(dev, l.qkv.w->m, h, EPI_QKV, a_qkv));
-    } else {         // NEOX with a partial rotary: pairs straddle the epilogue's register chunks
-      FC_TRY(k_qgemm_tc_f16(dev, l.qkv.w->m, h, EPI_F16, a_qkv));
-      FC_TRY(k_rope_f16(dev, qkv, rows, m->heads, m->kv_heads, m->hd, m->rope.cos, m->rope.sin, m->rope.rope_dim,
-                         m->rope.type, positions));
-    }
+    // (RoPE fused into this product's epilogue was measured at a third of the plain fp16 store's rate - the
+    // table gathers - so the rotation runs as its own 16-byte-vectorised pass over the q and k columns.)
+    FC_TRY(k_qgemm_tc_f16(dev, l.qkv.w->m, h, EPI_F16, a_qkv));
+    FC_TRY(k_rope_f16(dev, qkv, rows, m->heads, m->kv_heads, m->hd, m->rope.cos, m->rope.sin, m->rope.rope_dim, m->rope.type,
+                       positions));
     if (cache_stream >= 0)
       FC_TRY(k_kv_store_f16(dev, qkv, t, m->heads, m->kv_heads, m->hd, (uint32_t)cache_stream, 0, m->ctx, l.kv.k, l.kv.v));
     FC_TRY(k_attn_causal_f16(dev, qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, attn));
