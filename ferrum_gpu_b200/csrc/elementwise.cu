@@ -373,18 +373,41 @@ __global__ void __launch_bounds__(512)
     argmax_parts_kernel(const float* __restrict__ logits, uint32_t vocab, uint32_t parts, unsigned long long* keys,
                         uint32_t* done, int32_t* __restrict__ out) {
   __shared__ unsigned long long bk[16];
-  const uint32_t r = blockIdx.y, per = (vocab + parts - 1) / parts;
+  const uint32_t r = blockIdx.y, per = ((vocab + parts - 1) / parts + 3) & ~3u; // (whole float4s per CTA)
   const uint32_t i0 = blockIdx.x * per, i1 = min(vocab, i0 + per);
   const float* row = logits + (size_t)r * vocab;
-  unsigned long long best = 0; // "nothing above -inf yet"
-  for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-    const float v = row[i];
-    if (v > -INFINITY) { // (false for NaN)
-      uint32_t u = __float_as_uint(v + 0.0f); // (-0 and +0 compare equal: one key)
-      u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-      const unsigned long long key = ((unsigned long long)u << 32) | (uint32_t)~i;
-      best = key > best ? key : best;
+  // The thread's candidate as (value, index): a later entry replaces it only when strictly greater, so the
+  // lowest index of the largest value stays; NaN and -inf never win. Four float4 loads are in flight per pass
+  // (a pass per load was a chain of trips to L2: 37 us for 64 rows of 152K entries).
+  float bv = -INFINITY;
+  uint32_t bi = 0;
+  auto take = [&](float v, uint32_t i) {
+    if (v > bv) bv = v, bi = i;
+  };
+  if ((vocab & 3u) == 0 && i0 < i1) { // rows start on 16 bytes
+    const uint32_t n4 = (i1 - i0) / 4; // (i1 - i0 is a multiple of 4: vocab and per are)
+    const float4* row4 = reinterpret_cast<const float4*>(row + i0);
+    for (uint32_t j0 = threadIdx.x; j0 < n4; j0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const uint32_t j = j0 + u * blockDim.x;
+        v[u] = j < n4 ? row4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const uint32_t i = i0 + 4 * (j0 + u * blockDim.x);
+        take(v[u].x, i), take(v[u].y, i + 1), take(v[u].z, i + 2), take(v[u].w, i + 3);
+      }
     }
+  } else {
+    for (uint32_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) take(row[i], i);
+  }
+  unsigned long long best = 0; // "nothing above -inf yet"
+  if (bv > -INFINITY) {
+    uint32_t u = __float_as_uint(bv + 0.0f); // (-0 and +0 compare equal: one key)
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    best = ((unsigned long long)u << 32) | (uint32_t)~bi;
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

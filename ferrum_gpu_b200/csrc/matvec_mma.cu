@@ -226,7 +226,9 @@ __device__ __forceinline__ void block_frags(const BlockRegs<KIND>& r, uint32_t a
 // in one load; the 16-byte chunk index of odd rows is XORed with 4, so that the two rows a quarter-warp reads
 // lie in different halves of the banks (unpadded rows 256 bytes apart would all start on bank 0; with 8-byte
 // loads and rows padded by 32 bytes half of all shared-memory wavefronts of the kernel were bank conflicts).
-template <int KIND, int NB>
+// RW: 16-row tiles of the weight a warp holds at once. Two tiles share every load of x from shared memory (the
+// kernel's busiest unit at one tile): used for the long outputs that need no split of K, the vocabulary head.
+template <int KIND, int NB, int RW>
 __global__ void __launch_bounds__(128)
     qmatvec_mma_kernel(QMat w, const __half* __restrict__ xh, const __half* __restrict__ xl, uint32_t m, float* __restrict__ y,
                        float* __restrict__ partial, uint32_t blocks_per_split, Epilogue ep) {
@@ -236,8 +238,10 @@ __global__ void __launch_bounds__(128)
   constexpr int PART = MP * XROW;     // halves of one part of one buffer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const uint32_t n = w.n, k = w.k, nblocks = k / QK;
-  const uint32_t row0 = blockIdx.x * ROWS_PER_CTA + warp * 16;
-  const uint32_t row_g = min(row0 + g, n - 1), row_g8 = min(row0 + g + 8, n - 1);
+  const uint32_t row0 = blockIdx.x * (ROWS_PER_CTA * RW) + warp * (16 * RW);
+  uint32_t row_g[RW], row_g8[RW];
+#pragma unroll
+  for (int i = 0; i < RW; i++) row_g[i] = min(row0 + 16 * i + g, n - 1), row_g8[i] = min(row0 + 16 * i + g + 8, n - 1);
   const uint32_t kb_begin = blockIdx.y * blocks_per_split;
   const uint32_t kb_end = min(kb_begin + blocks_per_split, nblocks);
   const uint32_t n_slices = (kb_end - kb_begin + 3) / 4; // 4 blocks per staged slice
@@ -255,15 +259,26 @@ __global__ void __launch_bounds__(128)
     }
   };
 
-  float acc[NB][4];
+  float acc[RW][NB][4];
 #pragma unroll
-  for (int i = 0; i < NB; i++) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
+  for (int i = 0; i < RW; i++)
+#pragma unroll
+    for (int j = 0; j < NB; j++) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.0f;
 
-  BlockRegs<KIND> cur, nxt;
+  // The packed blocks of the warp's two rows are requested three blocks before they are multiplied (a ring of
+  // four register sets, indexed by the block's place in its slice): a block is 8 MMAs per n-block, about 250
+  // cycles of tensor work at 64 rows of x, and a load issued only one block ahead - several hundred cycles to L2 -
+  // left the tensor pipe a third busy on the long rows of the vocabulary head.
+  BlockRegs<KIND> ring[4][RW];
   if (n_slices > 0) {
     stage(0, 0);
     cp_async_commit();
-    load_block<KIND>(cur, w, row_g, row_g8, kb_begin, t);
+#pragma unroll
+    for (int p = 0; p < 3; p++)
+      if (kb_begin + p < kb_end) {
+#pragma unroll
+        for (int i = 0; i < RW; i++) load_block<KIND>(ring[p][i], w, row_g[i], row_g8[i], kb_begin + p, t);
+      }
   }
   for (uint32_t sl = 0; sl < n_slices; sl++) {
     const uint32_t buf = sl & 1;
@@ -278,40 +293,52 @@ __global__ void __launch_bounds__(128)
     const __half* xhb = xs + (size_t)buf * 2 * PART;
     const __half* xlb = xhb + PART;
     const uint32_t kb0 = kb_begin + sl * 4;
-#pragma unroll 1
-    for (uint32_t bi = 0; bi < 4 && kb0 + bi < kb_end; bi++) {
-      if (kb0 + bi + 1 < kb_end) load_block<KIND>(nxt, w, row_g, row_g8, kb0 + bi + 1, t); // in flight under this block's MMAs
-      uint32_t a[2][4];
-      block_frags<KIND>(cur, a);
-      const float dg = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(cur.d[0]);
-      const float dg8 = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(cur.d[1]);
+#pragma unroll
+    for (int bi = 0; bi < 4; bi++) {
+      if (kb0 + bi >= kb_end) break;
+      if (kb0 + bi + 3 < kb_end) {
+#pragma unroll
+        for (int i = 0; i < RW; i++) load_block<KIND>(ring[(bi + 3) & 3][i], w, row_g[i], row_g8[i], kb0 + bi + 3, t);
+      }
+      uint32_t a[RW][2][4];
+      float dg[RW], dg8[RW];
+#pragma unroll
+      for (int i = 0; i < RW; i++) {
+        block_frags<KIND>(ring[bi][i], a[i]);
+        dg[i] = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(ring[bi][i].d[0]);
+        dg8[i] = KIND == FC_F16 ? 1.0f : block_scale_f32<KIND>(ring[bi][i].d[1]);
+      }
 #pragma unroll
       for (int nb = 0; nb < NB; nb++) {
-        float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         const uint32_t off = (nb * 8 + g) * XROW + (((bi * 4 + t) ^ ((g & 1) << 2)) * 8);
         const uint4 bh = *reinterpret_cast<const uint4*>(xhb + off);
         const uint4 bl = *reinterpret_cast<const uint4*>(xlb + off);
-        mma_16816(c, a[0], bh.x, bh.y);
-        mma_16816(c, a[0], bl.x, bl.y);
-        mma_16816(c, a[1], bh.z, bh.w);
-        mma_16816(c, a[1], bl.z, bl.w);
-        acc[nb][0] = fmaf(dg, c[0], acc[nb][0]);
-        acc[nb][1] = fmaf(dg, c[1], acc[nb][1]);
-        acc[nb][2] = fmaf(dg8, c[2], acc[nb][2]);
-        acc[nb][3] = fmaf(dg8, c[3], acc[nb][3]);
+#pragma unroll
+        for (int i = 0; i < RW; i++) {
+          float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          mma_16816(c, a[i][0], bh.x, bh.y);
+          mma_16816(c, a[i][0], bl.x, bl.y);
+          mma_16816(c, a[i][1], bh.z, bh.w);
+          mma_16816(c, a[i][1], bl.z, bl.w);
+          acc[i][nb][0] = fmaf(dg[i], c[0], acc[i][nb][0]);
+          acc[i][nb][1] = fmaf(dg[i], c[1], acc[i][nb][1]);
+          acc[i][nb][2] = fmaf(dg8[i], c[2], acc[i][nb][2]);
+          acc[i][nb][3] = fmaf(dg8[i], c[3], acc[i][nb][3]);
+        }
       }
-      cur = nxt;
     }
     __syncthreads();
   }
   // c0, c1: weight row g, batch columns 2t, 2t + 1; c2, c3: weight row g + 8
 #pragma unroll
+  for (int i = 0; i < RW; i++)
+#pragma unroll
   for (int nb = 0; nb < NB; nb++) {
 #pragma unroll
     for (int j = 0; j < 4; j++) {
-      const uint32_t row = row0 + g + (j >> 1) * 8, col = nb * 8 + 2 * t + (j & 1);
+      const uint32_t row = row0 + 16 * i + g + (j >> 1) * 8, col = nb * 8 + 2 * t + (j & 1);
       if (row >= n || col >= m) continue;
-      float v = acc[nb][j];
+      float v = acc[i][nb][j];
       if (partial) {
         partial[((size_t)blockIdx.y * m + col) * n + row] = v;
       } else {
@@ -528,16 +555,16 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, uint32_t
   y[i] = v;
 }
 
-template <int KIND, int NB>
+template <int KIND, int NB, int RW = 1>
 int launch(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, uint32_t m, float* y, float* partial,
            uint32_t splits, uint32_t bps, const Epilogue& ep) {
-  auto kern = qmatvec_mma_kernel<KIND, NB>;
+  auto kern = qmatvec_mma_kernel<KIND, NB, RW>;
   const size_t smem = (size_t)2 * 2 * NB * 8 * XS * sizeof(__half);
   static OncePerDevice attr;
   if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
-  dim3 grid((w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, splits);
+  dim3 grid((w.n + ROWS_PER_CTA * RW - 1) / (ROWS_PER_CTA * RW), splits);
   FC_LAUNCH(dev, "qmatvec_mma", kern<<<grid, 128, smem, dev->stream>>>(w, xh, xl, m, y, partial, bps, ep));
   return FC_OK;
 }
@@ -547,6 +574,9 @@ int pick_nb(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, ui
             uint32_t splits, uint32_t bps, const Epilogue& ep) {
   if (m <= 16) return launch<KIND, 2>(dev, w, xh, xl, m, y, partial, splits, bps, ep);
   if (m <= 32) return launch<KIND, 4>(dev, w, xh, xl, m, y, partial, splits, bps, ep);
+  // an output long enough to fill the device many times over without a split of K: two row tiles per warp
+  if (splits == 1 && (w.n + 127) / 128 >= 4 * (uint32_t)dev->prop.multiProcessorCount)
+    return launch<KIND, 8, 2>(dev, w, xh, xl, m, y, partial, splits, bps, ep);
   return launch<KIND, 8>(dev, w, xh, xl, m, y, partial, splits, bps, ep);
 }
 
