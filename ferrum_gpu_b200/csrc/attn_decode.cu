@@ -21,8 +21,14 @@
 namespace {
 
 constexpr int HD = 64;
-constexpr int POS_PER_ITER = 64; // positions a CTA consumes per loop iteration (4 warps x 4 groups x 4)
-constexpr size_t TILE_BYTES = (size_t)2 * 2 * POS_PER_ITER * HD * 4; // two stages of a K and a V tile
+// NW warps per CTA (4, or 8 for the one-CTA-per-(row, kv-head) form that needs no merge launch): a CTA consumes
+// NW x 16 positions per loop iteration (4 lane groups x 4 positions per warp)
+template <int NW>
+struct Tile {
+  static constexpr int POS = NW * 16;
+  static constexpr size_t BYTES = (size_t)2 * 2 * POS * HD * 4; // two stages of a K and a V tile
+};
+constexpr int POS_PER_ITER = Tile<4>::POS;
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -49,13 +55,14 @@ struct DecodeOut {
 };
 
 // partial layout per (row, kv-head, split): [G] max (log2 domain), [G] sum, [G][64] weighted output
-template <int G>
-__global__ void __launch_bounds__(128)
+template <int G, int NW>
+__global__ void __launch_bounds__(NW * 32)
     attn_decode_split_kernel(const float* __restrict__ qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
                              const int32_t* __restrict__ positions, const int32_t* __restrict__ streams, KvLayer kv,
                              uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst, bool append) {
-  __shared__ float sm_m[4][G], sm_l[4][G];
-  __shared__ __align__(16) float sm_o[4][G][HD];
+  constexpr int POS_PER_ITER = Tile<NW>::POS; // (this kernel's own step; the host's split rule keeps the 4-warp one)
+  __shared__ float sm_m[NW][G], sm_l[NW][G];
+  __shared__ __align__(16) float sm_o[NW][G][HD];
   const uint32_t split = blockIdx.x, kvh = blockIdx.y, r = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
   const uint32_t len = (uint32_t)positions[r] + 1;
@@ -119,12 +126,12 @@ __global__ void __launch_bounds__(128)
     float* kc = kv.k + (((size_t)slot * kv_heads + kvh) * ctx + (len - 1)) * HD;
     float* vc = kv.v + (((size_t)slot * kv_heads + kvh) * ctx + (len - 1)) * HD;
     if (threadIdx.x < HD) kc[threadIdx.x] = krow_new[threadIdx.x];
-    else vc[threadIdx.x - HD] = vrow_new[threadIdx.x - HD];
+    else if (threadIdx.x < 2 * HD) vc[threadIdx.x - HD] = vrow_new[threadIdx.x - HD];
   }
   auto stage = [&](uint32_t j0, uint32_t buf) {
 #pragma unroll
-    for (int c = 0; c < 16; c++) { // 2 tensors x 64 positions x 16 chunks over 128 threads
-      const uint32_t id = threadIdx.x + 128 * c, tensor = id >> 10, pos = (id >> 4) & 63, ch = id & 15;
+    for (int c = 0; c < 16; c++) { // 2 tensors x POS positions x 16 chunks over NW x 32 threads
+      const uint32_t id = threadIdx.x + NW * 32 * c, tensor = id / (POS_PER_ITER * 16), pos = (id >> 4) % POS_PER_ITER, ch = id & 15;
       const uint32_t j = j0 + pos;
       const uint32_t jj = j < p1 ? j : p0; // past the range: any valid row (its scores are masked)
       const bool fresh = append && jj + 1 == len;
@@ -230,13 +237,15 @@ __global__ void __launch_bounds__(128)
     }
   }
   __syncthreads();
-  // merge the 4 warps: thread t handles channel t % 64 of heads g = t / 64, t / 64 + 2, ...
-  for (int g = threadIdx.x / HD; g < G; g += 2) {
+  // merge the warps: thread t handles channel t % 64 of heads g = t / 64, t / 64 + NW / 2, ...
+  for (int g = threadIdx.x / HD; g < G; g += NW / 2) {
     const int c = threadIdx.x % HD;
-    float mm = fmaxf(fmaxf(sm_m[0][g], sm_m[1][g]), fmaxf(sm_m[2][g], sm_m[3][g]));
+    float mm = sm_m[0][g];
+#pragma unroll
+    for (int w = 1; w < NW; w++) mm = fmaxf(mm, sm_m[w][g]);
     float ll = 0.0f, o = 0.0f;
 #pragma unroll
-    for (int w = 0; w < 4; w++) {
+    for (int w = 0; w < NW; w++) {
       const float sc = sm_m[w][g] == -INFINITY ? 0.0f : ex2(sm_m[w][g] - mm);
       ll = fmaf(sm_l[w][g], sc, ll);
       o = fmaf(sm_o[w][g][c], sc, o);
@@ -276,13 +285,25 @@ template <int G>
 int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
            const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t n_splits,
            float* scratch, const DecodeOut& dst, bool append) {
-  dim3 grid(n_splits, kv_heads, rows);
   static OncePerDevice attr;
-  if (attr.first(dev->ordinal))
-    FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILE_BYTES));
+  if (attr.first(dev->ordinal)) {
+    FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_split_kernel<G, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<4>::BYTES));
+    FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_split_kernel<G, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<8>::BYTES));
+  }
+  // Two splits of four-warp CTAs, two CTAs per SM, and a merge launch - or, where every (row, kv-head) can have
+  // an SM of its own, one eight-warp CTA over the whole context: the same eight warps per SM stream the same
+  // positions, and the partial results and the merge launch (about 4 us of a 64-row step's layer) fall away.
+  if (n_splits == 2 && rows * kv_heads <= (uint32_t)dev->prop.multiProcessorCount) {
+    dim3 grid(1, kv_heads, rows);
+    FC_LAUNCH(dev, "attn_decode",
+              attn_decode_split_kernel<G, 8><<<grid, 256, Tile<8>::BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams,
+                                                                                      kv, ctx, 1, scratch, dst, append));
+    return FC_OK;
+  }
+  dim3 grid(n_splits, kv_heads, rows);
   FC_LAUNCH(dev, "attn_decode",
-            attn_decode_split_kernel<G><<<grid, 128, TILE_BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv, ctx,
-                                                                       n_splits, scratch, dst, append));
+            attn_decode_split_kernel<G, 4><<<grid, 128, Tile<4>::BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv,
+                                                                                    ctx, n_splits, scratch, dst, append));
   if (n_splits > 1) {
     dim3 mg(kv_heads, rows);
     FC_LAUNCH(dev, "attn_decode_merge",
@@ -297,9 +318,9 @@ int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, ui
 template <int G>
 static int resident_ctas() {
   static int n = 0;
-  if (!n && (cudaFuncSetAttribute(attn_decode_split_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TILE_BYTES) !=
+  if (!n && (cudaFuncSetAttribute(attn_decode_split_kernel<G, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<4>::BYTES) !=
                  cudaSuccess ||
-             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_split_kernel<G>, 128, TILE_BYTES) != cudaSuccess)) {
+             cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_split_kernel<G, 4>, 128, Tile<4>::BYTES) != cudaSuccess)) {
     cudaGetLastError();
     n = 2;
   }
