@@ -205,15 +205,25 @@ __global__ void __launch_bounds__(256)
 bool attn_decode_appends(uint32_t heads, uint32_t kv_heads, uint32_t hd, const float* scratch) {
   return scratch && attn_decode_split_supports(heads, kv_heads, hd);
 }
+bool attn_decode_folds_rope(uint32_t heads, uint32_t kv_heads, uint32_t hd, const float* scratch, const DeferredReduce& pending,
+                            const float* qkv, uint32_t rows) {
+  if (!attn_decode_appends(heads, kv_heads, hd, scratch)) return false;
+  // Only with a pending sum: the kernel then builds the row from the partial sums, which nobody modifies, so the
+  // several CTAs (splits) of a (row, kv-head) can each do it; rotating a finished row in place would not be
+  // repeatable. The sum must be the qkv buffer's own, without a residual (the kernel adds none).
+  if (!pending.splits) return false;
+  return pending.y == qkv && pending.m == rows && pending.n == (heads + 2 * kv_heads) * hd && !pending.resid;
+}
 
 int k_attn_decode(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                   uint32_t hd, const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx,
-                  float* out, float* scratch, __half* xh, __half* xl, uint32_t mp, bool append_kv) {
+                  float* out, float* scratch, __half* xh, __half* xl, uint32_t mp, bool append_kv, const DeferredReduce* qkv_pending,
+                  const RopeParams* rope) {
   if (!rows) return FC_OK;
   if (scratch && attn_decode_split_supports(heads, kv_heads, hd))
     return k_attn_decode_split(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, scratch, out, xh, xl, mp,
-                               append_kv);
-  if (xh || append_kv) return fc_fail(dev, FC_ERR_ARG, "only the context-split decode attention writes fp16 terms or the cache");
+                               append_kv, qkv_pending, rope);
+  if (xh || append_kv || rope) return fc_fail(dev, FC_ERR_ARG, "only the context-split decode attention writes fp16 terms or the cache");
   if (hd % 4 || hd > 256 || 256 % hd)
     return fc_fail(dev, FC_ERR_UNSUPPORTED, "decode attention needs head_dim in {4,8,...,256} dividing 256, not %u", hd);
   const uint32_t G = heads / kv_heads;

@@ -54,12 +54,21 @@ struct DecodeOut {
   }
 };
 
+// What the launch does to the fused qkv row before it attends, when the RoPE / cache launch is folded into it
+// (`on`): finish the qkv product's pending split-K sum and bias exactly as its own reduce would (ascending split
+// order), rotate q and k, and write the slice back; the row's k and v then reach the cache through the append path.
+struct QkvFinish {
+  bool on = false;
+  DeferredReduce pend; // splits == 0: the row is already summed
+  RopeParams rope;
+};
+
 // partial layout per (row, kv-head, split): [G] max (log2 domain), [G] sum, [G][64] weighted output
 template <int G, int NW>
 __global__ void __launch_bounds__(NW * 32)
-    attn_decode_split_kernel(const float* __restrict__ qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
+    attn_decode_split_kernel(const float* qkv, uint32_t q_stride, uint32_t heads, uint32_t kv_heads,
                              const int32_t* __restrict__ positions, const int32_t* __restrict__ streams, KvLayer kv,
-                             uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst, bool append) {
+                             uint32_t ctx, uint32_t n_splits, float* __restrict__ partial, DecodeOut dst, bool append, QkvFinish fin) {
   constexpr int POS_PER_ITER = Tile<NW>::POS; // (this kernel's own step; the host's split rule keeps the 4-warp one)
   __shared__ float sm_m[NW][G], sm_l[NW][G];
   __shared__ __align__(16) float sm_o[NW][G][HD];
@@ -74,6 +83,48 @@ __global__ void __launch_bounds__(NW * 32)
       dst.xh[at] = dst.xl[at] = __float2half_rn(0.0f);
     }
   const uint32_t slot = streams ? (uint32_t)streams[r] : 0;
+  if (fin.on) {
+    // This CTA's slice of the row: its G query heads, its k head and its v head (every split of the same
+    // (row, kv-head) computes and writes the same values).
+    __shared__ float slice[(G + 2) * HD];
+    const uint32_t qd = heads * HD, kvd = kv_heads * HD, w = qd + 2 * kvd;
+    float* grow = const_cast<float*>(qkv) + (size_t)r * q_stride;
+    auto col_of = [&](uint32_t idx) {
+      const uint32_t hs = idx / HD, e = idx % HD;
+      return hs < (uint32_t)G ? (kvh * G + hs) * HD + e : hs == (uint32_t)G ? qd + kvh * HD + e : qd + kvd + kvh * HD + e;
+    };
+    for (uint32_t idx = threadIdx.x; idx < (G + 2) * HD; idx += blockDim.x) {
+      const uint32_t col = col_of(idx);
+      float v;
+      if (fin.pend.splits) {
+        v = 0.0f;
+        const float* p = fin.pend.partial + (size_t)r * w + col;
+        for (uint32_t sp = 0; sp < fin.pend.splits; sp++) v += p[(size_t)sp * fin.pend.m * w];
+        if (fin.pend.bias) v += fin.pend.bias[col];
+      } else {
+        v = grow[col]; // (host code folds the launch only with a pending sum: see attn_decode_folds_rope)
+      }
+      slice[idx] = v;
+    }
+    __syncthreads();
+    if (fin.rope.cos) { // the q heads and the k head: pairs (2p, 2p + 1) or (p, p + half) of the first rope_dim channels
+      const uint32_t half = fin.rope.rope_dim / 2, pos = (uint32_t)positions[r];
+      const float* cs = fin.rope.cos + (size_t)pos * half;
+      const float* sn = fin.rope.sin + (size_t)pos * half;
+      for (uint32_t i = threadIdx.x; i < (G + 1) * half; i += blockDim.x) {
+        const uint32_t h = i / half, pp = i % half;
+        float* base = slice + h * HD;
+        const uint32_t ia = fin.rope.type == FC_ROPE_NORM ? 2 * pp : pp, ib = fin.rope.type == FC_ROPE_NORM ? 2 * pp + 1 : pp + half;
+        const float c = cs[pp], sv = sn[pp], a = base[ia], b = base[ib];
+        base[ia] = a * c - b * sv;
+        base[ib] = a * sv + b * c;
+      }
+      __syncthreads();
+    }
+    for (uint32_t idx = threadIdx.x; idx < (G + 2) * HD; idx += blockDim.x) grow[col_of(idx)] = slice[idx];
+    __threadfence(); // (the tiles below fetch the row's k and v with cp.async, past this SM's L1)
+    __syncthreads();
+  }
 
   // The 8 lanes of a lane group share one cached position and divide it two ways: CP lanes split the 64
   // channels (CH each), 8 / CP groups of lanes split the G query heads (HL each). More head groups mean fewer
@@ -284,7 +335,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial, uint
 template <int G>
 int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
            const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, uint32_t n_splits,
-           float* scratch, const DecodeOut& dst, bool append) {
+           float* scratch, const DecodeOut& dst, bool append, const QkvFinish& fin) {
   static OncePerDevice attr;
   if (attr.first(dev->ordinal)) {
     FC_CUDA(dev, cudaFuncSetAttribute(attn_decode_split_kernel<G, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Tile<4>::BYTES));
@@ -297,13 +348,13 @@ int launch(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, ui
     dim3 grid(1, kv_heads, rows);
     FC_LAUNCH(dev, "attn_decode",
               attn_decode_split_kernel<G, 8><<<grid, 256, Tile<8>::BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams,
-                                                                                      kv, ctx, 1, scratch, dst, append));
+                                                                                      kv, ctx, 1, scratch, dst, append, fin));
     return FC_OK;
   }
   dim3 grid(n_splits, kv_heads, rows);
   FC_LAUNCH(dev, "attn_decode",
             attn_decode_split_kernel<G, 4><<<grid, 128, Tile<4>::BYTES, dev->stream>>>(qkv, q_stride, heads, kv_heads, positions, streams, kv,
-                                                                                    ctx, n_splits, scratch, dst, append));
+                                                                                    ctx, n_splits, scratch, dst, append, fin));
   if (n_splits > 1) {
     dim3 mg(kv_heads, rows);
     FC_LAUNCH(dev, "attn_decode_merge",
@@ -361,18 +412,25 @@ bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd) 
 
 int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                         const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
-                        float* out, __half* xh, __half* xl, uint32_t mp, bool append) {
+                        float* out, __half* xh, __half* xl, uint32_t mp, bool append, const DeferredReduce* qkv_pending,
+                        const RopeParams* rope) {
   if (!rows) return FC_OK;
   const uint32_t ns = attn_decode_splits(dev, rows, heads, kv_heads, ctx);
   DecodeOut dst;
   dst.out = out, dst.xh = xh, dst.xl = xl, dst.mp = mp;
+  QkvFinish fin;
+  if (rope) { // the RoPE / cache launch folded into this one (the caller passes append = true with it)
+    fin.on = true;
+    fin.rope = *rope;
+    if (qkv_pending) fin.pend = *qkv_pending;
+  }
   switch (heads / kv_heads) {
-    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
-    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
-    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
-    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
-    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
-    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append);
+    case 1: return launch<1>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
+    case 2: return launch<2>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
+    case 3: return launch<3>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
+    case 4: return launch<4>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
+    case 6: return launch<6>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
+    case 8: return launch<8>(dev, qkv, q_stride, rows, heads, kv_heads, positions, streams, kv, ctx, ns, scratch, dst, append, fin);
   }
   return fc_fail(dev, FC_ERR_UNSUPPORTED, "split decode attention: group size %u", heads / kv_heads);
 }

@@ -218,9 +218,13 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
     // Without RoPE the launch below would only copy k and v into the cache: the decode attention does that itself.
     const bool attn_appends =
         mode == ATTN_DECODE && !m->rope.cos && attn_decode_appends(m->heads, m->kv_heads, m->hd, m->attn_scratch);
+    // With RoPE, the decode attention can take the rotation, the pending sum and the cache append along as well:
+    // one launch less per layer.
+    const bool attn_folds = mode == ATTN_DECODE && m->rope.cos &&
+                            attn_decode_folds_rope(m->heads, m->kv_heads, m->hd, m->attn_scratch, qkv_sum, b.qkv, rows);
     if (attn_appends)
       FC_TRY(k_flush_deferred(dev, qkv_sum));
-    else
+    else if (!attn_folds)
       FC_TRY(k_rope_kv(dev, b.qkv, rows, m->heads, m->kv_heads, m->hd, m->rope, positions, streams,
                        to_cache ? &l.kv : nullptr, m->ctx, &qkv_sum));
     Epilogue e_wo;
@@ -233,7 +237,8 @@ int run_stack_f32(FcModel* m, const PassBufs& b, const int32_t* ids, const int32
         e_wo.presplit = true;
       }
       FC_TRY(k_attn_decode(dev, b.qkv, m->qkv_w(), rows, m->heads, m->kv_heads, m->hd, positions, streams, l.kv, m->ctx,
-                           b.attn, m->attn_scratch, xh, xl, mp, attn_appends));
+                           b.attn, m->attn_scratch, xh, xl, mp, attn_appends || attn_folds, attn_folds ? &qkv_sum : nullptr,
+                           attn_folds ? &m->rope : nullptr));
     } else if (mode == ATTN_STATELESS)
       FC_TRY(k_attn_causal_f32(dev, b.qkv, n_seqs, t, m->heads, m->kv_heads, m->hd, b.attn));
     else

@@ -48,7 +48,10 @@ int k_nll_sums(FcDevice* dev, const float* logprob, uint32_t n_seqs, uint32_t ro
 int k_attn_decode(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                   uint32_t hd, const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx,
                   float* out /*[rows][heads*hd]*/, float* scratch, __half* xh = nullptr, __half* xl = nullptr,
-                  uint32_t mp = 0, bool append_kv = false);
+                  uint32_t mp = 0, bool append_kv = false,
+                  // the context-split kernel only: fold the RoPE / cache launch into this one - finish the qkv
+                  // product's pending split-K sum (nullable: none), rotate q and k by `rope`, append k and v
+                  const DeferredReduce* qkv_pending = nullptr, const RopeParams* rope = nullptr);
 // Whether k_attn_decode can store the rows' own k and v into the cache itself (`append_kv`): the
 // context-split kernel does, for models whose k needs no rotation first.
 bool attn_decode_appends(uint32_t heads, uint32_t kv_heads, uint32_t hd, const float* scratch);
@@ -57,7 +60,11 @@ bool attn_decode_split_supports(uint32_t heads, uint32_t kv_heads, uint32_t hd);
 size_t attn_decode_scratch_bytes(const FcDevice* dev, uint32_t rows, uint32_t heads, uint32_t kv_heads, uint32_t ctx);
 int k_attn_decode_split(FcDevice* dev, const float* qkv, uint32_t q_stride, uint32_t rows, uint32_t heads, uint32_t kv_heads,
                         const int32_t* positions, const int32_t* streams, const KvLayer& kv, uint32_t ctx, float* scratch,
-                        float* out, __half* xh, __half* xl, uint32_t mp, bool append);
+                        float* out, __half* xh, __half* xl, uint32_t mp, bool append, const DeferredReduce* qkv_pending = nullptr,
+                        const RopeParams* rope = nullptr);
+// Whether the launch can take the qkv product's pending sum and the rotation along (attn_decode.cu).
+bool attn_decode_folds_rope(uint32_t heads, uint32_t kv_heads, uint32_t hd, const float* scratch, const DeferredReduce& pending,
+                            const float* qkv, uint32_t rows);
 // Stateless causal attention over `n_seqs` sequences of `t` rows in the fused qkv buffer (exact f32).
 int k_attn_causal_f32(FcDevice* dev, const float* qkv, uint32_t n_seqs, uint32_t t, uint32_t heads, uint32_t kv_heads,
                       uint32_t hd, float* out);
