@@ -46,6 +46,20 @@ constexpr int TS_THREADS = (4 + 4 * PSETS + 8) * 32;
 constexpr int TS_REGS_PROD = 64, TS_REGS_EPI = 120;
 constexpr int TS_REGS_NEEDED = 32 * (4 * REGS_CTRL + 4 * PSETS * TS_REGS_PROD + 8 * TS_REGS_EPI);
 
+// The batched-decode product at f32-class accuracy (gemm_tx_main.cuh)
+constexpr int TX_X_STAGES = 8, TX_W_STAGES = 4, TX_PSETS = 2;
+constexpr uint32_t TX_CHUNK = 4;                  // K steps (256 k) that tensor memory accumulates before the registers take over
+constexpr uint32_t TX_X_BYTES = 128 * TC_BK * 2;  // 16 KB: the xh box over the xl box
+constexpr uint32_t TX_Q_OFF = TX_X_BYTES;         // then the tile's packed weights of the step (128 rows of 64 or 32 bytes)
+constexpr uint32_t TX_SC_OFF = TX_Q_OFF + 8192;   // then eight f16 scales per row (the step's 256-k chunk)
+constexpr uint32_t TX_STAGE_BYTES = TX_SC_OFF + 2048; // 26 KB
+constexpr uint32_t TX_ACC_COLS = 128;             // wh.xh (64) | wh.xl + wl.xh (64)
+constexpr uint32_t TX_W_COLS = TC_BK;             // 32 columns of wh and 32 of wl per stage
+constexpr uint32_t TX_W_COL0 = 2 * TX_ACC_COLS;
+static_assert(TX_W_COL0 + TX_W_STAGES * TX_W_COLS <= 512, "tensor memory has 512 columns");
+constexpr int TX_THREADS = (4 + 4 * TX_PSETS + 8) * 32;
+constexpr uint32_t TX_SMEM_BYTES = TX_X_STAGES * TX_STAGE_BYTES + 512 /*barriers*/ + 4 * TC_BN * 4 /*row scales*/ + 1024 /*alignment slack*/;
+
 enum { ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_ACC = 3 };
 
 // Both operands are fp16 (f32 accumulation). The block scale is an f16 and a quant has at most 8
@@ -388,6 +402,7 @@ __device__ __forceinline__ void epilogue_lse(const TcArgs& a, LseState& s, uint3
 
 #include "gemm_tc_main.cuh"
 #include "gemm_ts_main.cuh"
+#include "gemm_tx_main.cuh"
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point: the library carries no link
 // dependency on libcuda, so it still loads (and exports its symbols) on a machine without a GPU.
@@ -481,7 +496,77 @@ int pick_epi(FcDevice* dev, const CUtensorMap& tmap, const QMat& w, const TcArgs
   return fc_fail(dev, FC_ERR_ARG, "unknown epilogue %d", epi);
 }
 
+template <int KIND>
+int launch_tx(FcDevice* dev, const CUtensorMap& txh, const CUtensorMap& txl, const CUtensorMap& tq, const CUtensorMap& tsc,
+              const TxArgs& a, dim3 grid) {
+  auto kern = qgemm_tx_kernel<KIND>;
+  static OncePerDevice attr;
+  if (attr.first(dev->ordinal)) {
+    FC_CUDA(dev, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TX_SMEM_BYTES));
+  }
+  FC_LAUNCH(dev, "qgemm_tx", kern<<<grid, TX_THREADS, TX_SMEM_BYTES, dev->stream>>>(txh, txl, tq, tsc, a));
+  return FC_OK;
+}
+
 } // namespace
+
+// Whether the product of `m` rows of x takes the exact-class tcgen05 kernel: Q8_0 / Q4_0, 9..64 rows (up to eight
+// rows the mma.sync kernel with x in registers streams the weights faster: 50 against 71 us on K 1024 x N 151936),
+// whole 256-wide rows of at least 8 K steps, and an output long enough that its 128-row tiles cover at least half
+// of the SMs without a split of K.
+bool qgemm_tx_takes(const FcDevice* dev, const QMat& w, uint32_t m) {
+  if (w.kind != FC_Q8_0 && w.kind != FC_Q4_0) return false;
+  if (m <= 8 || m > 64 || w.k % 256 || w.k < 512) return false;
+  if ((reinterpret_cast<uintptr_t>(w.qs) | reinterpret_cast<uintptr_t>(w.sc)) & 15) return false;
+  return (w.n + TC_BN - 1) / TC_BN >= (uint32_t)dev->prop.multiProcessorCount / 2;
+}
+
+// y[m][n] = epilogue(x . W^T), x given as its two fp16 terms xh, xl: [mp][k] each, rows m..mp-1 zero.
+int k_qgemm_tx(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, uint32_t mp, uint32_t m, float* y,
+               const Epilogue& ep) {
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  CUtensorMap maps[2];
+  const __half* src[2] = {xh, xl};
+  for (int i = 0; i < 2; i++) {
+    if (reinterpret_cast<uintptr_t>(src[i]) & 15) return fc_fail(dev, FC_ERR_ARG, "the split terms of x must be 16-byte aligned");
+    const cuuint64_t dims[2] = {w.k, mp};
+    const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
+    const cuuint32_t box[2] = {TC_BK, 64}; // (rows past mp are zero-filled)
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)src[i], dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled (x terms) failed with %d", (int)cr);
+  }
+  // the packed weights as bytes, [n][row bytes], in boxes of 128 rows by one K step; the scales, [n][k / 32] f16, in
+  // boxes of 128 rows by eight (rows past n read as zeros: scale 0)
+  const bool q8 = w.kind == FC_Q8_0;
+  const uint32_t row_bytes = q8 ? w.k : w.k / 2, step_bytes = q8 ? 64 : 32;
+  CUtensorMap tq, tsc;
+  {
+    const cuuint64_t dims[2] = {row_bytes, w.n};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {step_bytes, TC_BN};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.qs, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      q8 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled (packed weights) failed with %d", (int)cr);
+    const cuuint64_t sdims[2] = {(cuuint64_t)(w.k / QK) * 2, w.n};
+    const cuuint64_t sstrides[1] = {(cuuint64_t)(w.k / QK) * 2};
+    const cuuint32_t sbox[2] = {16, TC_BN};
+    cr = enc(&tsc, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w.sc, sdims, sstrides, sbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled (scales) failed with %d", (int)cr);
+  }
+  TxArgs a;
+  a.m = m, a.n = w.n, a.k = w.k, a.y = y, a.bias = ep.bias, a.resid = ep.resid, a.act = ep.act, a.err_flag = dev->d_flag;
+  const uint32_t tiles = (w.n + TC_BN - 1) / TC_BN, sms = (uint32_t)dev->prop.multiProcessorCount;
+  dim3 grid(tiles < sms ? tiles : sms);
+  if (q8) return launch_tx<FC_Q8_0>(dev, maps[0], maps[1], tq, tsc, a, grid);
+  return launch_tx<FC_Q4_0>(dev, maps[0], maps[1], tq, tsc, a, grid);
+}
 
 int k_qgemm_tc_f16(FcDevice* dev, const QMat& w, const __half* a_dev, int epi, TcArgs args) {
   if (args.m == 0) return FC_OK;

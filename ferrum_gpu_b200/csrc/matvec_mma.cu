@@ -665,7 +665,8 @@ void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, 
 }
 
 int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
-  if (m <= 8) return k_qmatvec_mma8(dev, w, x, m, y, ep, scratch);
+  const bool tx = dev->matvec_choice == 0 && qgemm_tx_takes(dev, w, m); // long outputs: the tcgen05 form (gemm_tc.cu)
+  if (m <= 8 && !tx) return k_qmatvec_mma8(dev, w, x, m, y, ep, scratch);
   uint32_t mp;
   __half *xh, *xl;
   qmatvec_mma_split_ptrs(scratch, m, w.k, &xh, &xl, &mp);
@@ -689,6 +690,7 @@ int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
               norm_split_kernel<<<mp, 256, 0, dev->stream>>>(x, m, w.k, ep.norm, ep.norm_g, ep.norm_b, ep.norm_eps, xh, xl, pend));
   else
     FC_LAUNCH(dev, "x_split", x_split_kernel<<<(unsigned)((total + 255) / 256), 256, 0, dev->stream>>>(x, m, mp, w.k, xh, xl));
+  if (tx) return k_qgemm_tx(dev, w, xh, xl, mp, m, y, ep);
   // split K until the grid covers the SMs about twice: whole 128-k slices per split, the last split may be
   // shorter (K = 2816 is 22 slices: 11 splits of 2, where a power-of-two rule stops at 2 splits of 11)
   const uint32_t row_ctas = (w.n + ROWS_PER_CTA - 1) / ROWS_PER_CTA, slices = w.k / XS;
