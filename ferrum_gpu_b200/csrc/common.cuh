@@ -247,7 +247,7 @@ int k_dequant(FcDevice* dev, const QMat& m, float* out_nk_dev);
 int k_qmatvec(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep);
 // matvec1.cu: one row of a block format, streamed through shared memory onto mma.sync
 // gemm_tc.cu: the exact-class tcgen05 product of 2..64 rows of x (x as its two fp16 terms)
-bool qgemm_tx_takes(const FcDevice* dev, const QMat& w, uint32_t m);
+bool qgemm_tx_takes(const FcDevice* dev, const QMat& w, uint32_t m, bool deferring);
 int k_qgemm_tx(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl, uint32_t mp, uint32_t m, float* y,
                const Epilogue& ep);
 bool qmatvec1_supports(const FcDevice* dev, const QMat& w);

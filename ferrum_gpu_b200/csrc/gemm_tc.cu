@@ -512,13 +512,16 @@ int launch_tx(FcDevice* dev, const CUtensorMap& txh, const CUtensorMap& txl, con
 
 // Whether the product of `m` rows of x takes the exact-class tcgen05 kernel: Q8_0 / Q4_0, 9..64 rows (up to eight
 // rows the mma.sync kernel with x in registers streams the weights faster: 50 against 71 us on K 1024 x N 151936),
-// whole 256-wide rows of at least 8 K steps, and an output long enough that its 128-row tiles cover at least half
-// of the SMs without a split of K.
-bool qgemm_tx_takes(const FcDevice* dev, const QMat& w, uint32_t m) {
+// whole 256-wide rows of at least 8 K steps, and an output long enough without a split of K: 128-row tiles for half
+// of the SMs, or for a quarter of them when more than 32 rows make the mma.sync product slow (K 4096 x N 5120 at 64
+// rows: 37 against 41 + 9 us for the product and its split-K reduce) - unless the caller would fold that reduce
+// into its next launch (`deferring`), which makes the two even there.
+bool qgemm_tx_takes(const FcDevice* dev, const QMat& w, uint32_t m, bool deferring) {
   if (w.kind != FC_Q8_0 && w.kind != FC_Q4_0) return false;
   if (m <= 8 || m > 64 || w.k % 256 || w.k < 512) return false;
   if ((reinterpret_cast<uintptr_t>(w.qs) | reinterpret_cast<uintptr_t>(w.sc)) & 15) return false;
-  return (w.n + TC_BN - 1) / TC_BN >= (uint32_t)dev->prop.multiProcessorCount / 2;
+  const uint32_t sms = (uint32_t)dev->prop.multiProcessorCount;
+  return (w.n + TC_BN - 1) / TC_BN >= ((m > 32 && !deferring) ? sms / 4 : sms / 2);
 }
 
 // y[m][n] = epilogue(x . W^T), x given as its two fp16 terms xh, xl: [mp][k] each, rows m..mp-1 zero.

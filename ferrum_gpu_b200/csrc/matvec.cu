@@ -409,8 +409,7 @@ int k_qlinear_f32(FcDevice* dev, const QMat& w, const float* x, uint32_t m, floa
   const bool mma_ok = ep.scratch && qmatvec_mma_supports(w, m) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0 || ep.presplit);
   if (ep.presplit && !(mma_ok && m > 8)) return fc_fail(dev, FC_ERR_ARG, "a pre-split x needs the 9..64-row tensor-core product");
   const bool use_fma = fma_ok && (!mma_ok || forced == 1 || (forced == 0 && m < 2));
-  // (long outputs of 2..8 rows take the wide path too: the exact-class tcgen05 product works on x's split terms)
-  const bool use_mma_wide = !use_fma && mma_ok && (m > 8 || (forced == 0 && !ep.presplit && qgemm_tx_takes(dev, w, m)));
+  const bool use_mma_wide = !use_fma && mma_ok && m > 8; // its x split takes the norm along
   if (ep.pending && ep.pending->splits && !use_mma_wide) { // only that split can finish a producer's split-K sum
     FC_TRY(k_flush_deferred(dev, *ep.pending));
     ep.pending = nullptr;

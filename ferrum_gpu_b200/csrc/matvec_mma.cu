@@ -665,7 +665,7 @@ void qmatvec_mma_split_ptrs(void* scratch, uint32_t m, uint32_t k, __half** xh, 
 }
 
 int k_qmatvec_mma(FcDevice* dev, const QMat& w, const float* x, uint32_t m, float* y, const Epilogue& ep, void* scratch) {
-  const bool tx = dev->matvec_choice == 0 && qgemm_tx_takes(dev, w, m); // long outputs: the tcgen05 form (gemm_tc.cu)
+  const bool tx = dev->matvec_choice == 0 && qgemm_tx_takes(dev, w, m, ep.defer_out != nullptr); // long outputs: the tcgen05 form (gemm_tc.cu)
   if (m <= 8 && !tx) return k_qmatvec_mma8(dev, w, x, m, y, ep, scratch);
   uint32_t mp;
   __half *xh, *xl;

@@ -53,7 +53,7 @@ def test_tensor_product_on_random_shapes(dev, m, k, n, kind, seed):
 
 @pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
 @pytest.mark.parametrize("m,k,n", [(9, 512, 9600), (12, 1024, 16000), (17, 768, 12000), (33, 4096, 11008), (64, 1024, 20000),
-                                   (64, 2048, 9473)])
+                                   (64, 2048, 9473), (64, 1024, 5632), (40, 4096, 4800)])
 def test_long_output_products_of_a_few_rows_keep_f32_accuracy(dev, kind, m, k, n):
     """Outputs long enough to fill the device take the tcgen05 form of the batched-decode product (weights and x both
     as two fp16 terms, products exact in the f32 accumulator, 256 k at a time): same 1e-5 bound as every exact-path
