@@ -130,21 +130,17 @@ __device__ __forceinline__ void dequant_q4_block(const uint4& q, __half d, Sink&
   one(words[3], o), sink.template put<C0 + 3>(o[0], o[1], o[2], o[3]);
 }
 
-// 16 int8 quants (one uint4 = half a Q8_0 block) -> chunks C0, C0 + 1
+// 16 int8 quants (one uint4 = half a Q8_0 block) -> chunks C0, C0 + 1. A byte b = q + 128 under the exponent byte
+// 0x64 is the fp16 1024 + b; minus 1152 leaves q exactly, and one half2 multiply by the block's f16 scale (`dd`: in
+// both halves) rounds d * q to fp16 once - the same bits as the f32 product (exact: 19 bits) converted to fp16.
 template <int C0, class Sink>
-__device__ __forceinline__ void dequant_q8_half(const uint4& q, float d, Sink& sink) {
+__device__ __forceinline__ void dequant_q8_half(const uint4& q, uint32_t dd, Sink& sink) {
   auto one = [&](uint32_t wa, uint32_t wb, uint32_t (&o)[4]) {
-    const uint32_t w2[2] = {wa, wb};
-#pragma unroll
-    for (int w = 0; w < 2; w++) {
-      const uint32_t u = w2[w] ^ 0x80808080u;
-      const float f0 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f;
-      const float f1 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f;
-      const float f2 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f;
-      const float f3 = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f;
-      o[2 * w] = pack_f16(f0 * d, f1 * d);
-      o[2 * w + 1] = pack_f16(f2 * d, f3 * d);
-    }
+    const uint32_t ua = wa ^ 0x80808080u, ub = wb ^ 0x80808080u;
+    o[0] = f16x2_mul(f16x2_sub(__byte_perm(ua, 0x64646464u, 0x5140), 0x64806480u), dd);
+    o[1] = f16x2_mul(f16x2_sub(__byte_perm(ua, 0x64646464u, 0x5342), 0x64806480u), dd);
+    o[2] = f16x2_mul(f16x2_sub(__byte_perm(ub, 0x64646464u, 0x5140), 0x64806480u), dd);
+    o[3] = f16x2_mul(f16x2_sub(__byte_perm(ub, 0x64646464u, 0x5342), 0x64806480u), dd);
   };
   uint32_t o[4];
   one(q.x, q.y, o), sink.template put<C0>(o[0], o[1], o[2], o[3]);
@@ -275,8 +271,7 @@ __device__ __forceinline__ void emit_row(const RowRegs<KIND>& r, Sink& sink) {
     dequant_q4_block<4>(rr.q[1], d1, sink);
   } else if (KIND == FC_Q8_0) {
     const RowRegs<FC_Q8_0>& rr = (const RowRegs<FC_Q8_0>&)r;
-    const float d0 = __half2float(__ushort_as_half((unsigned short)(rr.sc & 0xffff)));
-    const float d1 = __half2float(__ushort_as_half((unsigned short)(rr.sc >> 16)));
+    const uint32_t d0 = (rr.sc & 0xffffu) * 0x00010001u, d1 = (rr.sc >> 16) * 0x00010001u; // the f16 scale in both halves
     dequant_q8_half<0>(rr.q[0], d0, sink);
     dequant_q8_half<2>(rr.q[1], d0, sink);
     dequant_q8_half<4>(rr.q[2], d1, sink);
