@@ -403,6 +403,35 @@ def test_many_streams_take_the_tensor_decode_path_and_match_the_oracle(dev, kind
     g.close()
 
 
+@pytest.mark.parametrize("kind", [QKind.Q8_0, QKind.Q4_0])
+def test_forty_streams_of_a_wide_gpt2_match_the_oracle(dev, kind):
+    """Forty concurrent streams of a GPT-2-style layer with a 4864-wide feed-forward: its first product (K 512 ->
+    N 4864, bias, GELU) is long enough for the tcgen05 form of the batched-decode product, so that kernel's bias
+    and activation epilogue is held to the oracle here; every stream sees the logits it would see alone."""
+    cfg = Gpt2Config(vocab=300, ctx=8, dim=512, heads=8, layers=1, hidden=4864)
+    m = random_gpt2(cfg, seed=21, std=0.04, bias_std=0.05, gain_jitter=0.1)
+    ref = orc.dequantised_gpt2(m, int(kind), snap_embedding=False)
+    n_streams, steps, watch = 40, 3, (0, 17, 39)
+    toks = np.stack([random_tokens(300 + s, steps, cfg.vocab) for s in range(n_streams)])
+    want = {}
+    for s in watch:
+        o = orc.OracleGpt2(ref)
+        want[s] = [o.feed(int(t)) for t in toks[s]]
+    g = CudaGpt2(dev, m, kind, max_streams=n_streams)
+    for i in range(steps):  # the first step runs eagerly (its launches are listed), the second is captured, the third replayed
+        if i == 0:
+            dev.profile(True)
+        am, lg = g.feed_batch(toks[:, i], want_logits=True)
+        if i == 0:
+            assert "qgemm_tx" in dev.profile_report()
+            dev.profile(False)
+        for s in watch:
+            assert orc.max_rel_err(lg[s], want[s][i]) < 2 * FORWARD, (kind, i, s)
+        for s in range(n_streams):
+            assert am[s] == orc.argmax(lg[s])
+    g.close()
+
+
 def test_greedy_pick_over_a_long_row_keeps_the_first_maximum(dev):
     """A long vocabulary row is searched by several CTAs; the first-maximum rule of `sampling::argmax`
     (ferrum_model/src/sampling.rs:L32-L40) must survive that: every logit of this model appears twice, at
