@@ -530,7 +530,7 @@ int k_qgemm_tx(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl,
     if (reinterpret_cast<uintptr_t>(src[i]) & 15) return fc_fail(dev, FC_ERR_ARG, "the split terms of x must be 16-byte aligned");
     const cuuint64_t dims[2] = {w.k, mp};
     const cuuint64_t strides[1] = {(cuuint64_t)w.k * 2};
-    const cuuint32_t box[2] = {TC_BK, 64}; // (rows past mp are zero-filled)
+    const cuuint32_t box[2] = {TC_BK, mp}; // mp = 16, 32 or 64 rows (rows m .. mp - 1 of the buffers are zero)
     const cuuint32_t estr[2] = {1, 1};
     CUresult cr = enc(&maps[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)src[i], dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -559,6 +559,8 @@ int k_qgemm_tx(FcDevice* dev, const QMat& w, const __half* xh, const __half* xl,
     if (cr != CUDA_SUCCESS) return fc_fail(dev, FC_ERR_DEVICE, "cuTensorMapEncodeTiled (scales) failed with %d", (int)cr);
   }
   TxArgs a;
+  if (mp != 16 && mp != 32 && mp != 64) return fc_fail(dev, FC_ERR_ARG, "the split terms of x come in blocks of 16, 32 or 64 rows, not %u", mp);
+  a.mp = mp;
   a.m = m, a.n = w.n, a.k = w.k, a.y = y, a.bias = ep.bias, a.resid = ep.resid, a.act = ep.act, a.err_flag = dev->d_flag;
   const uint32_t tiles = (w.n + TC_BN - 1) / TC_BN, sms = (uint32_t)dev->prop.multiProcessorCount;
   dim3 grid(tiles < sms ? tiles : sms);

@@ -14,6 +14,7 @@
 // multiply-add, exact) in half2 arithmetic and writes 32 columns of each into tensor memory. So that wl keeps
 // its bits however small the scales are, the row's 256-k chunk is first multiplied by the power of two that brings
 // the largest of its eight scales to [2^7, 2^8); the epilogue divides it out chunk by chunk.
+// (For at most 32 or 16 rows of x the boxes, the tile and the MMAs' N shrink with them: 2 x 32 or 2 x 16 rows.)
 // The B operand of a K step is one shared-memory tile of 128 rows: rows 0..63 the xh slice, rows 64..127 the xl
 // slice (two TMA boxes). Two MMAs per 16 k, both against all 128 rows into the same 128 accumulator columns:
 // A = wh, then A = wl. Tensor memory: two accumulator buffers of 128 columns, four weight stages of 32 + 32.
@@ -106,6 +107,7 @@ __device__ __forceinline__ void emit_row_hilo(const RowRegs<KIND>& r, float mul,
 
 struct TxArgs {
   uint32_t m = 0, n = 0, k = 0; // rows of x (<= 64), weight rows, width
+  uint32_t mp = 64;             // rows of the xh and of the xl box: 16, 32 or 64 >= m (the MMAs' N is twice that)
   float* y = nullptr;           // [m][n]
   const float* bias = nullptr;  // [n]
   const float* resid = nullptr; // [m][n]; may alias y
@@ -176,9 +178,9 @@ __global__ void __launch_bounds__(TX_THREADS, 1)
               break;
             }
             uint8_t* st = smem + s * TX_STAGE_BYTES;
-            tc::mbar_arrive_expect_tx(&x_full[s], TX_X_BYTES + TC_BN * STEP_BYTES + TC_BN * 16);
+            tc::mbar_arrive_expect_tx(&x_full[s], 2 * a.mp * 128 + TC_BN * STEP_BYTES + TC_BN * 16);
             tc::tma_load_2d(st, &tmap_xh, &x_full[s], (int32_t)(kk * TC_BK), 0);
-            tc::tma_load_2d(st + TX_X_BYTES / 2, &tmap_xl, &x_full[s], (int32_t)(kk * TC_BK), 0);
+            tc::tma_load_2d(st + a.mp * 128, &tmap_xl, &x_full[s], (int32_t)(kk * TC_BK), 0); // (a multiple of 1024: swizzle atoms stay whole)
             tc::tma_load_2d(st + TX_Q_OFF, &tmap_q, &x_full[s], (int32_t)(kk * STEP_BYTES), (int32_t)(tile * TC_BN));
             tc::tma_load_2d(st + TX_SC_OFF, &tmap_sc, &x_full[s], (int32_t)((kk / TX_CHUNK) * 16), (int32_t)(tile * TC_BN));
           }
@@ -190,7 +192,7 @@ __global__ void __launch_bounds__(TX_THREADS, 1)
       // so it is kept to one wait and one commit per K step: w_full[t] implies the step's TMA bytes (the producers
       // waited for them), and one commit on x_empty[s] hands back the x stage and the weight stage together. ----
       if (tc::elect_one()) {
-        constexpr uint32_t idesc = tc::idesc_f16_f32(128, 128);
+        const uint32_t idesc = a.mp == 64 ? tc::idesc_f16_f32(128, 128) : a.mp == 32 ? tc::idesc_f16_f32(128, 64) : tc::idesc_f16_f32(128, 32);
         constexpr uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29); // stride 1024 B, version 1, 128B swizzle
         uint32_t it = 0, ccnt = 0; // K steps and chunks issued so far
         bool ok = true;
@@ -310,22 +312,25 @@ __global__ void __launch_bounds__(TX_THREADS, 1)
         if (!ok) break;
         tc::tc_fence_after();
         const float us = unscale[(ccnt & 3) * TC_BN + quad * 32 + lane]; // the chunk's power of two, divided out here
+        // columns [0, mp) hold the products with xh, [mp, 2 mp) those with xl; this warp's rows of x are
+        // [32 jhalf, 32 jhalf + 32) as far as they lie below mp
         const uint32_t taddr = tmem_base + ((quad * 32u) << 16) + buf * TX_ACC_COLS + jhalf * 32;
 #pragma unroll
         for (int c = 0; c < 2; c++) { // 16 rows of x at a time: two 16-column loads
-          uint32_t hh[16], sm[16];
-          tc::tmem_ld_32x16(taddr + c * 16, hh);        // (wh + wl) . xh
-          tc::tmem_ld_32x16(taddr + 64 + c * 16, sm);   // (wh + wl) . xl
-          tc::tmem_ld_wait();
-          if (c == 1) { // the chunk is in registers: the buffer may be refilled
-            tc::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
-          }
+          if (jhalf * 32 + c * 16 < a.mp) {
+            uint32_t hh[16], sm[16];
+            tc::tmem_ld_32x16(taddr + c * 16, hh);          // (wh + wl) . xh
+            tc::tmem_ld_32x16(taddr + a.mp + c * 16, sm);   // (wh + wl) . xl
+            tc::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; j++)
-            acc[c * 16 + j] = fmaf(__uint_as_float(sm[j]) + __uint_as_float(hh[j]), us, acc[c * 16 + j]);
+            for (int j = 0; j < 16; j++)
+              acc[c * 16 + j] = fmaf(__uint_as_float(sm[j]) + __uint_as_float(hh[j]), us, acc[c * 16 + j]);
+          }
         }
+        // the chunk is in registers: the buffer may be refilled
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&acc_empty[buf]);
       }
       if (!ok) break;
 #pragma unroll
